@@ -1,0 +1,396 @@
+// Forward attention kernel for sm_100a: O = softmax(scale * Q K^T + mask) V and LSE on block-scaled operands.
+//
+// Replaces the reference's FlashAttentionForwardSm100 (flash_attn/cute/flash_fwd_sm100_fp4.py:370) and its driver
+// _flash_attn_fwd (flash_attn/cute/interface_fwd_fp4.py:301) for the two in-scope routes:
+//   FL_MODE_FP8: S = E4M3 x E4M3 (kind::f8f6f4); the power-of-two token-block factors f_Q[row/32] * f_K[key/32] are
+//                folded into the softmax scale (exact); P.V = kind::mxf8f6f4.block_scale with V's UE8M0 exponent per
+//                32 keys as the B scale and a constant-one A scale (row-frame P-hat = E4M3(2^(x - m + 4))).
+//   FL_MODE_FP4: S = NVFP4 x NVFP4 (kind::mxf4nvf4.block_scale.scale_vec::4X), same P.V.
+//
+// CTA = 256 query rows (two 128-row stages) of one (batch | document, head); loop over 128-key tiles.
+//   warps 0-3   softmax stage 0 (thread r owns query row r: TMEM lane r)      warp 8  TMA producer
+//   warps 4-7   softmax stage 1                                               warp 9  UMMA issuer
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P-hat overlays columns [0,32) of its S, the
+// P.V scale factors columns [32,40).
+// All waits are bounded (sm100.cuh); a kernel that gives up writes a code to the status word and drains.
+#include "flamia_internal.h"
+
+namespace fl {
+
+static constexpr int KV_STAGES = 3;
+static constexpr float P_LOG2_OFFSET = 4.0f;      // P-hat = 2^(x - m + 4): keeps small probabilities out of E4M3 subnormals
+static constexpr float RESCALE_THRESHOLD = 4.0f;  // the running maximum is refreshed only when it grew by more than this
+
+struct FwdParams {
+  const float* fac_q;
+  const float* fac_k;
+  const float* fac_v;
+  void* out;
+  float* lse;
+  const int32_t* doc_start;
+  const int32_t* doc_len;
+  int n_docs;
+  int b, s_q, s_k, h, h_kv;
+  float scale_log2;
+  int causal;
+  int out_f16;
+  DevCtl ctl;
+};
+
+struct Tile {
+  int bat;    // batch coordinate of the tensor maps (0 for packed documents)
+  int q0;     // first query row (row index inside the batch entry)
+  int nq;     // valid query rows of this CTA (<= 256)
+  int k0;     // first key row of the document
+  int sk;     // keys of the document
+  int off;    // causal alignment: key j (document-relative) is visible to query i iff j <= i + off
+  int qrel;   // document-relative index of row q0
+};
+
+// barrier indices
+enum { B_Q = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + KV_STAGES, B_VFULL = B_KEMPTY + KV_STAGES,
+       B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES, B_PFULL = B_SFULL + 2, B_PVDONE = B_PFULL + 2,
+       B_COUNT = B_PVDONE + 2 };
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+           const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  constexpr int TILE_BYTES = 128 * D;
+  constexpr uint64_t SWZ = (D == 128) ? SWZ_128 : SWZ_64;
+  constexpr uint32_t SBO = 8 * D;                       // bytes between 8-row groups
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                                   // 2 tiles
+  uint8_t* sK = sQ + 2 * TILE_BYTES;                    // KV_STAGES tiles
+  uint8_t* sV = sK + KV_STAGES * TILE_BYTES;            // KV_STAGES tiles
+  __shared__ __align__(8) uint64_t bars[B_COUNT];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  __shared__ Tile tile_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int head = blockIdx.y;
+  const int hkv = head / (p.h / p.h_kv);
+
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(&bars[B_Q], 1);
+    for (int i = 0; i < KV_STAGES; ++i) {
+      mbar_init(&bars[B_KFULL + i], 1);
+      mbar_init(&bars[B_KEMPTY + i], 1);
+      mbar_init(&bars[B_VFULL + i], 1);
+      mbar_init(&bars[B_VEMPTY + i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[B_SFULL + i], 1);
+      mbar_init(&bars[B_PFULL + i], 128);
+      mbar_init(&bars[B_PVDONE + i], 1);
+    }
+    fence_barrier_init();
+    // ---- which tile
+    Tile t;
+    if (p.doc_start == nullptr) {
+      const int nqb = (p.s_q + 255) / 256;
+      const int qb = p.causal ? (nqb - 1 - (int)blockIdx.x) : (int)blockIdx.x;   // longest first under the causal mask
+      t.bat = blockIdx.z; t.q0 = qb * 256; t.nq = min(256, p.s_q - t.q0); t.k0 = 0; t.sk = p.s_k;
+      t.off = p.s_k - p.s_q; t.qrel = t.q0;
+    } else {
+      // documents sit at 128-aligned starts of one packed batch entry; block x -> (document, 256-row block)
+      int x = blockIdx.x, dsel = -1, blk = 0;
+      for (int dI = 0; dI < p.n_docs; ++dI) {
+        const int nb = (p.doc_len[dI] + 255) / 256;
+        if (x < nb) { dsel = dI; blk = x; break; }
+        x -= nb;
+      }
+      if (dsel < 0) { t.nq = 0; t.bat = 0; t.q0 = 0; t.k0 = 0; t.sk = 0; t.off = 0; t.qrel = 0; }
+      else {
+        const int len = p.doc_len[dsel], st = p.doc_start[dsel];
+        if (p.causal) blk = (len + 255) / 256 - 1 - blk;
+        t.bat = 0; t.q0 = st + blk * 256; t.nq = min(256, len - blk * 256); t.k0 = st; t.sk = len; t.off = 0;
+        t.qrel = blk * 256;
+      }
+    }
+    tile_s = t;
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const Tile T = tile_s;
+  volatile int* abortp = &abort_s;
+
+  // keys visible to stage i: [0, kmax_i); tiles n_i = ceil(kmax_i / 128)
+  int n_st[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rows = min(128, T.nq - 128 * i);             // valid rows of the stage (<= 0: stage absent)
+    int kmax = T.sk;
+    if (p.causal) kmax = min(T.sk, T.qrel + 128 * i + rows + T.off);
+    n_st[i] = (rows > 0 && kmax > 0) ? (kmax + 127) / 128 : 0;
+  }
+  const int n_max = max(n_st[0], n_st[1]);
+  const bool early_out = (T.nq <= 0) || (*p.ctl.status != 0);
+
+  if (!early_out) {
+    if (warp == 8) {
+      // =================================================================== TMA producer
+      if (lane == 0) {
+        tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+        mbar_arrive_expect_tx(&bars[B_Q], 2 * TILE_BYTES);
+        tma_load_4d(sQ, &tm_q, &bars[B_Q], 0, head, T.q0, T.bat);
+        tma_load_4d(sQ + TILE_BYTES, &tm_q, &bars[B_Q], 0, head, T.q0 + 128, T.bat);
+        for (int j = 0; j < n_max; ++j) {
+          const int st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+          if (j >= KV_STAGES && !mbar_wait(&bars[B_KEMPTY + st], ph ^ 1, p.ctl, abortp, 10)) break;
+          mbar_arrive_expect_tx(&bars[B_KFULL + st], TILE_BYTES);
+          tma_load_4d(sK + st * TILE_BYTES, &tm_k, &bars[B_KFULL + st], 0, hkv, T.k0 + j * 128, T.bat);
+          if (j >= KV_STAGES && !mbar_wait(&bars[B_VEMPTY + st], ph ^ 1, p.ctl, abortp, 11)) break;
+          mbar_arrive_expect_tx(&bars[B_VFULL + st], TILE_BYTES);
+          tma_load_4d(sV + st * TILE_BYTES, &tm_v, &bars[B_VFULL + st], 0, hkv, T.k0 + j * 128, T.bat);
+        }
+      }
+    } else if (warp == 9) {
+      // =================================================================== UMMA issuer
+      if (lane == 0) {
+        constexpr uint32_t ID_S = idesc_f8(128, 128, 0, 0);
+        const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+        auto issue_s = [&](int i, int st) {
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k)
+            umma_f8_ss(tmem + 128 * i, smem_desc(q_addr + i * TILE_BYTES + 32 * k, 16, SBO, SWZ),
+                       smem_desc(k_addr + st * TILE_BYTES + 32 * k, 16, SBO, SWZ), ID_S, k > 0);
+        };
+        auto issue_pv = [&](int i, int st, bool first) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)   // 32 keys per instruction: 32 rows of the V tile (MN-major operand)
+            umma_mxf8_ts(tmem + 256 + 128 * i, tmem + 128 * i + 8 * kk,
+                         smem_desc(v_addr + st * TILE_BYTES + kk * 32 * D, 16, SBO, SWZ),
+                         idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), tmem + 128 * i + 32, tmem + 128 * i + 36,
+                         (!first) || kk > 0);
+        };
+        bool ok = mbar_wait(&bars[B_Q], 0, p.ctl, abortp, 20);
+        if (ok && n_max > 0) ok = mbar_wait(&bars[B_KFULL], 0, p.ctl, abortp, 21);
+        if (ok && n_max > 0) {
+          tc_fence_after();
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            if (n_st[i] > 0) { issue_s(i, 0); tc_commit(&bars[B_SFULL + i]); }
+          tc_commit(&bars[B_KEMPTY + 0]);   // K tile 0 is free once both S(0) products have completed
+        }
+        for (int j = 0; ok && j < n_max; ++j) {
+          const int st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+          const int stn = (j + 1) % KV_STAGES, phn = ((j + 1) / KV_STAGES) & 1;
+          if (!(ok = mbar_wait(&bars[B_VFULL + st], ph, p.ctl, abortp, 22))) break;
+          bool k_next_ready = false;
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            if (j >= n_st[i]) continue;
+            if (!(ok = mbar_wait(&bars[B_PFULL + i], j & 1, p.ctl, abortp, 23 + i))) break;
+            tc_fence_after();
+            issue_pv(i, st, j == 0);
+            tc_commit(&bars[B_PVDONE + i]);
+            if (j + 1 < n_st[i]) {
+              if (!k_next_ready) {
+                if (!(ok = mbar_wait(&bars[B_KFULL + stn], phn, p.ctl, abortp, 25))) break;
+                k_next_ready = true;
+                tc_fence_after();
+              }
+              issue_s(i, stn);
+              tc_commit(&bars[B_SFULL + i]);
+            }
+          }
+          if (!ok) break;
+          // every MMA that reads K tile j+1 / V tile j has been issued: release the stages when they complete
+          if (j + 1 < n_max) tc_commit(&bars[B_KEMPTY + stn]);
+          tc_commit(&bars[B_VEMPTY + st]);
+        }
+      }
+    } else if (warp < 8) {
+      // =================================================================== softmax + correction + epilogue
+      const int i = warp >> 2;                          // stage
+      const int r = tid & 127;                          // row of the stage = TMEM lane
+      const int n_i = n_st[i];
+      const uint32_t t_s = tmem + 128 * i + ((uint32_t)((warp & 3) * 32) << 16);
+      const uint32_t t_o = tmem + 256 + 128 * i + ((uint32_t)((warp & 3) * 32) << 16);
+      const int qrow = T.q0 + 128 * i + r;              // row inside the batch entry
+      const int qrel = T.qrel + 128 * i + r;            // row inside the document
+      const bool row_valid = (128 * i + r) < T.nq;
+      const size_t bh_q = (size_t)T.bat * p.h + head, bh_k = (size_t)T.bat * p.h_kv + hkv;
+      const float fq = row_valid ? p.fac_q[bh_q * (p.s_q / 32) + qrow / 32] * p.scale_log2 : 0.f;
+      const float* fk_row = p.fac_k + bh_k * (p.s_k / 32) + T.k0 / 32;
+      const float* fv_row = p.fac_v + bh_k * (p.s_k / 32) + T.k0 / 32;
+      const int col_limit = p.causal ? min(qrel + T.off, T.sk - 1) : T.sk - 1;   // last visible key of this row
+
+      float m_used = -INFINITY, l_sum = 0.f;
+      bool ok = true;
+      for (int j = 0; j < n_i; ++j) {
+        float c[4];
+        uint32_t sfv = 0;
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          c[kb] = fq * fk_row[j * 4 + kb];
+          sfv |= ((__float_as_uint(fv_row[j * 4 + kb]) >> 23) & 0xFF) << (8 * kb);
+        }
+        if (!(ok = mbar_wait(&bars[B_SFULL + i], j & 1, p.ctl, abortp, 30 + i))) break;
+        tc_fence_after();
+        uint32_t su[128];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) FL_TMEM_LD_32(t_s + 32 * cc, (su + 32 * cc));
+        tc_wait_ld();
+        float s[128];
+#pragma unroll
+        for (int e = 0; e < 128; ++e) s[e] = __uint_as_float(su[e]);
+        const bool need_mask = (j * 128 + 127) > col_limit;    // only on diagonal / tail tiles
+        if (need_mask) {   // scale first, then mask: the factor product may underflow to zero and 0 * inf is NaN
+#pragma unroll
+          for (int e = 0; e < 128; ++e) s[e] = (j * 128 + e > col_limit) ? -INFINITY : s[e] * c[e >> 5];
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) c[kb] = 1.f;
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          float a = s[32 * kb];
+#pragma unroll
+          for (int e = 1; e < 32; ++e) a = fmaxf(a, s[32 * kb + e]);
+          mx = fmaxf(mx, a * c[kb]);
+        }
+        // lazy refresh of the running maximum
+        float alpha = 1.f;
+        const bool refresh = mx > m_used + RESCALE_THRESHOLD;
+        if (refresh) {
+          alpha = ex2(m_used - mx);     // 0 on the first tile (m_used = -inf)
+          m_used = mx;
+        }
+        if (j > 0 && __any_sync(0xFFFFFFFFu, refresh)) {
+          // rescale this row of O in tensor memory once the previous P.V has finished
+          if (!(ok = mbar_wait(&bars[B_PVDONE + i], (j - 1) & 1, p.ctl, abortp, 32 + i))) break;
+          tc_fence_after();
+#pragma unroll 1
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t ov[32];
+            FL_TMEM_LD_32(t_o + 32 * cc, ov);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+            FL_TMEM_ST_32(t_o + 32 * cc, ov);
+          }
+        }
+        const float mb = (m_used == -INFINITY) ? 0.f : (m_used - P_LOG2_OFFSET);
+        float psum = 0.f;
+        uint32_t pw[32];
+#pragma unroll
+        for (int w = 0; w < 32; ++w) {
+          const float cw = c[w >> 3];
+          float p0 = ex2(fmaf(s[4 * w], cw, -mb)), p1 = ex2(fmaf(s[4 * w + 1], cw, -mb));
+          float p2 = ex2(fmaf(s[4 * w + 2], cw, -mb)), p3 = ex2(fmaf(s[4 * w + 3], cw, -mb));
+          psum += (p0 + p1) + (p2 + p3);
+          pw[w] = cvt_e4m3x4(p0, p1, p2, p3);
+        }
+        l_sum = fmaf(l_sum, alpha, psum);
+        FL_TMEM_ST_32(t_s, pw);
+        {
+          uint32_t sf[8] = {0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, sfv, sfv, sfv, sfv};
+          FL_TMEM_ST_8(t_s + 32, sf);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars[B_PFULL + i]);
+      }
+      // ---- epilogue: O / l -> bf16, LSE
+      if (ok && n_i > 0) ok = mbar_wait(&bars[B_PVDONE + i], (n_i - 1) & 1, p.ctl, abortp, 34 + i);
+      if (ok) {
+        tc_fence_after();
+        const float inv_l = (l_sum > 0.f) ? 1.0f / l_sum : 0.f;
+        uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (((size_t)T.bat * p.s_q + qrow) * p.h + head) * D;
+#pragma unroll 1
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t ov[32];
+          if (n_i > 0) {
+            FL_TMEM_LD_32(t_o + 32 * cc, ov);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ov[e] = 0;
+          }
+          if (row_valid) {
+            uint32_t w[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              float a = __uint_as_float(ov[2 * e]) * inv_l, b2 = __uint_as_float(ov[2 * e + 1]) * inv_l;
+              if (p.out_f16) {
+                __half2 hh = __floats2half2_rn(a, b2);
+                w[e] = *reinterpret_cast<uint32_t*>(&hh);
+              } else {
+                w[e] = pack_bf16x2(a, b2);
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              *reinterpret_cast<uint4*>(orow + 32 * cc + 8 * e) = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
+          }
+        }
+        if (row_valid && p.lse) {
+          // l carries 2^4: lse = ln2 * (m - 4 + log2 l)
+          float v = (l_sum > 0.f) ? (m_used - P_LOG2_OFFSET + lg2(l_sum)) * 0.6931471805599453f : -INFINITY;
+          p.lse[bh_q * p.s_q + qrow] = v;
+        }
+      }
+    }
+  }
+  // ---- common exit: nothing of this CTA may still be in flight when tensor memory is released
+  if (abort_s) {
+    for (int it = 0; it < 200; ++it) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace fl
+
+extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
+  using namespace fl;
+  if (!a || !a->q_codes || !a->k_codes || !a->v_codes || !a->out || !a->status) return FL_ERR_BAD_ARG;
+  if (!a->fac_q || !a->fac_k || !a->fac_v) return FL_ERR_BAD_ARG;
+  if (a->d != 64 && a->d != 128) return FL_ERR_UNSUPPORTED;
+  if (a->mode != FL_MODE_FP8) return FL_ERR_UNSUPPORTED;
+  if (a->flags & FL_A_TOKEN_LOCAL) return FL_ERR_UNSUPPORTED;
+  if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
+  if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
+  if (a->doc_start && (a->b != 1 || a->n_docs <= 0 || !a->doc_len || a->s_q != a->s_k)) return FL_ERR_BAD_ARG;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = make_rows_map(&mq, a->q_codes, a->b, a->s_q, a->h, a->d, 128))) return rc;
+  if ((rc = make_rows_map(&mk, a->k_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
+  if ((rc = make_rows_map(&mv, a->v_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
+  FwdParams p;
+  p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.out = a->out; p.lse = a->lse;
+  p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;
+  p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  p.causal = (a->flags & FL_A_CAUSAL) ? 1 : 0;
+  p.out_f16 = (a->flags & FL_A_OUT_F16) ? 1 : 0;
+  p.ctl.status = a->status;
+  p.ctl.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kDefaultWaitCycles;
+  // packed documents: at most one extra 256-row block per document beyond total / 256
+  const int nblk = a->doc_start ? (a->s_q / 256 + a->n_docs + 1) : (a->s_q + 255) / 256;
+  dim3 grid(nblk, a->h, a->doc_start ? 1 : a->b);
+  const int smem = (2 + 2 * KV_STAGES) * 128 * a->d + 1024;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (a->d == 128) {
+    if (cudaFuncSetAttribute(fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return FL_ERR_CUDA;
+    fwd_kernel<128><<<grid, 320, smem, st>>>(mq, mk, mv, p);
+  } else {
+    if (cudaFuncSetAttribute(fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return FL_ERR_CUDA;
+    fwd_kernel<64><<<grid, 320, smem, st>>>(mq, mk, mv, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+}

@@ -1,0 +1,212 @@
+// HBM-bound side kernels of the backward: f16 dQ pre-scale table, dQ postprocess, packed-row gather / scatter.
+#include "flamia_internal.h"
+
+namespace fl {
+
+// ------------------------------------------------------------------------------------------------ dQ pre-scale
+// Restates flash_attn/cute/device_scales.py:124-132 (_dq_bound_pow2) and :158-184, 234-319 (_dq_row_bound,
+// _dq_tile_table) of the reference: bound = ((((4 unit) 2) sqrt(dn2)) sqrt(vn2)) kmax in fp32 (mul.rn / sqrt.rn / div.rn
+// only), B = the largest power of two <= 65504 / bound with its exponent clamped to [-40, 40].
+__device__ __forceinline__ float pow2_floor_clamped(float x, int lo, int hi) {
+  int e = (int)((__float_as_uint(x) >> 23) & 0xFF) - 127;
+  e = max(lo, min(hi, e));
+  return __uint_as_float((uint32_t)(e + 127) << 23);
+}
+
+__global__ void dq_prescale_kernel(const float* __restrict__ st_do, const float* __restrict__ st_v,
+                                   const float* __restrict__ st_k, int h, int h_kv, int nt_q, int nt_k, int causal_local,
+                                   float unit, float* kernel_scale, float* post_scale) {
+  const int bq = blockIdx.y, t = blockIdx.x, tid = threadIdx.x;
+  const int q_lo = causal_local ? t : 0, q_hi = causal_local ? t + 1 : nt_q;
+  const int k_lo = 0, k_hi = causal_local ? min(t + 1 + max(nt_k - nt_q, 0), nt_k) : nt_k;
+  float dn = 0.f, vn = 0.f, km = 0.f;
+  const int nq = q_hi - q_lo, nk = k_hi - k_lo;
+  for (int j = tid; j < h * nq; j += blockDim.x)
+    dn = fmaxf(dn, st_do[(((size_t)bq * h + j / nq) * nt_q + q_lo + j % nq) * 2 + 1]);
+  for (int j = tid; j < h_kv * nk; j += blockDim.x) {
+    const size_t o = (((size_t)bq * h_kv + j / nk) * nt_k + k_lo + j % nk) * 2;
+    vn = fmaxf(vn, st_v[o + 1]);
+    km = fmaxf(km, st_k[o]);
+  }
+  __shared__ float red[3][32];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    dn = fmaxf(dn, __shfl_xor_sync(0xFFFFFFFFu, dn, o));
+    vn = fmaxf(vn, __shfl_xor_sync(0xFFFFFFFFu, vn, o));
+    km = fmaxf(km, __shfl_xor_sync(0xFFFFFFFFu, km, o));
+  }
+  if ((tid & 31) == 0) { red[0][tid >> 5] = dn; red[1][tid >> 5] = vn; red[2][tid >> 5] = km; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+      dn = fmaxf(dn, red[0][w]); vn = fmaxf(vn, red[1][w]); km = fmaxf(km, red[2][w]);
+    }
+    float bnd = __fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(4.0f, unit), 2.0f), __fsqrt_rn(dn)), __fsqrt_rn(vn)), km);
+    float bb = pow2_floor_clamped(__fdiv_rn(65504.0f, bnd), -40, 40);
+    kernel_scale[(size_t)bq * nt_q + t] = bb;
+    post_scale[(size_t)bq * nt_q + t] = __fdiv_rn(1.0f, __fmul_rn(unit, bb));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ dQ postprocess
+// dq[b, q, h, :] = cast(f32(acc[b, h, q, :]) * post[b, q / 128] * mult), optionally rotated back:
+// (y H_128 / sqrt(128)) * signs in the quantiser's butterfly order. Replaces the reference's DQPostprocess
+// (flash_attn/cute/dq_postprocess_cute.py:46-124).
+template <int D>
+__global__ void __launch_bounds__(128) dq_post_kernel(const __half* __restrict__ acc, const float* __restrict__ post,
+                                                      uint16_t* __restrict__ dq, int s, int h, float mult, int unrotate,
+                                                      int out_f16) {
+  extern __shared__ __align__(16) uint8_t sm[];
+  constexpr int ROWB = D * 2 + 16;
+  const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z, tid = threadIdx.x;
+  const int t0 = tile * 128;
+  const __half* src = acc + (((size_t)bat * h + head) * s + t0) * D;
+  const float sc = post[(size_t)bat * (s / 128) + tile] * mult;
+  uint16_t* dst = dq + (((size_t)bat * s + t0) * h + head) * D;
+  const size_t row_stride = (size_t)h * D;
+  constexpr int CPR = D / 8;
+  auto cvt2 = [&](float a, float b) -> uint32_t {
+    if (out_f16) { __half2 hh = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&hh); }
+    return pack_bf16x2(a, b);
+  };
+  if (!unrotate) {
+    for (int i = tid; i < 128 * CPR; i += 128) {
+      const int r = i / CPR, c = i % CPR;
+      uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
+      const __half2* hv = reinterpret_cast<const __half2*>(&v);
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __half22float2(hv[j]);
+        w[j] = cvt2(f.x * sc, f.y * sc);
+      }
+      *reinterpret_cast<uint4*>(dst + (size_t)r * row_stride + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    return;
+  }
+  if constexpr (D == 128) {
+    for (int i = tid; i < 128 * CPR; i += 128) {
+      const int r = i / CPR, c = i % CPR;
+      *reinterpret_cast<uint4*>(sm + r * ROWB + c * 16) = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
+    }
+    __syncthreads();
+    float y[128];
+    {
+      const uint8_t* rowp = sm + tid * ROWB;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        uint4 v = *reinterpret_cast<const uint4*>(rowp + c * 16);
+        const __half2* hv = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __half22float2(hv[j]);
+          y[c * 8 + 2 * j] = f.x * sc;
+          y[c * 8 + 2 * j + 1] = f.y * sc;
+        }
+      }
+    }
+#pragma unroll
+    for (int hs = 1; hs < 128; hs <<= 1) {
+#pragma unroll
+      for (int i = 0; i < 128; ++i) {
+        if ((i & hs) == 0) {
+          float a = y[i], b2 = y[i + hs];
+          y[i] = __fadd_rn(a, b2);
+          y[i + hs] = __fsub_rn(a, b2);
+        }
+      }
+    }
+    constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
+    __syncthreads();
+    uint8_t* rowo = sm + tid * ROWB;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i0 = c * 8 + 2 * j, i1 = i0 + 1;
+        float a = __fmul_rn(y[i0], 0.08838834764831845f), b2 = __fmul_rn(y[i1], 0.08838834764831845f);
+        if ((NEG[i0 >> 5] >> (i0 & 31)) & 1) a = -a;
+        if ((NEG[i1 >> 5] >> (i1 & 31)) & 1) b2 = -b2;
+        w[j] = cvt2(a, b2);
+      }
+      *reinterpret_cast<uint4*>(rowo + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __syncthreads();
+    for (int i = tid; i < 128 * CPR; i += 128) {
+      const int r = i / CPR, c = i % CPR;
+      *reinterpret_cast<uint4*>(dst + (size_t)r * row_stride + c * 8) = *reinterpret_cast<const uint4*>(sm + r * ROWB + c * 16);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ packed rows
+__global__ void pack_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int32_t* __restrict__ map,
+                                 int n_rows, int chunks) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_rows * chunks) return;
+  const int r = (int)(i / chunks), c = (int)(i % chunks);
+  const int sr = map[r];
+  dst[i] = sr >= 0 ? src[(size_t)sr * chunks + c] : make_uint4(0, 0, 0, 0);
+}
+__global__ void unpack_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int32_t* __restrict__ map,
+                                   int n_rows, int chunks) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_rows * chunks) return;
+  const int r = (int)(i / chunks), c = (int)(i % chunks);
+  const int dr = map[r];
+  if (dr >= 0) dst[(size_t)dr * chunks + c] = src[i];
+}
+
+}  // namespace fl
+
+extern "C" int fl_dq_prescale(const float* stats_do, const float* stats_v, const float* stats_k, int32_t b, int32_t h,
+                              int32_t h_kv, int32_t nt_q, int32_t nt_k, int32_t causal_local, float unit,
+                              float* kernel_scale, float* post_scale, void* stream) {
+  using namespace fl;
+  if (!stats_do || !stats_v || !stats_k || !kernel_scale || !post_scale || b <= 0 || nt_q <= 0 || nt_k <= 0)
+    return FL_ERR_BAD_ARG;
+  dq_prescale_kernel<<<dim3(nt_q, b), 128, 0, (cudaStream_t)stream>>>(stats_do, stats_v, stats_k, h, h_kv, nt_q, nt_k,
+                                                                      causal_local, unit, kernel_scale, post_scale);
+  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+}
+
+extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, void* dq, int32_t b, int32_t s, int32_t h,
+                          int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
+  using namespace fl;
+  if (!dq_acc || !post_scale || !dq || b <= 0 || s <= 0 || (s % 128) || h <= 0) return FL_ERR_BAD_ARG;
+  if ((d != 64 && d != 128) || (unrotate && d != 128)) return FL_ERR_UNSUPPORTED;
+  dim3 grid(s / 128, h, b);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (d == 128) {
+    const int sm = unrotate ? 128 * 272 : 0;
+    if (cudaFuncSetAttribute(dq_post_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 272) != cudaSuccess)
+      return FL_ERR_CUDA;
+    dq_post_kernel<128><<<grid, 128, sm, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, 1.0f, unrotate, out_f16);
+  } else {
+    dq_post_kernel<64><<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, 1.0f, 0, out_f16);
+  }
+  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+}
+
+extern "C" int fl_pack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n_dst_rows, int32_t row_bytes,
+                            void* stream) {
+  using namespace fl;
+  if (!src || !dst || !row_map || n_dst_rows <= 0 || row_bytes <= 0 || (row_bytes % 16)) return FL_ERR_BAD_ARG;
+  const int chunks = row_bytes / 16;
+  const size_t n = (size_t)n_dst_rows * chunks;
+  pack_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, row_map,
+                                                                                  n_dst_rows, chunks);
+  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+}
+
+extern "C" int fl_unpack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n_src_rows, int32_t row_bytes,
+                              void* stream) {
+  using namespace fl;
+  if (!src || !dst || !row_map || n_src_rows <= 0 || row_bytes <= 0 || (row_bytes % 16)) return FL_ERR_BAD_ARG;
+  const int chunks = row_bytes / 16;
+  const size_t n = (size_t)n_src_rows * chunks;
+  unpack_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst,
+                                                                                    row_map, n_src_rows, chunks);
+  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+}

@@ -1,0 +1,161 @@
+"""Thin PyTorch wrappers over the C ABI: they allocate outputs with torch, pass raw device pointers and the current
+stream, and return tensors. No arithmetic happens here.
+
+quantize_fp8_blocks mirrors the reference's quant.fp8.quantize_fp8_blocks (flash_attn/cute/quant/fp8.py:2512): same
+argument names for the features this build serves, same output keys.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(t, name):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this library has no CPU path")
+
+
+def new_status(device):
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def read_status(status) -> int:
+    """Host value of a device status word (synchronises the current stream)."""
+    v = C.c_int32(0)
+    L.check(L.load().fl_read_status(L.ptr(status), C.byref(v), _stream()), "fl_read_status")
+    return int(v.value)
+
+
+def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_scope="all", token_local_exponents=False,
+                        make_channel_major_copy=False, output_exponent_table=True, output_token_block_factors=True,
+                        output_sf_atoms=False, also_make_nvfp4_copy=False, compute_d_with_output=None,
+                        shifted_log2_lse_from=None, log2_lse_shift=0.0, d_multiplier=1.0, zero_accumulator=None,
+                        output_tile_stats=False):
+    """Token-block MXFP8 quantiser of x (b, s, h, d) bf16 / f16 (s % 128 == 0, d in {64, 128}).
+    Returns a dict: codes (b,s,h,d) float8_e4m3fn; e (b,h,s/32,d/32) uint8; fac (b,h,s/32) f32; optionally codes_t,
+    sf_tok_raw, sf_dim_raw, token_factors, x4 / sf4_raw (NVFP4 copy), D, lse_log2, tile_stats.
+    hadamard_rotation_scope: "all" (codes and NVFP4 copy of the rotated rows) | "nvfp4_copy" (only the NVFP4 copy)."""
+    _require_cuda(x, "x")
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("x must be bf16 or f16")
+    x = x.contiguous()
+    b, s, h, d = x.shape
+    dev = x.device
+    u8 = dict(dtype=torch.uint8, device=dev)
+    out = {}
+    a = L.QuantArgs()
+    a.x = L.ptr(x)
+    a.b, a.s, a.h, a.d = b, s, h, d
+    a.in_f16 = int(x.dtype == torch.float16)
+    flags = 0
+    if apply_hadamard_rotation:
+        flags |= L.FL_Q_HADAMARD if hadamard_rotation_scope == "all" else L.FL_Q_HADAMARD_NVFP4_ONLY
+    if token_local_exponents:
+        flags |= L.FL_Q_TOKEN_LOCAL
+    a.flags = flags
+    out["codes"] = torch.empty(b, s, h, d, **u8)
+    a.codes = L.ptr(out["codes"])
+    if make_channel_major_copy:
+        out["codes_t"] = torch.empty(b, h, d, s, **u8)
+        a.codes_t = L.ptr(out["codes_t"])
+    if output_exponent_table:
+        out["e"] = torch.empty(b, h, s // 32, d // 32, **u8)
+        a.e_tab = L.ptr(out["e"])
+    if output_token_block_factors:
+        out["fac"] = torch.empty(b, h, s // 32, dtype=torch.float32, device=dev)
+        a.fac = L.ptr(out["fac"])
+    if output_sf_atoms:
+        out["sf_tok_raw"] = torch.empty(b, h, s // 128, 1, 32, 4, 4, **u8)
+        out["sf_dim_raw"] = torch.empty(b, h, 1, s // 128, 32, 4, 4, **u8)
+        a.sf_tok, a.sf_dim = L.ptr(out["sf_tok_raw"]), L.ptr(out["sf_dim_raw"])
+    if token_local_exponents:
+        out["token_factors"] = torch.empty(b, h, s, dtype=torch.float32, device=dev)
+        a.token_factors = L.ptr(out["token_factors"])
+    if also_make_nvfp4_copy:
+        out["x4"] = torch.empty(b, s, h, d // 2, **u8)
+        out["sf4_raw"] = torch.empty(b, h, s // 128, d // 64, 32, 4, 4, **u8)
+        a.x4, a.sf4 = L.ptr(out["x4"]), L.ptr(out["sf4_raw"])
+    keep = []
+    if compute_d_with_output is not None:
+        o = compute_d_with_output.contiguous()
+        assert o.shape == x.shape and o.dtype == x.dtype
+        keep.append(o)
+        a.o = L.ptr(o)
+        out["D"] = torch.empty(b, h, s, dtype=torch.float32, device=dev)
+        a.d_out = L.ptr(out["D"])
+    if shifted_log2_lse_from is not None:
+        lse = shifted_log2_lse_from.contiguous().float()
+        assert lse.shape == (b, h, s)
+        keep.append(lse)
+        a.lse = L.ptr(lse)
+        out["lse_log2"] = torch.empty(b, h, s, dtype=torch.float32, device=dev)
+        a.lse_log2 = L.ptr(out["lse_log2"])
+    if zero_accumulator is not None:
+        assert zero_accumulator.dtype == torch.float16 and zero_accumulator.numel() == b * h * s * d
+        a.zero_acc = L.ptr(zero_accumulator)
+    if output_tile_stats:
+        out["tile_stats"] = torch.empty(b, h, s // 128, 2, dtype=torch.float32, device=dev)
+        a.tile_stats = L.ptr(out["tile_stats"])
+    a.lse_shift, a.d_multiplier = float(log2_lse_shift), float(d_multiplier)
+    L.check(L.load().fl_quant_blocks(C.byref(a), _stream()), "fl_quant_blocks")
+    out["codes"] = out["codes"].view(torch.float8_e4m3fn)
+    if "codes_t" in out:
+        out["codes_t"] = out["codes_t"].view(torch.float8_e4m3fn)
+    return out
+
+
+def attn_args(q, k, v, *, causal, softmax_scale, mode=L.FL_MODE_FP8, flags=0, status=None, doc_start=None, doc_len=None,
+              wait_cycles=0):
+    """AttnArgs from quantiser outputs q / k / v (dicts with codes, fac [, x4, sf4_raw])."""
+    qc, kc, vc = q["codes"], k["codes"], v["codes"]
+    b, s_q, h, d = qc.shape
+    s_k, h_kv = kc.shape[1], kc.shape[2]
+    a = L.AttnArgs()
+    a.q_codes, a.k_codes, a.v_codes = L.ptr(qc), L.ptr(kc), L.ptr(vc)
+    a.fac_q, a.fac_k, a.fac_v = L.ptr(q["fac"]), L.ptr(k["fac"]), L.ptr(v["fac"])
+    if mode == L.FL_MODE_FP4:
+        a.q4, a.k4, a.sfq4, a.sfk4 = L.ptr(q["x4"]), L.ptr(k["x4"]), L.ptr(q["sf4_raw"]), L.ptr(k["sf4_raw"])
+    a.b, a.s_q, a.s_k, a.h, a.h_kv, a.d = b, s_q, s_k, h, h_kv, d
+    a.softmax_scale = float(softmax_scale)
+    a.mode = mode
+    a.flags = flags | (L.FL_A_CAUSAL if causal else 0)
+    if doc_start is not None:
+        a.doc_start, a.doc_len, a.n_docs = L.ptr(doc_start), L.ptr(doc_len), int(doc_len.numel())
+    a.status = L.ptr(status)
+    a.wait_cycles = int(wait_cycles)
+    return a
+
+
+def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L.FL_MODE_FP8, status=None,
+             doc_start=None, doc_len=None, wait_cycles=0):
+    """Forward kernel on quantised operands. Returns (out (b, s_q, h, d), lse (b, h, s_q) float32, status)."""
+    qc = q["codes"]
+    b, s_q, h, d = qc.shape
+    dev = qc.device
+    if status is None:
+        status = new_status(dev)
+    out = torch.empty(b, s_q, h, d, dtype=out_dtype, device=dev)
+    lse = torch.empty(b, h, s_q, dtype=torch.float32, device=dev)
+    a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode,
+                  flags=L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0, status=status, doc_start=doc_start,
+                  doc_len=doc_len, wait_cycles=wait_cycles)
+    a.out, a.lse = L.ptr(out), L.ptr(lse)
+    L.check(L.load().fl_fwd(C.byref(a), _stream()), "fl_fwd")
+    return out, lse, status
+
+
+def selftest_mma(which, a, b, sfa=None, sfb=None, wait_cycles=0):
+    """One 128x128x128 product through the library's tensor-core helpers; returns (d (128,128) f32, status value)."""
+    dev = a.device if a is not None else torch.device("cuda")
+    d = torch.zeros(128, 128, dtype=torch.float32, device=dev)
+    status = new_status(dev)
+    L.check(L.load().fl_selftest_mma(int(which), L.ptr(a), L.ptr(b), L.ptr(sfa), L.ptr(sfb), L.ptr(d), L.ptr(status),
+                                     int(wait_cycles), _stream()), "fl_selftest_mma")
+    return d, read_status(status)

@@ -1,0 +1,148 @@
+/* C ABI of the B200 microscaling-attention hot path (libflamia_b200.so).
+ *
+ * Plain pointers and sizes only; every pointer is a CUDA device pointer unless stated otherwise; every function
+ * enqueues on the given cudaStream_t (passed as void*), never synchronises the host, never allocates device memory,
+ * and returns 0 or a positive FL_ERR_* code. Device-side problems (a bounded wait that ran out) are reported through
+ * the int status word the caller passes in (0 = ok) and can be read with fl_read_status().
+ *
+ * The reference has no C ABI on this path: its boundary is Python over CuTe-DSL JIT kernels. Each entry point below
+ * names the reference interface it replaces (paths inside the reference repository).
+ */
+#ifndef FLAMIA_B200_H
+#define FLAMIA_B200_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FL_ABI_VERSION 1
+
+/* fl_quant_args.flags */
+#define FL_Q_HADAMARD 1            /* rotate rows by diag(signs) H_128 / sqrt(128) before quantising (d = 128) */
+#define FL_Q_TOKEN_LOCAL 2         /* codes / sf_tok from each token's own exponent */
+#define FL_Q_HADAMARD_NVFP4_ONLY 4 /* rotate only the values of the NVFP4 copy; the E4M3 codes stay unrotated */
+
+/* Fused block-scaled quantiser + backward prologue.
+ * Replaces flash_attn/cute/quant/fp8.py:2512 quantize_fp8_blocks (kernel :1639), the fused NVFP4 S-operand copy
+ * flash_attn/cute/quant/_fp8_nvfp4.py:121-158, and the fused backward preprocess (compute_d_with_output,
+ * shifted_log2_lse_from, zero_accumulator: quant/fp8.py:1980-2032). Any output pointer may be NULL = not produced. */
+typedef struct fl_quant_args {
+  const void* x;        /* (b, s, h, d) bf16 (in_f16 = 0) or f16 (1), contiguous; s % 128 == 0; d = 64 | 128 */
+  const void* o;        /* prologue: forward output, same layout / dtype as x */
+  const float* lse;     /* (b, h, s) natural-log LSE */
+  uint8_t* codes;       /* (b, s, h, d) E4M3 */
+  uint8_t* codes_t;     /* (b, h, d, s) channel-major copy */
+  uint8_t* e_tab;       /* (b, h, s/32, d/32) UE8M0 bytes (0 = all-zero block) */
+  float* fac;           /* (b, h, s/32) 2^(e-127), zero blocks take their tile's largest factor (1 if none) */
+  uint8_t* sf_tok;      /* (b, h, s/128, 512) SM100 128x4 atoms, rows = tokens, K = d/32 */
+  uint8_t* sf_dim;      /* (b, h, s/128, 512) atoms, rows = d, K = tokens/32 */
+  float* token_factors; /* (b, h, s) 2^(e_token-127) (1 for an all-zero token) */
+  uint8_t* x4;          /* (b, s, h, d/2) NVFP4 E2M1 codes, element 0 in the low nibble */
+  uint8_t* sf4;         /* (b, h, s/128, d/64, 512) E4M3 scale atoms, rows = tokens, K = d/16 */
+  float* d_out;         /* (b, h, s): d_multiplier * rowsum(O * dequant(codes)) in the fixed tree order */
+  float* lse_log2;      /* (b, h, s): (lse == -inf ? 0 : lse * log2 e) - lse_shift */
+  void* zero_acc;       /* (b, h, s, d) f16 accumulator, zero-filled */
+  float* tile_stats;    /* (b, h, s/128, 2): amax and max row sum of squares of the values quantised */
+  int32_t b, s, h, d;
+  int32_t flags;
+  int32_t in_f16;
+  float lse_shift;
+  float d_multiplier;
+} fl_quant_args;
+
+int fl_quant_blocks(const fl_quant_args* args, void* stream);
+
+/* fl_attn_args.mode */
+#define FL_MODE_FP8 0   /* S = E4M3 x E4M3 with the token-block factors folded into the softmax */
+#define FL_MODE_FP4 1   /* S = NVFP4 x NVFP4 block-scaled (kind::mxf4nvf4, scale_vec::4X) */
+/* fl_attn_args.flags */
+#define FL_A_CAUSAL 1        /* bottom-right aligned causal mask */
+#define FL_A_OUT_F16 2       /* outputs / gradients are f16 instead of bf16 */
+#define FL_A_TOKEN_LOCAL 4   /* per-token factor tables instead of per-32-token ones */
+#define FL_A_DQ_ROWLOCAL 8   /* backward: the dQ side of dS-hat gets one exponent per query row of each 32-key block */
+#define FL_A_HAD_DQ 16       /* backward: dQ accumulator holds rotated rows (post kernel rotates back) */
+#define FL_A_HAD_DK 32       /* backward: rotate dK back in the epilogue */
+
+/* One attention problem. Operands are the quantiser's outputs; q / k / v / dO codes are (b, s, heads, d) E4M3. */
+typedef struct fl_attn_args {
+  const uint8_t* q_codes;
+  const uint8_t* k_codes;
+  const uint8_t* v_codes;
+  const uint8_t* do_codes;   /* backward only */
+  const float* fac_q;        /* (b, h, s_q/32)    [token_local: (b, h, s_q)] */
+  const float* fac_k;        /* (b, h_kv, s_k/32) [token_local: (b, h_kv, s_k)] */
+  const float* fac_v;        /* (b, h_kv, s_k/32) [token_local: (b, h_kv, s_k)] */
+  const float* fac_do;       /* (b, h, s_q/32) backward only */
+  const uint8_t* q4;         /* FL_MODE_FP4: (b, s_q, h, d/2) */
+  const uint8_t* k4;         /* (b, s_k, h_kv, d/2) */
+  const uint8_t* sfq4;       /* (b, h, s_q/128, d/64, 512) */
+  const uint8_t* sfk4;       /* (b, h_kv, s_k/128, d/64, 512) */
+  void* out;                 /* forward: (b, s_q, h, d) bf16 | f16 */
+  float* lse;                /* forward: (b, h, s_q) natural log */
+  const float* lse_log2;     /* backward: (b, h, s_q) lse * log2 e - 8 */
+  const float* d_rows;       /* backward: (b, h, s_q) -2^-8 * rowsum(O * dO) */
+  void* dq_acc;              /* backward: (b, h, s_q, d) f16, zeroed by the prologue; reduce-added here */
+  const float* dq_scale;     /* backward: (b, s_q/128) pre-scale of the f16 accumulator per query tile (power of two) */
+  void* dk;                  /* backward: (b, s_k, h_kv, d) */
+  void* dv;                  /* backward: (b, s_k, h_kv, d) */
+  const int32_t* doc_start;  /* packed documents: (n_docs + 1) tile-aligned row starts, or NULL = batched */
+  const int32_t* doc_len;    /* (n_docs) true lengths */
+  int32_t n_docs;
+  int32_t b, s_q, s_k, h, h_kv, d;
+  float softmax_scale;
+  int32_t mode;
+  int32_t flags;
+  int32_t* status;           /* device int, 0 on entry; a kernel that gives up a wait writes a nonzero code */
+  int64_t wait_cycles;       /* budget of one device-side wait in SM clocks; 0 = default (2^31) */
+} fl_attn_args;
+
+/* Forward: O = softmax(scale Q K^T + mask) V, LSE.
+ * Replaces flash_attn/cute/interface_fwd_fp4.py:301 _flash_attn_fwd -> flash_fwd_sm100_fp4.py:370
+ * FlashAttentionForwardSm100. */
+int fl_fwd(const fl_attn_args* args, void* stream);
+
+/* Backward main kernel: dK, dV and the pre-scaled f16 dQ accumulator.
+ * Replaces flash_attn/cute/interface_bwd_fp4.py:1207 _flash_attn_bwd_fp4 -> flash_bwd_sm100_fp4.py:82
+ * FlashAttentionBackwardSm100FP4 (and the 2-CTA variant flash_bwd_sm100_2cta8.py:74). */
+int fl_bwd(const fl_attn_args* args, void* stream);
+
+/* f16 dQ pre-scale per query tile from the quantisers' tile statistics.
+ * Replaces flash_attn/cute/device_scales.py:124-155, 234-319 (_dq_bound_pow2, _dq_prescale, _dq_tile_table). */
+int fl_dq_prescale(const float* stats_do, const float* stats_v, const float* stats_k, int32_t b, int32_t h, int32_t h_kv,
+                   int32_t nt_q, int32_t nt_k, int32_t causal_local, float unit, float* kernel_scale, float* post_scale,
+                   void* stream);
+
+/* dQ postprocess: dq[b, s, h, :] = cast(acc[b, h, s, :] * post_scale[b, s/128]) with optional Hadamard back-rotation.
+ * Replaces flash_attn/cute/dq_postprocess_cute.py:46 DQPostprocess / bwd_2cta8_side.dq_postprocess_2cta8. */
+int fl_dq_post(const void* dq_acc, const float* post_scale, void* dq, int32_t b, int32_t s, int32_t h, int32_t d,
+               int32_t unrotate, int32_t out_f16, void* stream);
+
+/* Row gather / scatter between a packed (total, h, d) tensor and its 128-aligned repacked buffer.
+ * Replaces flash_attn/cute/lp_varlen.py:421 pack_rows / unpack_rows. row_map[i] = source row of padded row i or -1. */
+int fl_pack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n_dst_rows, int32_t row_bytes, void* stream);
+int fl_unpack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n_src_rows, int32_t row_bytes,
+                   void* stream);
+
+/* Building-block self test: one 128 x 128 x 128 tensor-core product through the library's own descriptor / TMEM helpers.
+ * `which` selects the operand path (see FL_ST_*); used by the unit tests to pin the descriptor encodings. */
+#define FL_ST_F8_KMAJOR 0      /* A, B K-major from shared memory, kind::f8f6f4 */
+#define FL_ST_F8_B_MNMAJOR 1   /* B MN-major */
+#define FL_ST_F8_A_TMEM 2      /* A from tensor memory, B MN-major */
+#define FL_ST_MX8_SS 3         /* block-scaled MXFP8, A K-major, B MN-major, scales written with tcgen05.st */
+#define FL_ST_MX8_TS 4         /* block-scaled MXFP8, A from tensor memory */
+#define FL_ST_NVF4 5           /* block-scaled NVFP4, scale atoms copied with tcgen05.cp */
+#define FL_ST_F8_A_MNMAJOR 6   /* A MN-major from shared memory */
+#define FL_ST_WAIT_TIMEOUT 7   /* a wait that nothing completes: returns through the bounded-wait path */
+int fl_selftest_mma(int32_t which, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, float* d,
+                    int32_t* status, int64_t wait_cycles, void* stream);
+
+/* Copies the device status word to the host (synchronises the stream). */
+int fl_read_status(const int32_t* status, int32_t* host_value, void* stream);
+
+int fl_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

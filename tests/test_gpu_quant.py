@@ -1,0 +1,124 @@
+"""GPU parity of the fused quantiser against the CPU oracle and the golden fixtures: every byte output bit-exact."""
+import json
+import hashlib
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from inputs import DISTS, make, attention_inputs
+from oracle import quant_oracle as Q
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def same(got, want, what):
+    g = got.detach().contiguous().cpu().view(torch.uint8).numpy() if isinstance(got, torch.Tensor) else got
+    w = np.ascontiguousarray(want).view(np.uint8)
+    assert g.size == w.size, (what, g.shape, w.shape)
+    n = int((g.reshape(-1) != w.reshape(-1)).sum())
+    assert n == 0, f"{what}: {n} of {w.size} bytes differ"
+
+
+def run(x, **kw):
+    from flamia_blackwell_attention_b200.kernels import quantize_fp8_blocks
+    return quantize_fp8_blocks(x.cuda(), **kw)
+
+
+@pytest.mark.parametrize("dist", DISTS)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_blocks_ten_families(dist, dtype):
+    x = make((2, 256, 3, 128), dist, dtype)
+    got = run(x, make_channel_major_copy=True, output_sf_atoms=True)
+    ref = Q.fp8_token_blocks(x.float().numpy())
+    for k in ("codes", "codes_t", "e", "fac", "sf_tok_raw", "sf_dim_raw"):
+        same(got[k], ref[k], f"{dist} {dtype} {k}")
+
+
+@pytest.mark.parametrize("dist", [d for d in DISTS if d != "huge"])   # rotated "huge" rows overflow to inf / NaN
+def test_blocks_rotated(dist):
+    x = make((2, 256, 3, 128), dist)
+    got = run(x, apply_hadamard_rotation=True, also_make_nvfp4_copy=True, output_sf_atoms=True)
+    ref = Q.fp8_token_blocks(x.float().numpy(), rotate=True, nvfp4_copy=True)
+    for k in ("codes", "e", "fac", "sf_tok_raw", "sf_dim_raw", "x4"):
+        same(got[k], ref[k], f"{dist} rot {k}")
+    same(got["sf4_raw"], ref["sf4"], f"{dist} rot sf4")
+
+
+@pytest.mark.parametrize("dist", DISTS)
+def test_nvfp4_copy_and_scope(dist):
+    x = make((2, 256, 3, 128), dist)
+    got = run(x, also_make_nvfp4_copy=True)
+    r4 = Q.nvfp4_rows(x.float().numpy())
+    same(got["x4"], r4["codes"], f"{dist} x4")
+    same(got["sf4_raw"], r4["sf"], f"{dist} sf4")
+    if dist != "huge":
+        got = run(x, also_make_nvfp4_copy=True, apply_hadamard_rotation=True, hadamard_rotation_scope="nvfp4_copy")
+        r4 = Q.nvfp4_rows(x.float().numpy(), rotate=True)
+        same(got["x4"], r4["codes"], f"{dist} rotated x4")
+        same(got["sf4_raw"], r4["sf"], f"{dist} rotated sf4")
+        same(got["codes"], Q.fp8_token_blocks(x.float().numpy())["codes"], f"{dist} unrotated codes")
+
+
+@pytest.mark.parametrize("dist", ["n01", "outlier", "zeros", "mixed", "subnorm_sf"])
+@pytest.mark.parametrize("d", [128, 64])
+def test_token_local_and_d64(dist, d):
+    x = make((1, 384, 2, d), dist)
+    got = run(x, token_local_exponents=True, output_sf_atoms=True)
+    ref = Q.fp8_token_blocks(x.float().numpy(), token_local=True)
+    for k in ("codes", "e", "fac", "sf_tok_raw", "sf_dim_raw", "token_factors"):
+        same(got[k], ref[k], f"{dist} tl {k}")
+    got = run(x, make_channel_major_copy=True, output_sf_atoms=True)
+    ref = Q.fp8_token_blocks(x.float().numpy())
+    for k in ("codes", "codes_t", "e", "fac", "sf_tok_raw", "sf_dim_raw"):
+        same(got[k], ref[k], f"{dist} d{d} {k}")
+
+
+@pytest.mark.parametrize("dist", ["n01", "outlier", "zeros", "mixed"])
+@pytest.mark.parametrize("d", [128, 64])
+def test_prologue_d_lse_and_zeroed_accumulator(dist, d):
+    x = make((1, 384, 2, d), dist)
+    o = make((1, 384, 2, d), "n01", seed=5)
+    lse = torch.randn(1, 2, 384, generator=torch.Generator().manual_seed(9))
+    lse[0, 1, 3:9] = -float("inf")
+    acc = torch.full((1, 2, 384, d), 7.0, dtype=torch.float16, device="cuda")
+    got = run(x, compute_d_with_output=o.cuda(), shifted_log2_lse_from=lse.cuda(), log2_lse_shift=8.0,
+              d_multiplier=-2.0 ** -8, zero_accumulator=acc)
+    ref = Q.fp8_token_blocks(x.float().numpy(), d_with_output=o.float().numpy(), lse=lse.numpy(), lse_shift=8.0,
+                             d_multiplier=-2.0 ** -8)
+    same(got["codes"], ref["codes"], "codes")
+    same(got["D"], ref["D"], "D (tree order, bitwise)")
+    same(got["lse_log2"], ref["lse_log2"], "lse_log2")
+    assert float(acc.abs().max()) == 0.0
+
+
+def test_golden_small_fixture_on_gpu():
+    small = np.load(os.path.join(HERE, "golden", "quant_small.npz"))
+    for dist in ("n01", "zeros", "mixed"):
+        for d in (128, 64):
+            key = f"{dist}.{d}."
+            x = torch.from_numpy(small[key + "x"]).view(torch.bfloat16)
+            got = run(x, output_sf_atoms=True)
+            same(got["codes"], small[key + "plain.codes"], key + "codes")
+            same(got["e"], small[key + "plain.e"], key + "e")
+            same(got["fac"], small[key + "plain.fac"], key + "fac")
+            same(got["sf_tok_raw"], small[key + "plain.sf_tok_raw"], key + "sf_tok")
+            if d == 128:
+                got = run(x, apply_hadamard_rotation=True, also_make_nvfp4_copy=True)
+                same(got["codes"], small[key + "rot.codes"], key + "rot codes")
+                same(got["x4"], small[key + "nvrot.codes"], key + "nvrot codes")
+                same(got["sf4_raw"], small[key + "nvrot.sf"], key + "nvrot sf")
+
+
+def test_config_shapes_digest_property():
+    # full-size property at the headline shape: dequantised codes reproduce x within half an E4M3 step of the block scale
+    q, _, _, _ = attention_inputs(1, 4096, 16, 16, 128, seed=0)
+    got = run(q)
+    codes = got["codes"].float()
+    fac = got["fac"].repeat_interleave(32, 2).permute(0, 2, 1)[..., None]
+    deq = codes * fac
+    err = (deq - q.cuda().float()).abs()
+    assert float((err / fac).max()) <= 16.0 + 1e-6      # half of the largest E4M3 step (32) in units of the block scale
+    assert float(codes.abs().max()) <= 448.0
