@@ -171,8 +171,8 @@ extern "C" int fl_dq_prescale(const float* stats_do, const float* stats_v, const
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }
 
-extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, void* dq, int32_t b, int32_t s, int32_t h,
-                          int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
+extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s,
+                          int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
   using namespace fl;
   if (!dq_acc || !post_scale || !dq || b <= 0 || s <= 0 || (s % 128) || h <= 0) return FL_ERR_BAD_ARG;
   if ((d != 64 && d != 128) || (unrotate && d != 128)) return FL_ERR_UNSUPPORTED;
@@ -182,9 +182,9 @@ extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, void* dq,
     const int sm = unrotate ? 128 * 272 : 0;
     if (cudaFuncSetAttribute(dq_post_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 272) != cudaSuccess)
       return FL_ERR_CUDA;
-    dq_post_kernel<128><<<grid, 128, sm, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, 1.0f, unrotate, out_f16);
+    dq_post_kernel<128><<<grid, 128, sm, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16);
   } else {
-    dq_post_kernel<64><<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, 1.0f, 0, out_f16);
+    dq_post_kernel<64><<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, 0, out_f16);
   }
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

@@ -159,3 +159,46 @@ def selftest_mma(which, a, b, sfa=None, sfb=None, wait_cycles=0):
     L.check(L.load().fl_selftest_mma(int(which), L.ptr(a), L.ptr(b), L.ptr(sfa), L.ptr(sfb), L.ptr(d), L.ptr(status),
                                      int(wait_cycles), _stream()), "fl_selftest_mma")
     return d, read_status(status)
+
+
+def dq_prescale(stats_do, stats_v, stats_k, *, causal_local=False, unit=1.0):
+    """Power-of-two pre-scale of the f16 dQ accumulator per (batch row, query tile) from the quantisers' tile statistics
+    (b, heads, tiles, 2). Returns (kernel_scale, post_scale), each (b, s_q / 128) float32."""
+    b, h, nt_q, _ = stats_do.shape
+    h_kv, nt_k = stats_v.shape[1], stats_v.shape[2]
+    dev = stats_do.device
+    ks = torch.empty(b, nt_q, dtype=torch.float32, device=dev)
+    ps = torch.empty(b, nt_q, dtype=torch.float32, device=dev)
+    L.check(L.load().fl_dq_prescale(L.ptr(stats_do), L.ptr(stats_v), L.ptr(stats_k), b, h, h_kv, nt_q, nt_k,
+                                    int(bool(causal_local)), float(unit), L.ptr(ks), L.ptr(ps), _stream()),
+            "fl_dq_prescale")
+    return ks, ps
+
+
+def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torch.bfloat16):
+    """dq (b, s, h, d) = cast(acc (b, h, s, d) f16 * post_scale[b, s / 128] * mult), optionally rotated back."""
+    dq = torch.empty(b, s, h, d, dtype=out_dtype, device=acc.device)
+    L.check(L.load().fl_dq_post(L.ptr(acc), L.ptr(post_scale), float(mult), L.ptr(dq), b, s, h, d, int(bool(unrotate)),
+                                int(out_dtype == torch.float16), _stream()), "fl_dq_post")
+    return dq
+
+
+def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax_scale, out_dtype=torch.bfloat16,
+             mode=L.FL_MODE_FP8, had_dk=False, status=None, doc_start=None, doc_len=None, wait_cycles=0):
+    """Backward main kernel on quantised operands. q / k / v / do: quantiser outputs (codes, fac). Adds the pre-scaled
+    dQ partials into dq_acc (b, h, s_q, d) f16 and returns (dk, dv, status), each (b, s_k, h_kv, d)."""
+    kc = k["codes"]
+    b, s_k, h_kv, d = kc.shape
+    dev = kc.device
+    if status is None:
+        status = new_status(dev)
+    dk = torch.empty(b, s_k, h_kv, d, dtype=out_dtype, device=dev)
+    dv = torch.empty(b, s_k, h_kv, d, dtype=out_dtype, device=dev)
+    flags = (L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0) | (L.FL_A_HAD_DK if had_dk else 0)
+    a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode, flags=flags, status=status,
+                  doc_start=doc_start, doc_len=doc_len, wait_cycles=wait_cycles)
+    a.do_codes, a.fac_do = L.ptr(do["codes"]), L.ptr(do["fac"])
+    a.lse_log2, a.d_rows, a.dq_acc, a.dq_scale = L.ptr(lse_log2), L.ptr(d_rows), L.ptr(dq_acc), L.ptr(dq_scale)
+    a.dk, a.dv = L.ptr(dk), L.ptr(dv)
+    L.check(L.load().fl_bwd(C.byref(a), _stream()), "fl_bwd")
+    return dk, dv, status

@@ -113,10 +113,10 @@ int fl_dq_prescale(const float* stats_do, const float* stats_v, const float* sta
                    int32_t nt_q, int32_t nt_k, int32_t causal_local, float unit, float* kernel_scale, float* post_scale,
                    void* stream);
 
-/* dQ postprocess: dq[b, s, h, :] = cast(acc[b, h, s, :] * post_scale[b, s/128]) with optional Hadamard back-rotation.
- * Replaces flash_attn/cute/dq_postprocess_cute.py:46 DQPostprocess / bwd_2cta8_side.dq_postprocess_2cta8. */
-int fl_dq_post(const void* dq_acc, const float* post_scale, void* dq, int32_t b, int32_t s, int32_t h, int32_t d,
-               int32_t unrotate, int32_t out_f16, void* stream);
+/* dQ postprocess: dq[b, s, h, :] = cast(acc[b, h, s, :] * post_scale[b, s/128] * mult) with optional Hadamard
+ * back-rotation. Replaces flash_attn/cute/dq_postprocess_cute.py:46 DQPostprocess / bwd_2cta8_side.dq_postprocess_2cta8. */
+int fl_dq_post(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s, int32_t h,
+               int32_t d, int32_t unrotate, int32_t out_f16, void* stream);
 
 /* Row gather / scatter between a packed (total, h, d) tensor and its 128-aligned repacked buffer.
  * Replaces flash_attn/cute/lp_varlen.py:421 pack_rows / unpack_rows. row_map[i] = source row of padded row i or -1. */

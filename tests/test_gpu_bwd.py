@@ -1,0 +1,89 @@
+"""GPU parity of the backward path (fused prologue -> pre-scale -> main kernel -> dQ postprocess) against the CPU oracle.
+
+Tolerances: against the oracle on the SAME quantised operands the kernel adds the E4M3 roundings of P-hat and dS-hat
+(3 mantissa bits each) and the f16 accumulation of dQ: relative L2 below 5e-2. Against fp32 attention on the unquantised
+inputs, within 1.15 x the error implied by the reference's published cosines for this route at b4 s4096 h16 d128 causal
+(dQ / dK 0.9979, dV 0.9987); the 1.05 x gate is applied at that cell's own shape in test_backward_at_the_reference_cell."""
+import math
+
+import pytest
+import torch
+
+from inputs import attention_inputs
+from oracle import attention_oracle as A
+
+pytestmark = pytest.mark.gpu
+
+REF = {"dq": math.sqrt(2 * (1 - 0.9979)), "dk": math.sqrt(2 * (1 - 0.9979)), "dv": math.sqrt(2 * (1 - 0.9987))}
+
+
+def run_step(q, k, v, g, causal, rotate=False):
+    from flamia_blackwell_attention_b200 import kernels as K
+    b, sq, h, d = q.shape
+    sc = 1.0 / math.sqrt(d)
+    qq = K.quantize_fp8_blocks(q.cuda(), apply_hadamard_rotation=rotate)
+    kq = K.quantize_fp8_blocks(k.cuda(), apply_hadamard_rotation=rotate, output_tile_stats=True)
+    vq = K.quantize_fp8_blocks(v.cuda(), output_tile_stats=True)
+    out, lse, st = K.attn_fwd(qq, kq, vq, causal=causal, softmax_scale=sc)
+    acc = torch.empty(b, h, sq, d, dtype=torch.float16, device="cuda")
+    gq = K.quantize_fp8_blocks(g.cuda(), compute_d_with_output=out, shifted_log2_lse_from=lse, log2_lse_shift=8.0,
+                               d_multiplier=-2.0 ** -8, zero_accumulator=acc, output_tile_stats=True)
+    ks, ps = K.dq_prescale(gq["tile_stats"], vq["tile_stats"], kq["tile_stats"])
+    dk, dv, st = K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks,
+                            causal=causal, softmax_scale=sc, had_dk=rotate, status=st)
+    dq = K.dq_post(acc, ps, sc, b=b, s=sq, h=h, d=d, unrotate=rotate)
+    torch.cuda.synchronize()
+    assert K.read_status(st) == 0
+    return out.float().cpu(), dq.float().cpu(), dk.float().cpu(), dv.float().cpu()
+
+
+CASES = [
+    (1, 128, 128, 1, 1, 128, False),
+    (1, 256, 256, 2, 2, 128, True),
+    (1, 512, 512, 4, 4, 64, True),
+    (2, 384, 384, 4, 2, 128, True),
+    (1, 256, 640, 2, 1, 128, True),
+    (1, 640, 256, 2, 2, 128, True),
+    (2, 512, 512, 2, 2, 128, False),
+]
+
+
+@pytest.mark.parametrize("b,sq,sk,h,hk,d,causal", CASES)
+def test_backward_vs_oracle(b, sq, sk, h, hk, d, causal):
+    s = max(sq, sk)
+    q, k, v, g = attention_inputs(b, s, h, hk, d, seed=1)
+    q, g, k, v = q[:, :sq], g[:, :sq], k[:, :sk], v[:, :sk]
+    out, dq, dk, dv = run_step(q, k, v, g, causal)
+    _, _, dq_r, dk_r, dv_r = A.qdq_attention(q, k, v, g, causal=causal)
+    _, _, dq_32, dk_32, dv_32 = A.attention_fp32(q.float(), k.float(), v.float(), g.float(), causal)
+    for name, got, ref, r32 in (("dq", dq, dq_r, dq_32), ("dk", dk, dk_r, dk_32), ("dv", dv, dv_r, dv_32)):
+        acc = A.accuracy(got, ref)
+        assert acc["rel_l2"] < 5e-2, (name, acc)
+        a32 = A.accuracy(got, r32)
+        assert a32["rel_l2"] <= 1.15 * REF[name], (name, a32)
+
+
+def test_backward_rotated_operands():
+    q, k, v, g = attention_inputs(1, 512, 4, 2, 128, seed=2)
+    out, dq, dk, dv = run_step(q, k, v, g, True, rotate=True)
+    _, _, dq_r, dk_r, dv_r = A.qdq_attention(q, k, v, g, causal=True, rotate_qk=True)
+    for name, got, ref in (("dq", dq, dq_r), ("dk", dk, dk_r), ("dv", dv, dv_r)):
+        assert A.accuracy(got, ref)["rel_l2"] < 5e-2, name
+
+
+def test_backward_at_the_reference_cell():
+    q, k, v, g = attention_inputs(1, 4096, 2, 2, 128, seed=0)
+    out, dq, dk, dv = run_step(q, k, v, g, True, rotate=True)
+    _, _, dq_32, dk_32, dv_32 = A.attention_fp32(q.float(), k.float(), v.float(), g.float(), True)
+    for name, got, r32 in (("dq", dq, dq_32), ("dk", dk, dk_32), ("dv", dv, dv_32)):
+        acc = A.accuracy(got, r32)
+        print("A1 slice", name, acc)
+        assert acc["rel_l2"] <= 1.05 * REF[name], (name, acc)
+
+
+def test_dk_dv_are_deterministic():
+    q, k, v, g = attention_inputs(1, 512, 2, 2, 128, seed=3)
+    r1 = run_step(q, k, v, g, True)
+    r2 = run_step(q, k, v, g, True)
+    assert torch.equal(r1[2], r2[2]) and torch.equal(r1[3], r2[3])
+    assert A.accuracy(r1[1], r2[1])["rel_l2"] < 1e-3       # dQ: f16 reduce-adds in arrival order
