@@ -1,0 +1,122 @@
+"""The attention call as registered torch ops, so that selective activation checkpointing can save it and torch.compile
+can trace it. Same op names and schemas as the reference's flash_attn/cute/lowprec/_op.py (:12-16, 428-476):
+
+    lowbit_attn::fp8(Tensor q, Tensor k, Tensor v, Tensor[] docs, int plan, int docs_id) -> (Tensor, Tensor, Tensor[])
+    lowbit_attn::fp8_bwd(Tensor dout, Tensor[] state, int entry) -> (Tensor, Tensor, Tensor)          (and ::fp4)
+
+`plan` is a process-local integer handle into an append-only registry of resolved plans; `docs` carries the varlen
+tensors (cu_seqlens_q, cu_seqlens_k[, seqused_q, seqused_k]). The saved state is codes + factor tables + O + LSE, not the
+bf16 inputs. LSE and the state are non-differentiable; gradients are not materialised for unused outputs.
+"""
+from __future__ import annotations
+
+import threading
+from typing import List
+
+import torch
+
+from . import _routes
+
+_REG_LOCK = threading.Lock()
+_PLANS: list = []          # handle -> AttnPlan
+_ENTRIES: list = []        # backward entry handle -> (plan handle, docs meta)
+
+
+def register_plan(plan) -> int:
+    with _REG_LOCK:
+        for i, p in enumerate(_PLANS):
+            if p is plan:
+                return i
+        _PLANS.append(plan)
+        return len(_PLANS) - 1
+
+
+def _register_entry(plan_id, docs_meta) -> int:
+    with _REG_LOCK:
+        key = (plan_id, docs_meta)
+        for i, e in enumerate(_ENTRIES):
+            if e == key:
+                return i
+        _ENTRIES.append(key)
+        return len(_ENTRIES) - 1
+
+
+def _fwd_impl(q, k, v, docs: List[torch.Tensor], plan: int, docs_id: int):
+    p = _PLANS[plan]
+    cu_q = docs[0] if len(docs) > 0 else None
+    cu_k = docs[1] if len(docs) > 1 else None
+    su_q = docs[2] if len(docs) > 2 else None
+    su_k = docs[3] if len(docs) > 3 else None
+    d = _routes.docs_of(p, q, cu_q, cu_k, su_q, su_k)
+    out, lse, state = _routes.forward(p, q, k, v, d)
+    meta = None if d is None else (d.capacity, d.aligned)
+    entry = _register_entry(plan, meta)
+    # batched form: the kernels' O / LSE ARE the op's outputs (the autograd node saves those itself, an op output may not
+    # alias another); documents: the padded O / LSE of the kernels stay in the state, the outputs are the unpacked copies.
+    # The entry handle rides along as a 0-d tensor so that the backward op needs no Python object.
+    state = list(state if d is not None else state[2:]) + [torch.tensor(entry, dtype=torch.int64)]
+    return out, lse, state
+
+
+def _bwd_impl(dout, state: List[torch.Tensor], entry: int):
+    plan_id, meta = _ENTRIES[entry]
+    return _routes.backward(_PLANS[plan_id], state[:-1], dout, meta)     # state = [out_k, lse_k, codes..., entry]
+
+
+def _fake_fwd(q, k, v, docs, plan, docs_id):
+    p = _PLANS[plan]
+    sh = p.shape
+    lse_shape = (sh.h, sh.tot_q) if sh.aligned_varlen else ((0,) if (sh.varlen or p.fwd.ragged_documents) else (sh.b, sh.h, sh.s_q))
+    return torch.empty_like(q), q.new_empty(lse_shape, dtype=torch.float32), []
+
+
+def _fake_bwd(dout, state, entry):
+    plan_id, _ = _ENTRIES[entry]
+    sh = _PLANS[plan_id].shape
+    if sh.varlen:
+        kshape = (sh.tot_k, sh.h_kv, sh.d)
+    else:
+        kshape = (sh.b, sh.s_k, sh.h_kv, sh.d)
+    return torch.empty_like(dout), dout.new_empty(kshape), dout.new_empty(kshape)
+
+
+def _define(entry: str):
+    name = f"lowbit_attn::{entry}"
+    torch.library.define(name, "(Tensor q, Tensor k, Tensor v, Tensor[] docs, int plan, int docs_id) -> "
+                               "(Tensor, Tensor, Tensor[])")
+    torch.library.define(name + "_bwd", "(Tensor dout, Tensor[] state, int entry) -> (Tensor, Tensor, Tensor)")
+    torch.library.impl(name, "CUDA")(_fwd_impl)
+    torch.library.impl(name + "_bwd", "CUDA")(_bwd_impl)
+    torch.library.register_fake(name)(_fake_fwd)
+    torch.library.register_fake(name + "_bwd")(_fake_bwd)
+
+    def setup_context(ctx, inputs, output):
+        out, lse, state = output
+        ctx.n_docs = len(inputs[3])
+        ctx.set_materialize_grads(False)
+        ctx.mark_non_differentiable(lse, *state)
+        ctx.save_for_backward(out, lse, *state)
+
+    def backward(ctx, dout, dlse, dstate):
+        saved = list(ctx.saved_tensors)
+        nodocs = [None] * ctx.n_docs
+        if dout is None:
+            return None, None, None, nodocs, None, None
+        entry_id = int(saved[-1])
+        state = saved[2:] if _ENTRIES[entry_id][1] is not None else saved
+        dq, dk, dv = getattr(torch.ops.lowbit_attn, entry + "_bwd")(dout.contiguous(), state, entry_id)
+        return dq, dk, dv, nodocs, None, None
+
+    torch.library.register_autograd(name, backward, setup_context=setup_context)
+
+
+for _e in ("fp8", "fp4"):
+    _define(_e)
+
+
+def op_apply(plan, q, k, v, docs_tensors):
+    """Runs the registered op of the plan's entry; returns (out, lse)."""
+    handle = register_plan(plan)
+    op = getattr(torch.ops.lowbit_attn, plan.entry)
+    out, lse, _state = op(q, k, v, list(docs_tensors), handle, 0)
+    return out, lse

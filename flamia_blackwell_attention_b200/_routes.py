@@ -1,0 +1,169 @@
+"""Route bodies: what one resolved plan launches, forward and backward. Host glue only (allocation, views, the order
+of the C-ABI calls); mirrors the launch sequence of the reference's flash_attn/cute/lowprec/_routes.py (_fp8_forward_mx
+:709, _fp8_backward_mx :911, _e4pv_forward_blk32 :308, run_documents :1388):
+
+  forward   3 quantiser launches (Q, K [rotated], V) + 1 forward kernel
+  backward  1 fused prologue (dO quantiser + D + shifted LSE + zeroed accumulator) + 1 pre-scale + 1 main kernel
+            + 1 dQ postprocess
+No host synchronisation anywhere; everything is enqueued on the current stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+from . import kernels as K
+
+P_SHIFT_LOG2 = 8.0     # the backward recomputes P' = 2^8 P (its E4M3 P-hat then uses the normal range)
+
+
+# --------------------------------------------------------------------------------------------------------------- docs
+class Docs:
+    """Packed documents laid out at 128-aligned starts of one padded buffer. Built on the device without a host sync:
+    the padded capacity is the host-known bound total + 127 * n_docs rounded up to 128."""
+
+    def __init__(self, cu, lens, total, aligned):
+        dev = cu.device
+        self.n = int(lens.numel())
+        self.len = lens.to(torch.int32).contiguous()
+        self.aligned = aligned
+        if aligned:
+            self.start = cu[:-1].to(torch.int32).contiguous()
+            self.capacity = int(total)
+            self.row_map = None
+            return
+        padded = ((self.len + 127) // 128) * 128
+        ends = torch.cumsum(padded, 0)
+        self.start = (ends - padded).to(torch.int32).contiguous()
+        self.capacity = ((int(total) + 127 * self.n + 127) // 128) * 128
+        rows = torch.arange(self.capacity, device=dev, dtype=torch.int32)
+        doc = torch.searchsorted(ends.to(torch.int32), rows, right=True).clamp_(max=self.n - 1)
+        off = rows - self.start[doc]
+        src = cu[:-1].to(torch.int32)[doc] + off
+        self.row_map = torch.where((off >= 0) & (off < self.len[doc]), src, torch.full_like(src, -1)).contiguous()
+
+    def pack(self, x):
+        """(total, h, d) -> (1, capacity, h, d) with zero padding rows."""
+        if self.aligned:
+            return x.unsqueeze(0)
+        x = x.contiguous()
+        out = torch.empty(1, self.capacity, *x.shape[1:], dtype=x.dtype, device=x.device)
+        rb = x.shape[1] * x.shape[2] * x.element_size()
+        L.check(L.load().fl_pack_rows(L.ptr(x), L.ptr(out), L.ptr(self.row_map), self.capacity, rb, K._stream()),
+                "fl_pack_rows")
+        return out
+
+    def unpack(self, y, total):
+        """(1, capacity, h, d) -> (total, h, d)."""
+        if self.aligned:
+            return y.squeeze(0)
+        out = torch.empty(total, *y.shape[2:], dtype=y.dtype, device=y.device)
+        rb = y.shape[2] * y.shape[3] * y.element_size()
+        L.check(L.load().fl_unpack_rows(L.ptr(y), L.ptr(out), L.ptr(self.row_map), self.capacity, rb, K._stream()),
+                "fl_unpack_rows")
+        return out
+
+
+def docs_of(plan, q, cu_q, cu_k, seqused_q, seqused_k):
+    """The document table of a call, or None for the batched form."""
+    sh = plan.shape
+    if sh.varlen:
+        if sh.aligned_varlen:
+            return Docs(cu_q, seqused_q, sh.tot_q, True)
+        lens = (cu_q[1:] - cu_q[:-1])
+        return Docs(cu_q, lens, sh.tot_q, False)
+    if plan.fwd.ragged_documents:     # batch rows of a length that is no multiple of 128 run as documents
+        b, s = sh.b, sh.s_q
+        cu = torch.arange(0, (b + 1) * s, s, device=q.device, dtype=torch.int32)
+        return Docs(cu, torch.full((b,), s, device=q.device, dtype=torch.int32), b * s, False)
+    return None
+
+
+# --------------------------------------------------------------------------------------------------------------- forward
+def forward(plan, q, k, v, docs):
+    """Returns (out, lse, state): out / lse in the caller's layout, state = the tensors the backward needs."""
+    sh, f = plan.shape, plan.fwd
+    fp4 = plan.entry == "fp4"
+    mode = L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8
+    tl = f.operand_scaling == "token_local"
+    if docs is not None:
+        qv = q.reshape(sh.b * sh.s_q, sh.h, sh.d) if q.dim() == 4 else q
+        kv = k.reshape(-1, sh.h_kv, sh.d) if k.dim() == 4 else k
+        vv = v.reshape(-1, sh.h_kv, sh.d) if v.dim() == 4 else v
+        qp, kp, vp = docs.pack(qv), docs.pack(kv), docs.pack(vv)
+    else:
+        qp, kp, vp = q, k, v
+    need_bwd = plan.bwd.kernel != "none"
+    # rotation: the 8-bit route rotates the E4M3 codes; the mixed route rotates only the NVFP4 S operands
+    qk_kw = dict(apply_hadamard_rotation=f.qk_hadamard, hadamard_rotation_scope="nvfp4_copy" if fp4 else "all",
+                 also_make_nvfp4_copy=fp4, token_local_exponents=tl)
+    qq = K.quantize_fp8_blocks(qp, **qk_kw)
+    kq = K.quantize_fp8_blocks(kp, output_tile_stats=need_bwd, **qk_kw)
+    vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl)
+    status = K.new_status(q.device)
+    out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=q.dtype, mode=mode,
+                             status=status, token_local=tl,
+                             doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
+    state = [out, lse, qq["codes"], qq["fac"], kq["codes"], kq["fac"], vq["codes"], vq["fac"], status]
+    if need_bwd:
+        state += [kq["tile_stats"], vq["tile_stats"]]
+    if fp4:
+        state += [qq["x4"], qq["sf4_raw"], kq["x4"], kq["sf4_raw"]]
+    if tl:
+        state += [qq["token_factors"], kq["token_factors"], vq["token_factors"]]
+    if docs is not None:
+        state += [docs.start, docs.len] + ([] if docs.row_map is None else [docs.row_map])
+        out_user = docs.unpack(out, sh.tot_q if sh.varlen else sh.b * sh.s_q)
+        if not sh.varlen:
+            out_user = out_user.reshape(sh.b, sh.s_q, sh.h, sh.d)
+        lse_user = lse[0] if sh.aligned_varlen else lse.new_zeros(0)     # (h, total_q) on the aligned form only
+    else:
+        out_user, lse_user = out, lse
+    return out_user, lse_user, state
+
+
+# --------------------------------------------------------------------------------------------------------------- backward
+def backward(plan, state, dout, docs_meta):
+    """dq, dk, dv in the caller's layout. state as returned by forward(); docs_meta = (capacity, aligned) or None."""
+    sh, f, bw = plan.shape, plan.fwd, plan.bwd
+    fp4 = plan.entry == "fp4"
+    tl = f.operand_scaling == "token_local"
+    it = iter(state)
+    out, lse, qc, qf, kc, kf, vc, vf, status, kstats, vstats = (next(it) for _ in range(11))
+    qq, kq, vq = dict(codes=qc, fac=qf), dict(codes=kc, fac=kf), dict(codes=vc, fac=vf)
+    if fp4:
+        qq["x4"], qq["sf4_raw"], kq["x4"], kq["sf4_raw"] = (next(it) for _ in range(4))
+    if tl:
+        qq["token_factors"], kq["token_factors"], vq["token_factors"] = (next(it) for _ in range(3))
+    docs = None
+    if docs_meta is not None:
+        docs = object.__new__(Docs)
+        docs.start, docs.len = next(it), next(it)
+        docs.capacity, docs.aligned = docs_meta
+        docs.n = int(docs.len.numel())
+        docs.row_map = None if docs.aligned else next(it)
+        g = dout.reshape(-1, sh.h, sh.d) if dout.dim() == 4 else dout
+        gp = docs.pack(g.contiguous())
+    else:
+        gp = dout.contiguous()
+    b, s_q, h, d = out.shape
+    acc = torch.empty(b, h, s_q, d, dtype=torch.float16, device=out.device)
+    gq = K.quantize_fp8_blocks(gp, compute_d_with_output=out, shifted_log2_lse_from=lse, log2_lse_shift=P_SHIFT_LOG2,
+                               d_multiplier=-2.0 ** -P_SHIFT_LOG2, zero_accumulator=acc, output_tile_stats=True,
+                               token_local_exponents=tl)
+    ks, ps = K.dq_prescale(gq["tile_stats"], vstats, kstats, causal_local=bw.dq_prescale == "causal_tile")
+    had8 = f.qk_hadamard and not fp4           # only the 8-bit route's E4M3 codes are rotated
+    dk, dv, _ = K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks,
+                           causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=out.dtype,
+                           mode=L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8, had_dk=had8, status=status,
+                           token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all",
+                           doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
+    dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype)
+    if docs is not None:
+        tq = sh.tot_q if sh.varlen else sh.b * sh.s_q
+        tk = sh.tot_k if sh.varlen else sh.b * sh.s_k
+        dq, dk, dv = docs.unpack(dq, tq), docs.unpack(dk, tk), docs.unpack(dv, tk)
+        if not sh.varlen:
+            dq = dq.reshape(sh.b, sh.s_q, sh.h, sh.d)
+            dk, dv = dk.reshape(sh.b, sh.s_k, sh.h_kv, sh.d), dv.reshape(sh.b, sh.s_k, sh.h_kv, sh.d)
+    return dq, dk, dv

@@ -1,0 +1,147 @@
+"""Public entry points flash_attn_fp8 / flash_attn_fp4: same signatures, defaults, return values and refusal convention
+as the reference's flash_attn/cute/lowprec/api.py (flash_attn_fp4 :169, flash_attn_fp8 :270). Each call resolves one
+immutable plan (cached per argument values and tensor metadata) before anything is quantised or launched, then runs the
+registered op lowbit_attn::fp8 / ::fp4, whose autograd node carries the plan handle to the backward.
+"""
+from __future__ import annotations
+
+import collections
+import threading
+import warnings
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from . import _op
+from .options import FP4AttnOptions, FP8AttnOptions
+from .plan import AttnPlan, _fail, resolve_fp4, resolve_fp8
+
+__all__ = ["flash_attn_fp4", "flash_attn_fp8"]
+
+_PLAN_CACHE_SIZE = 1024
+_PLAN_CACHE: "collections.OrderedDict" = collections.OrderedDict()
+_PLAN_LOCK = threading.Lock()
+_REPACK_WARNED = False
+REPACK_WARNING = (
+    "flash_attn_{entry} with cu_seqlens_q / cu_seqlens_k but without seqused_q / seqused_k: the documents are COPIED "
+    "into a buffer with every start rounded up to 128 tokens and unpacked afterwards (one extra read and write of q, k, "
+    "v, o and of dO, dQ, dK, dV). The zero-copy form lays each document out at a start that is a multiple of 128 "
+    "(cu_seqlens = those starts, total % 128 == 0) and passes its true length as seqused_q / seqused_k. (Warned once.)")
+
+
+def _meta(t):
+    if t is None:
+        return None
+    if isinstance(t, torch.Tensor):
+        return (tuple(t.shape), t.dtype, bool(t.requires_grad), t.device.type)
+    return ("obj", type(t).__name__)
+
+
+def _cached_plan(resolve, q, k, v, kw) -> AttnPlan:
+    from . import interface_bwd_fp4
+    try:
+        key = (resolve.__name__, torch.is_grad_enabled(), bool(interface_bwd_fp4.DQ_CAUSAL_PRESCALE), _meta(q), _meta(k),
+               _meta(v), tuple(sorted((n, _meta(x) if isinstance(x, torch.Tensor) else x) for n, x in kw.items())))
+        hash(key)
+    except TypeError:
+        return resolve(q, k, v, **kw)
+    with _PLAN_LOCK:
+        plan = _PLAN_CACHE.get(key)
+        if plan is not None:
+            _PLAN_CACHE.move_to_end(key)
+            return plan
+    plan = resolve(q, k, v, **kw)          # refusals raise here and are never cached
+    with _PLAN_LOCK:
+        _PLAN_CACHE[key] = plan
+        if len(_PLAN_CACHE) > _PLAN_CACHE_SIZE:
+            _PLAN_CACHE.popitem(last=False)
+    return plan
+
+
+def _run(plan, q, k, v, cu_q, cu_k, su_q, su_k, return_lse):
+    global _REPACK_WARNED
+    if not q.is_cuda:
+        raise RuntimeError(f"flash_attn_{plan.entry}: q, k, v must be CUDA tensors (this library has no CPU path)")
+    sh = plan.shape
+    if sh.varlen and sh.tot_q != sh.tot_k:
+        _fail("B8", NotImplementedError, "packed documents are self-attention documents here: q and k must share "
+                                         "cu_seqlens (total_q == total_k)")
+    if plan.fwd.ragged_documents and sh.s_q != sh.s_k:
+        _fail("B8", NotImplementedError, "lengths that are no multiple of 128 run the batch rows as self-attention "
+                                         f"documents: s_q must equal s_k; got {sh.s_q} and {sh.s_k}")
+    if sh.varlen and not sh.aligned_varlen and not _REPACK_WARNED:
+        _REPACK_WARNED = True
+        warnings.warn(REPACK_WARNING.format(entry=plan.entry), UserWarning, stacklevel=3)
+    docs = [t for t in (cu_q, cu_k, su_q, su_k) if t is not None] if sh.varlen else []
+    out, lse = _op.op_apply(plan, q, k, v, docs)
+    if return_lse:
+        if lse.numel() == 0:
+            _fail("B8", ValueError, "return_lse is served on the batched and the aligned varlen forms, not under "
+                                    "repacked documents")
+        return out, lse
+    return out
+
+
+def flash_attn_fp8(q, k, v, *, softmax_scale: Optional[float] = None, causal: bool = False,
+                   window_size: Tuple[Optional[int], Optional[int]] = (None, None), softcap: float = 0.0,
+                   score_mod: Optional[Callable] = None, score_mod_bwd: Optional[Callable] = None,
+                   mask_mod: Optional[Callable] = None, aux_tensors: Optional[tuple] = None,
+                   cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q: Optional[int] = None,
+                   max_seqlen_k: Optional[int] = None, seqused_k=None, seqused_q=None, deterministic: bool = False,
+                   return_lse: bool = False, qk_hadamard: Optional[bool] = None, q_quantized=None, k_quantized=None,
+                   q_scale_fused: bool = False, options: Optional[FP8AttnOptions] = None, q_descale=None, k_descale=None,
+                   v_descale=None, grad_proxies=None, doc_maps=None):
+    """8-bit (MXFP8) attention, forward and backward, on B200.
+
+    q: (b, s, h, d); k, v: (b, s, h_kv, d); bf16 or f16; h % h_kv == 0; d in {64, 128}. Packed (total, h, d) with
+    cu_seqlens_q / cu_seqlens_k (repacked), or with seqused_q / seqused_k as well (aligned, zero-copy: starts multiples of
+    128). Returns out (dtype and shape of q); with return_lse=True (out, lse) with lse (b, h, s) float32 in nats,
+    non-differentiable ((h, total_q) on the aligned varlen form). causal is bottom-right aligned.
+    E4M3 Q, K, V, dO with one UE8M0 exponent per 32 tokens x the whole head dim; qk_hadamard=None turns the random-sign
+    Hadamard rotation of Q / K on at d = 128. Every unserved combination raises with a `.rule` before any launch."""
+    if doc_maps is not None:
+        _fail("B8", NotImplementedError, "doc_maps (precomputed document maps) are not built: pass cu_seqlens_*")
+    if q_descale is not None or k_descale is not None or v_descale is not None or grad_proxies is not None or \
+            (isinstance(q, torch.Tensor) and q.dtype == torch.float8_e4m3fn):
+        _fail("B7", NotImplementedError, "FA3-style pre-quantised E4M3 inputs (q_descale / k_descale / v_descale / "
+                                         "grad_proxies) are not built")
+    if aux_tensors is not None:
+        _fail("B3", NotImplementedError, "aux_tensors belong to score_mod / mask_mod, which this library does not take")
+    plan = _cached_plan(resolve_fp8, q, k, v, dict(
+        softmax_scale=softmax_scale, causal=causal, window_size=tuple(window_size), softcap=softcap, score_mod=score_mod,
+        score_mod_bwd=score_mod_bwd, mask_mod=mask_mod, cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k,
+        max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, seqused_k=seqused_k, seqused_q=seqused_q,
+        deterministic=deterministic, return_lse=return_lse, qk_hadamard=qk_hadamard, q_quantized=q_quantized,
+        k_quantized=k_quantized, q_scale_fused=q_scale_fused, options=options))
+    return _run(plan, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k, return_lse)
+
+
+def flash_attn_fp4(q, k, v, *, softmax_scale: Optional[float] = None, causal: bool = False,
+                   window_size: Tuple[Optional[int], Optional[int]] = (None, None), softcap: float = 0.0,
+                   score_mod: Optional[Callable] = None, score_mod_bwd: Optional[Callable] = None,
+                   mask_mod: Optional[Callable] = None, aux_tensors: Optional[tuple] = None,
+                   cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q: Optional[int] = None,
+                   max_seqlen_k: Optional[int] = None, seqused_k=None, seqused_q=None, deterministic: bool = False,
+                   return_lse: bool = False, pv_precision: str = "fp8", backward: str = "e4m3",
+                   causal_safety: str = "auto", qk_hadamard: Optional[bool] = None,
+                   options: Optional[FP4AttnOptions] = None, q_descale=None, k_descale=None, v_descale=None,
+                   doc_maps=None):
+    """Mixed NVFP4 / FP8 attention, forward and backward, on B200: Q.K^T and its recomputation in the backward on NVFP4
+    codes (E2M1, one E4M3 scale per 16 along d); P.V, dP, dV, dK, dQ on E4M3 token blocks. Arguments, shapes and returns
+    as flash_attn_fp8; d = 128. With qk_hadamard on (default) the NVFP4 codes are of the rotated rows, the E4M3 copies of
+    the rows as given."""
+    if doc_maps is not None:
+        _fail("B8", NotImplementedError, "doc_maps (precomputed document maps) are not built: pass cu_seqlens_*")
+    if q_descale is not None or k_descale is not None or v_descale is not None or \
+            any(isinstance(t, torch.Tensor) and t.dtype == torch.float8_e4m3fn for t in (q, k, v)):
+        _fail("B7", TypeError, "flash_attn_fp4 takes bf16 / f16 inputs: pre-quantised E4M3 inputs are a flash_attn_fp8 "
+                               "feature of the reference and are not built here")
+    if aux_tensors is not None:
+        _fail("B3", NotImplementedError, "aux_tensors belong to score_mod / mask_mod, which this library does not take")
+    plan = _cached_plan(resolve_fp4, q, k, v, dict(
+        softmax_scale=softmax_scale, causal=causal, window_size=tuple(window_size), softcap=softcap, score_mod=score_mod,
+        score_mod_bwd=score_mod_bwd, mask_mod=mask_mod, cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k,
+        max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, seqused_k=seqused_k, seqused_q=seqused_q,
+        deterministic=deterministic, return_lse=return_lse, pv_precision=pv_precision, backward=backward,
+        causal_safety=causal_safety, qk_hadamard=qk_hadamard, options=options))
+    return _run(plan, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k, return_lse)

@@ -112,14 +112,17 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
 
 
 def attn_args(q, k, v, *, causal, softmax_scale, mode=L.FL_MODE_FP8, flags=0, status=None, doc_start=None, doc_len=None,
-              wait_cycles=0):
-    """AttnArgs from quantiser outputs q / k / v (dicts with codes, fac [, x4, sf4_raw])."""
+              wait_cycles=0, token_local=False):
+    """AttnArgs from quantiser outputs q / k / v (dicts with codes, fac [, x4, sf4_raw, token_factors])."""
     qc, kc, vc = q["codes"], k["codes"], v["codes"]
     b, s_q, h, d = qc.shape
     s_k, h_kv = kc.shape[1], kc.shape[2]
     a = L.AttnArgs()
     a.q_codes, a.k_codes, a.v_codes = L.ptr(qc), L.ptr(kc), L.ptr(vc)
-    a.fac_q, a.fac_k, a.fac_v = L.ptr(q["fac"]), L.ptr(k["fac"]), L.ptr(v["fac"])
+    fkey = "token_factors" if token_local else "fac"
+    a.fac_q, a.fac_k, a.fac_v = L.ptr(q[fkey]), L.ptr(k[fkey]), L.ptr(v[fkey])
+    if token_local:
+        flags |= L.FL_A_TOKEN_LOCAL
     if mode == L.FL_MODE_FP4:
         a.q4, a.k4, a.sfq4, a.sfk4 = L.ptr(q["x4"]), L.ptr(k["x4"]), L.ptr(q["sf4_raw"]), L.ptr(k["sf4_raw"])
     a.b, a.s_q, a.s_k, a.h, a.h_kv, a.d = b, s_q, s_k, h, h_kv, d
@@ -134,7 +137,7 @@ def attn_args(q, k, v, *, causal, softmax_scale, mode=L.FL_MODE_FP8, flags=0, st
 
 
 def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L.FL_MODE_FP8, status=None,
-             doc_start=None, doc_len=None, wait_cycles=0):
+             doc_start=None, doc_len=None, wait_cycles=0, token_local=False):
     """Forward kernel on quantised operands. Returns (out (b, s_q, h, d), lse (b, h, s_q) float32, status)."""
     qc = q["codes"]
     b, s_q, h, d = qc.shape
@@ -145,7 +148,7 @@ def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L
     lse = torch.empty(b, h, s_q, dtype=torch.float32, device=dev)
     a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode,
                   flags=L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0, status=status, doc_start=doc_start,
-                  doc_len=doc_len, wait_cycles=wait_cycles)
+                  doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local)
     a.out, a.lse = L.ptr(out), L.ptr(lse)
     L.check(L.load().fl_fwd(C.byref(a), _stream()), "fl_fwd")
     return out, lse, status
@@ -184,7 +187,8 @@ def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torc
 
 
 def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax_scale, out_dtype=torch.bfloat16,
-             mode=L.FL_MODE_FP8, had_dk=False, status=None, doc_start=None, doc_len=None, wait_cycles=0):
+             mode=L.FL_MODE_FP8, had_dk=False, status=None, doc_start=None, doc_len=None, wait_cycles=0,
+             token_local=False, dq_rowlocal=False):
     """Backward main kernel on quantised operands. q / k / v / do: quantiser outputs (codes, fac). Adds the pre-scaled
     dQ partials into dq_acc (b, h, s_q, d) f16 and returns (dk, dv, status), each (b, s_k, h_kv, d)."""
     kc = k["codes"]
@@ -194,10 +198,11 @@ def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax
         status = new_status(dev)
     dk = torch.empty(b, s_k, h_kv, d, dtype=out_dtype, device=dev)
     dv = torch.empty(b, s_k, h_kv, d, dtype=out_dtype, device=dev)
-    flags = (L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0) | (L.FL_A_HAD_DK if had_dk else 0)
+    flags = (L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0) | (L.FL_A_HAD_DK if had_dk else 0) | \
+        (L.FL_A_DQ_ROWLOCAL if dq_rowlocal else 0)
     a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode, flags=flags, status=status,
-                  doc_start=doc_start, doc_len=doc_len, wait_cycles=wait_cycles)
-    a.do_codes, a.fac_do = L.ptr(do["codes"]), L.ptr(do["fac"])
+                  doc_start=doc_start, doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local)
+    a.do_codes, a.fac_do = L.ptr(do["codes"]), L.ptr(do["token_factors" if token_local else "fac"])
     a.lse_log2, a.d_rows, a.dq_acc, a.dq_scale = L.ptr(lse_log2), L.ptr(d_rows), L.ptr(dq_acc), L.ptr(dq_scale)
     a.dk, a.dv = L.ptr(dk), L.ptr(dv)
     L.check(L.load().fl_bwd(C.byref(a), _stream()), "fl_bwd")

@@ -1,0 +1,122 @@
+"""GPU: the public entry points end to end (plan -> custom op -> autograd) against the CPU oracle: batched, GQA, f16,
+lengths that are no multiple of 128, repacked and aligned packed documents. Tolerances as tests/test_gpu_bwd.py."""
+import math
+
+import pytest
+import torch
+
+from inputs import attention_inputs, packed_doc_lengths
+from oracle import attention_oracle as A
+
+pytestmark = pytest.mark.gpu
+
+
+def _step(fn, q, k, v, g, **kw):
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = fn(qc, kc, vc, **kw)
+    lse = None
+    if isinstance(out, tuple):
+        out, lse = out
+    out.backward(g.cuda())
+    torch.cuda.synchronize()
+    return out.detach().float().cpu(), qc.grad.float().cpu(), kc.grad.float().cpu(), vc.grad.float().cpu(), lse
+
+
+def _check(got, ref, tol=5e-2, names=("o", "dq", "dk", "dv")):
+    for n, a, r in zip(names, got, ref):
+        acc = A.accuracy(a, r)
+        assert acc["rel_l2"] < tol, (n, acc)
+
+
+def test_fp8_batched_autograd_default_route():
+    from flamia_blackwell_attention_b200 import flash_attn_fp8
+    q, k, v, g = attention_inputs(2, 512, 4, 2, 128, seed=4)
+    o, dq, dk, dv, lse = _step(flash_attn_fp8, q, k, v, g, causal=True, return_lse=True)
+    ro, rl, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=True, rotate_qk=True)
+    _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))
+    assert lse.shape == (2, 4, 512) and not lse.requires_grad
+    assert float((lse.cpu() - rl).abs().max()) < 2e-3
+
+
+def test_fp8_f16_inputs_and_d64():
+    from flamia_blackwell_attention_b200 import flash_attn_fp8
+    q, k, v, g = (t.half() for t in attention_inputs(1, 512, 4, 4, 64, seed=5))
+    o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True)
+    ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=True)
+    _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))
+
+
+def test_fp8_forward_only_under_no_grad():
+    from flamia_blackwell_attention_b200 import flash_attn_fp8
+    q, k, v, _ = attention_inputs(1, 256, 2, 2, 128, seed=6)
+    with torch.no_grad():
+        o = flash_attn_fp8(q.cuda(), k.cuda(), v.cuda())
+    ro, *_ = A.qdq_attention(q, k, v, causal=False, rotate_qk=True)
+    assert A.accuracy(o.float().cpu(), ro)["rel_l2"] < 3.2e-2
+
+
+def test_fp8_lengths_that_are_no_multiple_of_128():
+    from flamia_blackwell_attention_b200 import flash_attn_fp8
+    q, k, v, g = attention_inputs(2, 300, 2, 2, 128, seed=7)
+    o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True)
+    ro, _, rdq, rdk, rdv = A.attention_fp32(q.float(), k.float(), v.float(), g.float(), True)
+    _check((o, dq, dk, dv), (ro, rdq, rdk, rdv), tol=7e-2)       # vs fp32 on the unquantised inputs
+
+
+@pytest.mark.parametrize("aligned", [False, True])
+def test_fp8_packed_documents(aligned):
+    from flamia_blackwell_attention_b200 import flash_attn_fp8
+    lens = [300, 128, 77, 515]
+    h, d = 2, 128
+    if aligned:
+        starts, pos = [], 0
+        for n in lens:
+            starts.append(pos)
+            pos += (n + 127) // 128 * 128
+        total = pos
+    else:
+        starts = [sum(lens[:i]) for i in range(len(lens))]
+        total = sum(lens)
+    q, k, v, g = (t[0] for t in attention_inputs(1, total, h, h, d, seed=8))
+    if aligned:      # padding rows are zero by contract
+        mask = torch.zeros(total, dtype=torch.bool)
+        for s0, n in zip(starts, lens):
+            mask[s0:s0 + n] = True
+        q, k, v, g = (t * mask[:, None, None] for t in (q, k, v, g))
+    cu = torch.tensor(starts + [total], dtype=torch.int32, device="cuda")
+    kw = dict(causal=True, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens))
+    if aligned:
+        su = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        kw.update(seqused_q=su, seqused_k=su)
+    with pytest.warns(UserWarning) if not aligned else _nullcontext():
+        o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, **kw)
+    for s0, n in zip(starts, lens):
+        sl = slice(s0, s0 + n)
+        ro, _, rdq, rdk, rdv = A.attention_fp32(q[None, sl].float(), k[None, sl].float(), v[None, sl].float(),
+                                                g[None, sl].float(), True)
+        _check((o[sl], dq[sl], dk[sl], dv[sl]), (ro[0], rdq[0], rdk[0], rdv[0]), tol=7e-2)
+
+
+class _nullcontext:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *a):
+        return False
+
+
+def test_inputs_are_not_mutated_and_no_host_sync():
+    from flamia_blackwell_attention_b200 import flash_attn_fp8
+    q, k, v, g = (t.cuda() for t in attention_inputs(1, 256, 2, 2, 128, seed=9))
+    q0, k0, v0, g0 = (t.clone() for t in (q, k, v, g))
+    qc, kc, vc = (t.requires_grad_(True) for t in (q, k, v))
+    flash_attn_fp8(qc, kc, vc, causal=True).backward(g)        # warm: plan cache, library load
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        flash_attn_fp8(qc, kc, vc, causal=True).backward(g)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    torch.cuda.synchronize()
+    for a, b in ((q, q0), (k, k0), (v, v0), (g, g0)):
+        assert torch.equal(a.detach(), b)
