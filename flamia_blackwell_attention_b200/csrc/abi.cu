@@ -59,6 +59,20 @@ int make_acc_map_16(CUtensorMap* m, const void* base, int b, int heads, int s, i
   return r == CUDA_SUCCESS ? FL_OK : FL_ERR_CUDA;
 }
 
+// (b, heads, d, s) layout (the transposed f16 dQ accumulator): dims {s, d, heads, b}; box {64 tokens, 128 rows, 1, 1}
+int make_acc_t_map_16(CUtensorMap* m, const void* base, int b, int heads, int d, int s) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return FL_ERR_CUDA;
+  cuuint64_t dims[4] = {(cuuint64_t)s, (cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)b};
+  cuuint64_t strides[3] = {(cuuint64_t)s * 2, (cuuint64_t)s * 2 * d, (cuuint64_t)s * 2 * d * heads};
+  cuuint32_t box[4] = {64, (cuuint32_t)d, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FL_OK : FL_ERR_CUDA;
+}
+
 }  // namespace fl
 
 extern "C" int fl_abi_version(void) { return FL_ABI_VERSION; }

@@ -20,6 +20,8 @@ int make_rows_map_16(CUtensorMap* m, const void* base, int b, int s, int heads, 
 // (b, heads, s, w) layout (the f16 dQ accumulator): dims {w, s, heads, b}; box {64, rows, 1, 1}
 int make_acc_map_16(CUtensorMap* m, const void* base, int b, int heads, int s, int w_elems, int box_rows);
 
+int make_acc_t_map_16(CUtensorMap* m, const void* base, int b, int heads, int d, int s);
+
 static constexpr long long kDefaultWaitCycles = 1ll << 31;
 
 }  // namespace fl

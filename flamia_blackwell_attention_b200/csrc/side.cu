@@ -55,7 +55,7 @@ __global__ void dq_prescale_kernel(const float* __restrict__ st_do, const float*
 template <int D>
 __global__ void __launch_bounds__(128) dq_post_kernel(const __half* __restrict__ acc, const float* __restrict__ post,
                                                       uint16_t* __restrict__ dq, int s, int h, float mult, int unrotate,
-                                                      int out_f16) {
+                                                      int out_f16, int acc_t) {
   extern __shared__ __align__(16) uint8_t sm[];
   constexpr int ROWB = D * 2 + 16;
   const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z, tid = threadIdx.x;
@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(128) dq_post_kernel(const __half* __restrict__
     if (out_f16) { __half2 hh = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&hh); }
     return pack_bf16x2(a, b);
   };
-  if (!unrotate) {
+  if (!unrotate && !acc_t) {
     for (int i = tid; i < 128 * CPR; i += 128) {
       const int r = i / CPR, c = i % CPR;
       uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
@@ -85,13 +85,19 @@ __global__ void __launch_bounds__(128) dq_post_kernel(const __half* __restrict__
     return;
   }
   if constexpr (D == 128) {
-    for (int i = tid; i < 128 * CPR; i += 128) {
-      const int r = i / CPR, c = i % CPR;
-      *reinterpret_cast<uint4*>(sm + r * ROWB + c * 16) = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
-    }
-    __syncthreads();
     float y[128];
-    {
+    if (acc_t) {
+      // (b, h, d, s) accumulator: this thread's token is one f16 in each of the 128 head-dim rows (a warp reads 64
+      // contiguous bytes per row)
+      const __half* col = acc + ((size_t)bat * h + head) * D * (size_t)s + t0 + tid;
+#pragma unroll
+      for (int c = 0; c < 128; ++c) y[c] = __half2float(col[(size_t)c * s]) * sc;
+    } else {
+      for (int i = tid; i < 128 * CPR; i += 128) {
+        const int r = i / CPR, c = i % CPR;
+        *reinterpret_cast<uint4*>(sm + r * ROWB + c * 16) = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
+      }
+      __syncthreads();
       const uint8_t* rowp = sm + tid * ROWB;
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
@@ -105,6 +111,7 @@ __global__ void __launch_bounds__(128) dq_post_kernel(const __half* __restrict__
         }
       }
     }
+    if (unrotate) {
 #pragma unroll
     for (int hs = 1; hs < 128; hs <<= 1) {
 #pragma unroll
@@ -116,6 +123,7 @@ __global__ void __launch_bounds__(128) dq_post_kernel(const __half* __restrict__
         }
       }
     }
+    }
     constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
     __syncthreads();
     uint8_t* rowo = sm + tid * ROWB;
@@ -125,9 +133,13 @@ __global__ void __launch_bounds__(128) dq_post_kernel(const __half* __restrict__
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int i0 = c * 8 + 2 * j, i1 = i0 + 1;
-        float a = __fmul_rn(y[i0], 0.08838834764831845f), b2 = __fmul_rn(y[i1], 0.08838834764831845f);
-        if ((NEG[i0 >> 5] >> (i0 & 31)) & 1) a = -a;
-        if ((NEG[i1 >> 5] >> (i1 & 31)) & 1) b2 = -b2;
+        float a = y[i0], b2 = y[i1];
+        if (unrotate) {
+          a = __fmul_rn(a, 0.08838834764831845f);
+          b2 = __fmul_rn(b2, 0.08838834764831845f);
+          if ((NEG[i0 >> 5] >> (i0 & 31)) & 1) a = -a;
+          if ((NEG[i1 >> 5] >> (i1 & 31)) & 1) b2 = -b2;
+        }
         w[j] = cvt2(a, b2);
       }
       *reinterpret_cast<uint4*>(rowo + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -171,6 +183,8 @@ extern "C" int fl_dq_prescale(const float* stats_do, const float* stats_v, const
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }
 
+// The accumulator layout follows the backward kernel that filled it: (b, h, d, s) for head_dim 128 (pipelined kernel,
+// transposed dQ tiles), (b, h, s, d) for head_dim 64.
 extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s,
                           int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
   using namespace fl;
@@ -179,12 +193,12 @@ extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, float mul
   dim3 grid(s / 128, h, b);
   cudaStream_t st = (cudaStream_t)stream;
   if (d == 128) {
-    const int sm = unrotate ? 128 * 272 : 0;
+    const int sm = 128 * 272;
     if (cudaFuncSetAttribute(dq_post_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 272) != cudaSuccess)
       return FL_ERR_CUDA;
-    dq_post_kernel<128><<<grid, 128, sm, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16);
+    dq_post_kernel<128><<<grid, 128, sm, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16, 1);
   } else {
-    dq_post_kernel<64><<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, 0, out_f16);
+    dq_post_kernel<64><<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, 0, out_f16, 0);
   }
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

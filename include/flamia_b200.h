@@ -82,7 +82,8 @@ typedef struct fl_attn_args {
   float* lse;                /* forward: (b, h, s_q) natural log */
   const float* lse_log2;     /* backward: (b, h, s_q) lse * log2 e - 8 */
   const float* d_rows;       /* backward: (b, h, s_q) -2^-8 * rowsum(O * dO) */
-  void* dq_acc;              /* backward: (b, h, s_q, d) f16, zeroed by the prologue; reduce-added here */
+  void* dq_acc;              /* backward: f16, zeroed by the prologue; reduce-added here. Layout (b, h, d, s_q) at d = 128,
+                                (b, h, s_q, d) at d = 64; fl_dq_post reads the same layout */
   const float* dq_scale;     /* backward: (b, s_q/128) pre-scale of the f16 accumulator per query tile (power of two) */
   void* dk;                  /* backward: (b, s_k, h_kv, d) */
   void* dv;                  /* backward: (b, s_k, h_kv, d) */
@@ -134,6 +135,7 @@ int fl_unpack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n
 #define FL_ST_NVF4 5           /* block-scaled NVFP4, scale atoms copied with tcgen05.cp */
 #define FL_ST_F8_A_MNMAJOR 6   /* A MN-major from shared memory */
 #define FL_ST_WAIT_TIMEOUT 7   /* a wait that nothing completes: returns through the bounded-wait path */
+#define FL_ST_MX8_MN_N64 8     /* block-scaled MXFP8, A MN-major (128 B rows), B MN-major with N = 64 (64 B rows) */
 int fl_selftest_mma(int32_t which, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, float* d,
                     int32_t* status, int64_t wait_cycles, void* stream);
 

@@ -84,3 +84,15 @@ def test_wait_that_nothing_completes_returns_a_status():
     # the context is still usable afterwards
     a, av = codes(1); b, bv = codes(2)
     np.testing.assert_array_equal(run(0, a, b), av @ bv.T)
+
+
+def test_block_scaled_mn_major_a_and_64_wide_mn_major_b():
+    # the operand layout of the backward's transposed dQ product: A (k, m) 128 B rows, B (k, n = 64) 64 B rows
+    a, av = codes(13)
+    b, bv = codes(14, (128, 64))
+    g = np.random.default_rng(15)
+    sfa = g.integers(120, 134, size=(128, 4)).astype(np.uint8)
+    sfb = g.integers(120, 134, size=(128, 4)).astype(np.uint8)
+    got = run(8, a, b, sfa, sfb)[:, :64]
+    want = _mx8_expected(np.ascontiguousarray(av.T), np.pad(bv, ((0, 0), (0, 64))), sfa, sfb)[:, :64]
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-4)
