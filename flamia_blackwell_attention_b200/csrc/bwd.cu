@@ -57,6 +57,20 @@ enum { BB_KV = 0, BB_QFULL = 1, BB_QEMPTY = 3, BB_S = 5, BB_DP = 7, BB_P = 9, BB
 enum { TC_S = 0, TO_P = 0, TO_DS = 16, TO_SFA_P = 32, TO_SFB_DO = 36, TO_SFA_DK = 40, TO_SFB_Q = 44, TO_SFA_DQ = 48,
        TO_SFB_DQ = 52, TC_DV = 128, TC_DP = 256, TC_DK = 384 };
 
+// Timeline tracing of one CTA (development aid, compiled out unless FL_TRACE is defined): clock64 stamps per role, step
+// and event into a caller-provided buffer of [8 roles][256 steps][8 events] int64.
+#ifdef FL_TRACE
+__device__ long long* g_trace = nullptr;
+#define TRACE_INIT() long long* const trace_p = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? g_trace : nullptr
+#define TRACE(role, step, ev)                                                                                     \
+  do {                                                                                                            \
+    if (trace_p && (step) < 256) trace_p[(((role) * 256) + (step)) * 8 + (ev)] = clock64();                       \
+  } while (0)
+#else
+#define TRACE_INIT()
+#define TRACE(role, step, ev)
+#endif
+
 __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
   uint32_t r;
   asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
@@ -106,6 +120,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hkv = blockIdx.y;
   const int grp = p.h / p.h_kv;
+  TRACE_INIT();
 
   if (tid == 0) {
     abort_s = 0;
@@ -158,7 +173,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const bool early_out = (T.nk <= 0) || (*p.ctl.status != 0);
 
   if (!early_out) {
-    if (warp >= 12) reg_dealloc<48>();
+    if (warp >= 12) reg_dealloc<80>();     // register budget per warpgroup: 176 / 176 / 80 / 80 (x 128 threads = 64 K)
     if (warp == 13) {
       // =================================================================== TMA producer
       if (lane == 0) {
@@ -180,63 +195,86 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
     } else if (warp == 12) {
       // =================================================================== UMMA issuer
-      if (lane == 0) {
+      // The whole warp stays converged through the waits and the descriptor arithmetic (warp-uniform values); one elected
+      // lane issues. Descriptors are built once; the loop only adds byte offsets.
+      {
         constexpr uint32_t ID_N64 = idesc_f8(128, 64, 0, 0);
+        const uint32_t tm = __shfl_sync(0xFFFFFFFFu, tmem, 0);
+        const int n_steps = 2 * __shfl_sync(0xFFFFFFFFu, n_it, 0);
         const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
                        ds_addr = smem_u32(sDS);
+        const uint64_t dK_k = smem_desc(k_addr, 16, 1024, SWZ_128), dV_k = smem_desc(v_addr, 16, 1024, SWZ_128),
+                       dQ0 = smem_desc(q_addr, 16, 1024, SWZ_128), dDO0 = smem_desc(do_addr, 16, 1024, SWZ_128),
+                       dDS0 = smem_desc(ds_addr, 16, 512, SWZ_64);
         bool ok = mbar_wait(&bars[BB_KV], 0, p.ctl, abortp, 20);
-        const int n_steps = 2 * n_it;
         for (int t = 0; ok && t <= n_steps; ++t) {
           if (t < n_steps) {
             // ---- front end of step t: S^T_x and dP^T_x
             const int it = t >> 1, x = t & 1, st = it & 1;
             if (x == 0 && !(ok = mbar_wait(&bars[BB_QFULL + st], (it >> 1) & 1, p.ctl, abortp, 21))) break;
             tc_fence_after();
-            const uint32_t qx = q_addr + st * TILE_BYTES + x * 64 * D, dox = do_addr + st * TILE_BYTES + x * 64 * D;
+            const uint64_t qx = desc_adv(dQ0, st * TILE_BYTES + x * 64 * D), dox = desc_adv(dDO0, st * TILE_BYTES + x * 64 * D);
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < D / 32; ++k)
-              umma_f8_ss(tmem + TC_S + 64 * x, smem_desc(k_addr + 32 * k, 16, 1024, SWZ_128),
-                         smem_desc(qx + 32 * k, 16, 1024, SWZ_128), ID_N64, k > 0);
-            tc_commit(&bars[BB_S + x]);
+              for (int k = 0; k < D / 32; ++k)
+                umma_f8_ss(tm + TC_S + 64 * x, desc_adv(dK_k, 32 * k), desc_adv(qx, 32 * k), ID_N64, k > 0);
+              tc_commit(&bars[BB_S + x]);
+              TRACE(0, t, 0);
+            }
+            __syncwarp();
             // the half's dP^T columns hold its previous dQ^T until the reduction warps have read it
             if (it > 0 && !(ok = mbar_wait(&bars[BB_DQE + x], (it - 1) & 1, p.ctl, abortp, 22))) break;
             tc_fence_after();
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < D / 32; ++k)
-              umma_f8_ss(tmem + TC_DP + 64 * x, smem_desc(v_addr + 32 * k, 16, 1024, SWZ_128),
-                         smem_desc(dox + 32 * k, 16, 1024, SWZ_128), ID_N64, k > 0);
-            tc_commit(&bars[BB_DP + x]);
+              for (int k = 0; k < D / 32; ++k)
+                umma_f8_ss(tm + TC_DP + 64 * x, desc_adv(dV_k, 32 * k), desc_adv(dox, 32 * k), ID_N64, k > 0);
+              tc_commit(&bars[BB_DP + x]);
+              TRACE(0, t, 1);
+            }
+            __syncwarp();
           }
           if (t >= 1) {
             // ---- back end of step t - 1: dV, dK, dQ^T of half y
             const int tb = t - 1, it = tb >> 1, y = tb & 1, st = it & 1;
-            const uint32_t sx = tmem + TC_S + 64 * y;
-            const uint32_t qy = q_addr + st * TILE_BYTES + y * 64 * D, doy = do_addr + st * TILE_BYTES + y * 64 * D;
+            const uint32_t sx = tm + TC_S + 64 * y;
+            const uint64_t qy = desc_adv(dQ0, st * TILE_BYTES + y * 64 * D), doy = desc_adv(dDO0, st * TILE_BYTES + y * 64 * D);
+            const uint32_t accum = tb > 0;
             if (!(ok = mbar_wait(&bars[BB_P + y], it & 1, p.ctl, abortp, 23))) break;
             tc_fence_after();
+            if (elect_one()) {
+              TRACE(0, tb, 2);
 #pragma unroll
-            for (int kk = 0; kk < 2; ++kk)     // K = 64 queries: two instructions of 32
-              umma_mxf8_ts(tmem + TC_DV, sx + TO_P + 8 * kk, smem_desc(doy + kk * 32 * D, 16, 1024, SWZ_128),
-                           idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), sx + TO_SFA_P, sx + TO_SFB_DO, tb > 0 || kk > 0);
+              for (int kk = 0; kk < 2; ++kk)     // K = 64 queries: two instructions of 32
+                umma_mxf8_ts(tm + TC_DV, sx + TO_P + 8 * kk, desc_adv(doy, kk * 32 * D),
+                             idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), sx + TO_SFA_P, sx + TO_SFB_DO, accum | kk);
+              TRACE(0, tb, 3);
+            }
+            __syncwarp();
             if (!(ok = mbar_wait(&bars[BB_DS + y], it & 1, p.ctl, abortp, 24))) break;
             tc_fence_after();
+            if (elect_one()) {
+              TRACE(0, tb, 4);
 #pragma unroll
-            for (int kk = 0; kk < 2; ++kk)
-              umma_mxf8_ts(tmem + TC_DK, sx + TO_DS + 8 * kk, smem_desc(qy + kk * 32 * D, 16, 1024, SWZ_128),
-                           idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), sx + TO_SFA_DK, sx + TO_SFB_Q, tb > 0 || kk > 0);
+              for (int kk = 0; kk < 2; ++kk)
+                umma_mxf8_ts(tm + TC_DK, sx + TO_DS + 8 * kk, desc_adv(qy, kk * 32 * D),
+                             idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), sx + TO_SFA_DK, sx + TO_SFB_Q, accum | kk);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)     // K = 128 keys; A = K tile (M = head dim), B = dS-hat half (N = 64 queries)
-              umma_mxf8_ss(tmem + TC_DP + 64 * y, smem_desc(k_addr + kk * 32 * D, 16, 1024, SWZ_128),
-                           smem_desc(ds_addr + y * 8192 + kk * 2048, 16, 512, SWZ_64),
-                           idesc_bs(128, 64, 0, 0, 1, 1, 1, kk, kk), sx + TO_SFA_DQ, sx + TO_SFB_DQ, kk > 0);
-            tc_commit(&bars[BB_DQF + y]);
-            if (y == 1) tc_commit(&bars[BB_QEMPTY + st]);
+              for (int kk = 0; kk < 4; ++kk)     // K = 128 keys; A = K tile (M = head dim), B = dS-hat half (N = 64 queries)
+                umma_mxf8_ss(tm + TC_DP + 64 * y, desc_adv(dK_k, kk * 32 * D), desc_adv(dDS0, y * 8192 + kk * 2048),
+                             idesc_bs(128, 64, 0, 0, 1, 1, 1, kk, kk), sx + TO_SFA_DQ, sx + TO_SFB_DQ, kk > 0);
+              tc_commit(&bars[BB_DQF + y]);
+              TRACE(0, tb, 5);
+              if (y == 1) tc_commit(&bars[BB_QEMPTY + st]);
+            }
+            __syncwarp();
           }
         }
-        if (ok) tc_commit(&bars[BB_ACC]);
+        if (ok && elect_one()) tc_commit(&bars[BB_ACC]);
+        __syncwarp();
       }
     } else if (warp >= 8 && warp < 12) {
-      reg_dealloc<96>();
+      reg_dealloc<80>();
       // =================================================================== dQ reduction (thread = head-dim row)
       const int r = tid & 127;
       const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -249,7 +287,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (tid == 256) tma_store_wait_read<1>();
         mbar_arrive(&bars[BB_R1]);
         if (!(ok = mbar_wait(&bars[BB_R1], t & 1, p.ctl, abortp, 41))) break;
+        if (r == 0) TRACE(3, t, 0);
         if (!(ok = mbar_wait(&bars[BB_DQF + y], it & 1, p.ctl, abortp, 40))) break;
+        if (r == 0) TRACE(3, t, 1);
         tc_fence_after();
         const uint32_t rowp = smem_u32(sDQ) + y * 16384 + r * 128;
 #pragma unroll
@@ -270,6 +310,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         tc_fence_before();
         mbar_arrive(&bars[BB_DQE + y]);
+        if (r == 0) TRACE(3, t, 2);
         fence_proxy_async();
         mbar_arrive(&bars[BB_R2]);
         if (!(ok = mbar_wait(&bars[BB_R2], t & 1, p.ctl, abortp, 42))) break;
@@ -280,7 +321,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       if (tid == 256) tma_store_wait<0>();
     } else if (warp < 8) {
-      reg_alloc<184>();
+      reg_alloc<176>();
       // =================================================================== compute (thread = key row, 64 query columns)
       const int x = warp >> 2;                         // the half this warpgroup owns
       const int wq = warp & 3;                         // lane quadrant = 32-key block of the tile
@@ -320,7 +361,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const bool full = key_valid && (q_first >= vis_from) && (q_first + 64 <= T.sq);
 
         // ---- P' = 2^(s c - lse2)
+        if (r == 0) TRACE(1 + x, it, 0);
         if (!(ok = mbar_wait(&bars[BB_S + x], it & 1, p.ctl, abortp, 31))) break;
+        if (r == 0) TRACE(1 + x, it, 1);
         tc_fence_after();
         uint32_t pv[64];
         FL_TMEM_LD_32(t_sx, pv);
@@ -355,9 +398,11 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&bars[BB_P + x]);
+        if (r == 0) TRACE(1 + x, it, 2);
 
         // ---- dS = P' (b dP + D''), block exponent per (this warp's 32 keys, 32 queries)
         if (!(ok = mbar_wait(&bars[BB_DP + x], it & 1, p.ctl, abortp, 32))) break;
+        if (r == 0) TRACE(1 + x, it, 3);
         tc_fence_after();
         FL_TMEM_LD_32(t_dpx, pv);
         FL_TMEM_LD_32(t_dpx + 32, (pv + 32));
@@ -397,7 +442,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4)
           sts128(ds_row + ((q4 ^ ((r >> 1) & 3)) << 4), dsw[4 * q4], dsw[4 * q4 + 1], dsw[4 * q4 + 2], dsw[4 * q4 + 3]);
+        if (r == 0) TRACE(1 + x, it, 4);
         if (!(ok = mbar_wait(&bars[BB_EX + x], it & 1, p.ctl, abortp, 36))) break;
+        if (r == 0) TRACE(1 + x, it, 5);
         {
           // dK:   A[key lane, column = key block]  bytes = the half's two query blocks;  B = Q's exponents
           // dQ^T: A[head-dim lane] = K's exponents (+ pre-scale) per key block; B[query lane, column = query block of
@@ -416,6 +463,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         fence_proxy_async();             // the dS-hat tile in shared memory is read by the tensor core (async proxy)
         tc_fence_before();
         mbar_arrive(&bars[BB_DS + x]);
+        if (r == 0) TRACE(1 + x, it, 6);
       }
       // ---- epilogue: warpgroup 0 writes dV, warpgroup 1 writes dK (full rows)
       if (ok) ok = mbar_wait(&bars[BB_ACC], 0, p.ctl, abortp, 33);
@@ -487,6 +535,12 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 }
 
 }  // namespace fl
+
+#ifdef FL_TRACE
+extern "C" int fl_debug_set_trace(void* buf) {
+  return cudaMemcpyToSymbol(fl::g_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   using namespace fl;

@@ -156,58 +156,70 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
     } else if (warp == 9) {
       // =================================================================== UMMA issuer
-      if (lane == 0) {
+      // The whole warp stays converged through the waits and the descriptor arithmetic (warp-uniform values); one elected
+      // lane issues. Descriptors are built once; the loop only adds byte offsets.
+      {
         constexpr uint32_t ID_S = idesc_f8(128, 128, 0, 0);
+        const uint32_t tm = __shfl_sync(0xFFFFFFFFu, tmem, 0);
+        const int n0 = __shfl_sync(0xFFFFFFFFu, n_st[0], 0), n1 = __shfl_sync(0xFFFFFFFFu, n_st[1], 0);
+        const int nmax = max(n0, n1);
         const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+        const uint64_t dq0 = smem_desc(q_addr, 16, SBO, SWZ), dk0 = smem_desc(k_addr, 16, SBO, SWZ),
+                       dv0 = smem_desc(v_addr, 16, SBO, SWZ);
         auto issue_s = [&](int i, int st) {
+          const uint64_t a = desc_adv(dq0, i * TILE_BYTES), b = desc_adv(dk0, st * TILE_BYTES);
 #pragma unroll
-          for (int k = 0; k < D / 32; ++k)
-            umma_f8_ss(tmem + 128 * i, smem_desc(q_addr + i * TILE_BYTES + 32 * k, 16, SBO, SWZ),
-                       smem_desc(k_addr + st * TILE_BYTES + 32 * k, 16, SBO, SWZ), ID_S, k > 0);
+          for (int k = 0; k < D / 32; ++k) umma_f8_ss(tm + 128 * i, desc_adv(a, 32 * k), desc_adv(b, 32 * k), ID_S, k > 0);
         };
-        auto issue_pv = [&](int i, int st, bool first) {
+        auto issue_pv = [&](int i, int st, uint32_t accum) {
+          const uint64_t b = desc_adv(dv0, st * TILE_BYTES);
+          const uint32_t ts = tm + 128 * i;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)   // 32 keys per instruction: 32 rows of the V tile (MN-major operand)
-            umma_mxf8_ts(tmem + 256 + 128 * i, tmem + 128 * i + 8 * kk,
-                         smem_desc(v_addr + st * TILE_BYTES + kk * 32 * D, 16, SBO, SWZ),
-                         idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), tmem + 128 * i + 32, tmem + 128 * i + 36,
-                         (!first) || kk > 0);
+            umma_mxf8_ts(tm + 256 + 128 * i, ts + 8 * kk, desc_adv(b, kk * 32 * D), idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk),
+                         ts + 32, ts + 36, accum | kk);
         };
         bool ok = mbar_wait(&bars[B_Q], 0, p.ctl, abortp, 20);
-        if (ok && n_max > 0) ok = mbar_wait(&bars[B_KFULL], 0, p.ctl, abortp, 21);
-        if (ok && n_max > 0) {
+        if (ok && nmax > 0) ok = mbar_wait(&bars[B_KFULL], 0, p.ctl, abortp, 21);
+        if (ok && nmax > 0) {
           tc_fence_after();
-#pragma unroll
-          for (int i = 0; i < 2; ++i)
-            if (n_st[i] > 0) { issue_s(i, 0); tc_commit(&bars[B_SFULL + i]); }
-          tc_commit(&bars[B_KEMPTY + 0]);   // K tile 0 is free once both S(0) products have completed
+          if (elect_one()) {
+            if (n0 > 0) { issue_s(0, 0); tc_commit(&bars[B_SFULL + 0]); }
+            if (n1 > 0) { issue_s(1, 0); tc_commit(&bars[B_SFULL + 1]); }
+            tc_commit(&bars[B_KEMPTY + 0]);   // K tile 0 is free once both S(0) products have completed
+          }
+          __syncwarp();
         }
-        for (int j = 0; ok && j < n_max; ++j) {
+        for (int j = 0; ok && j < nmax; ++j) {
           const int st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
           const int stn = (j + 1) % KV_STAGES, phn = ((j + 1) / KV_STAGES) & 1;
           if (!(ok = mbar_wait(&bars[B_VFULL + st], ph, p.ctl, abortp, 22))) break;
           bool k_next_ready = false;
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
-            if (j >= n_st[i]) continue;
+            const int n_i = i == 0 ? n0 : n1;
+            if (j >= n_i) continue;
             if (!(ok = mbar_wait(&bars[B_PFULL + i], j & 1, p.ctl, abortp, 23 + i))) break;
             tc_fence_after();
-            issue_pv(i, st, j == 0);
-            tc_commit(&bars[B_PVDONE + i]);
-            if (j + 1 < n_st[i]) {
+            if (elect_one()) { issue_pv(i, st, j > 0); tc_commit(&bars[B_PVDONE + i]); }
+            __syncwarp();
+            if (j + 1 < n_i) {
               if (!k_next_ready) {
                 if (!(ok = mbar_wait(&bars[B_KFULL + stn], phn, p.ctl, abortp, 25))) break;
                 k_next_ready = true;
                 tc_fence_after();
               }
-              issue_s(i, stn);
-              tc_commit(&bars[B_SFULL + i]);
+              if (elect_one()) { issue_s(i, stn); tc_commit(&bars[B_SFULL + i]); }
+              __syncwarp();
             }
           }
           if (!ok) break;
           // every MMA that reads K tile j+1 / V tile j has been issued: release the stages when they complete
-          if (j + 1 < n_max) tc_commit(&bars[B_KEMPTY + stn]);
-          tc_commit(&bars[B_VEMPTY + st]);
+          if (elect_one()) {
+            if (j + 1 < nmax) tc_commit(&bars[B_KEMPTY + stn]);
+            tc_commit(&bars[B_VEMPTY + st]);
+          }
+          __syncwarp();
         }
       }
     } else if (warp < 8) {

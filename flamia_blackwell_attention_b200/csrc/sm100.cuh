@@ -151,6 +151,13 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
+// one lane of a converged warp (the others skip); the UMMA issuer keeps the whole warp converged around its waits and
+// address arithmetic so that those stay warp-uniform, and elects a lane only for the issue itself
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -250,6 +257,10 @@ __host__ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t l
   return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
          ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | (swz << 61);
 }
+// A descriptor whose start address is `bytes` further (bytes % 16 == 0; the 14-bit address field must not wrap, which
+// holds for offsets inside one CTA's shared memory window below 256 KB). The UMMA issuer is a single thread whose own
+// instruction latency bounds the tensor pipe's issue rate, so descriptors are built once and only advanced in loops.
+__host__ __device__ __forceinline__ uint64_t desc_adv(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
 // Instruction descriptor, kind::f8f6f4 with E4M3 x E4M3 -> F32.
 __host__ __device__ constexpr uint32_t idesc_f8(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) |
