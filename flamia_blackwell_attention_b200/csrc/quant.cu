@@ -5,14 +5,17 @@
 // fused NVFP4 copy (flash_attn/cute/quant/_fp8_nvfp4.py:121-158). Outputs are byte-identical to the reference's eager
 // definitions (tests/cute/quant_reference.py:714-798, 270-369).
 //
-// One CTA per (128-token tile, head, batch); thread r owns token row r, warp w owns the 32-token block w, so the block
-// maximum is one warp reduction. The tile is staged through shared memory with 16-byte coalesced accesses on both sides:
-// the kernel is HBM-bound (2 B read + 1 B written per element, plus the optional copies).
+// One CTA (512 threads) per (128-token tile, head, batch). Four lanes share a token row: lane q of the row holds the
+// 16-byte chunks c = 4 j + q (8 elements each), so every global access of a row is 64 contiguous bytes per instruction
+// and no staging through shared memory is needed. Element index i = 32 j + 8 q + e: the Hadamard levels 1, 2, 4 and
+// 32, 64 are in-thread, levels 8, 16 are two lane exchanges; the same order of operations as the one-thread-per-row
+// butterfly, hence the same bits. The kernel is HBM-bound (2 B read + 1 B written per element, plus optional copies).
 #include "flamia_internal.h"
 
 namespace fl {
 
-static constexpr int QT = 128;  // tokens per tile = threads per CTA
+static constexpr int QT = 128;       // tokens per tile
+static constexpr int QTHREADS = 512; // four lanes per token
 
 struct QuantParams {
   const uint16_t* x;
@@ -29,7 +32,7 @@ struct QuantParams {
   uint8_t* sf4;           // (b, h, s/128, d/64, 512) or null
   float* d_out;           // (b, h, s) or null
   float* lse_log2;        // (b, h, s) or null
-  uint16_t* zero_acc;     // (b, h, s, d) f16 or null
+  uint16_t* zero_acc;     // f16 accumulator of b * h * s * d elements or null
   float* tile_stats;      // (b, h, s/128, 2): [amax of the values quantised, max row sum of squares] or null
   int b, s, h, d;
   int flags;
@@ -37,8 +40,8 @@ struct QuantParams {
   float lse_shift, d_multiplier;
 };
 
-__device__ __forceinline__ float in_to_f32(uint16_t v, int f16) {
-  return f16 ? __half2float(__ushort_as_half(v)) : __uint_as_float((uint32_t)v << 16);
+__device__ __forceinline__ float in_to_f32(uint32_t v16, int f16) {
+  return f16 ? __half2float(__ushort_as_half((uint16_t)v16)) : __uint_as_float(v16 << 16);
 }
 __device__ __forceinline__ float flush_sub(float v) { return fabsf(v) < 1.17549435e-38f ? v * 0.0f : v; }
 
@@ -59,290 +62,274 @@ __device__ __forceinline__ float e4m3_byte_to_f32(uint32_t c) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(QT) quant_blocks_kernel(const QuantParams p) {
-  constexpr int ROWB = D * 2 + 16;               // padded bf16 row in shared memory
-  constexpr int CROWB = D + 16;                  // padded code row
-  extern __shared__ __align__(16) uint8_t smem[];
-  uint8_t* sx = smem;                            // QT * ROWB  input tile (kept intact)
-  uint8_t* sc = smem + QT * ROWB;                // QT * CROWB staging of codes / packed NVFP4 codes
-  uint8_t* so = sc + QT * CROWB;                 // QT * ROWB  forward output tile (prologue only)
-  __shared__ uint32_t s_bytes[4];
+__global__ void __launch_bounds__(QTHREADS) quant_blocks_kernel(const QuantParams p) {
+  constexpr int NJ = D / 32;                     // 16-byte chunks per lane
+  constexpr int NE = 8 * NJ;                     // elements per lane
+  __shared__ float s_wmax[16];                   // per-warp (8 rows) maximum
+  __shared__ float s_wsq[16];                    // per-warp maximum row sum of squares
+  __shared__ __align__(16) uint8_t s_codes[QT * (D + 16)];   // channel-major copy only
 
   const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = tid >> 2, q = tid & 3;           // token row of the tile, lane of the row
   const int t0 = tile * QT;
   const size_t row_stride = (size_t)p.h * D;     // elements between consecutive tokens
-  const uint16_t* xg = p.x + ((size_t)bat * p.s + t0) * row_stride + (size_t)head * D;
+  const size_t row_off = ((size_t)bat * p.s + t0 + r) * row_stride + (size_t)head * D;
   const bool prologue = p.d_out != nullptr && p.o != nullptr;
 
-  // ---- stage the tile: 16 B per thread per step, D/8 threads per row
-  constexpr int TPR = D / 8;                     // threads per row
-  constexpr int RPS = QT / TPR;                  // rows per step
-  {
-    const int c = tid % TPR, r0 = tid / TPR;
-#pragma unroll 4
-    for (int r = r0; r < QT; r += RPS) {
-      uint4 v = *reinterpret_cast<const uint4*>(xg + (size_t)r * row_stride + c * 8);
-      *reinterpret_cast<uint4*>(sx + r * ROWB + c * 16) = v;
-    }
-    if (prologue) {
-      const uint16_t* og = p.o + ((size_t)bat * p.s + t0) * row_stride + (size_t)head * D;
-#pragma unroll 4
-      for (int r = r0; r < QT; r += RPS) {
-        uint4 v = *reinterpret_cast<const uint4*>(og + (size_t)r * row_stride + c * 8);
-        *reinterpret_cast<uint4*>(so + r * ROWB + c * 16) = v;
-      }
-    }
-  }
-  if (p.zero_acc) {   // the tile's slice of the (b, h, s, d) f16 accumulator is contiguous
-    uint4* z = reinterpret_cast<uint4*>(p.zero_acc + (((size_t)bat * p.h + head) * p.s + t0) * D);
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll 4
-    for (int i = tid; i < QT * D / 8; i += QT) z[i] = zero;
-  }
-  __syncthreads();
-
-  // ---- this thread's row in registers
-  float x[D];
-  auto load_row = [&]() {
-    const uint8_t* rowp = sx + tid * ROWB;
+  float x[NE];
+  auto load_row = [&](const uint16_t* base, float* dst) {
+    const uint4* src = reinterpret_cast<const uint4*>(base + row_off) + q;
+    uint4 v[NJ];
 #pragma unroll
-    for (int c = 0; c < D / 8; ++c) {
-      uint4 v = *reinterpret_cast<const uint4*>(rowp + c * 16);
-      uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    for (int j = 0; j < NJ; ++j) v[j] = src[4 * j];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        x[c * 8 + 2 * j] = in_to_f32((uint16_t)(w[j] & 0xFFFF), p.in_f16);
-        x[c * 8 + 2 * j + 1] = in_to_f32((uint16_t)(w[j] >> 16), p.in_f16);
+    for (int j = 0; j < NJ; ++j) {
+      const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        dst[8 * j + 2 * k] = in_to_f32(w[k] & 0xFFFF, p.in_f16);
+        dst[8 * j + 2 * k + 1] = in_to_f32(w[k] >> 16, p.in_f16);
       }
     }
   };
-  load_row();
+  load_row(p.x, x);
+  if (p.zero_acc) {   // this tile's share of the accumulator: 128 * D f16 = 32 D 16-byte chunks, contiguous
+    uint4* z = reinterpret_cast<uint4*>(p.zero_acc + (((size_t)bat * p.h + head) * p.s + t0) * D);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < QT * D / 8; i += QTHREADS) z[i] = zero;
+  }
 
   const bool rotate = (p.flags & (FL_Q_HADAMARD | FL_Q_HADAMARD_NVFP4_ONLY)) != 0;
   const bool rot_only4 = (p.flags & FL_Q_HADAMARD_NVFP4_ONLY) != 0;
   const bool want4 = p.x4 != nullptr;
 
-  // ---- NVFP4 copy first when it needs rotated values but the E4M3 copy does not (two passes over the registers)
+  // (y * signs) H_128 / sqrt(128): butterfly levels 1, 2, ..., 64 with (a, b) -> (a + b, a - b)
   auto rotate_row = [&](float* y) {
     if constexpr (D == 128) {
       constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
 #pragma unroll
-      for (int i = 0; i < 128; ++i)
-        if ((NEG[i >> 5] >> (i & 31)) & 1) y[i] = -y[i];
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t m = NEG[j] >> (8 * q);
 #pragma unroll
-      for (int hs = 1; hs < 128; hs <<= 1) {
+        for (int e = 0; e < 8; ++e)
+          if ((m >> e) & 1) y[8 * j + e] = -y[8 * j + e];
+      }
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
+      for (int hs = 1; hs < 8; hs <<= 1) {       // element bits 0..2: inside one chunk
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
           if ((i & hs) == 0) {
-            float a = y[i], b2 = y[i + hs];
+            const float a = y[i], b2 = y[i + hs];
             y[i] = __fadd_rn(a, b2);
             y[i + hs] = __fsub_rn(a, b2);
           }
+      }
+#pragma unroll
+      for (int lb = 1; lb < 4; lb <<= 1) {       // element bits 3, 4 = the lane of the row
+        const bool hi = (q & lb) != 0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float other = __shfl_xor_sync(0xFFFFFFFFu, y[i], lb);
+          y[i] = hi ? __fsub_rn(other, y[i]) : __fadd_rn(y[i], other);
         }
       }
 #pragma unroll
-      for (int i = 0; i < 128; ++i) y[i] = __fmul_rn(y[i], 0.08838834764831845f);
+      for (int jb = 1; jb < 4; jb <<= 1) {       // element bits 5, 6 = the chunk index j
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (((i >> 3) & jb) == 0) {
+            const float a = y[i], b2 = y[i + 8 * jb];
+            y[i] = __fadd_rn(a, b2);
+            y[i + 8 * jb] = __fsub_rn(a, b2);
+          }
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) y[i] = __fmul_rn(y[i], 0.08838834764831845f);
     }
   };
 
+  // NVFP4 copy of y: per 16 along d (two neighbouring lanes): SF = E4M3_rn(amax * f32(1/6)); codes = E2M1_rn(ftz(y * m)),
+  // m = 1 / SF | +inf (SF rounds to 0, amax > 0) | 0
   auto nvfp4_row = [&](const float* y) {
-    // per 16 along d: SF = E4M3_rn(amax * f32(1/6)); codes = E2M1_rn(ftz(x * m)), m = 1/SF | +inf | 0
-    uint8_t* x4row = sc + tid * CROWB;   // D/2 bytes staged for the coalesced store
-    uint32_t sfw[D / 64];
+    uint32_t sfpack = 0;                         // this lane's scale bytes: chunk j in byte j
+    uint8_t* x4row = p.x4 + (((size_t)bat * p.s + t0 + r) * p.h + head) * (D / 2);
 #pragma unroll
-    for (int a = 0; a < D / 64; ++a) sfw[a] = 0;
-#pragma unroll
-    for (int g = 0; g < D / 16; ++g) {
+    for (int j = 0; j < NJ; ++j) {
       float am = 0.f;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        float a = fabsf(flush_sub(y[g * 16 + j]));
-        am = (a > am) ? a : am;          // a NaN never wins
+      for (int e = 0; e < 8; ++e) {
+        const float a = fabsf(flush_sub(y[8 * j + e]));
+        am = (a > am) ? a : am;                  // a NaN never wins
       }
-      float u = __fmul_rn(am, 1.0f / 6.0f);
-      uint32_t sfb = cvt_e4m3x2(u, 0.f) & 0xFF;
-      float sfv = e4m3_byte_to_f32(sfb);
-      float m = sfv > 0.f ? __frcp_rn(sfv) : (u > 0.f ? __int_as_float(0x7F800000) : 0.f);
-      uint32_t packed[2] = {0, 0};
+      const float oth = __shfl_xor_sync(0xFFFFFFFFu, am, 1);
+      am = (oth > am) ? oth : am;
+      const float u = __fmul_rn(am, 1.0f / 6.0f);
+      const uint32_t sfb = cvt_e4m3x2(u, 0.f) & 0xFF;
+      const float sfv = e4m3_byte_to_f32(sfb);
+      const float m = sfv > 0.f ? __frcp_rn(sfv) : (u > 0.f ? __int_as_float(0x7F800000) : 0.f);
+      uint32_t packed = 0;
 #pragma unroll
-      for (int j = 0; j < 16; j += 2) {
-        float a0 = flush_sub(__fmul_rn(flush_sub(y[g * 16 + j]), m));
-        float a1 = flush_sub(__fmul_rn(flush_sub(y[g * 16 + j + 1]), m));
+      for (int e = 0; e < 8; e += 2) {
+        const float a0 = flush_sub(__fmul_rn(flush_sub(y[8 * j + e]), m));
+        const float a1 = flush_sub(__fmul_rn(flush_sub(y[8 * j + e + 1]), m));
         uint16_t c2;
-        asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}"
-            : "=h"(c2)
-            : "f"(a1), "f"(a0));
-        packed[j >> 3] |= (uint32_t)(c2 & 0xFF) << ((j & 7) * 4);
+        asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}" : "=h"(c2) : "f"(a1), "f"(a0));
+        packed |= (uint32_t)(c2 & 0xFF) << (e * 4);
       }
-      *reinterpret_cast<uint2*>(x4row + g * 8) = make_uint2(packed[0], packed[1]);
-      sfw[g >> 2] |= sfb << ((g & 3) * 8);
+      *reinterpret_cast<uint32_t*>(x4row + (4 * j + q) * 4) = packed;
+      sfpack |= sfb << (8 * j);
     }
-    if (p.sf4) {
+    // group g = 2 j + (q >> 1): atom g / 4 = j / 2, byte g % 4 = 2 (j & 1) + (q >> 1); lane 0 of the row assembles
+    const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, sfpack, 2);
+    if (p.sf4 && q == 0) {
       uint8_t* atom = p.sf4 + ((((size_t)bat * p.h + head) * (p.s / QT) + tile) * (D / 64)) * 512;
 #pragma unroll
-      for (int a = 0; a < D / 64; ++a)
-        *reinterpret_cast<uint32_t*>(atom + a * 512 + (tid & 31) * 16 + (tid >> 5) * 4) = sfw[a];
+      for (int a = 0; a < D / 64; ++a) {
+        const uint32_t lo0 = (sfpack >> (16 * a)) & 0xFF, lo1 = (sfpack >> (16 * a + 8)) & 0xFF;
+        const uint32_t hi0 = (hi >> (16 * a)) & 0xFF, hi1 = (hi >> (16 * a + 8)) & 0xFF;
+        *reinterpret_cast<uint32_t*>(atom + a * 512 + (r & 31) * 16 + (r >> 5) * 4) = lo0 | (hi0 << 8) | (lo1 << 16) | (hi1 << 24);
+      }
     }
-  };
-
-  auto store_x4 = [&]() {   // QT rows of D/2 bytes from the staging area, coalesced
-    __syncthreads();
-    constexpr int TPR4 = D / 32;   // 16-byte chunks per row
-    uint8_t* g4 = p.x4 + (((size_t)bat * p.s + t0) * p.h + head) * (D / 2);
-    for (int i = tid; i < QT * TPR4; i += QT) {
-      int r = i / TPR4, c = i % TPR4;
-      *reinterpret_cast<uint4*>(g4 + (size_t)r * p.h * (D / 2) + c * 16) =
-          *reinterpret_cast<const uint4*>(sc + r * CROWB + c * 16);
-    }
-    __syncthreads();
   };
 
   if (want4 && rotate && rot_only4) {   // NVFP4 codes of the rotated row, E4M3 codes of the row as read
     rotate_row(x);
     nvfp4_row(x);
-    store_x4();
-    load_row();
+    load_row(p.x, x);
   } else if (rotate) {
     rotate_row(x);
   }
-  if (want4 && !(rotate && rot_only4)) {
-    nvfp4_row(x);
-    store_x4();
-  }
+  if (want4 && !(rotate && rot_only4)) nvfp4_row(x);
 
-  // ---- token-block exponent
+  // ---- exponents: per token (4 lanes) and per 32-token block (4 warps)
   float amax = 0.f, sumsq = 0.f;
 #pragma unroll
-  for (int i = 0; i < D; ++i) {
+  for (int i = 0; i < NE; ++i) {
     x[i] = flush_sub(x[i]);
-    float a = fabsf(x[i]);
-    amax = fmaxf(amax, a);
+    amax = fmaxf(amax, fabsf(x[i]));
     sumsq = fmaf(x[i], x[i], sumsq);
   }
-  float bmax = amax;
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));      // the token's maximum
+  sumsq += __shfl_xor_sync(0xFFFFFFFFu, sumsq, 1);
+  sumsq += __shfl_xor_sync(0xFFFFFFFFu, sumsq, 2);
+  float wmax = amax, wsq = sumsq;
 #pragma unroll
-  for (int o = 16; o; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xFFFFFFFFu, bmax, o));
+  for (int o = 4; o < 32; o <<= 1) {
+    wmax = fmaxf(wmax, __shfl_xor_sync(0xFFFFFFFFu, wmax, o));
+    wsq = fmaxf(wsq, __shfl_xor_sync(0xFFFFFFFFu, wsq, o));
+  }
+  if (lane == 0) { s_wmax[warp] = wmax; s_wsq[warp] = wsq; }
+  __syncthreads();
+  const int blk = r >> 5;                                         // 32-token block of the tile
+  const float bmax = fmaxf(fmaxf(s_wmax[4 * blk], s_wmax[4 * blk + 1]), fmaxf(s_wmax[4 * blk + 2], s_wmax[4 * blk + 3]));
   const uint32_t bbyte = ue8m0_byte(bmax);
   const bool tl = (p.flags & FL_Q_TOKEN_LOCAL) != 0;
   const uint32_t tbyte = tl ? ue8m0_byte(amax) : bbyte;
   const float inv = tbyte ? pow2_from_field(254 - (int)tbyte) : 0.f;
   const float scale = tbyte ? pow2_from_field((int)tbyte) : 0.f;
 
-  uint32_t cw[D / 4];
+  uint32_t cw[2 * NJ];
 #pragma unroll
-  for (int i = 0; i < D / 4; ++i)
+  for (int i = 0; i < 2 * NJ; ++i)
     cw[i] = cvt_e4m3x4(__fmul_rn(x[4 * i], inv), __fmul_rn(x[4 * i + 1], inv), __fmul_rn(x[4 * i + 2], inv),
                        __fmul_rn(x[4 * i + 3], inv));
+  {
+    uint8_t* crow = p.codes + row_off;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+      *reinterpret_cast<uint2*>(crow + (4 * j + q) * 8) = make_uint2(cw[2 * j], cw[2 * j + 1]);
+  }
 
-  // ---- prologue: D in the fixed tree order, shifted log2 LSE
+  const size_t bh = (size_t)bat * p.h + head;
+  const size_t ri = bh * p.s + t0 + r;
+  // ---- prologue: D in the fixed tree order (column bits 1 (fma), 2, 3, 0, 6, 5, 4), shifted log2 LSE
   if (prologue) {
-    float a[D];
+    float o[NE];
+    load_row(p.o, o);
+    float v[4 * NJ];                               // columns with bit 1 clear: index (j, e bit 2, e bit 0)
 #pragma unroll
-    for (int i = 0; i < D / 4; ++i) {
+    for (int j = 0; j < NJ; ++j) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) a[4 * i + j] = __fmul_rn(e4m3_byte_to_f32((cw[i] >> (8 * j)) & 0xFF), scale);
-    }
-    const uint8_t* orow = so + tid * ROWB;
-    float v[64];
-#pragma unroll
-    for (int k = 0; k < 64; ++k) {
-      const int c = ((k >> 1) << 2) | (k & 1);   // columns with bit 1 clear
-      float prod = 0.f, acc = 0.f;
-      if (c < D) {
-        float o0 = in_to_f32(*reinterpret_cast<const uint16_t*>(orow + c * 2), p.in_f16);
-        float o2 = in_to_f32(*reinterpret_cast<const uint16_t*>(orow + (c + 2) * 2), p.in_f16);
-        prod = __fmul_rn(a[c + 2 < D ? c + 2 : 0], o2);
-        acc = __fmaf_rn(a[c], o0, prod);
+      for (int k = 0; k < 4; ++k) {
+        const int e = ((k >> 1) << 2) | (k & 1);   // 0, 1, 4, 5
+        const float a0 = __fmul_rn(e4m3_byte_to_f32((cw[2 * j + (e >> 2)] >> (8 * (e & 3))) & 0xFF), scale);
+        const float a2 = __fmul_rn(e4m3_byte_to_f32((cw[2 * j + ((e + 2) >> 2)] >> (8 * ((e + 2) & 3))) & 0xFF), scale);
+        v[4 * j + k] = __fmaf_rn(a0, o[8 * j + e], __fmul_rn(a2, o[8 * j + e + 2]));
       }
-      v[k] = acc;
     }
-    // v index k <-> column c(k); column bits (2,3,0,6,5,4) <-> k bits (1,2,0,5,4,3)
-    constexpr int KB[6] = {1, 2, 0, 5, 4, 3};
 #pragma unroll
-    for (int st = 0; st < 6; ++st) {
-      const int bit = 1 << KB[st];
+    for (int j = 0; j < NJ; ++j) {                 // bit 2
+      v[4 * j + 0] = __fadd_rn(v[4 * j + 0], v[4 * j + 2]);
+      v[4 * j + 1] = __fadd_rn(v[4 * j + 1], v[4 * j + 3]);
+    }
 #pragma unroll
-      for (int k = 0; k < 64; ++k)
-        if ((k & bit) == 0) v[k] = __fadd_rn(v[k], v[k | bit]);
+    for (int j = 0; j < NJ; ++j) {                 // bit 3 = lane bit 0
+      v[4 * j + 0] = __fadd_rn(v[4 * j + 0], __shfl_xor_sync(0xFFFFFFFFu, v[4 * j + 0], 1));
+      v[4 * j + 1] = __fadd_rn(v[4 * j + 1], __shfl_xor_sync(0xFFFFFFFFu, v[4 * j + 1], 1));
     }
-    const size_t ri = ((size_t)bat * p.h + head) * p.s + t0 + tid;
-    p.d_out[ri] = __fmul_rn(v[0], p.d_multiplier);
-    if (p.lse && p.lse_log2) {
-      float l = p.lse[ri];
-      float pr = __fmul_rn(l, 1.4426950408889634f);
-      p.lse_log2[ri] = __fsub_rn((l == -INFINITY) ? 0.f : pr, p.lse_shift);
-    }
-  } else if (p.lse && p.lse_log2) {
-    const size_t ri = ((size_t)bat * p.h + head) * p.s + t0 + tid;
-    float l = p.lse[ri];
+    float w4[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w4[j] = j < NJ ? __fadd_rn(v[4 * (j < NJ ? j : 0) + 0], v[4 * (j < NJ ? j : 0) + 1]) : 0.f;   // bit 0
+    const float w2a = __fadd_rn(w4[0], w4[2]), w2b = __fadd_rn(w4[1], w4[3]);                  // bit 6
+    float w1 = __fadd_rn(w2a, w2b);                                                            // bit 5
+    w1 = __fadd_rn(w1, __shfl_xor_sync(0xFFFFFFFFu, w1, 2));                                   // bit 4 = lane bit 1
+    if (q == 0) p.d_out[ri] = __fmul_rn(w1, p.d_multiplier);
+  }
+  if (p.lse && p.lse_log2 && q == 0) {
+    const float l = p.lse[ri];
     p.lse_log2[ri] = __fsub_rn((l == -INFINITY) ? 0.f : __fmul_rn(l, 1.4426950408889634f), p.lse_shift);
   }
 
   // ---- side tables
-  if (lane == 0) s_bytes[warp] = bbyte;
-  {
-    uint8_t* crow = sc + tid * CROWB;
-#pragma unroll
-    for (int i = 0; i < D / 16; ++i)
-      *reinterpret_cast<uint4*>(crow + i * 16) = make_uint4(cw[4 * i], cw[4 * i + 1], cw[4 * i + 2], cw[4 * i + 3]);
-  }
-  __syncthreads();
-  const size_t bh = (size_t)bat * p.h + head;
   const int ntile = p.s / QT;
-  if (p.e_tab && lane == 0) {
-    uint8_t* e = p.e_tab + (bh * (p.s / 32) + tile * 4 + warp) * (D / 32);
+  const uint32_t b0 = ue8m0_byte(fmaxf(fmaxf(s_wmax[0], s_wmax[1]), fmaxf(s_wmax[2], s_wmax[3])));
+  const uint32_t b1 = ue8m0_byte(fmaxf(fmaxf(s_wmax[4], s_wmax[5]), fmaxf(s_wmax[6], s_wmax[7])));
+  const uint32_t b2 = ue8m0_byte(fmaxf(fmaxf(s_wmax[8], s_wmax[9]), fmaxf(s_wmax[10], s_wmax[11])));
+  const uint32_t b3 = ue8m0_byte(fmaxf(fmaxf(s_wmax[12], s_wmax[13]), fmaxf(s_wmax[14], s_wmax[15])));
+  if ((tid & 127) == 0) {                          // one thread per 32-token block
+    if (p.e_tab) {
+      uint8_t* e = p.e_tab + (bh * (p.s / 32) + tile * 4 + blk) * (D / 32);
 #pragma unroll
-    for (int g = 0; g < D / 32; ++g) e[g] = (uint8_t)bbyte;
-  }
-  if (p.fac && lane == 0) {
-    uint32_t tm = max(max(s_bytes[0], s_bytes[1]), max(s_bytes[2], s_bytes[3]));
-    uint32_t e0 = bbyte ? bbyte : tm;
-    p.fac[bh * (p.s / 32) + tile * 4 + warp] = e0 ? pow2_from_field((int)e0) : 1.0f;
-  }
-  if (p.token_factors) p.token_factors[bh * p.s + t0 + tid] = tbyte ? scale : 1.0f;
-  if (p.sf_tok)
-    *reinterpret_cast<uint32_t*>(p.sf_tok + (bh * ntile + tile) * 512 + lane * 16 + warp * 4) = tbyte * 0x01010101u;
-  if (p.sf_dim) {
-    uint32_t w = s_bytes[0] | (s_bytes[1] << 8) | (s_bytes[2] << 16) | (s_bytes[3] << 24);
-    *reinterpret_cast<uint32_t*>(p.sf_dim + (bh * ntile + tile) * 512 + tid * 4) = w;
-  }
-  if (p.tile_stats) {
-    float a = bmax, q = sumsq;
-#pragma unroll
-    for (int o = 16; o; o >>= 1) q = fmaxf(q, __shfl_xor_sync(0xFFFFFFFFu, q, o));
-    __shared__ float s_st[8];
-    if (lane == 0) { s_st[warp] = a; s_st[4 + warp] = q; }
-    __syncthreads();
-    if (tid == 0) {
-      p.tile_stats[(bh * ntile + tile) * 2] = fmaxf(fmaxf(s_st[0], s_st[1]), fmaxf(s_st[2], s_st[3]));
-      p.tile_stats[(bh * ntile + tile) * 2 + 1] = fmaxf(fmaxf(s_st[4], s_st[5]), fmaxf(s_st[6], s_st[7]));
+      for (int g = 0; g < D / 32; ++g) e[g] = (uint8_t)bbyte;
     }
+    if (p.fac) {
+      const uint32_t tm = max(max(b0, b1), max(b2, b3));
+      const uint32_t e0 = bbyte ? bbyte : tm;
+      p.fac[bh * (p.s / 32) + tile * 4 + blk] = e0 ? pow2_from_field((int)e0) : 1.0f;
+    }
+  }
+  if (q == 0) {
+    if (p.token_factors) p.token_factors[ri] = tbyte ? scale : 1.0f;
+    if (p.sf_tok)
+      *reinterpret_cast<uint32_t*>(p.sf_tok + (bh * ntile + tile) * 512 + (r & 31) * 16 + (r >> 5) * 4) = tbyte * 0x01010101u;
+  }
+  if (p.sf_dim && tid < 128)
+    *reinterpret_cast<uint32_t*>(p.sf_dim + (bh * ntile + tile) * 512 + tid * 4) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+  if (p.tile_stats && tid == 0) {
+    float a = 0.f, sq = 0.f;
+#pragma unroll
+    for (int w = 0; w < 16; ++w) { a = fmaxf(a, s_wmax[w]); sq = fmaxf(sq, s_wsq[w]); }
+    p.tile_stats[(bh * ntile + tile) * 2] = a;
+    p.tile_stats[(bh * ntile + tile) * 2 + 1] = sq;
   }
 
-  // ---- codes (b, s, h, d): coalesced 16 B stores
-  {
-    constexpr int TPRC = D / 16;
-    uint8_t* cg = p.codes + ((size_t)bat * p.s + t0) * row_stride + (size_t)head * D;
-    for (int i = tid; i < QT * TPRC; i += QT) {
-      int r = i / TPRC, c = i % TPRC;
-      *reinterpret_cast<uint4*>(cg + (size_t)r * row_stride + c * 16) =
-          *reinterpret_cast<const uint4*>(sc + r * CROWB + c * 16);
-    }
-  }
-  // ---- channel-major copy (b, h, d, s): thread c gathers column c
+  // ---- channel-major copy (b, h, d, s): through shared memory, thread c gathers column c
   if (p.codes_t) {
-    for (int c = tid; c < D; c += QT) {
-      uint8_t* dst = p.codes_t + (bh * D + c) * (size_t)p.s + t0;
-#pragma unroll 2
-      for (int r = 0; r < QT; r += 16) {
-        uint32_t w[4];
+    constexpr int CROWB = D + 16;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          w[j] = (uint32_t)sc[(r + 4 * j) * CROWB + c] | ((uint32_t)sc[(r + 4 * j + 1) * CROWB + c] << 8) |
-                 ((uint32_t)sc[(r + 4 * j + 2) * CROWB + c] << 16) | ((uint32_t)sc[(r + 4 * j + 3) * CROWB + c] << 24);
-        *reinterpret_cast<uint4*>(dst + r) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
+    for (int j = 0; j < NJ; ++j)
+      *reinterpret_cast<uint2*>(s_codes + r * CROWB + (4 * j + q) * 8) = make_uint2(cw[2 * j], cw[2 * j + 1]);
+    __syncthreads();
+    for (int i = tid; i < D * 8; i += QTHREADS) {  // (channel, 16-token group)
+      const int c = i >> 3, rg = (i & 7) * 16;
+      uint32_t w[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        w[k] = (uint32_t)s_codes[(rg + 4 * k) * CROWB + c] | ((uint32_t)s_codes[(rg + 4 * k + 1) * CROWB + c] << 8) |
+               ((uint32_t)s_codes[(rg + 4 * k + 2) * CROWB + c] << 16) | ((uint32_t)s_codes[(rg + 4 * k + 3) * CROWB + c] << 24);
+      *reinterpret_cast<uint4*>(p.codes_t + (bh * D + c) * (size_t)p.s + t0 + rg) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 }
@@ -356,7 +343,7 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   if (a->d != 64 && a->d != 128) return FL_ERR_UNSUPPORTED;
   if ((a->flags & (FL_Q_HADAMARD | FL_Q_HADAMARD_NVFP4_ONLY)) && a->d != 128) return FL_ERR_UNSUPPORTED;
   if ((a->flags & FL_Q_HADAMARD) && (a->flags & FL_Q_TOKEN_LOCAL)) return FL_ERR_UNSUPPORTED;
-  if (a->s / 128 > 65535 * 64 || a->h > 65535 || a->b > 65535) return FL_ERR_TOO_LARGE;
+  if (a->h > 65535 || a->b > 65535) return FL_ERR_TOO_LARGE;
   QuantParams p;
   p.x = (const uint16_t*)a->x; p.o = (const uint16_t*)a->o; p.lse = a->lse;
   p.codes = a->codes; p.codes_t = a->codes_t; p.e_tab = a->e_tab; p.fac = a->fac; p.sf_tok = a->sf_tok;
@@ -366,19 +353,7 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   p.lse_shift = a->lse_shift; p.d_multiplier = a->d_multiplier;
   dim3 grid(a->s / 128, a->h, a->b);
   cudaStream_t st = (cudaStream_t)stream;
-  const bool pro = p.d_out && p.o;
-  if (a->d == 128) {
-    size_t sm = 128 * (128 * 2 + 16) * (pro ? 2 : 1) + 128 * (128 + 16);
-    if (cudaFuncSetAttribute(quant_blocks_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) !=
-        cudaSuccess)
-      return FL_ERR_CUDA;
-    quant_blocks_kernel<128><<<grid, 128, sm, st>>>(p);
-  } else {
-    size_t sm = 128 * (64 * 2 + 16) * (pro ? 2 : 1) + 128 * (64 + 16);
-    if (cudaFuncSetAttribute(quant_blocks_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) !=
-        cudaSuccess)
-      return FL_ERR_CUDA;
-    quant_blocks_kernel<64><<<grid, 128, sm, st>>>(p);
-  }
+  if (a->d == 128) quant_blocks_kernel<128><<<grid, QTHREADS, 0, st>>>(p);
+  else quant_blocks_kernel<64><<<grid, QTHREADS, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }
