@@ -128,11 +128,11 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[BB_QFULL + i], 1); mbar_init(&bars[BB_QEMPTY + i], 1);
       mbar_init(&bars[BB_S + i], 1); mbar_init(&bars[BB_DP + i], 1);
-      mbar_init(&bars[BB_P + i], 128); mbar_init(&bars[BB_DS + i], 128); mbar_init(&bars[BB_EX + i], 128);
-      mbar_init(&bars[BB_DQF + i], 1); mbar_init(&bars[BB_DQE + i], 128);
+      mbar_init(&bars[BB_P + i], 4); mbar_init(&bars[BB_DS + i], 4); mbar_init(&bars[BB_EX + i], 4);      // one arrival per warp
+      mbar_init(&bars[BB_DQF + i], 1); mbar_init(&bars[BB_DQE + i], 4);
     }
-    mbar_init(&bars[BB_R1], 128);
-    mbar_init(&bars[BB_R2], 128);
+    mbar_init(&bars[BB_R1], 4);
+    mbar_init(&bars[BB_R2], 4);
     mbar_init(&bars[BB_ACC], 1);
     fence_barrier_init();
     BTile t;
@@ -285,7 +285,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
         // the staging buffer of this half was last read by the reduction of step t - 2
         if (tid == 256) tma_store_wait_read<1>();
-        mbar_arrive(&bars[BB_R1]);
+        mbar_arrive_warp(&bars[BB_R1]);
         if (!(ok = mbar_wait(&bars[BB_R1], t & 1, p.ctl, abortp, 41))) break;
         if (r == 0) TRACE(3, t, 0);
         if (!(ok = mbar_wait(&bars[BB_DQF + y], it & 1, p.ctl, abortp, 40))) break;
@@ -309,10 +309,10 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
         tc_fence_before();
-        mbar_arrive(&bars[BB_DQE + y]);
+        mbar_arrive_warp(&bars[BB_DQE + y]);
         if (r == 0) TRACE(3, t, 2);
         fence_proxy_async();
-        mbar_arrive(&bars[BB_R2]);
+        mbar_arrive_warp(&bars[BB_R2]);
         if (!(ok = mbar_wait(&bars[BB_R2], t & 1, p.ctl, abortp, 42))) break;
         if (tid == 256) {
           tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, T.q0 + m * 128 + 64 * y, 0, head, T.bat);
@@ -397,7 +397,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&bars[BB_P + x]);
+        mbar_arrive_warp(&bars[BB_P + x]);
         if (r == 0) TRACE(1 + x, it, 2);
 
         // ---- dS = P' (b dP + D''), block exponent per (this warp's 32 keys, 32 queries)
@@ -426,7 +426,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           ebyte[qh] = (uint32_t)min(max(e, 1), 254);
         }
         if (lane == 0) sE[x][wq] = ebyte[0] | (ebyte[1] << 8);
-        mbar_arrive(&bars[BB_EX + x]);
+        mbar_arrive_warp(&bars[BB_EX + x]);
         uint32_t dsw[16];
 #pragma unroll
         for (int qh = 0; qh < 2; ++qh) {
@@ -462,7 +462,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_wait_st();
         fence_proxy_async();             // the dS-hat tile in shared memory is read by the tensor core (async proxy)
         tc_fence_before();
-        mbar_arrive(&bars[BB_DS + x]);
+        mbar_arrive_warp(&bars[BB_DS + x]);
         if (r == 0) TRACE(1 + x, it, 6);
       }
       // ---- epilogue: warpgroup 0 writes dV, warpgroup 1 writes dK (full rows)

@@ -84,7 +84,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[B_SFULL + i], 1);
-      mbar_init(&bars[B_PFULL + i], 128);
+      mbar_init(&bars[B_PFULL + i], 4);      // one arrival per softmax warp
       mbar_init(&bars[B_PVDONE + i], 1);
     }
     fence_barrier_init();
@@ -312,7 +312,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&bars[B_PFULL + i]);
+        mbar_arrive_warp(&bars[B_PFULL + i]);
       }
       // ---- epilogue: O / l -> bf16, LSE
       if (ok && n_i > 0) ok = mbar_wait(&bars[B_PVDONE + i], (n_i - 1) & 1, p.ctl, abortp, 34 + i);

@@ -72,6 +72,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   return true;
 }
 
+// Warp-level forms for a CONVERGED warp: one lane polls / arrives for the warp (32 lanes polling the same mbarrier
+// serialise in the barrier unit and cost hundreds of cycles per wait). __syncwarp orders the other lanes' accesses.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const DevCtl& ctl, volatile int* abort,
+                                               int site) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, abort, site) ? 1 : 0;
+  return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+}
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
