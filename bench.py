@@ -142,6 +142,9 @@ def main():
     ap.add_argument("--route", default="fp8", choices=["fp8", "fp4"])
     ap.add_argument("--dense", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-case", action="store_true",
+                    help="run `--steps` plain steps of a reduced cell (b2, same s/h/d) and exit: the command profilers wrap; "
+                         "prints no bench value")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -162,6 +165,15 @@ def main():
     from tests.inputs import attention_inputs
     fn = flash_attn_fp8 if args.route == "fp8" else flash_attn_fp4
     causal = not args.dense
+    if args.profile_case:
+        pq, pk, pv, pg = (t.to(dev) for t in attention_inputs(2, S, H, HKV, D, seed=0))
+        pq.requires_grad_(True); pk.requires_grad_(True); pv.requires_grad_(True)
+        for _ in range(args.warmup + args.steps):
+            pq.grad = pk.grad = pv.grad = None
+            fn(pq, pk, pv, causal=causal).backward(pg)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_case": f"b2 s{S} h{H} d{D}", "steps": args.warmup + args.steps, "launches_per_step": 8}))
+        return
     W = max(args.warmup, 3)
 
     # this rank's slice of the global batch of 4 * world rows: rows [lo, hi) of the (batch, head) groups
