@@ -43,6 +43,7 @@ EXPORTS = {
     "fl_fwd": (i32, [C.POINTER(AttnArgs), vp]),
     "fl_bwd": (i32, [C.POINTER(AttnArgs), vp]),
     "fl_dq_prescale": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp]),
+    "fl_bwd_static_acc": (i32, [C.POINTER(AttnArgs), vp, f32, vp, vp]),
     "fl_dq_post": (i32, [vp, vp, f32, vp, i32, i32, i32, i32, i32, i32, vp]),
     "fl_pack_rows": (i32, [vp, vp, vp, i32, i32, vp]),
     "fl_unpack_rows": (i32, [vp, vp, vp, i32, i32, vp]),

@@ -119,6 +119,18 @@ int fl_dq_prescale(const float* stats_do, const float* stats_v, const float* sta
 int fl_dq_post(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s, int32_t h,
                int32_t d, int32_t unrotate, int32_t out_f16, void* stream);
 
+/* Backward pass with the f16 dQ accumulator held in a fixed device array of the library (no counterpart in the
+ * reference, which always takes torch-allocated buffers). For callers that cannot allocate device memory where the
+ * backward runs: a pool sized before this operator was known, a serving loop that keeps the allocator off its hot
+ * path, a C / cgo / JNI embedder without an allocator. Runs fl_bwd with args->dq_acc replaced by that array (the field
+ * is ignored), then fl_dq_post into dq (b, s_q, h, d) with unrotate = (flags & FL_A_HAD_DQ), out_f16 =
+ * (flags & FL_A_OUT_F16). Calls no allocating routine. Limit: b * h * s_q * d <= FL_STATIC_ACC_MAX_ELEMS, otherwise
+ * FL_ERR_TOO_LARGE (4) is returned and nothing is enqueued. The used part of the array is cleared on the stream by
+ * every call. The first call on a device resolves the array's address (cudaGetSymbolAddress): make it before any
+ * stream capture starts. One array per device: calls that overlap in time on one device race on it. */
+#define FL_STATIC_ACC_MAX_ELEMS (1 << 23)   /* 16 MiB of f16: e.g. b1 h16 s4096 d128 */
+int fl_bwd_static_acc(const fl_attn_args* args, const float* post_scale, float mult, void* dq, void* stream);
+
 /* Row gather / scatter between a packed (total, h, d) tensor and its 128-aligned repacked buffer.
  * Replaces flash_attn/cute/lp_varlen.py:421 pack_rows / unpack_rows. row_map[i] = source row of padded row i or -1. */
 int fl_pack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n_dst_rows, int32_t row_bytes, void* stream);
