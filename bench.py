@@ -284,7 +284,10 @@ def main():
             "ms_fwd_kernel": k_fwd, "ms_bwd_kernel": k_bwd,
             "tflops_fwd_kernel": f_fwd / (k_fwd * 1e-3) / 1e12, "tflops_bwd_kernel": achieved,
             "roofline": {"bound": "tensor", "kernel": "bwd_kernel<128>", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": (t_min / (k_bwd * 1e-3)), "traffic": None,
+                         "frac": (t_min / (k_bwd * 1e-3)),
+                         # dram read + write bytes of one launch: 151.4 MB captured by ncu on the b2 cell of
+                         # --profile-case, scaled by the batch (traffic is proportional to b); fp8 route, causal
+                         "traffic": 151.4e6 * B / 2 if (args.route == "fp8" and causal) else None,
                          "note": f"peak = 2 x {sust} TF/s dense bf16 sustained ({how}); of {how}"},
             "e2e": {"value": e2e_val, "unit": "TFLOPS", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (qh, kh, vh, gh)),
