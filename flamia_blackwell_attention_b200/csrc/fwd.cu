@@ -12,6 +12,10 @@
 //   warps 4-7   softmax stage 1                                               warp 9  UMMA issuer
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P-hat overlays columns [0,32) of its S, the
 // P.V scale factors columns [32,40).
+// FL_MODE_FP4: all 512 columns are taken, so the 16 scale columns of an S product (Q and K atoms, tcgen05.cp from shared
+// memory) are parked in columns [64,80) of the OTHER stage's S region once that stage's softmax warps have read their
+// scores into registers (B_SDRAIN), and in O1 for the two products of the first key tile (nothing lives there yet). The
+// tensor pipe runs in issue order, so the next product that overwrites the parked columns starts after the reader.
 // All waits are bounded (sm100.cuh); a kernel that gives up writes a code to the status word and drains.
 #include "flamia_internal.h"
 
@@ -25,6 +29,8 @@ struct FwdParams {
   const float* fac_q;
   const float* fac_k;
   const float* fac_v;
+  const uint8_t* sfq4;   // FL_MODE_FP4: E4M3 scale atoms of the NVFP4 Q / K copies, 1 KB per 128-row tile at d = 128
+  const uint8_t* sfk4;
   void* out;
   float* lse;
   const int32_t* doc_start;
@@ -50,9 +56,9 @@ struct Tile {
 // barrier indices
 enum { B_Q = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + KV_STAGES, B_VFULL = B_KEMPTY + KV_STAGES,
        B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES, B_PFULL = B_SFULL + 2, B_PVDONE = B_PFULL + 2,
-       B_COUNT = B_PVDONE + 2 };
+       B_SDRAIN = B_PVDONE + 2, B_COUNT = B_SDRAIN + 2 };
 
-template <int D>
+template <int D, bool FP4>
 __global__ void __launch_bounds__(320, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
@@ -64,6 +70,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   uint8_t* sQ = smem;                                   // 2 tiles
   uint8_t* sK = sQ + 2 * TILE_BYTES;                    // KV_STAGES tiles
   uint8_t* sV = sK + KV_STAGES * TILE_BYTES;            // KV_STAGES tiles
+  uint8_t* sSF = sV + KV_STAGES * TILE_BYTES;           // FP4: scale atoms, Q 2 x 1 KB then K KV_STAGES x 1 KB
+  constexpr int OP_BYTES = FP4 ? TILE_BYTES / 2 : TILE_BYTES;   // bytes of one Q / K operand tile (4-bit codes: half)
   __shared__ __align__(8) uint64_t bars[B_COUNT];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
@@ -86,6 +94,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       mbar_init(&bars[B_SFULL + i], 1);
       mbar_init(&bars[B_PFULL + i], 4);      // one arrival per softmax warp
       mbar_init(&bars[B_PVDONE + i], 1);
+      mbar_init(&bars[B_SDRAIN + i], 4);
     }
     fence_barrier_init();
     // ---- which tile
@@ -141,14 +150,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       // =================================================================== TMA producer
       if (lane == 0) {
         tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-        mbar_arrive_expect_tx(&bars[B_Q], 2 * TILE_BYTES);
+        const bool two = T.nq > 128;
+        mbar_arrive_expect_tx(&bars[B_Q], 2 * OP_BYTES + (FP4 ? (two ? 2048 : 1024) : 0));
         tma_load_4d(sQ, &tm_q, &bars[B_Q], 0, head, T.q0, T.bat);
         tma_load_4d(sQ + TILE_BYTES, &tm_q, &bars[B_Q], 0, head, T.q0 + 128, T.bat);
+        if (FP4) {
+          const uint8_t* src = p.sfq4 + (((size_t)T.bat * p.h + head) * (p.s_q / 128) + T.q0 / 128) * 1024;
+          bulk_load(sSF, src, two ? 2048 : 1024, &bars[B_Q]);
+        }
         for (int j = 0; j < n_max; ++j) {
           const int st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
           if (j >= KV_STAGES && !mbar_wait(&bars[B_KEMPTY + st], ph ^ 1, p.ctl, abortp, 10)) break;
-          mbar_arrive_expect_tx(&bars[B_KFULL + st], TILE_BYTES);
+          mbar_arrive_expect_tx(&bars[B_KFULL + st], OP_BYTES + (FP4 ? 1024 : 0));
           tma_load_4d(sK + st * TILE_BYTES, &tm_k, &bars[B_KFULL + st], 0, hkv, T.k0 + j * 128, T.bat);
+          if (FP4)
+            bulk_load(sSF + 2048 + st * 1024,
+                      p.sfk4 + (((size_t)T.bat * p.h_kv + hkv) * (p.s_k / 128) + T.k0 / 128 + j) * 1024, 1024,
+                      &bars[B_KFULL + st]);
           if (j >= KV_STAGES && !mbar_wait(&bars[B_VEMPTY + st], ph ^ 1, p.ctl, abortp, 11)) break;
           mbar_arrive_expect_tx(&bars[B_VFULL + st], TILE_BYTES);
           tma_load_4d(sV + st * TILE_BYTES, &tm_v, &bars[B_VFULL + st], 0, hkv, T.k0 + j * 128, T.bat);
@@ -164,12 +182,37 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const int n0 = __shfl_sync(0xFFFFFFFFu, n_st[0], 0), n1 = __shfl_sync(0xFFFFFFFFu, n_st[1], 0);
         const int nmax = max(n0, n1);
         const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-        const uint64_t dq0 = smem_desc(q_addr, 16, SBO, SWZ), dk0 = smem_desc(k_addr, 16, SBO, SWZ),
+        // FP4: rows of D / 2 bytes (64 B swizzle at d = 128), K = 64 elements = 32 bytes per instruction
+        const uint64_t dq0 = FP4 ? smem_desc(q_addr, 16, 512, SWZ_64) : smem_desc(q_addr, 16, SBO, SWZ),
+                       dk0 = FP4 ? smem_desc(k_addr, 16, 512, SWZ_64) : smem_desc(k_addr, 16, SBO, SWZ),
                        dv0 = smem_desc(v_addr, 16, SBO, SWZ);
-        auto issue_s = [&](int i, int st) {
+        const uint64_t dsf0 = smem_desc(smem_u32(sSF), 0, 128, SWZ_NONE);   // scale atoms: 32 rows x 16 B, unswizzled
+        // issue_s(i, st, t): S of stage i against the K tile in buffer st; t = key tile index (FP4 parking rule)
+        auto issue_s = [&](int i, int st, int t) {
           const uint64_t a = desc_adv(dq0, i * TILE_BYTES), b = desc_adv(dk0, st * TILE_BYTES);
+          if (FP4) {
+            constexpr uint32_t ID_S4 = idesc_bs(128, 128, 1, 1, 0, 0, 0, 0, 0);
+            const uint32_t park = (t == 0) ? (tm + 384 + 16 * i) : (tm + 128 * (1 - i) + 64);
 #pragma unroll
-          for (int k = 0; k < D / 32; ++k) umma_f8_ss(tm + 128 * i, desc_adv(a, 32 * k), desc_adv(b, 32 * k), ID_S, k > 0);
+            for (int k = 0; k < D / 64; ++k) {
+              tmem_cp_sf_atom(park + 4 * k, desc_adv(dsf0, i * 1024 + 512 * k));
+              tmem_cp_sf_atom(park + 8 + 4 * k, desc_adv(dsf0, 2048 + st * 1024 + 512 * k));
+            }
+#pragma unroll
+            for (int k = 0; k < D / 64; ++k)
+              umma_nvf4_ss(tm + 128 * i, desc_adv(a, 32 * k), desc_adv(b, 32 * k), ID_S4, park + 4 * k, park + 8 + 4 * k, k > 0);
+          } else {
+#pragma unroll
+            for (int k = 0; k < D / 32; ++k) umma_f8_ss(tm + 128 * i, desc_adv(a, 32 * k), desc_adv(b, 32 * k), ID_S, k > 0);
+          }
+        };
+        // FP4: the other stage's latest scores must have been read before their region takes the scale columns
+        auto drained = [&](int i, int t) -> bool {
+          if (!FP4 || t == 0) return true;
+          const int n_y = i == 0 ? n1 : n0;
+          if (n_y <= 0) return true;
+          const int last = min(i == 0 ? t - 1 : t, n_y - 1);
+          return mbar_wait(&bars[B_SDRAIN + (1 - i)], last & 1, p.ctl, abortp, 26 + i);
         };
         auto issue_pv = [&](int i, int st, uint32_t accum) {
           const uint64_t b = desc_adv(dv0, st * TILE_BYTES);
@@ -184,8 +227,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (ok && nmax > 0) {
           tc_fence_after();
           if (elect_one()) {
-            if (n0 > 0) { issue_s(0, 0); tc_commit(&bars[B_SFULL + 0]); }
-            if (n1 > 0) { issue_s(1, 0); tc_commit(&bars[B_SFULL + 1]); }
+            if (n0 > 0) { issue_s(0, 0, 0); tc_commit(&bars[B_SFULL + 0]); }
+            if (n1 > 0) { issue_s(1, 0, 0); tc_commit(&bars[B_SFULL + 1]); }
             tc_commit(&bars[B_KEMPTY + 0]);   // K tile 0 is free once both S(0) products have completed
           }
           __syncwarp();
@@ -209,7 +252,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 k_next_ready = true;
                 tc_fence_after();
               }
-              if (elect_one()) { issue_s(i, stn); tc_commit(&bars[B_SFULL + i]); }
+              if (!(ok = drained(i, j + 1))) break;
+              if (FP4) tc_fence_after();
+              if (elect_one()) { issue_s(i, stn, j + 1); tc_commit(&bars[B_SFULL + i]); }
               __syncwarp();
             }
           }
@@ -233,7 +278,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const int qrel = T.qrel + 128 * i + r;            // row inside the document
       const bool row_valid = (128 * i + r) < T.nq;
       const size_t bh_q = (size_t)T.bat * p.h + head, bh_k = (size_t)T.bat * p.h_kv + hkv;
-      const float fq = row_valid ? p.fac_q[bh_q * (p.s_q / 32) + qrow / 32] * p.scale_log2 : 0.f;
+      const float fq = !row_valid ? 0.f : FP4 ? p.scale_log2 : p.fac_q[bh_q * (p.s_q / 32) + qrow / 32] * p.scale_log2;
       const float* fk_row = p.fac_k + bh_k * (p.s_k / 32) + T.k0 / 32;
       const float* fv_row = p.fac_v + bh_k * (p.s_k / 32) + T.k0 / 32;
       const int col_limit = p.causal ? min(qrel + T.off, T.sk - 1) : T.sk - 1;   // last visible key of this row
@@ -245,7 +290,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         uint32_t sfv = 0;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
-          c[kb] = fq * fk_row[j * 4 + kb];
+          c[kb] = FP4 ? fq : fq * fk_row[j * 4 + kb];      // FP4: the block scales were applied by the tensor core
           sfv |= ((__float_as_uint(fv_row[j * 4 + kb]) >> 23) & 0xFF) << (8 * kb);
         }
         if (!(ok = mbar_wait(&bars[B_SFULL + i], j & 1, p.ctl, abortp, 30 + i))) break;
@@ -254,6 +299,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) FL_TMEM_LD_32(t_s + 32 * cc, (su + 32 * cc));
         tc_wait_ld();
+        if (FP4) {      // the scores are in registers: this S region may take the other stage's scale columns
+          tc_fence_before();
+          mbar_arrive_warp(&bars[B_SDRAIN + i]);
+        }
         float s[128];
 #pragma unroll
         for (int e = 0; e < 128; ++e) s[e] = __uint_as_float(su[e]);
@@ -371,18 +420,22 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   if (!a || !a->q_codes || !a->k_codes || !a->v_codes || !a->out || !a->status) return FL_ERR_BAD_ARG;
   if (!a->fac_q || !a->fac_k || !a->fac_v) return FL_ERR_BAD_ARG;
   if (a->d != 64 && a->d != 128) return FL_ERR_UNSUPPORTED;
-  if (a->mode != FL_MODE_FP8) return FL_ERR_UNSUPPORTED;
+  if (a->mode != FL_MODE_FP8 && a->mode != FL_MODE_FP4) return FL_ERR_UNSUPPORTED;
+  const bool fp4 = a->mode == FL_MODE_FP4;
+  if (fp4 && a->d != 128) return FL_ERR_UNSUPPORTED;
+  if (fp4 && (!a->q4 || !a->k4 || !a->sfq4 || !a->sfk4)) return FL_ERR_BAD_ARG;
   if (a->flags & FL_A_TOKEN_LOCAL) return FL_ERR_UNSUPPORTED;
   if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
   if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
   if (a->doc_start && (a->b != 1 || a->n_docs <= 0 || !a->doc_len || a->s_q != a->s_k)) return FL_ERR_BAD_ARG;
   CUtensorMap mq, mk, mv;
   int rc;
-  if ((rc = make_rows_map(&mq, a->q_codes, a->b, a->s_q, a->h, a->d, 128))) return rc;
-  if ((rc = make_rows_map(&mk, a->k_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
+  if ((rc = make_rows_map(&mq, fp4 ? a->q4 : a->q_codes, a->b, a->s_q, a->h, fp4 ? a->d / 2 : a->d, 128))) return rc;
+  if ((rc = make_rows_map(&mk, fp4 ? a->k4 : a->k_codes, a->b, a->s_k, a->h_kv, fp4 ? a->d / 2 : a->d, 128))) return rc;
   if ((rc = make_rows_map(&mv, a->v_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
   FwdParams p;
   p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.out = a->out; p.lse = a->lse;
+  p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;
   p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
@@ -393,16 +446,20 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   // packed documents: at most one extra 256-row block per document beyond total / 256
   const int nblk = a->doc_start ? (a->s_q / 256 + a->n_docs + 1) : (a->s_q + 255) / 256;
   dim3 grid(nblk, a->h, a->doc_start ? 1 : a->b);
-  const int smem = (2 + 2 * KV_STAGES) * 128 * a->d + 1024;
+  const int smem = (2 + 2 * KV_STAGES) * 128 * a->d + 1024 + (fp4 ? (2 + KV_STAGES) * 1024 : 0);
   cudaStream_t st = (cudaStream_t)stream;
-  if (a->d == 128) {
-    if (cudaFuncSetAttribute(fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+  if (fp4) {
+    if (cudaFuncSetAttribute(fwd_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return FL_ERR_CUDA;
-    fwd_kernel<128><<<grid, 320, smem, st>>>(mq, mk, mv, p);
+    fwd_kernel<128, true><<<grid, 320, smem, st>>>(mq, mk, mv, p);
+  } else if (a->d == 128) {
+    if (cudaFuncSetAttribute(fwd_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return FL_ERR_CUDA;
+    fwd_kernel<128, false><<<grid, 320, smem, st>>>(mq, mk, mv, p);
   } else {
-    if (cudaFuncSetAttribute(fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(fwd_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return FL_ERR_CUDA;
-    fwd_kernel<64><<<grid, 320, smem, st>>>(mq, mk, mv, p);
+    fwd_kernel<64, false><<<grid, 320, smem, st>>>(mq, mk, mv, p);
   }
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

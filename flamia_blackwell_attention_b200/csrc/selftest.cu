@@ -50,7 +50,8 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   if (which == FL_ST_WAIT_TIMEOUT) {
     if (tid == 0) mbar_wait(&bar_never, 0, p.ctl, &abort_s, 1);
   } else {
-    const bool nvf4 = which == FL_ST_NVF4;
+    const bool nvf4 = which == FL_ST_NVF4 || which == FL_ST_NVF4_N64_HI;
+    const bool hi64 = which == FL_ST_NVF4_N64_HI;
     const bool dqt = which == FL_ST_MX8_MN_N64;
     const bool a_tmem = which == FL_ST_F8_A_TMEM || which == FL_ST_MX8_TS;
     const bool scaled8 = which == FL_ST_MX8_SS || which == FL_ST_MX8_TS || dqt;
@@ -101,9 +102,16 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
           // rows of 64 bytes (128 E2M1), 64 B swizzle; K = 64 elements = 32 bytes per instruction
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
-            uint32_t id = idesc_bs(128, 128, 1, 1, 0, 0, 0, 0, 0);
-            umma_nvf4_ss(tmem + ST_COL_D, smem_desc(a0 + 32 * k, 16, 512, SWZ_64), smem_desc(b0 + 32 * k, 16, 512, SWZ_64),
-                         id, tmem + ST_COL_SFA + 4 * k, tmem + ST_COL_SFB + 4 * k, k > 0);
+            if (hi64) {
+              // N = 64: rows 64..127 of the B tile (4 KB further down); their scales are columns 2, 3 of each atom
+              umma_nvf4_ss(tmem + ST_COL_D, smem_desc(a0 + 32 * k, 16, 512, SWZ_64),
+                           smem_desc(b0 + 4096 + 32 * k, 16, 512, SWZ_64), idesc_bs(128, 64, 1, 1, 0, 0, 0, 0, 0),
+                           tmem + ST_COL_SFA + 4 * k, tmem + ST_COL_SFB + 4 * k + 2, k > 0);
+            } else {
+              umma_nvf4_ss(tmem + ST_COL_D, smem_desc(a0 + 32 * k, 16, 512, SWZ_64), smem_desc(b0 + 32 * k, 16, 512, SWZ_64),
+                           idesc_bs(128, 128, 1, 1, 0, 0, 0, 0, 0), tmem + ST_COL_SFA + 4 * k, tmem + ST_COL_SFB + 4 * k,
+                           k > 0);
+            }
           }
         } else if (dqt) {
 #pragma unroll
@@ -153,7 +161,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
     if (mbar_wait(&bar_mma, 0, p.ctl, &abort_s, 3)) {
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < (which == FL_ST_MX8_MN_N64 ? 2 : 4); ++c) {
+      for (int c = 0; c < ((which == FL_ST_MX8_MN_N64 || which == FL_ST_NVF4_N64_HI) ? 2 : 4); ++c) {
         uint32_t v[32];
         FL_TMEM_LD_32(lane_addr + ST_COL_D + 32 * c, v);
         tc_wait_ld();
@@ -172,11 +180,11 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
 extern "C" int fl_selftest_mma(int32_t which, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                                float* d, int32_t* status, int64_t wait_cycles, void* stream) {
   using namespace fl;
-  if (which < 0 || which > FL_ST_MX8_MN_N64 || !status) return FL_ERR_BAD_ARG;
+  if (which < 0 || which > FL_ST_NVF4_N64_HI || !status) return FL_ERR_BAD_ARG;
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return FL_ERR_CUDA;
   CUtensorMap ma, mb;
-  const bool nvf4 = which == FL_ST_NVF4;
+  const bool nvf4 = which == FL_ST_NVF4 || which == FL_ST_NVF4_N64_HI;
   if (which != FL_ST_WAIT_TIMEOUT) {
     if (!a || !b || !d) return FL_ERR_BAD_ARG;
     const cuuint64_t rowb = nvf4 ? 64 : 128;

@@ -17,14 +17,19 @@ from oracle import attention_oracle as A
 pytestmark = pytest.mark.gpu
 
 REF_REL_L2_O_FP8 = math.sqrt(2 * (1 - 0.9988))
+REF_REL_L2_O_FP4 = math.sqrt(2 * (1 - 0.9920))      # published cosine of the mixed NVFP4 / FP8 route at the same cell
 
 
-def run_fwd(q, k, v, causal, rotate=False):
-    from flamia_blackwell_attention_b200 import kernels as K
-    qq = K.quantize_fp8_blocks(q.cuda(), apply_hadamard_rotation=rotate)
-    kq = K.quantize_fp8_blocks(k.cuda(), apply_hadamard_rotation=rotate)
+def run_fwd(q, k, v, causal, rotate=False, fp4=False):
+    from flamia_blackwell_attention_b200 import kernels as K, _lib as L
+    kw = dict(apply_hadamard_rotation=rotate)
+    if fp4:     # the mixed route: NVFP4 copies of Q / K feed S; with rotation on only those copies are rotated
+        kw.update(also_make_nvfp4_copy=True, hadamard_rotation_scope="nvfp4_copy")
+    qq = K.quantize_fp8_blocks(q.cuda(), **kw)
+    kq = K.quantize_fp8_blocks(k.cuda(), **kw)
     vq = K.quantize_fp8_blocks(v.cuda())
-    out, lse, st = K.attn_fwd(qq, kq, vq, causal=causal, softmax_scale=1.0 / math.sqrt(q.shape[-1]))
+    out, lse, st = K.attn_fwd(qq, kq, vq, causal=causal, softmax_scale=1.0 / math.sqrt(q.shape[-1]),
+                              mode=L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8)
     torch.cuda.synchronize()
     assert K.read_status(st) == 0
     return out.float().cpu(), lse.cpu()
@@ -92,3 +97,40 @@ def test_forward_at_the_reference_cell_shape():
     assert acc["rel_l2"] <= 1.05 * REF_REL_L2_O_FP8, acc
     print("max |lse - lse_fp32|", float((lse - lse32).abs().max()))
     assert float((lse - lse32).abs().mean()) < 2e-2
+
+
+FP4_CASES = [
+    # b, s_q, s_k, h, h_kv, causal, rotate
+    (1, 128, 128, 1, 1, False, False),
+    (1, 256, 256, 2, 2, True, False),
+    (2, 384, 384, 4, 2, True, True),          # odd tile count (second stage absent in the last block), GQA
+    (1, 256, 640, 2, 1, True, True),          # s_q != s_k
+    (1, 640, 256, 2, 2, True, False),         # leading rows see no key
+    (2, 1024, 1024, 2, 2, False, True),
+]
+
+
+@pytest.mark.parametrize("b,sq,sk,h,hk,causal,rotate", FP4_CASES)
+def test_forward_fp4_vs_oracle(b, sq, sk, h, hk, causal, rotate):
+    """Mixed route: S from the NVFP4 codes (block-scaled tensor-core product), P.V as on the 8-bit route."""
+    s = max(sq, sk)
+    q, k, v, _ = attention_inputs(b, s, h, hk, 128, seed=4)
+    q, k, v = q[:, :sq], k[:, :sk], v[:, :sk]
+    out, lse = run_fwd(q, k, v, causal, rotate=rotate, fp4=True)
+    o_ref, lse_ref, *_ = A.qdq_attention(q, k, v, causal=causal, fp4_qk=True, rotate_qk=rotate)
+    acc = A.accuracy(out, o_ref)
+    assert acc["rel_l2"] < 3.2e-2, acc
+    vis = torch.isfinite(lse_ref)
+    assert torch.equal(torch.isfinite(lse), vis)
+    assert float((lse[vis] - lse_ref[vis]).abs().max()) < 2e-3
+    o1, l1 = run_fwd(q, k, v, causal, rotate=rotate, fp4=True)
+    assert torch.equal(o1, out) and torch.equal(l1, lse)
+
+
+def test_forward_fp4_at_the_reference_cell_shape():
+    q, k, v, _ = attention_inputs(1, 4096, 2, 2, 128, seed=0)
+    out, lse = run_fwd(q, k, v, True, rotate=True, fp4=True)
+    o32, lse32, *_ = A.attention_fp32(q.float(), k.float(), v.float(), None, True)
+    acc = A.accuracy(out, o32)
+    print("A1 slice accuracy vs fp32 (mixed route):", acc)
+    assert acc["rel_l2"] <= 1.05 * REF_REL_L2_O_FP4, acc

@@ -77,6 +77,20 @@ def test_block_scaled_nvfp4():
     np.testing.assert_array_equal(got, want.astype(np.float32))
 
 
+def test_block_scaled_nvfp4_upper_half_of_b():
+    # the operand path of the backward's NVFP4 S^T recompute for the second 64-query half tile
+    g = np.random.default_rng(16)
+    ca = g.integers(0, 16, size=(128, 128)).astype(np.uint8)
+    cb = g.integers(0, 16, size=(128, 128)).astype(np.uint8)
+    av, bv = Q.e2m1_decode(ca), Q.e2m1_decode(cb)
+    sfa_v = 2.0 ** g.integers(-2, 3, size=(128, 8)).astype(np.float32)
+    sfb_v = 2.0 ** g.integers(-2, 3, size=(128, 8)).astype(np.float32)
+    atoms = lambda t: Q.sf_atoms(t.reshape(1, 1, 128, 8)).reshape(-1)
+    got = run(9, Q.pack_nibbles(ca), Q.pack_nibbles(cb), atoms(Q.e4m3_encode(sfa_v)), atoms(Q.e4m3_encode(sfb_v)))[:, :64]
+    want = (av * np.repeat(sfa_v, 16, 1)).astype(np.float64) @ (bv * np.repeat(sfb_v, 16, 1)).astype(np.float64)[64:].T
+    np.testing.assert_array_equal(got, want.astype(np.float32))
+
+
 def test_wait_that_nothing_completes_returns_a_status():
     from flamia_blackwell_attention_b200.kernels import selftest_mma
     d, st = selftest_mma(7, None, None, wait_cycles=200000)
