@@ -19,6 +19,11 @@
 //   warps 8-11 dQ reduction (thread = head-dim row)      warp 12 UMMA issuer      warp 13 TMA producer
 // TMEM: [0,64) / [64,128) S^T_x, then P-hat +0, dS-hat +16, six scale tiles +32..+56; [128,256) dV;
 //       [256,320) / [320,384) dP^T_x, then dQ^T_x; [384,512) dK.  Every wait is bounded (sm100.cuh).
+// FL_MODE_FP4 (the mixed route): S^T_x is recomputed at the forward's precision, K4 Q4_x^T with
+// kind::mxf4nvf4.block_scale.scale_vec::4X on the NVFP4 copies; everything after P' is the E4M3 path above. The 16 scale
+// columns of that product (tcgen05.cp of the K and Q atoms) are parked in the half's own dP^T columns: they are free
+// once the previous dQ^T_x has been read out, and the dP^T_x product that overwrites them is issued right after S^T_x
+// (the tensor pipe runs in issue order). The second half's Q scales are columns 2, 3 of each atom.
 #include "flamia_internal.h"
 
 int fl_bwd_v1(const fl_attn_args* a, void* stream);
@@ -33,6 +38,8 @@ struct BwdParams {
   const float* lse_log2;
   const float* d_rows;
   const float* dq_scale;
+  const uint8_t* sfq4;   // FL_MODE_FP4: E4M3 scale atoms of the NVFP4 Q / K copies (1 KB per 128-row tile)
+  const uint8_t* sfk4;
   void* dk;
   void* dv;
   const int32_t* doc_start;
@@ -96,10 +103,12 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
       "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])                                           \
       : "memory")
 
+template <bool FP4>
 __global__ void __launch_bounds__(512, 1)
 bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                     const __grid_constant__ CUtensorMap tm_acc, const BwdParams p) {
+                     const __grid_constant__ CUtensorMap tm_acc, const __grid_constant__ CUtensorMap tm_q4,
+                     const __grid_constant__ CUtensorMap tm_k4, const BwdParams p) {
   constexpr int D = 128;
   constexpr int TILE_BYTES = 128 * D;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -111,6 +120,10 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint8_t* sDS = sDO + 2 * TILE_BYTES;                 // per half: 128 key rows x 64 query bytes, 64 B swizzle
   uint8_t* sDQ = sDS + 2 * 8192;                       // per half: 128 head-dim rows x 64 queries f16, 128 B swizzle
   float* sVec = reinterpret_cast<float*>(sDQ + 2 * 16384);   // 2 stages x {lse_log2[128], D''[128]}
+  // FP4 only: NVFP4 K tile (8 KB), two Q4 stages (8 KB each), scale atoms K 1 KB + Q 2 x 1 KB
+  uint8_t* sK4 = reinterpret_cast<uint8_t*>(sVec) + 2048;
+  uint8_t* sQ4 = sK4 + 8192;
+  uint8_t* sSF = sQ4 + 2 * 8192;
   __shared__ __align__(8) uint64_t bars[BB_COUNT];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
@@ -178,15 +191,25 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // =================================================================== TMA producer
       if (lane == 0) {
         tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_do);
-        mbar_arrive_expect_tx(&bars[BB_KV], 2 * TILE_BYTES);
+        mbar_arrive_expect_tx(&bars[BB_KV], 2 * TILE_BYTES + (FP4 ? 8192 + 1024 : 0));
         tma_load_4d(sK, &tm_k, &bars[BB_KV], 0, hkv, T.k0, T.bat);
         tma_load_4d(sV, &tm_v, &bars[BB_KV], 0, hkv, T.k0, T.bat);
+        if (FP4) {
+          tma_load_4d(sK4, &tm_k4, &bars[BB_KV], 0, hkv, T.k0, T.bat);
+          bulk_load(sSF, p.sfk4 + (((size_t)T.bat * p.h_kv + hkv) * (p.s_k / 128) + T.k0 / 128) * 1024, 1024, &bars[BB_KV]);
+        }
         for (int it = 0; it < n_it; ++it) {
           const int st = it & 1, u = it >> 1;
           const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
           if (it >= 2 && !mbar_wait(&bars[BB_QEMPTY + st], (u & 1) ^ 1, p.ctl, abortp, 10)) break;
-          mbar_arrive_expect_tx(&bars[BB_QFULL + st], 2 * TILE_BYTES + 1024);
+          mbar_arrive_expect_tx(&bars[BB_QFULL + st], 2 * TILE_BYTES + 1024 + (FP4 ? 8192 + 1024 : 0));
           tma_load_4d(sQ + st * TILE_BYTES, &tm_q, &bars[BB_QFULL + st], 0, head, T.q0 + m * 128, T.bat);
+          if (FP4) {
+            tma_load_4d(sQ4 + st * 8192, &tm_q4, &bars[BB_QFULL + st], 0, head, T.q0 + m * 128, T.bat);
+            bulk_load(sSF + 1024 + st * 1024,
+                      p.sfq4 + (((size_t)T.bat * p.h + head) * (p.s_q / 128) + (T.q0 + m * 128) / 128) * 1024, 1024,
+                      &bars[BB_QFULL + st]);
+          }
           tma_load_4d(sDO + st * TILE_BYTES, &tm_do, &bars[BB_QFULL + st], 0, head, T.q0 + m * 128, T.bat);
           const size_t ro = ((size_t)T.bat * p.h + head) * p.s_q + T.q0 + m * 128;
           bulk_load(sVec + st * 256, p.lse_log2 + ro, 512, &bars[BB_QFULL + st]);
@@ -206,6 +229,8 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint64_t dK_k = smem_desc(k_addr, 16, 1024, SWZ_128), dV_k = smem_desc(v_addr, 16, 1024, SWZ_128),
                        dQ0 = smem_desc(q_addr, 16, 1024, SWZ_128), dDO0 = smem_desc(do_addr, 16, 1024, SWZ_128),
                        dDS0 = smem_desc(ds_addr, 16, 512, SWZ_64);
+        const uint64_t dK4 = smem_desc(smem_u32(sK4), 16, 512, SWZ_64), dQ40 = smem_desc(smem_u32(sQ4), 16, 512, SWZ_64),
+                       dSF0 = smem_desc(smem_u32(sSF), 0, 128, SWZ_NONE);
         bool ok = mbar_wait(&bars[BB_KV], 0, p.ctl, abortp, 20);
         for (int t = 0; ok && t <= n_steps; ++t) {
           if (t < n_steps) {
@@ -214,16 +239,35 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (x == 0 && !(ok = mbar_wait(&bars[BB_QFULL + st], (it >> 1) & 1, p.ctl, abortp, 21))) break;
             tc_fence_after();
             const uint64_t qx = desc_adv(dQ0, st * TILE_BYTES + x * 64 * D), dox = desc_adv(dDO0, st * TILE_BYTES + x * 64 * D);
+            if (FP4) {
+              // the scale columns go into the half's dP^T region: its previous dQ^T must have been read out first
+              if (it > 0 && !(ok = mbar_wait(&bars[BB_DQE + x], (it - 1) & 1, p.ctl, abortp, 22))) break;
+              tc_fence_after();
+            }
             if (elect_one()) {
+              if (FP4) {
+                const uint32_t park = tm + TC_DP + 64 * x;
+                const uint64_t q4x = desc_adv(dQ40, st * 8192 + x * 4096);
 #pragma unroll
-              for (int k = 0; k < D / 32; ++k)
-                umma_f8_ss(tm + TC_S + 64 * x, desc_adv(dK_k, 32 * k), desc_adv(qx, 32 * k), ID_N64, k > 0);
+                for (int k = 0; k < 2; ++k) {
+                  tmem_cp_sf_atom(park + 4 * k, desc_adv(dSF0, 512 * k));
+                  tmem_cp_sf_atom(park + 8 + 4 * k, desc_adv(dSF0, 1024 + st * 1024 + 512 * k));
+                }
+#pragma unroll
+                for (int k = 0; k < 2; ++k)   // K = 64 elements = 32 bytes per instruction
+                  umma_nvf4_ss(tm + TC_S + 64 * x, desc_adv(dK4, 32 * k), desc_adv(q4x, 32 * k),
+                               idesc_bs(128, 64, 1, 1, 0, 0, 0, 0, 0), park + 4 * k, park + 8 + 4 * k + 2 * x, k > 0);
+              } else {
+#pragma unroll
+                for (int k = 0; k < D / 32; ++k)
+                  umma_f8_ss(tm + TC_S + 64 * x, desc_adv(dK_k, 32 * k), desc_adv(qx, 32 * k), ID_N64, k > 0);
+              }
               tc_commit(&bars[BB_S + x]);
               TRACE(0, t, 0);
             }
             __syncwarp();
             // the half's dP^T columns hold its previous dQ^T until the reduction warps have read it
-            if (it > 0 && !(ok = mbar_wait(&bars[BB_DQE + x], (it - 1) & 1, p.ctl, abortp, 22))) break;
+            if (!FP4 && it > 0 && !(ok = mbar_wait(&bars[BB_DQE + x], (it - 1) & 1, p.ctl, abortp, 22))) break;
             tc_fence_after();
             if (elect_one()) {
 #pragma unroll
@@ -349,7 +393,8 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const float fq0 = p.fac_q[bh_q * (p.s_q / 32) + qb0], fq1 = p.fac_q[bh_q * (p.s_q / 32) + qb0 + 1];
         const float fd0 = p.fac_do[bh_q * (p.s_q / 32) + qb0], fd1 = p.fac_do[bh_q * (p.s_q / 32) + qb0 + 1];
         const float bsc = p.dq_scale[(size_t)T.bat * (p.s_q / 128) + T.q0 / 128 + m];
-        const float c[2] = {fk * fq0, fk * fq1}, b8[2] = {fv8 * fd0, fv8 * fd1};
+        // FP4: the block scales of S were applied by the tensor core; only the softmax scale remains
+        const float c[2] = {FP4 ? p.scale_log2 : fk * fq0, FP4 ? p.scale_log2 : fk * fq1}, b8[2] = {fv8 * fd0, fv8 * fd1};
         const uint32_t eq2 = ((__float_as_uint(fq0) >> 23) & 0xFF) | (((__float_as_uint(fq1) >> 23) & 0xFF) << 8);
         const uint32_t edo2 = ((__float_as_uint(fd0) >> 23) & 0xFF) | (((__float_as_uint(fd1) >> 23) & 0xFF) << 8);
         // K's exponent bytes with the power-of-two f16 pre-scale of this query tile folded in (A scale of dQ^T)
@@ -550,21 +595,30 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
       !a->dk || !a->dv)
     return FL_ERR_BAD_ARG;
   if (a->d != 128) return FL_ERR_UNSUPPORTED;
-  if (a->mode != FL_MODE_FP8) return FL_ERR_UNSUPPORTED;
+  if (a->mode != FL_MODE_FP8 && a->mode != FL_MODE_FP4) return FL_ERR_UNSUPPORTED;
+  const bool fp4 = a->mode == FL_MODE_FP4;
+  if (fp4 && (!a->q4 || !a->k4 || !a->sfq4 || !a->sfk4)) return FL_ERR_BAD_ARG;
   if (a->flags & (FL_A_TOKEN_LOCAL | FL_A_DQ_ROWLOCAL)) return FL_ERR_UNSUPPORTED;
   if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
   if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
   if (a->doc_start && (a->b != 1 || a->n_docs <= 0 || !a->doc_len || a->s_q != a->s_k)) return FL_ERR_BAD_ARG;
-  CUtensorMap mq, mk, mv, mdo, macc;
+  CUtensorMap mq, mk, mv, mdo, macc, mq4, mk4;
   int rc;
   if ((rc = make_rows_map(&mq, a->q_codes, a->b, a->s_q, a->h, a->d, 128))) return rc;
   if ((rc = make_rows_map(&mk, a->k_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
   if ((rc = make_rows_map(&mv, a->v_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
   if ((rc = make_rows_map(&mdo, a->do_codes, a->b, a->s_q, a->h, a->d, 128))) return rc;
   if ((rc = make_acc_t_map_16(&macc, a->dq_acc, a->b, a->h, a->d, a->s_q))) return rc;
+  // the NVFP4 copies (64-byte rows); the 8-bit route passes the E4M3 maps again, which the kernel never touches
+  if ((rc = make_rows_map(&mq4, fp4 ? (const void*)a->q4 : (const void*)a->q_codes, a->b, a->s_q, a->h, fp4 ? 64 : 128, 128)))
+    return rc;
+  if ((rc = make_rows_map(&mk4, fp4 ? (const void*)a->k4 : (const void*)a->k_codes, a->b, a->s_k, a->h_kv, fp4 ? 64 : 128,
+                          128)))
+    return rc;
   BwdParams p;
   p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.fac_do = a->fac_do; p.lse_log2 = a->lse_log2;
   p.d_rows = a->d_rows; p.dq_scale = a->dq_scale; p.dk = a->dk; p.dv = a->dv;
+  p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;
   p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
   p.softmax_scale = a->softmax_scale;
@@ -576,9 +630,15 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.ctl.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kDefaultWaitCycles;
   const int ntile = a->doc_start ? (a->s_k / 128 + a->n_docs) : a->s_k / 128;
   dim3 grid(ntile, a->h_kv, a->doc_start ? 1 : a->b);
-  const int smem = 6 * 128 * 128 + 2 * 8192 + 2 * 16384 + 2048 + 1024;
-  if (cudaFuncSetAttribute(bwd_kernel_pipelined, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-    return FL_ERR_CUDA;
-  bwd_kernel_pipelined<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, p);
+  const int smem = 6 * 128 * 128 + 2 * 8192 + 2 * 16384 + 2048 + 1024 + (fp4 ? 3 * 8192 + 3 * 1024 : 0);
+  if (fp4) {
+    if (cudaFuncSetAttribute(bwd_kernel_pipelined<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return FL_ERR_CUDA;
+    bwd_kernel_pipelined<true><<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, p);
+  } else {
+    if (cudaFuncSetAttribute(bwd_kernel_pipelined<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return FL_ERR_CUDA;
+    bwd_kernel_pipelined<false><<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, p);
+  }
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

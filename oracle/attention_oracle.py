@@ -23,15 +23,20 @@ import torch
 from . import quant_oracle as Q
 
 
-def attention_fp32(q, k, v, g=None, causal=False, softmax_scale=None, chunk=1024):
+def attention_fp32(q, k, v, g=None, causal=False, softmax_scale=None, chunk=1024, q_grad=None, k_grad=None):
     """q (b, s_q, h, d), k / v (b, s_k, h_kv, d) float32 CPU tensors -> (o, lse, dq, dk, dv); lse (b, h, s_q) in nats.
-    Causal: key j visible to query i iff j <= i + (s_k - s_q). g = dO or None (forward only)."""
+    Causal: key j visible to query i iff j <= i + (s_k - s_q). g = dO or None (forward only).
+    q_grad / k_grad: the copies of Q / K used as operands of dK = dS^T Q and dQ = dS K when they differ from the S
+    operands (the mixed route: S from the NVFP4 copies, gradient GEMMs from the E4M3 copies)."""
     q, k, v = q.float(), k.float(), v.float()
+    qg = q if q_grad is None else q_grad.float()
+    kg = k if k_grad is None else k_grad.float()
     b, sq, h, d = q.shape
     sk, hk = k.shape[1], k.shape[2]
     grp = h // hk
     sc = 1.0 / math.sqrt(d) if softmax_scale is None else float(softmax_scale)
     kr, vr = k.repeat_interleave(grp, 2), v.repeat_interleave(grp, 2)
+    kgr = kg.repeat_interleave(grp, 2)
     o = torch.zeros_like(q)
     lse = torch.zeros(b, h, sq)
     bwd = g is not None
@@ -57,8 +62,8 @@ def attention_fp32(q, k, v, g=None, causal=False, softmax_scale=None, chunk=1024
                 if bwd:
                     dO = g[bi, r0:r0 + chunk, hi].float()
                     dS = P * (dO @ Vm.T - (dO * O).sum(-1, keepdim=True))
-                    dq[bi, r0:r0 + chunk, hi] = (dS @ Km) * sc
-                    dk[bi, :, hi] += (dS.T @ Qm[r0:r0 + chunk]) * sc
+                    dq[bi, r0:r0 + chunk, hi] = (dS @ kgr[bi, :, hi]) * sc
+                    dk[bi, :, hi] += (dS.T @ qg[bi, r0:r0 + chunk, hi]) * sc
                     dv[bi, :, hi] += P.T @ dO
     if bwd and grp > 1:
         dk, dv = (t.view(b, sk, hk, grp, d).sum(3) for t in (dk, dv))
@@ -111,9 +116,10 @@ def qdq_attention(q, k, v, g=None, *, causal=False, softmax_scale=None, fp4_qk=F
     if not fp4_qk:
         return attention_fp32(q8, k8, v8, g8, causal, softmax_scale)
     q4, k4 = back(_qdq4(q, rotate_qk)), back(_qdq4(k, rotate_qk))
-    # forward and P from the 4-bit S operands
-    o, lse, dq, dk, dv = attention_fp32(q4, k4, v8, g8, causal, softmax_scale)
-    return o, lse, dq, dk, dv
+    # forward and P from the 4-bit S operands; with rotation on only the 4-bit copies are rotated on this route, so the
+    # E4M3 copies for the gradient GEMMs are those of the unrotated rows
+    q8u, k8u = (q8, k8) if not rotate_qk else (_qdq8(q, False, token_local), _qdq8(k, False, token_local))
+    return attention_fp32(q4, k4, v8, g8, causal, softmax_scale, q_grad=q8u, k_grad=k8u)
 
 
 def accuracy(x, ref):
