@@ -283,7 +283,7 @@ def main():
                        "published_reference_ms": 0.865 if causal else 1.416},
             "ms_fwd_kernel": k_fwd, "ms_bwd_kernel": k_bwd,
             "tflops_fwd_kernel": f_fwd / (k_fwd * 1e-3) / 1e12, "tflops_bwd_kernel": achieved,
-            "roofline": {"bound": "tensor", "kernel": "bwd_kernel<128>", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "roofline": {"bound": "tensor", "kernel": "bwd_kernel_pipelined", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": (t_min / (k_bwd * 1e-3)),
                          # dram read + write bytes of one launch: 151.4 MB captured by ncu on the b2 cell of
                          # --profile-case, scaled by the batch (traffic is proportional to b); fp8 route, causal

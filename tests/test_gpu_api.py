@@ -120,3 +120,43 @@ def test_inputs_are_not_mutated_and_no_host_sync():
     torch.cuda.synchronize()
     for a, b in ((q, q0), (k, k0), (v, v0), (g, g0)):
         assert torch.equal(a.detach(), b)
+
+
+def test_fp4_batched_autograd_default_route():
+    """flash_attn_fp4 defaults: NVFP4 S operands of the rotated rows, E4M3 P.V and gradient products."""
+    from flamia_blackwell_attention_b200 import flash_attn_fp4
+    q, k, v, g = attention_inputs(2, 512, 4, 2, 128, seed=14)
+    o, dq, dk, dv, lse = _step(flash_attn_fp4, q, k, v, g, causal=True, return_lse=True)
+    ro, rl, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=True, fp4_qk=True, rotate_qk=True)
+    _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))
+    assert lse.shape == (2, 4, 512)
+    assert float((lse.cpu() - rl).abs().max()) < 2e-3
+
+
+def test_fp4_forward_only_and_dense():
+    from flamia_blackwell_attention_b200 import flash_attn_fp4
+    q, k, v, _ = attention_inputs(1, 384, 2, 2, 128, seed=15)
+    with torch.no_grad():
+        o = flash_attn_fp4(q.cuda(), k.cuda(), v.cuda())
+    ro, *_ = A.qdq_attention(q, k, v, causal=False, fp4_qk=True, rotate_qk=True)
+    assert A.accuracy(o.float().cpu(), ro)["rel_l2"] < 3.2e-2
+
+
+def test_fp4_packed_documents():
+    from flamia_blackwell_attention_b200 import flash_attn_fp4
+    lens = [300, 128, 77, 515]
+    h, d = 2, 128
+    starts = [sum(lens[:i]) for i in range(len(lens))]
+    total = sum(lens)
+    q, k, v, g = (t[0] for t in attention_inputs(1, total, h, h, d, seed=16))
+    cu = torch.tensor(starts + [total], dtype=torch.int32, device="cuda")
+    kw = dict(causal=True, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens))
+    import warnings
+    with warnings.catch_warnings():          # the repacking notice is issued once per process
+        warnings.simplefilter("ignore")
+        o, dq, dk, dv, _ = _step(flash_attn_fp4, q, k, v, g, **kw)
+    for s0, n in zip(starts, lens):
+        sl = slice(s0, s0 + n)
+        ro, _, rdq, rdk, rdv = A.attention_fp32(q[None, sl].float(), k[None, sl].float(), v[None, sl].float(),
+                                                g[None, sl].float(), True)
+        _check((o[sl], dq[sl], dk[sl], dv[sl]), (ro[0], rdq[0], rdk[0], rdv[0]), tol=0.17)   # 4-bit S operands vs fp32
