@@ -24,6 +24,12 @@
 // columns of that product (tcgen05.cp of the K and Q atoms) are parked in the half's own dP^T columns: they are free
 // once the previous dQ^T_x has been read out, and the dP^T_x product that overwrites them is issued right after S^T_x
 // (the tensor pipe runs in issue order). The second half's Q scales are columns 2, 3 of each atom.
+// VAR = 1 (FL_A_DQ_ROWLOCAL, the reference's ds_dq_rowlocal="all", flash_bwd_sm100_fp4.py:3637-3642): the dQ side of
+// dS-hat gets its own codes with one exponent per (query row, 32-key block) instead of sharing the 32 x 32 block's.
+// VAR = 2 (FL_A_TOKEN_LOCAL + row-local, flash_bwd_sm100_fp4.py:152-158): every token of Q, K, V, dO carries its own
+// power-of-two factor. Per-key factors are per-thread scalars here, per-query factors are read per element; S and dP
+// take f_K f_Q and f_V f_dO in the elementwise math; dV takes f_dO inside a block-scaled P-hat (one exponent per key row
+// x 32 queries); dK takes f_Q inside its dS-hat codes, dQ takes f_K inside its own; the operand scale tiles are unit.
 #include "flamia_internal.h"
 
 int fl_bwd_v1(const fl_attn_args* a, void* stream);
@@ -59,7 +65,7 @@ struct BTile {
 };
 
 enum { BB_KV = 0, BB_QFULL = 1, BB_QEMPTY = 3, BB_S = 5, BB_DP = 7, BB_P = 9, BB_DS = 11, BB_EX = 13, BB_DQF = 15,
-       BB_DQE = 17, BB_R1 = 19, BB_R2 = 20, BB_ACC = 21, BB_COUNT = 22 };
+       BB_DQE = 17, BB_R1 = 19, BB_R2 = 20, BB_ACC = 21, BB_EP = 22, BB_COUNT = 24 };
 // TMEM columns; the per-half regions are at + 64 * x
 enum { TC_S = 0, TO_P = 0, TO_DS = 16, TO_SFA_P = 32, TO_SFB_DO = 36, TO_SFA_DK = 40, TO_SFB_Q = 44, TO_SFA_DQ = 48,
        TO_SFB_DQ = 52, TC_DV = 128, TC_DP = 256, TC_DK = 384 };
@@ -103,7 +109,14 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
       "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])                                           \
       : "memory")
 
-template <bool FP4>
+// 448 * 2^(e - 127) >= amax for the returned UE8M0 byte (bits = the non-negative float's pattern), clamped to [1, 254]
+__device__ __forceinline__ uint32_t exp448(uint32_t bits) {
+  const int e = (int)((bits + 0x00200000u) >> 23) - 8;
+  return (uint32_t)min(max(e, 1), 254);
+}
+__device__ __forceinline__ float pow2_inv(uint32_t ebyte) { return __uint_as_float((uint32_t)(254 - (int)ebyte) << 23); }
+
+template <bool FP4, int VAR>
 __global__ void __launch_bounds__(512, 1)
 bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -129,6 +142,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __shared__ int abort_s;
   __shared__ BTile tile_s;
   __shared__ uint32_t sE[2][4];                        // [half][key block] = exponent bytes of the half's two query blocks
+  __shared__ uint32_t sEP[2][128];                     // VAR 2: [half][key row] = P-hat exponent bytes of the two query blocks
+  __shared__ __align__(4) uint8_t sEQ[2][64][4];       // VAR >= 1: [half][query][key block] = dQ-side dS-hat exponents
+  constexpr bool RL = VAR >= 1, TL = VAR == 2;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hkv = blockIdx.y;
@@ -143,6 +159,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(&bars[BB_S + i], 1); mbar_init(&bars[BB_DP + i], 1);
       mbar_init(&bars[BB_P + i], 4); mbar_init(&bars[BB_DS + i], 4); mbar_init(&bars[BB_EX + i], 4);      // one arrival per warp
       mbar_init(&bars[BB_DQF + i], 1); mbar_init(&bars[BB_DQE + i], 4);
+      mbar_init(&bars[BB_EP + i], 4);
     }
     mbar_init(&bars[BB_R1], 4);
     mbar_init(&bars[BB_R2], 4);
@@ -376,12 +393,16 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const bool key_valid = r < T.nk;
       const size_t bh_k = (size_t)T.bat * p.h_kv + hkv;
       const int kblk = (T.k0 + r) / 32;
-      const float fk = p.fac_k[bh_k * (p.s_k / 32) + kblk] * p.scale_log2;
-      const float fv8 = p.fac_v[bh_k * (p.s_k / 32) + kblk] * 0.00390625f;   // f_V 2^-8
-      uint32_t ek_word = 0;                            // UE8M0 bytes of the tile's four key blocks
+      // token-local: this key's own factors; otherwise its 32-key block's
+      const float fk_true = TL ? p.fac_k[bh_k * p.s_k + T.k0 + r] : p.fac_k[bh_k * (p.s_k / 32) + kblk];
+      const float fk = fk_true * p.scale_log2;
+      const float fv8 = (TL ? p.fac_v[bh_k * p.s_k + T.k0 + r] : p.fac_v[bh_k * (p.s_k / 32) + kblk]) * 0.00390625f;   // f_V 2^-8
+      uint32_t ek_word = TL ? 0x7F7F7F7Fu : 0u;        // UE8M0 bytes of the tile's four key blocks (unit when token-local)
+      if (!TL) {
 #pragma unroll
-      for (int kb = 0; kb < 4; ++kb)
-        ek_word |= ((__float_as_uint(p.fac_k[bh_k * (p.s_k / 32) + T.k0 / 32 + kb]) >> 23) & 0xFF) << (8 * kb);
+        for (int kb = 0; kb < 4; ++kb)
+          ek_word |= ((__float_as_uint(p.fac_k[bh_k * (p.s_k / 32) + T.k0 / 32 + kb]) >> 23) & 0xFF) << (8 * kb);
+      }
       const uint32_t ds_row = smem_u32(sDS) + x * 8192 + r * 64;
       const int vis_from = p.causal ? (krel - T.off) : 0;                  // queries >= vis_from see this key
       bool ok = true;
@@ -390,11 +411,15 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
         const size_t bh_q = (size_t)T.bat * p.h + head;
         const int qb0 = (T.q0 + m * 128) / 32 + 2 * x;                     // first of the half's two 32-query blocks
-        const float fq0 = p.fac_q[bh_q * (p.s_q / 32) + qb0], fq1 = p.fac_q[bh_q * (p.s_q / 32) + qb0 + 1];
-        const float fd0 = p.fac_do[bh_q * (p.s_q / 32) + qb0], fd1 = p.fac_do[bh_q * (p.s_q / 32) + qb0 + 1];
+        const float fq0 = TL ? 1.f : p.fac_q[bh_q * (p.s_q / 32) + qb0], fq1 = TL ? 1.f : p.fac_q[bh_q * (p.s_q / 32) + qb0 + 1];
+        const float fd0 = TL ? 1.f : p.fac_do[bh_q * (p.s_q / 32) + qb0], fd1 = TL ? 1.f : p.fac_do[bh_q * (p.s_q / 32) + qb0 + 1];
+        // token-local: the 64 per-query factors of the half (same addresses for every thread: broadcast loads)
+        const float4* fq_vec = reinterpret_cast<const float4*>(p.fac_q + (TL ? bh_q * p.s_q + T.q0 + m * 128 + 64 * x : 0));
+        const float4* fdo_vec = reinterpret_cast<const float4*>(p.fac_do + (TL ? bh_q * p.s_q + T.q0 + m * 128 + 64 * x : 0));
         const float bsc = p.dq_scale[(size_t)T.bat * (p.s_q / 128) + T.q0 / 128 + m];
         // FP4: the block scales of S were applied by the tensor core; only the softmax scale remains
         const float c[2] = {FP4 ? p.scale_log2 : fk * fq0, FP4 ? p.scale_log2 : fk * fq1}, b8[2] = {fv8 * fd0, fv8 * fd1};
+        // token-local: fq0 = fq1 = fd0 = fd1 = 1, i.e. unit scale bytes for the Q and dO operands
         const uint32_t eq2 = ((__float_as_uint(fq0) >> 23) & 0xFF) | (((__float_as_uint(fq1) >> 23) & 0xFF) << 8);
         const uint32_t edo2 = ((__float_as_uint(fd0) >> 23) & 0xFF) | (((__float_as_uint(fd1) >> 23) & 0xFF) << 8);
         // K's exponent bytes with the power-of-two f16 pre-scale of this query tile folded in (A scale of dQ^T)
@@ -419,10 +444,15 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int j4 = 0; j4 < 16; ++j4) {
           const float4 l4 = lds128(v_lse + 16 * j4);
           const float cc = c[j4 >> 3];
-          pf[4 * j4 + 0] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 0]), cc, -l4.x));
-          pf[4 * j4 + 1] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 1]), cc, -l4.y));
-          pf[4 * j4 + 2] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 2]), cc, -l4.z));
-          pf[4 * j4 + 3] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 3]), cc, -l4.w));
+          float4 c4 = make_float4(cc, cc, cc, cc);
+          if (TL) {
+            const float4 f4 = __ldg(fq_vec + j4);
+            c4 = make_float4(fk * f4.x, fk * f4.y, fk * f4.z, fk * f4.w);
+          }
+          pf[4 * j4 + 0] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 0]), c4.x, -l4.x));
+          pf[4 * j4 + 1] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 1]), c4.y, -l4.y));
+          pf[4 * j4 + 2] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 2]), c4.z, -l4.z));
+          pf[4 * j4 + 3] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 3]), c4.w, -l4.w));
         }
         if (!full) {      // diagonal / tail tiles only
 #pragma unroll
@@ -431,7 +461,36 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             pf[j] = (key_valid && qi >= vis_from && qi < T.sq) ? pf[j] : 0.f;
           }
         }
-        {
+        if (TL) {
+          // block-scaled P-hat carrying f_dO(query): one exponent per (this key row, 32 queries)
+          uint32_t pw[16], ep[2];
+#pragma unroll
+          for (int qh = 0; qh < 2; ++qh) {
+            float t[32];
+            float am = 0.f;
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              const float4 f4 = __ldg(fdo_vec + qh * 8 + j4);
+              const int j = qh * 32 + 4 * j4;
+              t[4 * j4 + 0] = pf[j + 0] * f4.x; t[4 * j4 + 1] = pf[j + 1] * f4.y;
+              t[4 * j4 + 2] = pf[j + 2] * f4.z; t[4 * j4 + 3] = pf[j + 3] * f4.w;
+              am = fmaxf(am, fmaxf(fmaxf(t[4 * j4], t[4 * j4 + 1]), fmaxf(t[4 * j4 + 2], t[4 * j4 + 3])));
+            }
+            ep[qh] = exp448(__float_as_uint(am));
+            const float inv = pow2_inv(ep[qh]);
+#pragma unroll
+            for (int w = 0; w < 8; ++w)
+              pw[qh * 8 + w] = cvt_e4m3x4(t[4 * w] * inv, t[4 * w + 1] * inv, t[4 * w + 2] * inv, t[4 * w + 3] * inv);
+          }
+          FL_TMEM_ST_16(t_sx + TO_P, pw);
+          // every lane quadrant holds the whole A scale tile: column = key block, lane = row of the block
+          sEP[x][r] = ep[0] | (ep[1] << 8);
+          mbar_arrive_warp(&bars[BB_EP + x]);
+          if (!(ok = mbar_wait(&bars[BB_EP + x], it & 1, p.ctl, abortp, 37))) break;
+          uint32_t sf[8] = {sEP[x][lane], sEP[x][32 + lane], sEP[x][64 + lane], sEP[x][96 + lane],
+                            0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu};
+          FL_TMEM_ST_8(t_sx + TO_SFA_P, sf);
+        } else {
           uint32_t pw[16];
 #pragma unroll
           for (int w = 0; w < 16; ++w) pw[w] = cvt_e4m3x4(pf[4 * w], pf[4 * w + 1], pf[4 * w + 2], pf[4 * w + 3]);
@@ -460,30 +519,63 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int j4 = 0; j4 < 8; ++j4) {
             const float4 d4 = lds128(v_dpp + 16 * (qh * 8 + j4));
             const int j = qh * 32 + 4 * j4;
-            pf[j + 0] *= fmaf(__uint_as_float(pv[j + 0]), b8[qh], d4.x);
-            pf[j + 1] *= fmaf(__uint_as_float(pv[j + 1]), b8[qh], d4.y);
-            pf[j + 2] *= fmaf(__uint_as_float(pv[j + 2]), b8[qh], d4.z);
-            pf[j + 3] *= fmaf(__uint_as_float(pv[j + 3]), b8[qh], d4.w);
-            am = fmaxf(am, fmaxf(fmaxf(fabsf(pf[j]), fabsf(pf[j + 1])), fmaxf(fabsf(pf[j + 2]), fabsf(pf[j + 3]))));
+            float4 b4 = make_float4(b8[qh], b8[qh], b8[qh], b8[qh]);
+            float4 q4 = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (TL) {
+              const float4 f4 = __ldg(fdo_vec + qh * 8 + j4);
+              b4 = make_float4(fv8 * f4.x, fv8 * f4.y, fv8 * f4.z, fv8 * f4.w);
+              q4 = __ldg(fq_vec + qh * 8 + j4);
+            }
+            pf[j + 0] *= fmaf(__uint_as_float(pv[j + 0]), b4.x, d4.x);
+            pf[j + 1] *= fmaf(__uint_as_float(pv[j + 1]), b4.y, d4.y);
+            pf[j + 2] *= fmaf(__uint_as_float(pv[j + 2]), b4.z, d4.z);
+            pf[j + 3] *= fmaf(__uint_as_float(pv[j + 3]), b4.w, d4.w);
+            // the dK side carries f_Q(query) when the operands are token-local
+            am = fmaxf(am, fmaxf(fmaxf(fabsf(pf[j] * q4.x), fabsf(pf[j + 1] * q4.y)),
+                                 fmaxf(fabsf(pf[j + 2] * q4.z), fabsf(pf[j + 3] * q4.w))));
           }
           const uint32_t wm = warp_max_u32(__float_as_uint(am));          // non-negative floats order as integers
-          int e = (int)((wm + 0x00200000u) >> 23) - 8;                     // 448 * 2^(e-127) >= amax
-          ebyte[qh] = (uint32_t)min(max(e, 1), 254);
+          ebyte[qh] = exp448(wm);                                          // 448 * 2^(e-127) >= amax
         }
         if (lane == 0) sE[x][wq] = ebyte[0] | (ebyte[1] << 8);
-        mbar_arrive_warp(&bars[BB_EX + x]);
+        if (!RL) mbar_arrive_warp(&bars[BB_EX + x]);
         uint32_t dsw[16];
 #pragma unroll
         for (int qh = 0; qh < 2; ++qh) {
-          const float inv = __uint_as_float((uint32_t)(254 - (int)ebyte[qh]) << 23);   // 2^(127 - e)
+          const float inv = pow2_inv(ebyte[qh]);                           // 2^(127 - e)
 #pragma unroll
           for (int w = 0; w < 8; ++w) {
             const int j0 = qh * 32 + 4 * w;
-            dsw[qh * 8 + w] = cvt_e4m3x4(pf[j0] * inv, pf[j0 + 1] * inv, pf[j0 + 2] * inv, pf[j0 + 3] * inv);
+            float4 q4 = make_float4(inv, inv, inv, inv);
+            if (TL) {
+              const float4 f4 = __ldg(fq_vec + qh * 8 + w);
+              q4 = make_float4(f4.x * inv, f4.y * inv, f4.z * inv, f4.w * inv);   // powers of two: exact, in range
+            }
+            dsw[qh * 8 + w] = cvt_e4m3x4(pf[j0] * q4.x, pf[j0 + 1] * q4.y, pf[j0 + 2] * q4.z, pf[j0 + 3] * q4.w);
           }
         }
         FL_TMEM_ST_16(t_sx + TO_DS, dsw);
-        // the same codes as the MN-major B operand of dQ^T: row = key, 64 bytes = 4 chunks of 16 B, 64 B swizzle
+        if (RL) {
+          // the dQ side's own codes: one exponent per (query, this warp's 32 keys); token-local: they carry f_K(key)
+          uint32_t mine[2] = {1u, 1u};
+#pragma unroll
+          for (int w = 0; w < 16; ++w) {
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = 4 * w + e;
+              const float a = TL ? pf[j] * fk_true : pf[j];
+              const uint32_t eq = exp448(warp_max_u32(__float_as_uint(fabsf(a))));
+              if (lane == (j & 31)) mine[j >> 5] = eq;
+              v[e] = a * pow2_inv(eq);
+            }
+            dsw[w] = cvt_e4m3x4(v[0], v[1], v[2], v[3]);
+          }
+          sEQ[x][lane][wq] = (uint8_t)mine[0];
+          sEQ[x][32 + lane][wq] = (uint8_t)mine[1];
+          mbar_arrive_warp(&bars[BB_EX + x]);
+        }
+        // the dQ^T product's MN-major B operand: row = key, 64 bytes = 4 chunks of 16 B, 64 B swizzle
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4)
           sts128(ds_row + ((q4 ^ ((r >> 1) & 3)) << 4), dsw[4 * q4], dsw[4 * q4 + 1], dsw[4 * q4 + 2], dsw[4 * q4 + 3]);
@@ -499,8 +591,13 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           sf[0] = e0; sf[1] = e1; sf[2] = e2; sf[3] = e3;
           sf[4] = sf[5] = sf[6] = sf[7] = eq2;
           sf[8] = sf[9] = sf[10] = sf[11] = ekb_word;
-          sf[12] = (e0 & 0xFF) | ((e1 & 0xFF) << 8) | ((e2 & 0xFF) << 16) | ((e3 & 0xFF) << 24);
-          sf[13] = ((e0 >> 8) & 0xFF) | (((e1 >> 8) & 0xFF) << 8) | (((e2 >> 8) & 0xFF) << 16) | (((e3 >> 8) & 0xFF) << 24);
+          if (RL) {   // B[query lane, column = query block] bytes = that query's exponents over the four key blocks
+            sf[12] = *reinterpret_cast<const uint32_t*>(&sEQ[x][lane][0]);
+            sf[13] = *reinterpret_cast<const uint32_t*>(&sEQ[x][32 + lane][0]);
+          } else {
+            sf[12] = (e0 & 0xFF) | ((e1 & 0xFF) << 8) | ((e2 & 0xFF) << 16) | ((e3 & 0xFF) << 24);
+            sf[13] = ((e0 >> 8) & 0xFF) | (((e1 >> 8) & 0xFF) << 8) | (((e2 >> 8) & 0xFF) << 16) | (((e3 >> 8) & 0xFF) << 24);
+          }
           sf[14] = sf[15] = 0x7F7F7F7Fu;
           FL_TMEM_ST_16(t_sx + TO_SFA_DK, sf);
         }
@@ -598,7 +695,8 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   if (a->mode != FL_MODE_FP8 && a->mode != FL_MODE_FP4) return FL_ERR_UNSUPPORTED;
   const bool fp4 = a->mode == FL_MODE_FP4;
   if (fp4 && (!a->q4 || !a->k4 || !a->sfq4 || !a->sfk4)) return FL_ERR_BAD_ARG;
-  if (a->flags & (FL_A_TOKEN_LOCAL | FL_A_DQ_ROWLOCAL)) return FL_ERR_UNSUPPORTED;
+  const bool tl = (a->flags & FL_A_TOKEN_LOCAL) != 0, rl = (a->flags & FL_A_DQ_ROWLOCAL) != 0;
+  if (tl && (!rl || fp4 || a->doc_start)) return FL_ERR_UNSUPPORTED;   // token-local needs the dQ side's own codes
   if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
   if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
   if (a->doc_start && (a->b != 1 || a->n_docs <= 0 || !a->doc_len || a->s_q != a->s_k)) return FL_ERR_BAD_ARG;
@@ -631,14 +729,14 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   const int ntile = a->doc_start ? (a->s_k / 128 + a->n_docs) : a->s_k / 128;
   dim3 grid(ntile, a->h_kv, a->doc_start ? 1 : a->b);
   const int smem = 6 * 128 * 128 + 2 * 8192 + 2 * 16384 + 2048 + 1024 + (fp4 ? 3 * 8192 + 3 * 1024 : 0);
-  if (fp4) {
-    if (cudaFuncSetAttribute(bwd_kernel_pipelined<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FL_ERR_CUDA;
-    bwd_kernel_pipelined<true><<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, p);
-  } else {
-    if (cudaFuncSetAttribute(bwd_kernel_pipelined<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FL_ERR_CUDA;
-    bwd_kernel_pipelined<false><<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, p);
-  }
+  auto launch = [&](auto kern) -> int {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
+    kern<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, p);
+    return FL_OK;
+  };
+  if (fp4) rc = rl ? launch(bwd_kernel_pipelined<true, 1>) : launch(bwd_kernel_pipelined<true, 0>);
+  else if (tl) rc = launch(bwd_kernel_pipelined<false, 2>);
+  else rc = rl ? launch(bwd_kernel_pipelined<false, 1>) : launch(bwd_kernel_pipelined<false, 0>);
+  if (rc) return rc;
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

@@ -6,6 +6,9 @@
 //                folded into the softmax scale (exact); P.V = kind::mxf8f6f4.block_scale with V's UE8M0 exponent per
 //                32 keys as the B scale and a constant-one A scale (row-frame P-hat = E4M3(2^(x - m + 4))).
 //   FL_MODE_FP4: S = NVFP4 x NVFP4 (kind::mxf4nvf4.block_scale.scale_vec::4X), same P.V.
+//   FL_A_TOKEN_LOCAL (the reference's "fold forward", flash_attn/cute/lowprec/_routes.py:749-786): every token of Q, K,
+//                V has its own power-of-two factor; f_Q f_K multiplies each score, log2 f_V(key) is added to the exponent
+//                argument of P-hat (so P.V runs with unit scales) and the row sum takes P / f_V(key) back out.
 //
 // CTA = 256 query rows (two 128-row stages) of one (batch | document, head); loop over 128-key tiles.
 //   warps 0-3   softmax stage 0 (thread r owns query row r: TMEM lane r)      warp 8  TMA producer
@@ -58,7 +61,7 @@ enum { B_Q = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + KV_STAGES, B_VFULL = B_KEMPTY 
        B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES, B_PFULL = B_SFULL + 2, B_PVDONE = B_PFULL + 2,
        B_SDRAIN = B_PVDONE + 2, B_COUNT = B_SDRAIN + 2 };
 
-template <int D, bool FP4>
+template <int D, bool FP4, bool TL>
 __global__ void __launch_bounds__(320, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
@@ -278,7 +281,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const int qrel = T.qrel + 128 * i + r;            // row inside the document
       const bool row_valid = (128 * i + r) < T.nq;
       const size_t bh_q = (size_t)T.bat * p.h + head, bh_k = (size_t)T.bat * p.h_kv + hkv;
-      const float fq = !row_valid ? 0.f : FP4 ? p.scale_log2 : p.fac_q[bh_q * (p.s_q / 32) + qrow / 32] * p.scale_log2;
+      const float fq = !row_valid ? 0.f
+                       : FP4     ? p.scale_log2
+                       : TL      ? p.fac_q[bh_q * p.s_q + qrow] * p.scale_log2
+                                 : p.fac_q[bh_q * (p.s_q / 32) + qrow / 32] * p.scale_log2;
       const float* fk_row = p.fac_k + bh_k * (p.s_k / 32) + T.k0 / 32;
       const float* fv_row = p.fac_v + bh_k * (p.s_k / 32) + T.k0 / 32;
       const int col_limit = p.causal ? min(qrel + T.off, T.sk - 1) : T.sk - 1;   // last visible key of this row
@@ -290,8 +296,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         uint32_t sfv = 0;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
+          if (TL) continue;
           c[kb] = FP4 ? fq : fq * fk_row[j * 4 + kb];      // FP4: the block scales were applied by the tensor core
           sfv |= ((__float_as_uint(fv_row[j * 4 + kb]) >> 23) & 0xFF) << (8 * kb);
+        }
+        // token-local: the tile's 128 per-key factors (same addresses for every thread: broadcast loads)
+        const float4* fk4 = reinterpret_cast<const float4*>(p.fac_k + (TL ? bh_k * p.s_k + T.k0 + j * 128 : 0));
+        const float4* fv4 = reinterpret_cast<const float4*>(p.fac_v + (TL ? bh_k * p.s_k + T.k0 + j * 128 : 0));
+        if (TL) {
+          sfv = 0x7F7F7F7Fu;
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) c[kb] = 1.f;
         }
         if (!(ok = mbar_wait(&bars[B_SFULL + i], j & 1, p.ctl, abortp, 30 + i))) break;
         tc_fence_after();
@@ -306,6 +321,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         float s[128];
 #pragma unroll
         for (int e = 0; e < 128; ++e) s[e] = __uint_as_float(su[e]);
+        if (TL) {   // y = s f_Q f_K(key) scale + log2 f_V(key)
+#pragma unroll
+          for (int e4 = 0; e4 < 32; ++e4) {
+            const float4 k4 = __ldg(fk4 + e4), v4 = __ldg(fv4 + e4);
+            s[4 * e4 + 0] = fmaf(s[4 * e4 + 0], fq * k4.x, (float)((int)(__float_as_uint(v4.x) >> 23) - 127));
+            s[4 * e4 + 1] = fmaf(s[4 * e4 + 1], fq * k4.y, (float)((int)(__float_as_uint(v4.y) >> 23) - 127));
+            s[4 * e4 + 2] = fmaf(s[4 * e4 + 2], fq * k4.z, (float)((int)(__float_as_uint(v4.z) >> 23) - 127));
+            s[4 * e4 + 3] = fmaf(s[4 * e4 + 3], fq * k4.w, (float)((int)(__float_as_uint(v4.w) >> 23) - 127));
+          }
+        }
         const bool need_mask = (j * 128 + 127) > col_limit;    // only on diagonal / tail tiles
         if (need_mask) {   // scale first, then mask: the factor product may underflow to zero and 0 * inf is NaN
 #pragma unroll
@@ -350,7 +375,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           const float cw = c[w >> 3];
           float p0 = ex2(fmaf(s[4 * w], cw, -mb)), p1 = ex2(fmaf(s[4 * w + 1], cw, -mb));
           float p2 = ex2(fmaf(s[4 * w + 2], cw, -mb)), p3 = ex2(fmaf(s[4 * w + 3], cw, -mb));
-          psum += (p0 + p1) + (p2 + p3);
+          if (TL) {     // the row sum is that of the probabilities: take f_V(key) back out
+            const float4 v4 = __ldg(fv4 + w);
+            psum += (p0 * __uint_as_float((254u << 23) - (__float_as_uint(v4.x) & 0x7F800000u)) +
+                     p1 * __uint_as_float((254u << 23) - (__float_as_uint(v4.y) & 0x7F800000u))) +
+                    (p2 * __uint_as_float((254u << 23) - (__float_as_uint(v4.z) & 0x7F800000u)) +
+                     p3 * __uint_as_float((254u << 23) - (__float_as_uint(v4.w) & 0x7F800000u)));
+          } else {
+            psum += (p0 + p1) + (p2 + p3);
+          }
           pw[w] = cvt_e4m3x4(p0, p1, p2, p3);
         }
         l_sum = fmaf(l_sum, alpha, psum);
@@ -424,7 +457,8 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   const bool fp4 = a->mode == FL_MODE_FP4;
   if (fp4 && a->d != 128) return FL_ERR_UNSUPPORTED;
   if (fp4 && (!a->q4 || !a->k4 || !a->sfq4 || !a->sfk4)) return FL_ERR_BAD_ARG;
-  if (a->flags & FL_A_TOKEN_LOCAL) return FL_ERR_UNSUPPORTED;
+  const bool tl = (a->flags & FL_A_TOKEN_LOCAL) != 0;
+  if (tl && (a->doc_start || a->mode != FL_MODE_FP8)) return FL_ERR_UNSUPPORTED;   // token-local: batched 8-bit route
   if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
   if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
   if (a->doc_start && (a->b != 1 || a->n_docs <= 0 || !a->doc_len || a->s_q != a->s_k)) return FL_ERR_BAD_ARG;
@@ -448,18 +482,14 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   dim3 grid(nblk, a->h, a->doc_start ? 1 : a->b);
   const int smem = (2 + 2 * KV_STAGES) * 128 * a->d + 1024 + (fp4 ? (2 + KV_STAGES) * 1024 : 0);
   cudaStream_t st = (cudaStream_t)stream;
-  if (fp4) {
-    if (cudaFuncSetAttribute(fwd_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FL_ERR_CUDA;
-    fwd_kernel<128, true><<<grid, 320, smem, st>>>(mq, mk, mv, p);
-  } else if (a->d == 128) {
-    if (cudaFuncSetAttribute(fwd_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FL_ERR_CUDA;
-    fwd_kernel<128, false><<<grid, 320, smem, st>>>(mq, mk, mv, p);
-  } else {
-    if (cudaFuncSetAttribute(fwd_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FL_ERR_CUDA;
-    fwd_kernel<64, false><<<grid, 320, smem, st>>>(mq, mk, mv, p);
-  }
+  auto launch = [&](auto kern) -> int {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
+    kern<<<grid, 320, smem, st>>>(mq, mk, mv, p);
+    return FL_OK;
+  };
+  if (fp4) rc = launch(fwd_kernel<128, true, false>);
+  else if (a->d == 128) rc = tl ? launch(fwd_kernel<128, false, true>) : launch(fwd_kernel<128, false, false>);
+  else rc = tl ? launch(fwd_kernel<64, false, true>) : launch(fwd_kernel<64, false, false>);
+  if (rc) return rc;
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

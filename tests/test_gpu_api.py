@@ -160,3 +160,31 @@ def test_fp4_packed_documents():
         ro, _, rdq, rdk, rdv = A.attention_fp32(q[None, sl].float(), k[None, sl].float(), v[None, sl].float(),
                                                 g[None, sl].float(), True)
         _check((o[sl], dq[sl], dk[sl], dv[sl]), (ro[0], rdq[0], rdk[0], rdv[0]), tol=0.17)   # 4-bit S operands vs fp32
+
+
+def test_fp8_token_local_rowlocal_causal_prescale_gqa():
+    """The GQA configuration's options: token-local operand scales, dQ-side row-local dS-hat, causal dQ pre-scale, with
+    1 % of the Q / K channels scaled x20."""
+    from flamia_blackwell_attention_b200 import flash_attn_fp8, FP8AttnOptions
+    import flamia_blackwell_attention_b200.interface_bwd_fp4 as I
+    q, k, v, g = attention_inputs(1, 1024, 8, 2, 128, seed=17)
+    ch = torch.randperm(128, generator=torch.Generator().manual_seed(5))[:1]
+    q, k = q.clone(), k.clone()
+    q[..., ch] *= 20
+    k[..., ch] *= 20
+    opts = FP8AttnOptions(operand_scaling="token_local", ds_dq_rowlocal="all")
+    old = I.DQ_CAUSAL_PRESCALE
+    I.DQ_CAUSAL_PRESCALE = True
+    try:
+        o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True, options=opts)
+    finally:
+        I.DQ_CAUSAL_PRESCALE = old
+    # bound: the default route's own error on the same inputs (outlier channels make near one-hot rows, where the E4M3
+    # roundings of P-hat / dS-hat weigh more whatever the operand scaling)
+    ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=True, token_local=True)
+    base = _step(flash_attn_fp8, q, k, v, g, causal=True)
+    bo, _, bdq, bdk, bdv = A.qdq_attention(q, k, v, g, causal=True, rotate_qk=True)
+    for n, a, r, ba, br in zip(("o", "dq", "dk", "dv"), (o, dq, dk, dv), (ro, rdq, rdk, rdv), base[:4], (bo, bdq, bdk, bdv)):
+        e_new, e_base = A.accuracy(a, r)["rel_l2"], A.accuracy(ba, br)["rel_l2"]
+        print("token-local", n, e_new, "default route", e_base)
+        assert e_new <= 1.15 * e_base + 1e-3, (n, e_new, e_base)

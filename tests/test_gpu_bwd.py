@@ -19,24 +19,27 @@ REF = {"dq": math.sqrt(2 * (1 - 0.9979)), "dk": math.sqrt(2 * (1 - 0.9979)), "dv
 REF4 = {"dq": math.sqrt(2 * (1 - 0.9906)), "dk": math.sqrt(2 * (1 - 0.9906)), "dv": math.sqrt(2 * (1 - 0.9919))}
 
 
-def run_step(q, k, v, g, causal, rotate=False, fp4=False):
+def run_step(q, k, v, g, causal, rotate=False, fp4=False, token_local=False, rowlocal=False):
     from flamia_blackwell_attention_b200 import kernels as K, _lib as L
     b, sq, h, d = q.shape
     sc = 1.0 / math.sqrt(d)
     mode = L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8
-    kw = dict(apply_hadamard_rotation=rotate)
+    tl = token_local
+    kw = dict(apply_hadamard_rotation=rotate, token_local_exponents=tl)
     if fp4:     # the mixed route: NVFP4 copies feed S (rotated when rotation is on), the E4M3 codes stay unrotated
         kw.update(also_make_nvfp4_copy=True, hadamard_rotation_scope="nvfp4_copy")
     qq = K.quantize_fp8_blocks(q.cuda(), **kw)
     kq = K.quantize_fp8_blocks(k.cuda(), output_tile_stats=True, **kw)
-    vq = K.quantize_fp8_blocks(v.cuda(), output_tile_stats=True)
-    out, lse, st = K.attn_fwd(qq, kq, vq, causal=causal, softmax_scale=sc, mode=mode)
+    vq = K.quantize_fp8_blocks(v.cuda(), output_tile_stats=True, token_local_exponents=tl)
+    out, lse, st = K.attn_fwd(qq, kq, vq, causal=causal, softmax_scale=sc, mode=mode, token_local=tl)
     acc = torch.empty(b, h, sq, d, dtype=torch.float16, device="cuda")
     gq = K.quantize_fp8_blocks(g.cuda(), compute_d_with_output=out, shifted_log2_lse_from=lse, log2_lse_shift=8.0,
-                               d_multiplier=-2.0 ** -8, zero_accumulator=acc, output_tile_stats=True)
+                               d_multiplier=-2.0 ** -8, zero_accumulator=acc, output_tile_stats=True,
+                               token_local_exponents=tl)
     ks, ps = K.dq_prescale(gq["tile_stats"], vq["tile_stats"], kq["tile_stats"])
     dk, dv, st = K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks,
-                            causal=causal, softmax_scale=sc, had_dk=rotate and not fp4, status=st, mode=mode)
+                            causal=causal, softmax_scale=sc, had_dk=rotate and not fp4, status=st, mode=mode,
+                            token_local=tl, dq_rowlocal=rowlocal or tl)
     dq = K.dq_post(acc, ps, sc, b=b, s=sq, h=h, d=d, unrotate=rotate and not fp4)
     torch.cuda.synchronize()
     assert K.read_status(st) == 0
@@ -127,3 +130,56 @@ def test_backward_fp4_at_the_reference_cell():
         acc = A.accuracy(got, r32)
         print("A1 slice (mixed route)", name, acc)
         assert acc["rel_l2"] <= 1.05 * REF4[name], (name, acc)
+
+
+def _outlier_inputs(b, s, h, hk, d, seed):
+    """N(0,1) with a seeded 1 % of the head-dim channels of Q and K scaled x20 (the outlier workload of the GQA config)."""
+    q, k, v, g = attention_inputs(b, s, h, hk, d, seed=seed)
+    gen = torch.Generator().manual_seed(seed + 1000)
+    ch = torch.randperm(d, generator=gen)[:max(1, d // 100)]
+    q, k = q.clone(), k.clone()
+    q[..., ch] *= 20
+    k[..., ch] *= 20
+    return q, k, v, g
+
+
+ROWLOCAL_CASES = [
+    # b, s_q, s_k, h, h_kv, causal, token_local, fp4, outliers
+    (1, 128, 128, 1, 1, False, False, False, False),
+    (1, 384, 384, 4, 2, True, False, False, False),
+    (1, 256, 256, 2, 2, True, False, True, False),       # the mixed route with the dQ side's own codes
+    (1, 128, 128, 1, 1, False, True, False, False),
+    (2, 384, 384, 4, 2, True, True, False, False),
+    (1, 256, 640, 4, 1, True, True, False, False),
+    (1, 512, 512, 2, 2, False, True, False, False),
+    (1, 512, 512, 4, 1, True, False, False, True),
+    (1, 512, 512, 4, 1, True, True, False, True),
+]
+
+
+@pytest.mark.parametrize("b,sq,sk,h,hk,causal,tl,fp4,outliers", ROWLOCAL_CASES)
+def test_backward_rowlocal_and_token_local_vs_oracle(b, sq, sk, h, hk, causal, tl, fp4, outliers):
+    """ds_dq_rowlocal='all' (dQ side with its own codes) alone and with token-local operands (per-token factors).
+    On N(0,1) inputs: the usual bounds against the oracle's emulation of the same operand scaling. With outlier channels
+    (scores of several hundred, near one-hot rows) the E4M3 roundings of P-hat and dS-hat weigh more whatever the scaling,
+    so the bound there is the default route's own error on the same inputs (x 1.15)."""
+    s = max(sq, sk)
+    mk = _outlier_inputs if outliers else (lambda *a, seed: attention_inputs(*a, seed=seed))
+    q, k, v, g = mk(b, s, h, hk, 128, seed=6)
+    q, g, k, v = q[:, :sq], g[:, :sq], k[:, :sk], v[:, :sk]
+    out, dq, dk, dv = run_step(q, k, v, g, causal, fp4=fp4, token_local=tl, rowlocal=True)
+    o_r, _, dq_r, dk_r, dv_r = A.qdq_attention(q, k, v, g, causal=causal, token_local=tl, fp4_qk=fp4)
+    got = dict(o=out, dq=dq, dk=dk, dv=dv)
+    ref = dict(o=o_r, dq=dq_r, dk=dk_r, dv=dv_r)
+    if not outliers:
+        for name, tol in (("o", 3.2e-2), ("dq", 5e-2), ("dk", 5e-2), ("dv", 5e-2)):
+            acc = A.accuracy(got[name], ref[name])
+            assert acc["rel_l2"] < tol, (name, acc)
+    else:
+        base = dict(zip(("o", "dq", "dk", "dv"), run_step(q, k, v, g, causal)))
+        b_r = A.qdq_attention(q, k, v, g, causal=causal)
+        base_ref = dict(o=b_r[0], dq=b_r[2], dk=b_r[3], dv=b_r[4])
+        for name in ("o", "dq", "dk", "dv"):
+            e_new = A.accuracy(got[name], ref[name])["rel_l2"]
+            e_base = A.accuracy(base[name], base_ref[name])["rel_l2"]
+            assert e_new <= 1.15 * e_base + 1e-3, (name, e_new, e_base)
