@@ -167,11 +167,7 @@ def test_fp8_token_local_rowlocal_causal_prescale_gqa():
     1 % of the Q / K channels scaled x20."""
     from flamia_blackwell_attention_b200 import flash_attn_fp8, FP8AttnOptions
     import flamia_blackwell_attention_b200.interface_bwd_fp4 as I
-    q, k, v, g = attention_inputs(1, 1024, 8, 2, 128, seed=17)
-    ch = torch.randperm(128, generator=torch.Generator().manual_seed(5))[:1]
-    q, k = q.clone(), k.clone()
-    q[..., ch] *= 20
-    k[..., ch] *= 20
+    q, k, v, g = attention_inputs(1, 1024, 8, 2, 128, seed=17, outlier_channels=True)
     opts = FP8AttnOptions(operand_scaling="token_local", ds_dq_rowlocal="all")
     old = I.DQ_CAUSAL_PRESCALE
     I.DQ_CAUSAL_PRESCALE = True

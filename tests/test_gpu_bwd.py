@@ -133,14 +133,8 @@ def test_backward_fp4_at_the_reference_cell():
 
 
 def _outlier_inputs(b, s, h, hk, d, seed):
-    """N(0,1) with a seeded 1 % of the head-dim channels of Q and K scaled x20 (the outlier workload of the GQA config)."""
-    q, k, v, g = attention_inputs(b, s, h, hk, d, seed=seed)
-    gen = torch.Generator().manual_seed(seed + 1000)
-    ch = torch.randperm(d, generator=gen)[:max(1, d // 100)]
-    q, k = q.clone(), k.clone()
-    q[..., ch] *= 20
-    k[..., ch] *= 20
-    return q, k, v, g
+    """N(0,1) with a seeded 1 % of the (head, channel) pairs of Q and of K scaled x20 (the GQA configuration's workload)."""
+    return attention_inputs(b, s, h, hk, d, seed=seed, outlier_channels=True)
 
 
 ROWLOCAL_CASES = [

@@ -55,13 +55,11 @@ def test_headline_cell_sharding_invariance(route, causal):
 
 
 def test_gqa_token_local_configuration_full_size():
-    """b2 s8192 h32 h_kv8 d128 causal, token-local scales, row-local dQ side, causal dQ pre-scale, 1 % outlier channels."""
+    """b2 s8192 h32 h_kv8 d128 causal, token-local scales, row-local dQ side, causal dQ pre-scale, 1 % of the
+    (head, channel) pairs of Q and K scaled x20 (configuration 4)."""
     import flamia_blackwell_attention_b200 as F
     import flamia_blackwell_attention_b200.interface_bwd_fp4 as I
-    q, k, v, g = (t.cuda() for t in attention_inputs(2, 8192, 32, 8, 128, seed=3))
-    ch = torch.randperm(128, generator=torch.Generator().manual_seed(7))[:1].cuda()
-    q[..., ch] *= 20
-    k[..., ch] *= 20
+    q, k, v, g = (t.cuda() for t in attention_inputs(2, 8192, 32, 8, 128, seed=0, outlier_channels=True))
     opts = F.FP8AttnOptions(operand_scaling="token_local", ds_dq_rowlocal="all")
     old = I.DQ_CAUSAL_PRESCALE
     I.DQ_CAUSAL_PRESCALE = True
