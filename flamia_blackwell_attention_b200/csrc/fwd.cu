@@ -13,6 +13,8 @@
 // CTA = 256 query rows (two 128-row stages) of one (batch | document, head); loop over 128-key tiles.
 //   warps 0-3   softmax stage 0 (thread r owns query row r: TMEM lane r)      warp 8  TMA producer
 //   warps 4-7   softmax stage 1                                               warp 9  UMMA issuer
+//   warps 10-11 idle: they complete the third warpgroup, which hands its registers to the softmax warpgroups
+//   (setmaxnreg 216 / 216 / 72 of a 168-register launch: a softmax thread keeps 128 scores and 32 packed words live)
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P-hat overlays columns [0,32) of its S, the
 // P.V scale factors columns [32,40).
 // FL_MODE_FP4: all 512 columns are taken, so the 16 scale columns of an S product (Q and K atoms, tcgen05.cp from shared
@@ -61,8 +63,27 @@ enum { B_Q = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + KV_STAGES, B_VFULL = B_KEMPTY 
        B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES, B_PFULL = B_SFULL + 2, B_PVDONE = B_PFULL + 2,
        B_SDRAIN = B_PVDONE + 2, B_COUNT = B_SDRAIN + 2 };
 
+template <int N>
+__device__ __forceinline__ void fwd_reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void fwd_reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// Timeline tracing of one CTA (development aid, compiled out unless FL_TRACE is defined): clock64 stamps per role, key
+// tile and event into a caller-provided buffer of [8 roles][256 tiles][8 events] int64.
+#ifdef FL_TRACE
+__device__ long long* g_trace_fwd = nullptr;
+#define FTRACE_INIT() long long* const trace_p = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? g_trace_fwd : nullptr
+#define FTRACE(role, step, ev)                                                                                    \
+  do {                                                                                                            \
+    if (trace_p && (step) < 256) trace_p[(((role) * 256) + (step)) * 8 + (ev)] = clock64();                       \
+  } while (0)
+#else
+#define FTRACE_INIT()
+#define FTRACE(role, step, ev)
+#endif
+
 template <int D, bool FP4, bool TL>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   constexpr int TILE_BYTES = 128 * D;
@@ -82,6 +103,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.y;
+  FTRACE_INIT();
   const int hkv = head / (p.h / p.h_kv);
 
   if (tid == 0) {
@@ -149,6 +171,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const bool early_out = (T.nq <= 0) || (*p.ctl.status != 0);
 
   if (!early_out) {
+    if (warp >= 8) fwd_reg_dealloc<72>();
     if (warp == 8) {
       // =================================================================== TMA producer
       if (lane == 0) {
@@ -240,6 +263,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           const int st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
           const int stn = (j + 1) % KV_STAGES, phn = ((j + 1) / KV_STAGES) & 1;
           if (!(ok = mbar_wait(&bars[B_VFULL + st], ph, p.ctl, abortp, 22))) break;
+          if (lane == 0) FTRACE(0, j, 0);
           bool k_next_ready = false;
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
@@ -247,8 +271,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             if (j >= n_i) continue;
             if (!(ok = mbar_wait(&bars[B_PFULL + i], j & 1, p.ctl, abortp, 23 + i))) break;
             tc_fence_after();
+            if (lane == 0) FTRACE(0, j, 1 + 3 * i);
             if (elect_one()) { issue_pv(i, st, j > 0); tc_commit(&bars[B_PVDONE + i]); }
             __syncwarp();
+            if (lane == 0) FTRACE(0, j, 2 + 3 * i);
             if (j + 1 < n_i) {
               if (!k_next_ready) {
                 if (!(ok = mbar_wait(&bars[B_KFULL + stn], phn, p.ctl, abortp, 25))) break;
@@ -259,6 +285,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
               if (FP4) tc_fence_after();
               if (elect_one()) { issue_s(i, stn, j + 1); tc_commit(&bars[B_SFULL + i]); }
               __syncwarp();
+              if (lane == 0) FTRACE(0, j, 3 + 3 * i);
             }
           }
           if (!ok) break;
@@ -272,6 +299,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
     } else if (warp < 8) {
       // =================================================================== softmax + correction + epilogue
+      fwd_reg_alloc<216>();
       const int i = warp >> 2;                          // stage
       const int r = tid & 127;                          // row of the stage = TMEM lane
       const int n_i = n_st[i];
@@ -308,12 +336,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) c[kb] = 1.f;
         }
+        if (r == 0) FTRACE(1 + i, j, 0);
         if (!(ok = mbar_wait(&bars[B_SFULL + i], j & 1, p.ctl, abortp, 30 + i))) break;
+        if (r == 0) FTRACE(1 + i, j, 1);
         tc_fence_after();
         uint32_t su[128];
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) FL_TMEM_LD_32(t_s + 32 * cc, (su + 32 * cc));
         tc_wait_ld();
+        if (r == 0) FTRACE(1 + i, j, 2);
         if (FP4) {      // the scores are in registers: this S region may take the other stage's scale columns
           tc_fence_before();
           mbar_arrive_warp(&bars[B_SDRAIN + i]);
@@ -346,6 +377,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           for (int e = 1; e < 32; ++e) a = fmaxf(a, s[32 * kb + e]);
           mx = fmaxf(mx, a * c[kb]);
         }
+        if (r == 0) FTRACE(1 + i, j, 3);
         // lazy refresh of the running maximum
         float alpha = 1.f;
         const bool refresh = mx > m_used + RESCALE_THRESHOLD;
@@ -374,7 +406,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int w = 0; w < 32; ++w) {
           const float cw = c[w >> 3];
           float p0 = ex2(fmaf(s[4 * w], cw, -mb)), p1 = ex2(fmaf(s[4 * w + 1], cw, -mb));
-          float p2 = ex2(fmaf(s[4 * w + 2], cw, -mb)), p3 = ex2(fmaf(s[4 * w + 3], cw, -mb));
+          float p2, p3;
+          if (w & 1) {    // one pair in four on the FMA pipe: the transcendental unit is the binding one
+            ex2_poly2(fmaf(s[4 * w + 2], cw, -mb), fmaf(s[4 * w + 3], cw, -mb), p2, p3);
+          } else {
+            p2 = ex2(fmaf(s[4 * w + 2], cw, -mb));
+            p3 = ex2(fmaf(s[4 * w + 3], cw, -mb));
+          }
           if (TL) {     // the row sum is that of the probabilities: take f_V(key) back out
             const float4 v4 = __ldg(fv4 + w);
             psum += (p0 * __uint_as_float((254u << 23) - (__float_as_uint(v4.x) & 0x7F800000u)) +
@@ -387,14 +425,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           pw[w] = cvt_e4m3x4(p0, p1, p2, p3);
         }
         l_sum = fmaf(l_sum, alpha, psum);
+        if (r == 0) FTRACE(1 + i, j, 4);
         FL_TMEM_ST_32(t_s, pw);
         {
           uint32_t sf[8] = {0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, sfv, sfv, sfv, sfv};
           FL_TMEM_ST_8(t_s + 32, sf);
         }
         tc_wait_st();
+        if (r == 0) FTRACE(1 + i, j, 5);
         tc_fence_before();
         mbar_arrive_warp(&bars[B_PFULL + i]);
+        if (r == 0) FTRACE(1 + i, j, 6);
       }
       // ---- epilogue: O / l -> bf16, LSE
       if (ok && n_i > 0) ok = mbar_wait(&bars[B_PVDONE + i], (n_i - 1) & 1, p.ctl, abortp, 34 + i);
@@ -448,6 +489,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
 }  // namespace fl
 
+#ifdef FL_TRACE
+extern "C" int fl_debug_set_trace_fwd(void* buf) {
+  return cudaMemcpyToSymbol(fl::g_trace_fwd, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
+}
+#endif
+
 extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   using namespace fl;
   if (!a || !a->q_codes || !a->k_codes || !a->v_codes || !a->out || !a->status) return FL_ERR_BAD_ARG;
@@ -484,7 +531,7 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
-    kern<<<grid, 320, smem, st>>>(mq, mk, mv, p);
+    kern<<<grid, 384, smem, st>>>(mq, mk, mv, p);
     return FL_OK;
   };
   if (fp4) rc = launch(fwd_kernel<128, true, false>);

@@ -298,6 +298,44 @@ __device__ __forceinline__ float lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed pairs of floats in one 64-bit register (fma / add .f32x2: one issue slot for two elements).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^x for two arguments on the FMA pipe instead of the transcendental unit (which retires one warp instruction per
+// 8 clocks and is what bounds the softmax): n = round(x) through the 1.5 * 2^23 trick, f = x - n in [-0.5, 0.5],
+// 2^f by a degree-3 polynomial (weighted least-squares fit of the relative error on Chebyshev nodes: max 7.5e-5),
+// then n is added into the exponent field. Arguments below -126 give 2^-126.
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& r0, float& r1) {
+  constexpr float MAGIC = 12582912.f;
+  const uint64_t x = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t xr = add2(x, pack2(MAGIC, MAGIC));
+  const uint64_t n = add2(xr, pack2(-MAGIC, -MAGIC));
+  const uint64_t f = fma2(n, pack2(-1.f, -1.f), x);
+  uint64_t p = fma2(f, pack2(0.0551716685295105f, 0.0551716685295105f), pack2(0.2426111251115799f, 0.2426111251115799f));
+  p = fma2(p, f, pack2(0.6932609677314758f, 0.6932609677314758f));
+  p = fma2(p, f, pack2(0.9999280571937561f, 0.9999280571937561f));
+  float a0, a1, b0, b1;
+  unpack2(p, a0, a1);
+  unpack2(xr, b0, b1);
+  r0 = __uint_as_float(__float_as_uint(a0) + (__float_as_uint(b0) << 23));
+  r1 = __uint_as_float(__float_as_uint(a1) + (__float_as_uint(b1) << 23));
+}
 // two floats -> two E4M3 bytes (lo in bits 0-7), round to nearest even, saturating
 __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
   uint16_t r;
