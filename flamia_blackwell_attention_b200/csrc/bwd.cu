@@ -101,14 +101,6 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-#define FL_TMEM_ST_16(taddr, v)                                                                                        \
-  asm volatile(                                                                                                        \
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, " \
-      "%16};" ::"r"(taddr),                                                                                            \
-      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),     \
-      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])                                           \
-      : "memory")
-
 // 448 * 2^(e - 127) >= amax for the returned UE8M0 byte (bits = the non-negative float's pattern), clamped to [1, 254]
 __device__ __forceinline__ uint32_t exp448(uint32_t bits) {
   const int e = (int)((bits + 0x00200000u) >> 23) - 8;

@@ -28,6 +28,7 @@ namespace fl {
 
 static constexpr int KV_STAGES = 3;
 static constexpr float P_LOG2_OFFSET = 4.0f;      // P-hat = 2^(x - m + 4): keeps small probabilities out of E4M3 subnormals
+static constexpr long long STAGE_SKEW_CLOCKS = 1000;   // see the UMMA issuer's prologue
 static constexpr float RESCALE_THRESHOLD = 4.0f;  // the running maximum is refreshed only when it grew by more than this
 
 struct FwdParams {
@@ -254,6 +255,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           tc_fence_after();
           if (elect_one()) {
             if (n0 > 0) { issue_s(0, 0, 0); tc_commit(&bars[B_SFULL + 0]); }
+          }
+          __syncwarp();
+          // Start the second stage about half a softmax period after the first: the two softmax warpgroups share each
+          // scheduler's transcendental unit, which saturates when their exponential phases coincide and idles while
+          // both wait for the tensor core. Nothing pulls the phases apart later, so the offset is set here, once.
+          if (n0 > 0 && n1 > 0) {
+            const long long t_skew = clock64();
+            while (clock64() - t_skew < STAGE_SKEW_CLOCKS) {}
+          }
+          if (elect_one()) {
             if (n1 > 0) { issue_s(1, 0, 0); tc_commit(&bars[B_SFULL + 1]); }
             tc_commit(&bars[B_KEMPTY + 0]);   // K tile 0 is free once both S(0) products have completed
           }
@@ -272,7 +283,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             if (!(ok = mbar_wait(&bars[B_PFULL + i], j & 1, p.ctl, abortp, 23 + i))) break;
             tc_fence_after();
             if (lane == 0) FTRACE(0, j, 1 + 3 * i);
-            if (elect_one()) { issue_pv(i, st, j > 0); tc_commit(&bars[B_PVDONE + i]); }
+            // P.V(j) completes before S(j + 1) does (issue order), which the softmax threads wait for anyway: a
+            // separate completion signal is needed only after the stage's last tile (each commit costs the issuer ~60 clocks)
+            if (elect_one()) { issue_pv(i, st, j > 0); if (j + 1 == n_i) tc_commit(&bars[B_PVDONE + i]); }
             __syncwarp();
             if (lane == 0) FTRACE(0, j, 2 + 3 * i);
             if (j + 1 < n_i) {
@@ -372,10 +385,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         float mx = -INFINITY;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
-          float a = s[32 * kb];
+          // eight independent chains of three-input maxima, then a tree: a serial chain would cost its latency 31 times
+          float a[8];
 #pragma unroll
-          for (int e = 1; e < 32; ++e) a = fmaxf(a, s[32 * kb + e]);
-          mx = fmaxf(mx, a * c[kb]);
+          for (int t = 0; t < 8; ++t)
+            a[t] = fmaxf(fmax3(s[32 * kb + 4 * t], s[32 * kb + 4 * t + 1], s[32 * kb + 4 * t + 2]), s[32 * kb + 4 * t + 3]);
+          const float m8 = fmax3(fmax3(a[0], a[1], a[2]), fmax3(a[3], a[4], a[5]), fmaxf(a[6], a[7]));
+          mx = fmaxf(mx, m8 * c[kb]);
         }
         if (r == 0) FTRACE(1 + i, j, 3);
         // lazy refresh of the running maximum
@@ -387,8 +403,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         if (j > 0 && __any_sync(0xFFFFFFFFu, refresh)) {
           // rescale this row of O in tensor memory once the previous P.V has finished
-          if (!(ok = mbar_wait(&bars[B_PVDONE + i], (j - 1) & 1, p.ctl, abortp, 32 + i))) break;
-          tc_fence_after();
+          // P.V(j - 1) has completed: S(j), which this thread has read, was issued after it
 #pragma unroll 1
           for (int cc = 0; cc < D / 32; ++cc) {
             uint32_t ov[32];
@@ -400,14 +415,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
         const float mb = (m_used == -INFINITY) ? 0.f : (m_used - P_LOG2_OFFSET);
-        float psum = 0.f;
+        float ps[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};     // independent partial sums
         uint32_t pw[32];
 #pragma unroll
         for (int w = 0; w < 32; ++w) {
           const float cw = c[w >> 3];
           float p0 = ex2(fmaf(s[4 * w], cw, -mb)), p1 = ex2(fmaf(s[4 * w + 1], cw, -mb));
           float p2, p3;
-          if (w & 1) {    // one pair in four on the FMA pipe: the transcendental unit is the binding one
+          if (w & 1) {    // one pair in four on the FMA pipe (measured: -3 % kernel time on the dense cell)
             ex2_poly2(fmaf(s[4 * w + 2], cw, -mb), fmaf(s[4 * w + 3], cw, -mb), p2, p3);
           } else {
             p2 = ex2(fmaf(s[4 * w + 2], cw, -mb));
@@ -415,15 +430,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
           if (TL) {     // the row sum is that of the probabilities: take f_V(key) back out
             const float4 v4 = __ldg(fv4 + w);
-            psum += (p0 * __uint_as_float((254u << 23) - (__float_as_uint(v4.x) & 0x7F800000u)) +
+            ps[w & 7] += (p0 * __uint_as_float((254u << 23) - (__float_as_uint(v4.x) & 0x7F800000u)) +
                      p1 * __uint_as_float((254u << 23) - (__float_as_uint(v4.y) & 0x7F800000u))) +
                     (p2 * __uint_as_float((254u << 23) - (__float_as_uint(v4.z) & 0x7F800000u)) +
                      p3 * __uint_as_float((254u << 23) - (__float_as_uint(v4.w) & 0x7F800000u)));
           } else {
-            psum += (p0 + p1) + (p2 + p3);
+            ps[w & 7] += (p0 + p1) + (p2 + p3);
           }
           pw[w] = cvt_e4m3x4(p0, p1, p2, p3);
         }
+        const float psum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         l_sum = fmaf(l_sum, alpha, psum);
         if (r == 0) FTRACE(1 + i, j, 4);
         FL_TMEM_ST_32(t_s, pw);
@@ -438,7 +454,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (r == 0) FTRACE(1 + i, j, 6);
       }
       // ---- epilogue: O / l -> bf16, LSE
-      if (ok && n_i > 0) ok = mbar_wait(&bars[B_PVDONE + i], (n_i - 1) & 1, p.ctl, abortp, 34 + i);
+      if (ok && n_i > 0) ok = mbar_wait(&bars[B_PVDONE + i], 0, p.ctl, abortp, 34 + i);
       if (ok) {
         tc_fence_after();
         const float inv_l = (l_sum > 0.f) ? 1.0f / l_sum : 0.f;

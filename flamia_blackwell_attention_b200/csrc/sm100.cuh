@@ -229,6 +229,14 @@ __device__ __forceinline__ void tmem_cp_sf_atom(uint32_t taddr, uint64_t sdesc) 
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
+#define FL_TMEM_ST_16(taddr, v)                                                                                        \
+  asm volatile(                                                                                                        \
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, " \
+      "%16};" ::"r"(taddr),                                                                                            \
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),     \
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])                                           \
+      : "memory")
+
 #define FL_TMEM_LD_32(taddr, v)                                                                                        \
   asm volatile(                                                                                                        \
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "  \
@@ -298,6 +306,11 @@ __device__ __forceinline__ float lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 // Packed pairs of floats in one 64-bit register (fma / add .f32x2: one issue slot for two elements).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   uint64_t r;
@@ -317,8 +330,8 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-// 2^x for two arguments on the FMA pipe instead of the transcendental unit (which retires one warp instruction per
-// 8 clocks and is what bounds the softmax): n = round(x) through the 1.5 * 2^23 trick, f = x - n in [-0.5, 0.5],
+// 2^x for two arguments on the FMA pipe instead of the transcendental unit (one warp instruction per 8 clocks and
+// scheduler, shared by the two softmax warpgroups): n = round(x) through the 1.5 * 2^23 trick, f = x - n in [-0.5, 0.5],
 // 2^f by a degree-3 polynomial (weighted least-squares fit of the relative error on Chebyshev nodes: max 7.5e-5),
 // then n is added into the exponent field. Arguments below -126 give 2^-126.
 __device__ __forceinline__ void ex2_poly2(float x0, float x1, float& r0, float& r1) {
