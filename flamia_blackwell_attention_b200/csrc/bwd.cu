@@ -139,7 +139,11 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   constexpr bool RL = VAR >= 1, TL = VAR == 2;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int hkv = blockIdx.y;
+  // causal: grid = (kv heads, batch rows, key tiles), so key tiles with the same number of query tiles are dispatched
+  // together, longest first. Otherwise grid = (key tiles, kv heads, batch rows): the CTAs of one head run together and
+  // share its Q / dO tiles in L2.
+  const int hkv = p.causal ? blockIdx.x : blockIdx.y;
+  const int tile_id = p.causal ? blockIdx.z : blockIdx.x, bat_id = p.causal ? blockIdx.y : blockIdx.z;
   const int grp = p.h / p.h_kv;
   TRACE_INIT();
 
@@ -159,10 +163,10 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     fence_barrier_init();
     BTile t;
     if (p.doc_start == nullptr) {
-      t.bat = blockIdx.z; t.k0 = blockIdx.x * 128; t.nk = min(128, p.s_k - t.k0); t.krel = t.k0; t.q0 = 0; t.sq = p.s_q;
+      t.bat = bat_id; t.k0 = tile_id * 128; t.nk = min(128, p.s_k - t.k0); t.krel = t.k0; t.q0 = 0; t.sq = p.s_q;
       t.off = p.s_k - p.s_q;
     } else {
-      int x = blockIdx.x, dsel = -1;
+      int x = tile_id, dsel = -1;
       for (int dI = 0; dI < p.n_docs; ++dI) {
         const int nb = (p.doc_len[dI] + 127) / 128;
         if (x < nb) { dsel = dI; break; }
@@ -719,7 +723,8 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.ctl.status = a->status;
   p.ctl.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kDefaultWaitCycles;
   const int ntile = a->doc_start ? (a->s_k / 128 + a->n_docs) : a->s_k / 128;
-  dim3 grid(ntile, a->h_kv, a->doc_start ? 1 : a->b);
+  const int nb = a->doc_start ? 1 : a->b;
+  dim3 grid = p.causal ? dim3(a->h_kv, nb, ntile) : dim3(ntile, a->h_kv, nb);
   const int smem = 6 * 128 * 128 + 2 * 8192 + 2 * 16384 + 2048 + 1024 + (fp4 ? 3 * 8192 + 3 * 1024 : 0);
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;

@@ -99,7 +99,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __shared__ uint32_t sE[4];                           // dS exponent bytes: sE[key block] = bytes of query blocks 0..3
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int hkv = blockIdx.y;
+  // causal: grid = (kv heads, batch rows, key tiles), so key tiles with the same number of query tiles are dispatched
+  // together, longest first. Otherwise grid = (key tiles, kv heads, batch rows): the CTAs of one head run together and
+  // share its Q / dO tiles in L2.
+  const int hkv = p.causal ? blockIdx.x : blockIdx.y;
+  const int tile_id = p.causal ? blockIdx.z : blockIdx.x, bat_id = p.causal ? blockIdx.y : blockIdx.z;
   const int grp = p.h / p.h_kv;
 
   if (tid == 0) {
@@ -120,10 +124,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     fence_barrier_init();
     BTile t;
     if (p.doc_start == nullptr) {
-      t.bat = blockIdx.z; t.k0 = blockIdx.x * 128; t.nk = min(128, p.s_k - t.k0); t.krel = t.k0; t.q0 = 0; t.sq = p.s_q;
+      t.bat = bat_id; t.k0 = tile_id * 128; t.nk = min(128, p.s_k - t.k0); t.krel = t.k0; t.q0 = 0; t.sq = p.s_q;
       t.off = p.s_k - p.s_q;
     } else {
-      int x = blockIdx.x, dsel = -1;
+      int x = tile_id, dsel = -1;
       for (int dI = 0; dI < p.n_docs; ++dI) {
         const int nb = (p.doc_len[dI] + 127) / 128;
         if (x < nb) { dsel = dI; break; }
@@ -543,7 +547,8 @@ int fl_bwd_v1(const fl_attn_args* a, void* stream) {
   p.ctl.status = a->status;
   p.ctl.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kDefaultWaitCycles;
   const int ntile = a->doc_start ? (a->s_k / 128 + a->n_docs) : a->s_k / 128;
-  dim3 grid(ntile, a->h_kv, a->doc_start ? 1 : a->b);
+  const int nb = a->doc_start ? 1 : a->b;
+  dim3 grid = p.causal ? dim3(a->h_kv, nb, ntile) : dim3(ntile, a->h_kv, nb);
   const int smem = 6 * 128 * a->d + 16384 + 128 * a->d * 2 + 2048 + 1024;
   cudaStream_t st = (cudaStream_t)stream;
   if (a->d == 128) {

@@ -103,7 +103,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __shared__ Tile tile_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int head = blockIdx.y;
+  // causal: grid = (heads, batch rows, 256-row blocks), so blocks of equal length are dispatched together, longest first,
+  // and the SMs run out of work at nearly the same time. Otherwise grid = (blocks, heads, batch rows): every block costs
+  // the same and neighbours share their K / V tiles in L2.
+  const int head = p.causal ? blockIdx.x : blockIdx.y;
+  const int blk_id = p.causal ? blockIdx.z : blockIdx.x, bat_id = p.causal ? blockIdx.y : blockIdx.z;
   FTRACE_INIT();
   const int hkv = head / (p.h / p.h_kv);
 
@@ -127,12 +131,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     Tile t;
     if (p.doc_start == nullptr) {
       const int nqb = (p.s_q + 255) / 256;
-      const int qb = p.causal ? (nqb - 1 - (int)blockIdx.x) : (int)blockIdx.x;   // longest first under the causal mask
-      t.bat = blockIdx.z; t.q0 = qb * 256; t.nq = min(256, p.s_q - t.q0); t.k0 = 0; t.sk = p.s_k;
+      const int qb = p.causal ? (nqb - 1 - blk_id) : blk_id;   // longest first under the causal mask
+      t.bat = bat_id; t.q0 = qb * 256; t.nq = min(256, p.s_q - t.q0); t.k0 = 0; t.sk = p.s_k;
       t.off = p.s_k - p.s_q; t.qrel = t.q0;
     } else {
       // documents sit at 128-aligned starts of one packed batch entry; block x -> (document, 256-row block)
-      int x = blockIdx.x, dsel = -1, blk = 0;
+      int x = blk_id, dsel = -1, blk = 0;
       for (int dI = 0; dI < p.n_docs; ++dI) {
         const int nb = (p.doc_len[dI] + 255) / 256;
         if (x < nb) { dsel = dI; blk = x; break; }
@@ -542,7 +546,8 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   p.ctl.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kDefaultWaitCycles;
   // packed documents: at most one extra 256-row block per document beyond total / 256
   const int nblk = a->doc_start ? (a->s_q / 256 + a->n_docs + 1) : (a->s_q + 255) / 256;
-  dim3 grid(nblk, a->h, a->doc_start ? 1 : a->b);
+  const int nb = a->doc_start ? 1 : a->b;
+  dim3 grid = p.causal ? dim3(a->h, nb, nblk) : dim3(nblk, a->h, nb);
   const int smem = (2 + 2 * KV_STAGES) * 128 * a->d + 1024 + (fp4 ? (2 + KV_STAGES) * 1024 : 0);
   cudaStream_t st = (cudaStream_t)stream;
   auto launch = [&](auto kern) -> int {
