@@ -113,7 +113,8 @@ __global__ void __launch_bounds__(512, 1)
 bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                      const __grid_constant__ CUtensorMap tm_acc, const __grid_constant__ CUtensorMap tm_q4,
-                     const __grid_constant__ CUtensorMap tm_k4, const BwdParams p) {
+                     const __grid_constant__ CUtensorMap tm_k4, const __grid_constant__ CUtensorMap tm_dk,
+                     const __grid_constant__ CUtensorMap tm_dv, const BwdParams p) {
   constexpr int D = 128;
   constexpr int TILE_BYTES = 128 * D;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -146,6 +147,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int tile_id = p.causal ? blockIdx.z : blockIdx.x, bat_id = p.causal ? blockIdx.y : blockIdx.z;
   const int grp = p.h / p.h_kv;
   TRACE_INIT();
+  if (tid == 0) TRACE(6, 0, 0);
 
   if (tid == 0) {
     abort_s = 0;
@@ -197,6 +199,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int n_m = (T.nk > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
   const int n_it = n_m * grp;                                          // tile iterations: GQA heads x query tiles
   const bool early_out = (T.nk <= 0) || (*p.ctl.status != 0);
+  if (tid == 0) TRACE(6, 0, 1);
 
   if (!early_out) {
     if (warp >= 12) reg_dealloc<80>();     // register budget per warpgroup: 176 / 176 / 80 / 80 (x 128 threads = 64 K)
@@ -604,7 +607,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (r == 0) TRACE(1 + x, it, 6);
       }
       // ---- epilogue: warpgroup 0 writes dV, warpgroup 1 writes dK (full rows)
+      if (r == 0) TRACE(6, 0, 2 + 3 * x);
       if (ok) ok = mbar_wait(&bars[BB_ACC], 0, p.ctl, abortp, 33);
+      if (r == 0) TRACE(6, 0, 3 + 3 * x);
       if (ok) {
         tc_fence_after();
         const uint32_t t_acc = lane_base + (x == 0 ? TC_DV : TC_DK);
@@ -642,34 +647,45 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if ((NEG[i >> 5] >> (i & 31)) & 1) y[i] = -y[i];
           }
         }
-        if (key_valid) {
-          uint16_t* orow = reinterpret_cast<uint16_t*>(x == 0 ? p.dv : p.dk) +
-                           (((size_t)T.bat * p.s_k + T.k0 + r) * p.h_kv + hkv) * D;
+        // rows -> shared memory (two boxes of 64 elements, 128 B swizzle) -> one TMA store per box: a thread's own 256-byte
+        // row written straight to global memory costs 32 separate 128-byte lines per warp instruction
+        uint8_t* stage = (x == 0) ? sQ : sDO;            // the operand stages are dead: every product has completed
+        const uint32_t srow = smem_u32(stage) + r * 128;
 #pragma unroll
-          for (int c8 = 0; c8 < D / 8; ++c8) {
-            uint32_t w[4];
+        for (int c8 = 0; c8 < D / 8; ++c8) {
+          uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float a = y[8 * c8 + 2 * e], b2 = y[8 * c8 + 2 * e + 1];
-              if (p.out_f16) {
-                __half2 hh = __floats2half2_rn(a, b2);
-                w[e] = *reinterpret_cast<uint32_t*>(&hh);
-              } else {
-                w[e] = pack_bf16x2(a, b2);
-              }
+          for (int e = 0; e < 4; ++e) {
+            const float a = key_valid ? y[8 * c8 + 2 * e] : 0.f, b2 = key_valid ? y[8 * c8 + 2 * e + 1] : 0.f;
+            if (p.out_f16) {
+              __half2 hh = __floats2half2_rn(a, b2);
+              w[e] = *reinterpret_cast<uint32_t*>(&hh);
+            } else {
+              w[e] = pack_bf16x2(a, b2);
             }
-            *reinterpret_cast<uint4*>(orow + 8 * c8) = make_uint4(w[0], w[1], w[2], w[3]);
           }
+          sts128(srow + (c8 >> 3) * 16384 + (((c8 & 7) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+        }
+        fence_proxy_async();
+        mbar_arrive_warp(&bars[BB_EX + x]);              // the warpgroup's four warps; phase n_it of that barrier
+        if (mbar_wait(&bars[BB_EX + x], n_it & 1, p.ctl, abortp, 38) && r == 0) {
+          const CUtensorMap* tm_out = (x == 0) ? &tm_dv : &tm_dk;
+          tma_store_4d(tm_out, stage, 0, hkv, T.k0, T.bat);
+          tma_store_4d(tm_out, stage + 16384, 64, hkv, T.k0, T.bat);
+          tma_store_commit();
+          tma_store_wait<0>();
         }
       }
     }
   }
+  if (tid == 0 || tid == 128) TRACE(6, 0, 4 + 3 * (tid >> 7));
   if (abort_s) {
     for (int it = 0; it < 200; ++it) __nanosleep(1000);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
+  if (tid == 0) TRACE(6, 1, 0);
 }
 
 }  // namespace fl
@@ -696,7 +712,7 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
   if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
   if (a->doc_start && (a->b != 1 || a->n_docs <= 0 || !a->doc_len || a->s_q != a->s_k)) return FL_ERR_BAD_ARG;
-  CUtensorMap mq, mk, mv, mdo, macc, mq4, mk4;
+  CUtensorMap mq, mk, mv, mdo, macc, mq4, mk4, mdk, mdv;
   int rc;
   if ((rc = make_rows_map(&mq, a->q_codes, a->b, a->s_q, a->h, a->d, 128))) return rc;
   if ((rc = make_rows_map(&mk, a->k_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
@@ -709,6 +725,8 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   if ((rc = make_rows_map(&mk4, fp4 ? (const void*)a->k4 : (const void*)a->k_codes, a->b, a->s_k, a->h_kv, fp4 ? 64 : 128,
                           128)))
     return rc;
+  if ((rc = make_rows_map_16(&mdk, a->dk, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
+  if ((rc = make_rows_map_16(&mdv, a->dv, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
   BwdParams p;
   p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.fac_do = a->fac_do; p.lse_log2 = a->lse_log2;
   p.d_rows = a->d_rows; p.dq_scale = a->dq_scale; p.dk = a->dk; p.dv = a->dv;
@@ -728,7 +746,7 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   const int smem = 6 * 128 * 128 + 2 * 8192 + 2 * 16384 + 2048 + 1024 + (fp4 ? 3 * 8192 + 3 * 1024 : 0);
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
-    kern<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, p);
+    kern<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, mdk, mdv, p);
     return FL_OK;
   };
   if (fp4) rc = rl ? launch(bwd_kernel_pipelined<true, 1>) : launch(bwd_kernel_pipelined<true, 0>);
