@@ -102,7 +102,7 @@ def forward(plan, q, k, v, docs):
     vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl)
     status = K.new_status(q.device)
     out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=q.dtype, mode=mode,
-                             status=status, token_local=tl,
+                             status=status, token_local=tl, window=f.window,
                              doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     state = [out, lse, qq["codes"], qq["fac"], kq["codes"], kq["fac"], vq["codes"], vq["fac"], status]
     if need_bwd:
@@ -156,7 +156,7 @@ def backward(plan, state, dout, docs_meta):
     dk, dv, _ = K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks,
                            causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=out.dtype,
                            mode=L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8, had_dk=had8, status=status,
-                           token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all",
+                           token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all", window=f.window,
                            doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype)
     if docs is not None:

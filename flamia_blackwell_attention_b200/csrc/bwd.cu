@@ -55,6 +55,7 @@ struct BwdParams {
   float scale_log2;
   float softmax_scale;
   int causal;
+  int win_l, win_r;      // sliding window sides, -1 = unlimited (causal: the right side is 0)
   int out_f16;
   int had_dk;
   DevCtl ctl;
@@ -193,9 +194,11 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const BTile T = tile_s;
   volatile int* abortp = &abort_s;
 
-  const int m_hi = (T.sq + 127) / 128;
+  // query tiles that see this key tile: the first query that sees its first key, the last one that sees its last key
+  int m_hi = (T.sq + 127) / 128;
   int m_lo = 0;
-  if (p.causal && T.krel - T.off > 0) m_lo = (T.krel - T.off) / 128;   // first tile holding a query that sees key krel
+  if (p.win_r >= 0 && T.krel - T.off - p.win_r > 0) m_lo = (T.krel - T.off - p.win_r) / 128;
+  if (p.win_l >= 0) m_hi = min(m_hi, max(0, T.krel + T.nk - 1 - T.off + p.win_l) / 128 + 1);
   const int n_m = (T.nk > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
   const int n_it = n_m * grp;                                          // tile iterations: GQA heads x query tiles
   const bool early_out = (T.nk <= 0) || (*p.ctl.status != 0);
@@ -403,7 +406,8 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           ek_word |= ((__float_as_uint(p.fac_k[bh_k * (p.s_k / 32) + T.k0 / 32 + kb]) >> 23) & 0xFF) << (8 * kb);
       }
       const uint32_t ds_row = smem_u32(sDS) + x * 8192 + r * 64;
-      const int vis_from = p.causal ? (krel - T.off) : 0;                  // queries >= vis_from see this key
+      const int vis_from = p.win_r >= 0 ? (krel - T.off - p.win_r) : 0;    // queries in [vis_from, vis_to] see this key
+      const int vis_to = p.win_l >= 0 ? (krel - T.off + p.win_l) : 0x7FFFFFFF;
       bool ok = true;
       for (int it = 0; it < n_it; ++it) {
         const int st = it & 1, u = it >> 1;
@@ -427,7 +431,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (!(ok = mbar_wait(&bars[BB_QFULL + st], u & 1, p.ctl, abortp, 30))) break;   // lse / D'' vectors visible
         const uint32_t v_lse = smem_u32(sVec) + (st * 256 + 64 * x) * 4, v_dpp = v_lse + 512;
         const int q_first = m * 128 + 64 * x;                              // document-relative query of column 0
-        const bool full = key_valid && (q_first >= vis_from) && (q_first + 64 <= T.sq);
+        const bool full = key_valid && (q_first >= vis_from) && (q_first + 63 <= vis_to) && (q_first + 64 <= T.sq);
 
         // ---- P' = 2^(s c - lse2)
         if (r == 0) TRACE(1 + x, it, 0);
@@ -457,7 +461,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 64; ++j) {
             const int qi = q_first + j;
-            pf[j] = (key_valid && qi >= vis_from && qi < T.sq) ? pf[j] : 0.f;
+            pf[j] = (key_valid && qi >= vis_from && qi <= vis_to && qi < T.sq) ? pf[j] : 0.f;
           }
         }
         if (TL) {
@@ -736,6 +740,8 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.causal = (a->flags & FL_A_CAUSAL) ? 1 : 0;
+  p.win_l = a->window_left_p1 - 1;
+  p.win_r = p.causal ? 0 : a->window_right_p1 - 1;
   p.out_f16 = (a->flags & FL_A_OUT_F16) ? 1 : 0;
   p.had_dk = (a->flags & FL_A_HAD_DK) ? 1 : 0;
   p.ctl.status = a->status;

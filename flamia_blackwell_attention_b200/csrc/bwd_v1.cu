@@ -43,6 +43,7 @@ struct BwdParams {
   float scale_log2;
   float softmax_scale;
   int causal;
+  int win_l, win_r;      // sliding window sides, -1 = unlimited (causal: the right side is 0)
   int out_f16;
   int had_dk;
   DevCtl ctl;
@@ -153,10 +154,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   volatile int* abortp = &abort_s;
 
   // query tiles that see this key tile: m in [m_lo, m_hi)
-  const int m_hi = (T.sq + 127) / 128;
+  int m_hi = (T.sq + 127) / 128;
   int m_lo = 0;
-  if (p.causal) m_lo = max(0, (T.krel - T.off) / 128);      // first tile holding a query i with i + off >= krel
-  if (p.causal && T.krel - T.off < 0) m_lo = 0;
+  if (p.win_r >= 0 && T.krel - T.off - p.win_r > 0) m_lo = (T.krel - T.off - p.win_r) / 128;
+  if (p.win_l >= 0) m_hi = min(m_hi, max(0, T.krel + T.nk - 1 - T.off + p.win_l) / 128 + 1);
   const int n_m = (T.nk > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
   const int n_it = n_m * grp;                                // iterations: query heads of the group x query tiles
   const bool early_out = (T.nk <= 0) || (*p.ctl.status != 0);
@@ -318,8 +319,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const float* dpp = sVec + st * 256 + 128 + hc * 64;
         // element (key r, query column hc*64 + j) is live iff the key is valid, the query exists and sees the key
         const int q_first = m * 128 + hc * 64;                            // document-relative query of column 0
-        const int vis_from = p.causal ? (krel - T.off) : 0;               // queries >= vis_from see this key
-        const bool full = key_valid && (q_first >= vis_from) && (q_first + 64 <= T.sq);
+        const int vis_from = p.win_r >= 0 ? (krel - T.off - p.win_r) : 0;  // queries in [vis_from, vis_to] see this key
+        const int vis_to = p.win_l >= 0 ? (krel - T.off + p.win_l) : 0x7FFFFFFF;
+        const bool full = key_valid && (q_first >= vis_from) && (q_first + 63 <= vis_to) && (q_first + 64 <= T.sq);
 
         if (!(ok = mbar_wait(&bars[BB_S], it & 1, p.ctl, abortp, 31))) break;
         tc_fence_after();
@@ -338,7 +340,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           float e = ex2(x);
           if (!full) {
             const int qi = q_first + j;
-            e = (key_valid && qi >= vis_from && qi < T.sq) ? e : 0.f;
+            e = (key_valid && qi >= vis_from && qi <= vis_to && qi < T.sq) ? e : 0.f;
           }
           pf[j] = e;
         }
@@ -542,6 +544,8 @@ int fl_bwd_v1(const fl_attn_args* a, void* stream) {
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.causal = (a->flags & FL_A_CAUSAL) ? 1 : 0;
+  p.win_l = a->window_left_p1 - 1;
+  p.win_r = p.causal ? 0 : a->window_right_p1 - 1;
   p.out_f16 = (a->flags & FL_A_OUT_F16) ? 1 : 0;
   p.had_dk = (a->flags & FL_A_HAD_DK) ? 1 : 0;
   p.ctl.status = a->status;

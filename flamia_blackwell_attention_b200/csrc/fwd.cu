@@ -45,6 +45,7 @@ struct FwdParams {
   int b, s_q, s_k, h, h_kv;
   float scale_log2;
   int causal;
+  int win_l, win_r;      // sliding window sides, -1 = unlimited (causal: the right side is 0)
   int out_f16;
   DevCtl ctl;
 };
@@ -57,6 +58,7 @@ struct Tile {
   int sk;     // keys of the document
   int off;    // causal alignment: key j (document-relative) is visible to query i iff j <= i + off
   int qrel;   // document-relative index of row q0
+  int kofs;   // document-relative key of the first key row this CTA loads (a multiple of 128; > 0 under a left window)
 };
 
 // barrier indices
@@ -150,6 +152,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         t.qrel = blk * 256;
       }
     }
+    // left window: the first key any row of this block can see; both stages start at that key tile
+    t.kofs = 0;
+    if (p.win_l >= 0 && t.nq > 0) t.kofs = (max(0, t.qrel + t.off - p.win_l) / 128) * 128;
+    t.k0 += t.kofs;
     tile_s = t;
   }
   if (warp == 0) {
@@ -163,14 +169,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const Tile T = tile_s;
   volatile int* abortp = &abort_s;
 
-  // keys visible to stage i: [0, kmax_i); tiles n_i = ceil(kmax_i / 128)
+  // keys visible to stage i: [kofs, kmax_i); tiles n_i = ceil((kmax_i - kofs) / 128)
   int n_st[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int rows = min(128, T.nq - 128 * i);             // valid rows of the stage (<= 0: stage absent)
     int kmax = T.sk;
-    if (p.causal) kmax = min(T.sk, T.qrel + 128 * i + rows + T.off);
-    n_st[i] = (rows > 0 && kmax > 0) ? (kmax + 127) / 128 : 0;
+    if (p.win_r >= 0) kmax = min(T.sk, T.qrel + 128 * i + rows + T.off + p.win_r);
+    n_st[i] = (rows > 0 && kmax > T.kofs) ? (kmax - T.kofs + 127) / 128 : 0;
   }
   const int n_max = max(n_st[0], n_st[1]);
   const bool early_out = (T.nq <= 0) || (*p.ctl.status != 0);
@@ -332,7 +338,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                                  : p.fac_q[bh_q * (p.s_q / 32) + qrow / 32] * p.scale_log2;
       const float* fk_row = p.fac_k + bh_k * (p.s_k / 32) + T.k0 / 32;
       const float* fv_row = p.fac_v + bh_k * (p.s_k / 32) + T.k0 / 32;
-      const int col_limit = p.causal ? min(qrel + T.off, T.sk - 1) : T.sk - 1;   // last visible key of this row
+      const int col_limit = p.win_r >= 0 ? min(qrel + T.off + p.win_r, T.sk - 1) : T.sk - 1;   // last visible key of this row
+      const int col_first = p.win_l >= 0 ? qrel + T.off - p.win_l : 0;                          // first visible key
 
       float m_used = -INFINITY, l_sum = 0.f;
       bool ok = true;
@@ -379,10 +386,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             s[4 * e4 + 3] = fmaf(s[4 * e4 + 3], fq * k4.w, (float)((int)(__float_as_uint(v4.w) >> 23) - 127));
           }
         }
-        const bool need_mask = (j * 128 + 127) > col_limit;    // only on diagonal / tail tiles
+        const int kb0 = T.kofs + j * 128;                       // document-relative key of column 0
+        const bool need_mask = (kb0 + 127 > col_limit) || (kb0 < col_first);    // only on boundary tiles
         if (need_mask) {   // scale first, then mask: the factor product may underflow to zero and 0 * inf is NaN
 #pragma unroll
-          for (int e = 0; e < 128; ++e) s[e] = (j * 128 + e > col_limit) ? -INFINITY : s[e] * c[e >> 5];
+          for (int e = 0; e < 128; ++e)
+            s[e] = (kb0 + e > col_limit || kb0 + e < col_first) ? -INFINITY : s[e] * c[e >> 5];
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) c[kb] = 1.f;
         }
@@ -541,6 +550,8 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.causal = (a->flags & FL_A_CAUSAL) ? 1 : 0;
+  p.win_l = a->window_left_p1 - 1;
+  p.win_r = p.causal ? 0 : a->window_right_p1 - 1;
   p.out_f16 = (a->flags & FL_A_OUT_F16) ? 1 : 0;
   p.ctl.status = a->status;
   p.ctl.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kDefaultWaitCycles;

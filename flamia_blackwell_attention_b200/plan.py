@@ -154,8 +154,10 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
     if score_mod is not None or score_mod_bwd is not None or mask_mod is not None:
         _fail("B3", NotImplementedError, "score_mod / mask_mod are CuTe-DSL callables of the reference's kernels; "
                                          "this library takes causal and dense masks")
-    if tuple(window_size) != (None, None):
-        _fail("B4", NotImplementedError, "window_size (sliding window) is not built yet: causal and dense masks only")
+    wl, wr = tuple(window_size)
+    for w in (wl, wr):
+        if w is not None and (not isinstance(w, int) or w < -1):
+            _fail(28, ValueError, f"window_size entries are None, -1 (unlimited) or a non-negative int; got {window_size}")
     if softcap:
         _fail("B4", NotImplementedError, "softcap is not built yet")
     if seqused_k is not None and not shape.aligned_varlen:
@@ -237,10 +239,12 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
 
 
 def _finish(entry, route, qk_format, shape, log_rows, opts, *, softmax_scale, causal, return_lse, had, scaling, rowlocal,
-            ragged, dq_causal):
+            ragged, dq_causal, window_size=(None, None)):
     sc = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(shape.d)
+    # sliding window (left, right): None / -1 = unlimited on that side; causal caps the right side at 0 in the kernels
+    win = tuple(None if (w is None or w < 0) else int(w) for w in tuple(window_size))
     fwd = FwdSpec("fwd_sm100", qk_format, "e4m3", scaling, "row", "exp2", had, bool(causal), shape.varlen,
-                  shape.aligned_varlen, ragged, bool(return_lse))
+                  shape.aligned_varlen, ragged, bool(return_lse), None if win == (None, None) else win)
     bwd = BwdSpec("1cta" if shape.requires_grad else "none", scaling, "block_32x32", rowlocal, "row", "e4m3", False,
                   "causal_tile" if dq_causal else "row")
     return AttnPlan(entry, route, sc, shape, fwd, bwd, opts.tuning, False, False, tuple(log_rows), opts)
@@ -289,7 +293,7 @@ def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     log("dq_prescale", "causal_tile" if dq_causal else "row", "per query tile from the prefix of key tiles"
         if dq_causal else "one power of two per batch row / document")
     return _finish("fp8", "fp8", "e4m3", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
-                   return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=dq_causal)
+                   return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=dq_causal, window_size=window_size)
 
 
 def resolve_fp4(q, k, v, *, softmax_scale=None, causal=False, window_size=(None, None), softcap=0.0, score_mod=None,
@@ -354,4 +358,4 @@ def resolve_fp4(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     log("p_hat_frame", "row", "the row-frame E4M3 P-hat (the group frame is not built)")
     log("backward_kernel", "1cta", "the 1-CTA backward; S recomputed from the forward's NVFP4 codes")
     return _finish("fp4", "fp4.e4m3_pv", "nvfp4", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
-                   return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=False)
+                   return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=False, window_size=window_size)

@@ -16,7 +16,7 @@
 extern "C" {
 #endif
 
-#define FL_ABI_VERSION 1
+#define FL_ABI_VERSION 2
 
 /* fl_quant_args.flags */
 #define FL_Q_HADAMARD 1            /* rotate rows by diag(signs) H_128 / sqrt(128) before quantising (d = 128) */
@@ -96,6 +96,11 @@ typedef struct fl_attn_args {
   int32_t flags;
   int32_t* status;           /* device int, 0 on entry; a kernel that gives up a wait writes a nonzero code */
   int64_t wait_cycles;       /* budget of one device-side wait in SM clocks; 0 = default (2^31) */
+  /* Sliding window (the reference's window_size=(left, right), flash_attn/cute/lowprec/api.py:270): query i sees key j
+   * iff i + off - left <= j <= i + off + right, off = s_k - s_q. Stored as window + 1; 0 = unlimited on that side, so
+   * a zero-filled struct means no window. FL_A_CAUSAL caps the right side at 0. */
+  int32_t window_left_p1;
+  int32_t window_right_p1;
 } fl_attn_args;
 
 /* Forward: O = softmax(scale Q K^T + mask) V, LSE.

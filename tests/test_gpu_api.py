@@ -184,3 +184,33 @@ def test_fp8_token_local_rowlocal_causal_prescale_gqa():
         e_new, e_base = A.accuracy(a, r)["rel_l2"], A.accuracy(ba, br)["rel_l2"]
         print("token-local", n, e_new, "default route", e_base)
         assert e_new <= 1.15 * e_base + 1e-3, (n, e_new, e_base)
+
+
+WINDOW_CASES = [
+    # s_q, s_k, causal, window, route
+    (512, 512, True, (200, 0), "fp8"),
+    (1024, 1024, True, (256, None), "fp8"),        # the right side is capped by causal
+    (640, 640, False, (100, 50), "fp8"),
+    (384, 768, False, (None, 64), "fp8"),          # only a right limit, s_q != s_k
+    (768, 768, True, (300, 0), "fp4"),
+    (300, 300, True, (64, 0), "fp8"),              # a length that is no multiple of 128 (repacked internally)
+]
+
+
+@pytest.mark.parametrize("sq,sk,causal,window,route", WINDOW_CASES)
+def test_sliding_window(sq, sk, causal, window, route):
+    """window_size=(left, right): key j visible iff i + off - left <= j <= i + off + right."""
+    import flamia_blackwell_attention_b200 as F
+    fn = F.flash_attn_fp8 if route == "fp8" else F.flash_attn_fp4
+    s = max(sq, sk)
+    q, k, v, g = attention_inputs(2, s, 4, 2, 128, seed=21)
+    q, g, k, v = q[:, :sq], g[:, :sq], k[:, :sk], v[:, :sk]
+    o, dq, dk, dv, _ = _step(fn, q, k, v, g, causal=causal, window_size=window)
+    if sq % 128 == 0:
+        ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=causal, rotate_qk=True, fp4_qk=route == "fp4", window=window)
+        _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))
+    else:
+        ro, _, rdq, rdk, rdv = A.attention_fp32(q.float(), k.float(), v.float(), g.float(), causal, window=window)
+        _check((o, dq, dk, dv), (ro, rdq, rdk, rdv), tol=7e-2)
+    # rows / keys outside every window get exact zeros
+    assert torch.isfinite(o).all() and torch.isfinite(dq).all()
