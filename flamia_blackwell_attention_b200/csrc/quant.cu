@@ -44,6 +44,12 @@ __device__ __forceinline__ float in_to_f32(uint32_t v16, int f16) {
   return f16 ? __half2float(__ushort_as_half((uint16_t)v16)) : __uint_as_float(v16 << 16);
 }
 __device__ __forceinline__ float flush_sub(float v) { return fabsf(v) < 1.17549435e-38f ? v * 0.0f : v; }
+// a * b rounded to nearest with subnormal inputs and results flushed to zero (the product and its flush in one instruction)
+__device__ __forceinline__ float mul_ftz(float a, float b) {
+  float r;
+  asm("mul.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
 
 // UE8M0 round-up selector: smallest e with 448 * 2^e >= amax; byte 0 when fp32(amax * fp32(1/448)) is subnormal / zero
 __device__ __forceinline__ uint32_t ue8m0_byte(float amax) {
@@ -127,11 +133,12 @@ __global__ void __launch_bounds__(QTHREADS) quant_blocks_kernel(const QuantParam
       }
 #pragma unroll
       for (int lb = 1; lb < 4; lb <<= 1) {       // element bits 3, 4 = the lane of the row
-        const bool hi = (q & lb) != 0;
+        // low lane: y + other; high lane: other - y. Both are other + (+-1) y: one fma (the product is exact)
+        const float sg = (q & lb) ? -1.0f : 1.0f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float other = __shfl_xor_sync(0xFFFFFFFFu, y[i], lb);
-          y[i] = hi ? __fsub_rn(other, y[i]) : __fadd_rn(y[i], other);
+          y[i] = __fmaf_rn(y[i], sg, other);
         }
       }
 #pragma unroll
@@ -145,7 +152,7 @@ __global__ void __launch_bounds__(QTHREADS) quant_blocks_kernel(const QuantParam
           }
       }
 #pragma unroll
-      for (int i = 0; i < 32; ++i) y[i] = __fmul_rn(y[i], 0.08838834764831845f);
+      for (int i = 0; i < 32; ++i) y[i] = mul_ftz(y[i], 0.08838834764831845f);   // scaled and flushed
     }
   };
 
@@ -206,9 +213,12 @@ __global__ void __launch_bounds__(QTHREADS) quant_blocks_kernel(const QuantParam
   float amax = 0.f, sumsq = 0.f;
 #pragma unroll
   for (int i = 0; i < NE; ++i) {
-    x[i] = flush_sub(x[i]);
+    x[i] = mul_ftz(x[i], 1.0f);      // subnormal -> zero of the same sign (rotated rows were flushed by their scaling)
     amax = fmaxf(amax, fabsf(x[i]));
-    sumsq = fmaf(x[i], x[i], sumsq);
+  }
+  if (p.tile_stats) {     // the row norm is only wanted with the tile statistics (K, V, dO)
+#pragma unroll
+    for (int i = 0; i < NE; ++i) sumsq = fmaf(x[i], x[i], sumsq);
   }
   amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));      // the token's maximum
