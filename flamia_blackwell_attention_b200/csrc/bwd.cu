@@ -619,16 +619,15 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t t_acc = lane_base + (x == 0 ? TC_DV : TC_DK);
         const float mult = (x == 0) ? 0.00390625f : p.softmax_scale;       // dV carries 2^8 (P'), dK the softmax scale
         float y[D];
-        if (n_it > 0) {
+        if (n_it > 0) {                  // (CTA-uniform: the tensor-memory loads are warp-collective)
+          uint32_t v[D];                 // all four loads in flight, one wait
 #pragma unroll
-          for (int cc = 0; cc < D / 32; ++cc) {
-            uint32_t v[32];
-            FL_TMEM_LD_32(t_acc + 32 * cc, v);
-            tc_wait_ld();
+          for (int cc = 0; cc < D / 32; ++cc) FL_TMEM_LD_32(t_acc + 32 * cc, (v + 32 * cc));
+          tc_wait_ld();
+          const float mk = key_valid ? mult : 0.f;     // rows past the end of the document store zeros
 #pragma unroll
-            for (int e = 0; e < 32; ++e) y[32 * cc + e] = __uint_as_float(v[e]) * mult;
-          }
-        } else {
+          for (int e = 0; e < D; ++e) y[e] = __uint_as_float(v[e]) * mk;
+        } else {                         // no query tile saw this key tile
 #pragma unroll
           for (int e = 0; e < D; ++e) y[e] = 0.f;
         }
@@ -660,7 +659,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float a = key_valid ? y[8 * c8 + 2 * e] : 0.f, b2 = key_valid ? y[8 * c8 + 2 * e + 1] : 0.f;
+            const float a = y[8 * c8 + 2 * e], b2 = y[8 * c8 + 2 * e + 1];
             if (p.out_f16) {
               __half2 hh = __floats2half2_rn(a, b2);
               w[e] = *reinterpret_cast<uint32_t*>(&hh);
@@ -677,7 +676,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           tma_store_4d(tm_out, stage, 0, hkv, T.k0, T.bat);
           tma_store_4d(tm_out, stage + 16384, 64, hkv, T.k0, T.bat);
           tma_store_commit();
-          tma_store_wait<0>();
+          tma_store_wait_read<0>();      // the shared-memory source must outlive the copy; the writes complete with the grid
         }
       }
     }
