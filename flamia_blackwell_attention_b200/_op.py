@@ -66,8 +66,14 @@ def _bwd_impl(dout, state: List[torch.Tensor], entry: int):
 def _fake_fwd(q, k, v, docs, plan, docs_id):
     p = _PLANS[plan]
     sh = p.shape
-    lse_shape = (sh.h, sh.tot_q) if sh.aligned_varlen else ((0,) if (sh.varlen or p.fwd.ragged_documents) else (sh.b, sh.h, sh.s_q))
-    return torch.empty_like(q), q.new_empty(lse_shape, dtype=torch.float32), []
+    is_docs = sh.varlen or p.fwd.ragged_documents
+    lse_shape = (sh.h, sh.tot_q) if sh.aligned_varlen else ((0,) if is_docs else (sh.b, sh.h, sh.s_q))
+    n_docs = int(docs[0].shape[0]) - 1 if len(docs) > 0 else 0
+    spec = _routes.state_spec(p, n_docs, q.dtype)
+    # as _fwd_impl: the batched form hands O / LSE out as the op's outputs, documents keep the padded ones in the state
+    state = [q.new_empty(shape, dtype=dt) for shape, dt in (spec if is_docs else spec[2:])]
+    state.append(torch.empty((), dtype=torch.int64))
+    return torch.empty_like(q), q.new_empty(lse_shape, dtype=torch.float32), state
 
 
 def _fake_bwd(dout, state, entry):

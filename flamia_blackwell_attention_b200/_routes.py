@@ -79,6 +79,41 @@ def docs_of(plan, q, cu_q, cu_k, seqused_q, seqused_k):
     return None
 
 
+def state_spec(plan, n_docs=0, dtype=torch.bfloat16):
+    """Shapes and dtypes of the tensors forward() returns as `state`, in order, from the plan alone (n_docs = number of
+    documents of a packed call). The fake implementations of the registered ops are built from this, and a GPU test
+    checks it against the real state."""
+    sh, f = plan.shape, plan.fwd
+    fp4 = plan.entry == "fp4"
+    tl = f.operand_scaling == "token_local"
+    need_bwd = plan.bwd.kernel != "none"
+    f8, u8, f32, i32 = torch.float8_e4m3fn, torch.uint8, torch.float32, torch.int32
+    docs = sh.varlen or f.ragged_documents
+    if docs:
+        if sh.aligned_varlen:
+            n, cap = n_docs, sh.tot_q
+        else:
+            n, tot = (n_docs, sh.tot_q) if sh.varlen else (sh.b, sh.b * sh.s_q)
+            cap = ((tot + 127 * n + 127) // 128) * 128
+        b, s_q, s_k = 1, cap, cap
+    else:
+        b, s_q, s_k = sh.b, sh.s_q, sh.s_k
+    h, hk, d = sh.h, sh.h_kv, sh.d
+    spec = [((b, s_q, h, d), dtype), ((b, h, s_q), f32),                                       # O, LSE of the kernels
+            ((b, s_q, h, d), f8), ((b, h, s_q // 32), f32), ((b, s_k, hk, d), f8), ((b, hk, s_k // 32), f32),
+            ((b, s_k, hk, d), f8), ((b, hk, s_k // 32), f32), ((1,), i32)]                     # codes, factors, status
+    if need_bwd:
+        spec += [((b, hk, s_k // 128, 2), f32)] * 2
+    if fp4:
+        spec += [((b, s_q, h, d // 2), u8), ((b, h, s_q // 128, d // 64, 32, 4, 4), u8),
+                 ((b, s_k, hk, d // 2), u8), ((b, hk, s_k // 128, d // 64, 32, 4, 4), u8)]
+    if tl:
+        spec += [((b, h, s_q), f32), ((b, hk, s_k), f32), ((b, hk, s_k), f32)]
+    if docs:
+        spec += [((n,), i32), ((n,), i32)] + ([] if sh.aligned_varlen else [((cap,), i32)])
+    return spec
+
+
 # --------------------------------------------------------------------------------------------------------------- forward
 def forward(plan, q, k, v, docs):
     """Returns (out, lse, state): out / lse in the caller's layout, state = the tensors the backward needs."""

@@ -214,3 +214,48 @@ def test_sliding_window(sq, sk, causal, window, route):
         _check((o, dq, dk, dv), (ro, rdq, rdk, rdv), tol=7e-2)
     # rows / keys outside every window get exact zeros
     assert torch.isfinite(o).all() and torch.isfinite(dq).all()
+
+
+@pytest.mark.parametrize("form", ["batched_fp8", "batched_fp4", "token_local", "ragged", "packed", "aligned"])
+def test_state_matches_its_spec(form):
+    """The saved state of the registered forward op has exactly the shapes and dtypes the fake implementation announces
+    (flamia_blackwell_attention_b200/_routes.py::state_spec)."""
+    import flamia_blackwell_attention_b200 as F
+    from flamia_blackwell_attention_b200 import _op, _routes
+    h, hk, d = 4, 2, 128
+    kw = dict(causal=True)
+    entry = "fp4" if form == "batched_fp4" else "fp8"
+    docs, n_docs = [], 0
+    if form in ("packed", "aligned"):
+        lens = [300, 128, 77, 515]
+        if form == "aligned":
+            starts = [0, 384, 512, 640]
+            total = 1280
+            su = torch.tensor(lens, dtype=torch.int32, device="cuda")
+            kw.update(seqused_q=su, seqused_k=su)
+        else:
+            starts = [sum(lens[:i]) for i in range(4)]
+            total = sum(lens)
+        q, k, v, _ = (t[0].cuda() for t in attention_inputs(1, total, h, hk, d, seed=31))
+        cu = torch.tensor(starts + [total], dtype=torch.int32, device="cuda")
+        kw.update(cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens))
+        docs = [cu, cu] + ([su, su] if form == "aligned" else [])
+        n_docs = len(lens)
+    else:
+        s = 300 if form == "ragged" else 384
+        q, k, v, _ = (t.cuda() for t in attention_inputs(2, s, h, hk, d, seed=31))
+        if form == "token_local":
+            kw["options"] = F.FP8AttnOptions(operand_scaling="token_local", ds_dq_rowlocal="all")
+    for t in (q, k, v):
+        t.requires_grad_(True)
+    plan = (F.resolve_fp4 if entry == "fp4" else F.resolve_fp8)(q, k, v, **kw)
+    pid = _op.register_plan(plan)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out, lse, state = getattr(torch.ops.lowbit_attn, entry)(q.detach(), k.detach(), v.detach(), docs, pid, 0)
+    spec = _routes.state_spec(plan, n_docs, q.dtype)
+    is_docs = plan.shape.varlen or plan.fwd.ragged_documents
+    want = (spec if is_docs else spec[2:]) + [((), torch.int64)]
+    assert [(tuple(t.shape), t.dtype) for t in state] == [(tuple(sh), dt) for sh, dt in want]
+    assert out.shape == q.shape
