@@ -185,54 +185,67 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
     } else if (warp == 12) {
       // =================================================================== UMMA issuer
-      if (lane == 0) {
+      // The whole warp stays converged through the waits and the descriptor arithmetic (warp-uniform values); one elected
+      // lane issues. Descriptors are built once; the loop only adds byte offsets (the issuing thread's own instruction
+      // latency is what bounds the tensor pipe's issue rate).
+      {
         constexpr uint32_t ID_KK = idesc_f8(128, 128, 0, 0);
-        const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
-                       ds_addr = smem_u32(sDS);
+        const uint32_t tm = __shfl_sync(0xFFFFFFFFu, tmem, 0);
+        const int nit = __shfl_sync(0xFFFFFFFFu, n_it, 0);
+        const uint64_t dK0 = smem_desc(smem_u32(sK), 16, SBO, SWZ), dV0 = smem_desc(smem_u32(sV), 16, SBO, SWZ),
+                       dQ0 = smem_desc(smem_u32(sQ), 16, SBO, SWZ), dDO0 = smem_desc(smem_u32(sDO), 16, SBO, SWZ),
+                       dDS0 = smem_desc(smem_u32(sDS), 16, 1024, SWZ_128);
         bool ok = mbar_wait(&bars[BB_KV], 0, p.ctl, abortp, 20);
-        for (int it = 0; ok && it < n_it; ++it) {
+        for (int it = 0; ok && it < nit; ++it) {
           const int st = it & 1, u = it >> 1;
+          const uint64_t dQs = desc_adv(dQ0, st * TILE_BYTES), dDOs = desc_adv(dDO0, st * TILE_BYTES);
+          const uint32_t accum = it > 0;
           if (!(ok = mbar_wait(&bars[BB_QFULL + st], u & 1, p.ctl, abortp, 21))) break;
           tc_fence_after();
-          // S^T = K Q^T
+          if (elect_one()) {   // S^T = K Q^T
 #pragma unroll
-          for (int k = 0; k < D / 32; ++k)
-            umma_f8_ss(tmem + TC_S, smem_desc(k_addr + 32 * k, 16, SBO, SWZ),
-                       smem_desc(q_addr + st * TILE_BYTES + 32 * k, 16, SBO, SWZ), ID_KK, k > 0);
-          tc_commit(&bars[BB_S]);
+            for (int k = 0; k < D / 32; ++k) umma_f8_ss(tm + TC_S, desc_adv(dK0, 32 * k), desc_adv(dQs, 32 * k), ID_KK, k > 0);
+            tc_commit(&bars[BB_S]);
+          }
+          __syncwarp();
           // dP^T = V dO^T (its columns are the previous dQ tile's: wait until that one has been read out)
           if (it > 0 && !(ok = mbar_wait(&bars[BB_DQEMPTY], (it - 1) & 1, p.ctl, abortp, 22))) break;
           tc_fence_after();
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < D / 32; ++k)
-            umma_f8_ss(tmem + TC_DP, smem_desc(v_addr + 32 * k, 16, SBO, SWZ),
-                       smem_desc(do_addr + st * TILE_BYTES + 32 * k, 16, SBO, SWZ), ID_KK, k > 0);
-          tc_commit(&bars[BB_DP]);
+            for (int k = 0; k < D / 32; ++k) umma_f8_ss(tm + TC_DP, desc_adv(dV0, 32 * k), desc_adv(dDOs, 32 * k), ID_KK, k > 0);
+            tc_commit(&bars[BB_DP]);
+          }
+          __syncwarp();
           // dV += P-hat^T dO-hat
           if (!(ok = mbar_wait(&bars[BB_P], it & 1, p.ctl, abortp, 23))) break;
           tc_fence_after();
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_mxf8_ts(tmem + TC_DV, tmem + TC_P + 8 * kk,
-                         smem_desc(do_addr + st * TILE_BYTES + kk * 32 * D, 16, SBO, SWZ),
-                         idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), tmem + TC_SFA_P, tmem + TC_SFB_DO, it > 0 || kk > 0);
+            for (int kk = 0; kk < 4; ++kk)
+              umma_mxf8_ts(tm + TC_DV, tm + TC_P + 8 * kk, desc_adv(dDOs, kk * 32 * D), idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk),
+                           tm + TC_SFA_P, tm + TC_SFB_DO, accum | kk);
+          }
+          __syncwarp();
           // dK += dS-hat^T Q-hat ; dQ_m = dS-hat K-hat
           if (!(ok = mbar_wait(&bars[BB_DS], it & 1, p.ctl, abortp, 24))) break;
           tc_fence_after();
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_mxf8_ts(tmem + TC_DK, tmem + TC_DS + 8 * kk,
-                         smem_desc(q_addr + st * TILE_BYTES + kk * 32 * D, 16, SBO, SWZ),
-                         idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), tmem + TC_SFA_DK, tmem + TC_SFB_Q, it > 0 || kk > 0);
+            for (int kk = 0; kk < 4; ++kk)
+              umma_mxf8_ts(tm + TC_DK, tm + TC_DS + 8 * kk, desc_adv(dQs, kk * 32 * D), idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk),
+                           tm + TC_SFA_DK, tm + TC_SFB_Q, accum | kk);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_mxf8_ss(tmem + TC_DQ, smem_desc(ds_addr + kk * 4096, 16, 1024, SWZ_128),
-                         smem_desc(k_addr + kk * 32 * D, 16, SBO, SWZ), idesc_bs(128, D, 0, 0, 1, 1, 1, kk, kk),
-                         tmem + TC_SFA_DQ, tmem + TC_SFB_K, kk > 0);
-          tc_commit(&bars[BB_DQFULL]);
-          tc_commit(&bars[BB_QEMPTY + st]);
+            for (int kk = 0; kk < 4; ++kk)
+              umma_mxf8_ss(tm + TC_DQ, desc_adv(dDS0, kk * 4096), desc_adv(dK0, kk * 32 * D), idesc_bs(128, D, 0, 0, 1, 1, 1, kk, kk),
+                           tm + TC_SFA_DQ, tm + TC_SFB_K, kk > 0);
+            tc_commit(&bars[BB_DQFULL]);
+            tc_commit(&bars[BB_QEMPTY + st]);
+          }
+          __syncwarp();
         }
-        if (ok) tc_commit(&bars[BB_ACC]);
+        if (ok && elect_one()) tc_commit(&bars[BB_ACC]);
+        __syncwarp();
       }
     } else if (warp >= 8 && warp < 12) {
       reg_dealloc<96>();

@@ -53,13 +53,17 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
     const bool nvf4 = which == FL_ST_NVF4 || which == FL_ST_NVF4_N64_HI;
     const bool hi64 = which == FL_ST_NVF4_N64_HI;
     const bool dqt = which == FL_ST_MX8_MN_N64;
+    const bool a2 = which == FL_ST_MX8_A_MN_2X64;      // A = two 64-byte-row blocks side by side along M
     const bool a_tmem = which == FL_ST_F8_A_TMEM || which == FL_ST_MX8_TS;
-    const bool scaled8 = which == FL_ST_MX8_SS || which == FL_ST_MX8_TS || dqt;
+    const bool scaled8 = which == FL_ST_MX8_SS || which == FL_ST_MX8_TS || dqt || a2;
     const uint32_t tile_bytes = nvf4 ? 8192u : 16384u;
     if (tid == 0) {
-      uint32_t tx = (a_tmem ? 0u : tile_bytes) + (dqt ? 8192u : tile_bytes) + (nvf4 ? 2048u : 0u);
+      uint32_t tx = (a_tmem ? 0u : tile_bytes) + ((dqt || a2) ? 8192u : tile_bytes) + (nvf4 ? 2048u : 0u);
       mbar_arrive_expect_tx(&bar_load, tx);
-      if (!a_tmem) tma_load_2d(sA, &tm_a, &bar_load, 0, 0);
+      if (a2) {                       // columns [0, 64) and [64, 128) of A as two 128 x 64-byte blocks, 8 KB apart
+        tma_load_2d(sA, &tm_a, &bar_load, 0, 0);
+        tma_load_2d(sA + 8192, &tm_a, &bar_load, 64, 0);
+      } else if (!a_tmem) tma_load_2d(sA, &tm_a, &bar_load, 0, 0);
       tma_load_2d(sB, &tm_b, &bar_load, 0, 0);
       if (nvf4) {
         bulk_load(sSF, p.sfa, 1024, &bar_load);
@@ -113,6 +117,12 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
                            k > 0);
             }
           }
+        } else if (a2) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)   // A MN-major: 32 K rows of 64 B per step, second M block 8 KB further (leading byte offset)
+            umma_mxf8_ss(tmem + ST_COL_D, smem_desc(a0 + 2048 * k, 8192, 512, SWZ_64),
+                         smem_desc(b0 + 2048 * k, 16, 512, SWZ_64), idesc_bs(128, 64, 0, 0, 1, 1, 1, k, k),
+                         tmem + ST_COL_SFA, tmem + ST_COL_SFB, k > 0);
         } else if (dqt) {
 #pragma unroll
           for (int k = 0; k < 4; ++k)   // A: 32 K rows of 128 B further down; B: 32 K rows of 64 B (64 B swizzle, 512 B atoms)
@@ -161,7 +171,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
     if (mbar_wait(&bar_mma, 0, p.ctl, &abort_s, 3)) {
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < ((which == FL_ST_MX8_MN_N64 || which == FL_ST_NVF4_N64_HI) ? 2 : 4); ++c) {
+      for (int c = 0; c < ((which == FL_ST_MX8_MN_N64 || which == FL_ST_NVF4_N64_HI || which == FL_ST_MX8_A_MN_2X64) ? 2 : 4); ++c) {
         uint32_t v[32];
         FL_TMEM_LD_32(lane_addr + ST_COL_D + 32 * c, v);
         tc_wait_ld();
@@ -180,7 +190,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
 extern "C" int fl_selftest_mma(int32_t which, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                                float* d, int32_t* status, int64_t wait_cycles, void* stream) {
   using namespace fl;
-  if (which < 0 || which > FL_ST_NVF4_N64_HI || !status) return FL_ERR_BAD_ARG;
+  if (which < 0 || which > FL_ST_MX8_A_MN_2X64 || !status) return FL_ERR_BAD_ARG;
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return FL_ERR_CUDA;
   CUtensorMap ma, mb;
@@ -193,11 +203,14 @@ extern "C" int fl_selftest_mma(int32_t which, const uint8_t* a, const uint8_t* b
     cuuint32_t box[2] = {(cuuint32_t)rowb, 128};
     cuuint32_t estr[2] = {1, 1};
     const CUtensorMapSwizzle sw = nvf4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+    const bool a2x64 = which == FL_ST_MX8_A_MN_2X64;
+    if (a2x64) box[0] = 64;
     if (enc(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) !=
-        CUDA_SUCCESS)
+            CU_TENSOR_MAP_INTERLEAVE_NONE, a2x64 ? CU_TENSOR_MAP_SWIZZLE_64B : sw, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return FL_ERR_CUDA;
-    const bool b64 = which == FL_ST_MX8_MN_N64;     // B tile with 64-byte rows
+    box[0] = (cuuint32_t)rowb;
+    const bool b64 = which == FL_ST_MX8_MN_N64 || which == FL_ST_MX8_A_MN_2X64;     // B tile with 64-byte rows
     if (b64) { dims[0] = 64; strides[0] = 64; box[0] = 64; }
     if (enc(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(b), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, b64 ? CU_TENSOR_MAP_SWIZZLE_64B : sw, CU_TENSOR_MAP_L2_PROMOTION_NONE,

@@ -154,6 +154,7 @@ int fl_unpack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n
 #define FL_ST_WAIT_TIMEOUT 7   /* a wait that nothing completes: returns through the bounded-wait path */
 #define FL_ST_MX8_MN_N64 8     /* block-scaled MXFP8, A MN-major (128 B rows), B MN-major with N = 64 (64 B rows) */
 #define FL_ST_NVF4_N64_HI 9     /* NVFP4 with N = 64: rows 64..127 of B, whose scales are columns 2, 3 of each atom */
+#define FL_ST_MX8_A_MN_2X64 10  /* block-scaled MXFP8, A MN-major as two 64-byte-row blocks (M = 2 x 64), B MN-major N = 64 */
 int fl_selftest_mma(int32_t which, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, float* d,
                     int32_t* status, int64_t wait_cycles, void* stream);
 

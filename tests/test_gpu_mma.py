@@ -110,3 +110,15 @@ def test_block_scaled_mn_major_a_and_64_wide_mn_major_b():
     got = run(8, a, b, sfa, sfb)[:, :64]
     want = _mx8_expected(np.ascontiguousarray(av.T), np.pad(bv, ((0, 0), (0, 64))), sfa, sfb)[:, :64]
     np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-4)
+
+
+def test_block_scaled_a_as_two_64_wide_mn_major_blocks():
+    # the operand layout of the d = 64 backward's dQ product: A (k, m) held as two (k, 64) blocks of 64-byte rows
+    a, av = codes(17)
+    b, bv = codes(18, (128, 64))
+    g = np.random.default_rng(19)
+    sfa = g.integers(120, 134, size=(128, 4)).astype(np.uint8)
+    sfb = g.integers(120, 134, size=(128, 4)).astype(np.uint8)
+    got = run(10, a, b, sfa, sfb)[:, :64]
+    want = _mx8_expected(np.ascontiguousarray(av.T), np.pad(bv, ((0, 0), (0, 64))), sfa, sfb)[:, :64]
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-4)
