@@ -11,12 +11,12 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libflamia_b200.so")
-SOURCES = ["abi.cu", "quant.cu", "selftest.cu", "fwd.cu", "bwd.cu", "bwd_v1.cu", "side.cu", "noalloc.cu"]
+SOURCES = ["abi.cu", "quant.cu", "selftest.cu", "fwd.cu", "bwd.cu", "side.cu", "noalloc.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-O2", "--expt-relaxed-constexpr"]
 # the attention kernels may flush denormals and use approximate division; the quantisers and the scalar / post kernels
 # must not (their outputs are compared byte for byte)
-FAST_MATH = {"fwd.cu", "bwd.cu", "bwd_v1.cu"}
+FAST_MATH = {"fwd.cu", "bwd.cu"}
 
 
 def _stale(obj, srcs):

@@ -1,4 +1,4 @@
-// Backward main kernel for sm_100a (head_dim 128): dK, dV and the pre-scaled f16 dQ accumulator from block-scaled
+// Backward main kernel for sm_100a (head_dim 128 or 64): dK, dV and the pre-scaled f16 dQ accumulator from block-scaled
 // operands, software-pipelined over 64-query half tiles.
 //
 // Replaces the reference's FlashAttentionBackwardSm100FP4 (flash_attn/cute/flash_bwd_sm100_fp4.py:82; driver
@@ -15,6 +15,9 @@
 //   dQ^T_x = K^T dS-hat^T             block-scaled, M = head dim, N = 64 queries; A = K tile and B = dS-hat (shared
 //                                     memory) both MN-major; the f16 pre-scale B_m is folded into the A scale bytes
 //   dQ^T_x -> f16 -> TMA reduce-add into the (b, h, d, s) accumulator
+//   d = 64: block-scaled products need M = 128, so the product is taken the other way round, dQ_x = dS-hat_x K with
+//   A = dS-hat (shared memory, MN-major; its second 64-row block is whatever follows in memory and only fills the
+//   unused rows 64..127 of the result) and B = the K tile; rows = queries, accumulator layout (b, h, s, d)
 //   warps 0-3 compute half 0, warps 4-7 compute half 1 (thread = key row = TMEM lane, 64 query columns)
 //   warps 8-11 dQ reduction (thread = head-dim row)      warp 12 UMMA issuer      warp 13 TMA producer
 // TMEM: [0,64) / [64,128) S^T_x, then P-hat +0, dS-hat +16, six scale tiles +32..+56; [128,256) dV;
@@ -31,8 +34,6 @@
 // take f_K f_Q and f_V f_dO in the elementwise math; dV takes f_dO inside a block-scaled P-hat (one exponent per key row
 // x 32 queries); dK takes f_Q inside its dS-hat codes, dQ takes f_K inside its own; the operand scale tiles are unit.
 #include "flamia_internal.h"
-
-int fl_bwd_v1(const fl_attn_args* a, void* stream);
 
 namespace fl {
 
@@ -62,7 +63,13 @@ struct BwdParams {
 };
 
 struct BTile {
-  int bat, k0, nk, krel, q0, sq, off;     // as in bwd_v1.cu
+  int bat;    // batch coordinate of the tensor maps (0 for packed documents)
+  int k0;     // first key row of the tile (row index inside the batch entry)
+  int nk;     // valid keys of the tile (<= 128)
+  int krel;   // document-relative index of key row k0
+  int q0;     // first query row of the document (row index inside the batch entry)
+  int sq;     // queries of the document
+  int off;    // causal alignment: key j (document-relative) is visible to query i iff j <= i + off
 };
 
 enum { BB_KV = 0, BB_QFULL = 1, BB_QEMPTY = 3, BB_S = 5, BB_DP = 7, BB_P = 9, BB_DS = 11, BB_EX = 13, BB_DQF = 15,
@@ -109,15 +116,16 @@ __device__ __forceinline__ uint32_t exp448(uint32_t bits) {
 }
 __device__ __forceinline__ float pow2_inv(uint32_t ebyte) { return __uint_as_float((uint32_t)(254 - (int)ebyte) << 23); }
 
-template <bool FP4, int VAR>
+template <int D, bool FP4, int VAR>
 __global__ void __launch_bounds__(512, 1)
 bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                      const __grid_constant__ CUtensorMap tm_acc, const __grid_constant__ CUtensorMap tm_q4,
                      const __grid_constant__ CUtensorMap tm_k4, const __grid_constant__ CUtensorMap tm_dk,
                      const __grid_constant__ CUtensorMap tm_dv, const BwdParams p) {
-  constexpr int D = 128;
   constexpr int TILE_BYTES = 128 * D;
+  constexpr uint64_t OP_SWZ = (D == 128) ? SWZ_128 : SWZ_64;     // operand tiles: rows of D bytes
+  constexpr uint32_t OP_SBO = 8 * D;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;                                  // 1 tile
@@ -245,8 +253,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int n_steps = 2 * __shfl_sync(0xFFFFFFFFu, n_it, 0);
         const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
                        ds_addr = smem_u32(sDS);
-        const uint64_t dK_k = smem_desc(k_addr, 16, 1024, SWZ_128), dV_k = smem_desc(v_addr, 16, 1024, SWZ_128),
-                       dQ0 = smem_desc(q_addr, 16, 1024, SWZ_128), dDO0 = smem_desc(do_addr, 16, 1024, SWZ_128),
+        const uint64_t dK_k = smem_desc(k_addr, 16, OP_SBO, OP_SWZ), dV_k = smem_desc(v_addr, 16, OP_SBO, OP_SWZ),
+                       dQ0 = smem_desc(q_addr, 16, OP_SBO, OP_SWZ), dDO0 = smem_desc(do_addr, 16, OP_SBO, OP_SWZ),
+                       dDS_A = smem_desc(ds_addr, 8192, 512, SWZ_64),   // d = 64: dS-hat as A, next M block 8 KB further
                        dDS0 = smem_desc(ds_addr, 16, 512, SWZ_64);
         const uint64_t dK4 = smem_desc(smem_u32(sK4), 16, 512, SWZ_64), dQ40 = smem_desc(smem_u32(sQ4), 16, 512, SWZ_64),
                        dSF0 = smem_desc(smem_u32(sSF), 0, 128, SWZ_NONE);
@@ -323,9 +332,14 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 umma_mxf8_ts(tm + TC_DK, sx + TO_DS + 8 * kk, desc_adv(qy, kk * 32 * D),
                              idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), sx + TO_SFA_DK, sx + TO_SFB_Q, accum | kk);
 #pragma unroll
-              for (int kk = 0; kk < 4; ++kk)     // K = 128 keys; A = K tile (M = head dim), B = dS-hat half (N = 64 queries)
-                umma_mxf8_ss(tm + TC_DP + 64 * y, desc_adv(dK_k, kk * 32 * D), desc_adv(dDS0, y * 8192 + kk * 2048),
-                             idesc_bs(128, 64, 0, 0, 1, 1, 1, kk, kk), sx + TO_SFA_DQ, sx + TO_SFB_DQ, kk > 0);
+              for (int kk = 0; kk < 4; ++kk) {   // K = 128 keys
+                if (D == 128)      // A = K tile (M = head dim), B = dS-hat half (N = 64 queries)
+                  umma_mxf8_ss(tm + TC_DP + 64 * y, desc_adv(dK_k, kk * 32 * D), desc_adv(dDS0, y * 8192 + kk * 2048),
+                               idesc_bs(128, 64, 0, 0, 1, 1, 1, kk, kk), sx + TO_SFA_DQ, sx + TO_SFB_DQ, kk > 0);
+                else               // A = dS-hat half (M = 64 queries + 64 unused rows), B = K tile (N = head dim)
+                  umma_mxf8_ss(tm + TC_DP + 64 * y, desc_adv(dDS_A, y * 8192 + kk * 2048), desc_adv(dK_k, kk * 32 * D),
+                               idesc_bs(128, 64, 0, 0, 1, 1, 1, kk, kk), sx + TO_SFB_DQ, sx + TO_SFA_DQ, kk > 0);
+              }
               tc_commit(&bars[BB_DQF + y]);
               TRACE(0, tb, 5);
               if (y == 1) tc_commit(&bars[BB_QEMPTY + st]);
@@ -355,20 +369,24 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (r == 0) TRACE(3, t, 1);
         tc_fence_after();
         const uint32_t rowp = smem_u32(sDQ) + y * 16384 + r * 128;
+        // d = 128: thread = head-dim row of dQ^T, 64 query columns. d = 64: thread = query row (the first 64 lanes; the
+        // other two warps hold the product's unused rows), 64 head-dim columns. Either way 64 f16 = one 128-byte row.
+        if (D == 128 || warp < 10) {
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t v[32];
-          FL_TMEM_LD_32(lane_base + TC_DP + 64 * y + 32 * cc, v);
-          tc_wait_ld();
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t v[32];
+            FL_TMEM_LD_32(lane_base + TC_DP + 64 * y + 32 * cc, v);
+            tc_wait_ld();
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {     // 8 f16 = 16 bytes per chunk; 128 B swizzle by the row
-            uint32_t w[4];
+            for (int q4 = 0; q4 < 4; ++q4) {     // 8 f16 = 16 bytes per chunk; 128 B swizzle by the row
+              uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __half2 hh = __floats2half2_rn(__uint_as_float(v[8 * q4 + 2 * e]), __uint_as_float(v[8 * q4 + 2 * e + 1]));
-              w[e] = *reinterpret_cast<uint32_t*>(&hh);
+              for (int e = 0; e < 4; ++e) {
+                __half2 hh = __floats2half2_rn(__uint_as_float(v[8 * q4 + 2 * e]), __uint_as_float(v[8 * q4 + 2 * e + 1]));
+                w[e] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+              sts128(rowp + (((cc * 4 + q4) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
             }
-            sts128(rowp + (((cc * 4 + q4) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
           }
         }
         tc_fence_before();
@@ -378,7 +396,8 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_arrive_warp(&bars[BB_R2]);
         if (!(ok = mbar_wait(&bars[BB_R2], t & 1, p.ctl, abortp, 42))) break;
         if (tid == 256) {
-          tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, T.q0 + m * 128 + 64 * y, 0, head, T.bat);
+          if (D == 128) tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, T.q0 + m * 128 + 64 * y, 0, head, T.bat);
+          else tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, 0, T.q0 + m * 128 + 64 * y, head, T.bat);
           tma_store_commit();
         }
       }
@@ -631,11 +650,11 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
           for (int e = 0; e < D; ++e) y[e] = 0.f;
         }
-        if (x == 1 && p.had_dk) {       // dK of rotated operands: (y H / sqrt(128)) * signs
+        if (D == 128 && x == 1 && p.had_dk) {       // dK of rotated operands: (y H / sqrt(128)) * signs
 #pragma unroll
-          for (int hs = 1; hs < 128; hs <<= 1) {
+          for (int hs = 1; hs < D; hs <<= 1) {
 #pragma unroll
-            for (int i = 0; i < 128; ++i) {
+            for (int i = 0; i < D; ++i) {
               if ((i & hs) == 0) {
                 const float a = y[i], b2 = y[i + hs];
                 y[i] = a + b2;
@@ -645,7 +664,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
           constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
 #pragma unroll
-          for (int i = 0; i < 128; ++i) {
+          for (int i = 0; i < D; ++i) {
             y[i] *= 0.08838834764831845f;
             if ((NEG[i >> 5] >> (i & 31)) & 1) y[i] = -y[i];
           }
@@ -674,7 +693,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (mbar_wait(&bars[BB_EX + x], n_it & 1, p.ctl, abortp, 38) && r == 0) {
           const CUtensorMap* tm_out = (x == 0) ? &tm_dv : &tm_dk;
           tma_store_4d(tm_out, stage, 0, hkv, T.k0, T.bat);
-          tma_store_4d(tm_out, stage + 16384, 64, hkv, T.k0, T.bat);
+          if (D == 128) tma_store_4d(tm_out, stage + 16384, 64, hkv, T.k0, T.bat);
           tma_store_commit();
           tma_store_wait_read<0>();      // the shared-memory source must outlive the copy; the writes complete with the grid
         }
@@ -701,17 +720,17 @@ extern "C" int fl_debug_set_trace(void* buf) {
 
 extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   using namespace fl;
-  if (a && a->d == 64) return fl_bwd_v1(a, stream);
   if (!a || !a->q_codes || !a->k_codes || !a->v_codes || !a->do_codes || !a->status) return FL_ERR_BAD_ARG;
   if (!a->fac_q || !a->fac_k || !a->fac_v || !a->fac_do || !a->lse_log2 || !a->d_rows || !a->dq_acc || !a->dq_scale ||
       !a->dk || !a->dv)
     return FL_ERR_BAD_ARG;
-  if (a->d != 128) return FL_ERR_UNSUPPORTED;
+  if (a->d != 128 && a->d != 64) return FL_ERR_UNSUPPORTED;
   if (a->mode != FL_MODE_FP8 && a->mode != FL_MODE_FP4) return FL_ERR_UNSUPPORTED;
   const bool fp4 = a->mode == FL_MODE_FP4;
   if (fp4 && (!a->q4 || !a->k4 || !a->sfq4 || !a->sfk4)) return FL_ERR_BAD_ARG;
   const bool tl = (a->flags & FL_A_TOKEN_LOCAL) != 0, rl = (a->flags & FL_A_DQ_ROWLOCAL) != 0;
   if (tl && (!rl || fp4 || a->doc_start)) return FL_ERR_UNSUPPORTED;   // token-local needs the dQ side's own codes
+  if (a->d == 64 && (fp4 || rl || tl)) return FL_ERR_UNSUPPORTED;       // d = 64: the default 8-bit route only
   if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
   if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
   if (a->doc_start && (a->b != 1 || a->n_docs <= 0 || !a->doc_len || a->s_q != a->s_k)) return FL_ERR_BAD_ARG;
@@ -721,11 +740,13 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   if ((rc = make_rows_map(&mk, a->k_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
   if ((rc = make_rows_map(&mv, a->v_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
   if ((rc = make_rows_map(&mdo, a->do_codes, a->b, a->s_q, a->h, a->d, 128))) return rc;
-  if ((rc = make_acc_t_map_16(&macc, a->dq_acc, a->b, a->h, a->d, a->s_q))) return rc;
+  if (a->d == 128) rc = make_acc_t_map_16(&macc, a->dq_acc, a->b, a->h, a->d, a->s_q);
+  else rc = make_acc_map_16(&macc, a->dq_acc, a->b, a->h, a->s_q, a->d, 64);       // (b, h, s, d): boxes of 64 query rows
+  if (rc) return rc;
   // the NVFP4 copies (64-byte rows); the 8-bit route passes the E4M3 maps again, which the kernel never touches
-  if ((rc = make_rows_map(&mq4, fp4 ? (const void*)a->q4 : (const void*)a->q_codes, a->b, a->s_q, a->h, fp4 ? 64 : 128, 128)))
+  if ((rc = make_rows_map(&mq4, fp4 ? (const void*)a->q4 : (const void*)a->q_codes, a->b, a->s_q, a->h, fp4 ? 64 : a->d, 128)))
     return rc;
-  if ((rc = make_rows_map(&mk4, fp4 ? (const void*)a->k4 : (const void*)a->k_codes, a->b, a->s_k, a->h_kv, fp4 ? 64 : 128,
+  if ((rc = make_rows_map(&mk4, fp4 ? (const void*)a->k4 : (const void*)a->k_codes, a->b, a->s_k, a->h_kv, fp4 ? 64 : a->d,
                           128)))
     return rc;
   if ((rc = make_rows_map_16(&mdk, a->dk, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
@@ -748,15 +769,16 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   const int ntile = a->doc_start ? (a->s_k / 128 + a->n_docs) : a->s_k / 128;
   const int nb = a->doc_start ? 1 : a->b;
   dim3 grid = p.causal ? dim3(a->h_kv, nb, ntile) : dim3(ntile, a->h_kv, nb);
-  const int smem = 6 * 128 * 128 + 2 * 8192 + 2 * 16384 + 2048 + 1024 + (fp4 ? 3 * 8192 + 3 * 1024 : 0);
+  const int smem = 6 * 128 * a->d + 2 * 8192 + 2 * 16384 + 2048 + 1024 + (fp4 ? 3 * 8192 + 3 * 1024 : 0);
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
     kern<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, mdk, mdv, p);
     return FL_OK;
   };
-  if (fp4) rc = rl ? launch(bwd_kernel_pipelined<true, 1>) : launch(bwd_kernel_pipelined<true, 0>);
-  else if (tl) rc = launch(bwd_kernel_pipelined<false, 2>);
-  else rc = rl ? launch(bwd_kernel_pipelined<false, 1>) : launch(bwd_kernel_pipelined<false, 0>);
+  if (a->d == 64) rc = launch(bwd_kernel_pipelined<64, false, 0>);
+  else if (fp4) rc = rl ? launch(bwd_kernel_pipelined<128, true, 1>) : launch(bwd_kernel_pipelined<128, true, 0>);
+  else if (tl) rc = launch(bwd_kernel_pipelined<128, false, 2>);
+  else rc = rl ? launch(bwd_kernel_pipelined<128, false, 1>) : launch(bwd_kernel_pipelined<128, false, 0>);
   if (rc) return rc;
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }
