@@ -259,3 +259,28 @@ def test_state_matches_its_spec(form):
     want = (spec if is_docs else spec[2:]) + [((), torch.int64)]
     assert [(tuple(t.shape), t.dtype) for t in state] == [(tuple(sh), dt) for sh, dt in want]
     assert out.shape == q.shape
+
+
+def test_fp8_d64_packed_documents_and_window():
+    """Head dimension 64 through the packed form (repacked documents) and with a sliding window."""
+    import warnings
+    from flamia_blackwell_attention_b200 import flash_attn_fp8
+    lens = [300, 128, 77, 515]
+    h, d = 4, 64
+    starts = [sum(lens[:i]) for i in range(len(lens))]
+    total = sum(lens)
+    q, k, v, g = (t[0] for t in attention_inputs(1, total, h, 2, d, seed=41))
+    cu = torch.tensor(starts + [total], dtype=torch.int32, device="cuda")
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True, cu_seqlens_q=cu, cu_seqlens_k=cu,
+                                 max_seqlen_q=max(lens), max_seqlen_k=max(lens))
+    for s0, n in zip(starts, lens):
+        sl = slice(s0, s0 + n)
+        ro, _, rdq, rdk, rdv = A.attention_fp32(q[None, sl].float(), k[None, sl].float(), v[None, sl].float(),
+                                                g[None, sl].float(), True)
+        _check((o[sl], dq[sl], dk[sl], dv[sl]), (ro[0], rdq[0], rdk[0], rdv[0]), tol=7e-2)
+    q, k, v, g = attention_inputs(2, 512, 4, 2, d, seed=42)
+    o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True, window_size=(150, 0))
+    ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=True, window=(150, 0))
+    _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))

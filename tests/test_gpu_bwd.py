@@ -54,6 +54,10 @@ CASES = [
     (1, 256, 640, 2, 1, 128, True),
     (1, 640, 256, 2, 2, 128, True),
     (2, 512, 512, 2, 2, 128, False),
+    (2, 384, 384, 4, 1, 64, True),           # d = 64: GQA, odd tile count
+    (1, 256, 640, 2, 2, 64, True),           # d = 64: s_q != s_k
+    (1, 640, 256, 2, 1, 64, True),           # d = 64: leading rows see no key
+    (2, 512, 512, 2, 2, 64, False),          # d = 64: dense
 ]
 
 
