@@ -579,7 +579,10 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         FL_TMEM_ST_16(t_sx + TO_DS, dsw);
         if (RL) {
           // the dQ side's own codes: one exponent per (query, this warp's 32 keys); token-local: they carry f_K(key)
-          uint32_t mine[2] = {1u, 1u};
+          // per column: t = the exponent field of 2^(e - 119), e the UE8M0 byte with 448 * 2^(e - 127) >= amax, floored
+          // at e = 1; 2^(127 - e) is then the field 262 - (e + 8). (Integer and min / max instructions issue at half rate:
+          // the fewer per column the better.)
+          uint32_t mine[2] = {9u << 23, 9u << 23};
 #pragma unroll
           for (int w = 0; w < 16; ++w) {
             float v[4];
@@ -587,14 +590,15 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             for (int e = 0; e < 4; ++e) {
               const int j = 4 * w + e;
               const float a = TL ? pf[j] * fk_true : pf[j];
-              const uint32_t eq = exp448(warp_max_u32(__float_as_uint(fabsf(a))));
-              if (lane == (j & 31)) mine[j >> 5] = eq;
-              v[e] = a * pow2_inv(eq);
+              const uint32_t wm = warp_max_u32(__float_as_uint(a) & 0x7FFFFFFFu);
+              const uint32_t t = max((wm + 0x00200000u) & 0x7F800000u, 9u << 23);
+              if (lane == (j & 31)) mine[j >> 5] = t;
+              v[e] = a * __uint_as_float(0x83000000u - t);
             }
             dsw[w] = cvt_e4m3x4(v[0], v[1], v[2], v[3]);
           }
-          sEQ[x][lane][wq] = (uint8_t)mine[0];
-          sEQ[x][32 + lane][wq] = (uint8_t)mine[1];
+          sEQ[x][lane][wq] = (uint8_t)((mine[0] >> 23) - 8);
+          sEQ[x][32 + lane][wq] = (uint8_t)((mine[1] >> 23) - 8);
           mbar_arrive_warp(&bars[BB_EX + x]);
         }
         // the dQ^T product's MN-major B operand: row = key, 64 bytes = 4 chunks of 16 B, 64 B swizzle

@@ -352,7 +352,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           c[kb] = FP4 ? fq : fq * fk_row[j * 4 + kb];      // FP4: the block scales were applied by the tensor core
           sfv |= ((__float_as_uint(fv_row[j * 4 + kb]) >> 23) & 0xFF) << (8 * kb);
         }
-        // token-local: the tile's 128 per-key factors (same addresses for every thread: broadcast loads)
+        // token-local: the tile's 128 per-key factors (same addresses for every thread: broadcast loads through L1;
+        // staging them in shared memory was twice as slow: 384 broadcast reads per thread and tile saturate the
+        // shared-memory port that the tensor core's operand reads also go through)
         const float4* fk4 = reinterpret_cast<const float4*>(p.fac_k + (TL ? bh_k * p.s_k + T.k0 + j * 128 : 0));
         const float4* fv4 = reinterpret_cast<const float4*>(p.fac_v + (TL ? bh_k * p.s_k + T.k0 + j * 128 : 0));
         if (TL) {
@@ -379,11 +381,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (TL) {   // y = s f_Q f_K(key) scale + log2 f_V(key)
 #pragma unroll
           for (int e4 = 0; e4 < 32; ++e4) {
+            // log2 of a power of two without an int-to-float conversion (those run on the transcendental unit, which
+            // binds this kernel): the exponent field dropped into the mantissa of 2^23 reads as 2^23 + field
             const float4 k4 = __ldg(fk4 + e4), v4 = __ldg(fv4 + e4);
-            s[4 * e4 + 0] = fmaf(s[4 * e4 + 0], fq * k4.x, (float)((int)(__float_as_uint(v4.x) >> 23) - 127));
-            s[4 * e4 + 1] = fmaf(s[4 * e4 + 1], fq * k4.y, (float)((int)(__float_as_uint(v4.y) >> 23) - 127));
-            s[4 * e4 + 2] = fmaf(s[4 * e4 + 2], fq * k4.z, (float)((int)(__float_as_uint(v4.z) >> 23) - 127));
-            s[4 * e4 + 3] = fmaf(s[4 * e4 + 3], fq * k4.w, (float)((int)(__float_as_uint(v4.w) >> 23) - 127));
+            auto lg = [](float f) { return __uint_as_float(0x4B000000u | (__float_as_uint(f) >> 23)) - 8388735.0f; };
+            s[4 * e4 + 0] = fmaf(s[4 * e4 + 0], fq * k4.x, lg(v4.x));
+            s[4 * e4 + 1] = fmaf(s[4 * e4 + 1], fq * k4.y, lg(v4.y));
+            s[4 * e4 + 2] = fmaf(s[4 * e4 + 2], fq * k4.z, lg(v4.z));
+            s[4 * e4 + 3] = fmaf(s[4 * e4 + 3], fq * k4.w, lg(v4.w));
           }
         }
         const int kb0 = T.kofs + j * 128;                       // document-relative key of column 0
