@@ -284,3 +284,15 @@ def test_fp8_d64_packed_documents_and_window():
     o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True, window_size=(150, 0))
     ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=True, window=(150, 0))
     _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))
+
+
+@pytest.mark.parametrize("route", ["fp8", "fp4"])
+def test_f16_inputs_d128(route):
+    """float16 inputs and gradients at head dimension 128 on both routes."""
+    import flamia_blackwell_attention_b200 as F
+    fn = F.flash_attn_fp8 if route == "fp8" else F.flash_attn_fp4
+    q, k, v, g = (t.half() for t in attention_inputs(2, 384, 4, 2, 128, seed=51))
+    o, dq, dk, dv, _ = _step(fn, q, k, v, g, causal=True)
+    assert o.dtype == torch.float32 and dq.shape == q.shape          # _step returns float copies
+    ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=True, rotate_qk=True, fp4_qk=route == "fp4")
+    _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))
