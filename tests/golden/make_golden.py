@@ -93,7 +93,9 @@ def run_case(R, x, o=None, lse=None):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of the reference repository>")
+    root = sys.argv[1]
     R = load_reference(root)
     small = {}
     for dist in ("n01", "zeros", "mixed"):
