@@ -296,3 +296,26 @@ def test_f16_inputs_d128(route):
     assert o.dtype == torch.float32 and dq.shape == q.shape          # _step returns float copies
     ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=True, rotate_qk=True, fp4_qk=route == "fp4")
     _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))
+
+
+@pytest.mark.parametrize("dist", ["logit3", "outlier", "zeros", "tiny", "near_min_normal", "mixed", "subnorm_sf"])
+def test_extreme_input_families(dist):
+    """The quantiser test's input families through the whole fwd+bwd call: zeros, values near the bottom of the float range,
+    scattered x1000 outliers, per-group exponents spread over 2^+-60 (in V and dO). Outputs must be finite and track the
+    oracle's quantise-dequantise emulation of the same inputs (against fp32 attention the x1000 outliers alone cost 40 %:
+    that is the format, not the kernels). One known limit, shared with the reference: the f16 dQ accumulator's pre-scale
+    exponent is clamped to +-40, so gradients beyond 65504 * 2^40 (the 'mixed' family reaches 1e34) overflow it."""
+    from flamia_blackwell_attention_b200 import flash_attn_fp8
+    from inputs import make
+    b, s, h, d = 1, 384, 2, 128
+    q, k, v, g = (make((b, s, h, d), dist, seed=60 + i) for i in range(4))
+    if dist == "mixed":      # keep the scores representable: the spread goes to V and dO only
+        q, k = make((b, s, h, d), "n01", seed=70), make((b, s, h, d), "n01", seed=71)
+    o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True)
+    ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=True, rotate_qk=True)
+    for name, t, r in (("o", o, ro), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+        if dist == "mixed" and name == "dq":
+            continue
+        assert torch.isfinite(t).all(), (dist, name)
+        if torch.isfinite(r).all() and float(r.abs().max()) > 0:
+            assert A.accuracy(t, r)["rel_l2"] < 6e-2, (dist, name, A.accuracy(t, r))
