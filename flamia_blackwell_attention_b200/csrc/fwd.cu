@@ -10,6 +10,9 @@
 //                V has its own power-of-two factor; f_Q f_K multiplies each score, log2 f_V(key) is added to the exponent
 //                argument of P-hat (so P.V runs with unit scales) and the row sum takes P / f_V(key) back out.
 //
+// Masks: bottom-right aligned causal and / or a sliding window (query i sees keys i + off - left .. i + off + right); a block
+// starts at the first key tile any of its rows can see and only boundary tiles are masked element by element.
+//
 // CTA = 256 query rows (two 128-row stages) of one (batch | document, head); loop over 128-key tiles.
 //   warps 0-3   softmax stage 0 (thread r owns query row r: TMEM lane r)      warp 8  TMA producer
 //   warps 4-7   softmax stage 1                                               warp 9  UMMA issuer
