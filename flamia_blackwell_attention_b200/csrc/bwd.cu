@@ -158,7 +158,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   TRACE_INIT();
   if (tid == 0) TRACE(6, 0, 0);
 
-  if (tid == 0) {
+  // Set-up by the TMA thread itself, which then starts the first loads (K, V and the first Q / dO tile) before the CTA-wide
+  // barrier: they fly while tensor memory is allocated and the other warps arrive (~1300 clocks earlier first scores).
+  if (tid == 13 * 32) {
     abort_s = 0;
     mbar_init(&bars[BB_KV], 1);
     for (int i = 0; i < 2; ++i) {
@@ -190,6 +192,33 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
     }
     tile_s = t;
+    int mh = (t.sq + 127) / 128, ml = 0;      // as below: the query tiles that see this key tile
+    if (p.win_r >= 0 && t.krel - t.off - p.win_r > 0) ml = (t.krel - t.off - p.win_r) / 128;
+    if (p.win_l >= 0) mh = min(mh, max(0, t.krel + t.nk - 1 - t.off + p.win_l) / 128 + 1);
+    if (t.nk > 0) {
+      tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_do);
+      mbar_arrive_expect_tx(&bars[BB_KV], 2 * TILE_BYTES + (FP4 ? 8192 + 1024 : 0));
+      tma_load_4d(sK, &tm_k, &bars[BB_KV], 0, hkv, t.k0, t.bat);
+      tma_load_4d(sV, &tm_v, &bars[BB_KV], 0, hkv, t.k0, t.bat);
+      if (FP4) {
+        tma_load_4d(sK4, &tm_k4, &bars[BB_KV], 0, hkv, t.k0, t.bat);
+        bulk_load(sSF, p.sfk4 + (((size_t)t.bat * p.h_kv + hkv) * (p.s_k / 128) + t.k0 / 128) * 1024, 1024, &bars[BB_KV]);
+      }
+      if (mh > ml) {       // iteration 0: first head of the group, first query tile
+        const int head = hkv * grp, m = ml;
+        mbar_arrive_expect_tx(&bars[BB_QFULL + 0], 2 * TILE_BYTES + 1024 + (FP4 ? 8192 + 1024 : 0));
+        tma_load_4d(sQ, &tm_q, &bars[BB_QFULL + 0], 0, head, t.q0 + m * 128, t.bat);
+        if (FP4) {
+          tma_load_4d(sQ4, &tm_q4, &bars[BB_QFULL + 0], 0, head, t.q0 + m * 128, t.bat);
+          bulk_load(sSF + 1024, p.sfq4 + (((size_t)t.bat * p.h + head) * (p.s_q / 128) + (t.q0 + m * 128) / 128) * 1024, 1024,
+                    &bars[BB_QFULL + 0]);
+        }
+        tma_load_4d(sDO, &tm_do, &bars[BB_QFULL + 0], 0, head, t.q0 + m * 128, t.bat);
+        const size_t ro = ((size_t)t.bat * p.h + head) * p.s_q + t.q0 + m * 128;
+        bulk_load(sVec, p.lse_log2 + ro, 512, &bars[BB_QFULL + 0]);
+        bulk_load(sVec + 128, p.d_rows + ro, 512, &bars[BB_QFULL + 0]);
+      }
+    }
   }
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 512);
@@ -209,7 +238,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (p.win_l >= 0) m_hi = min(m_hi, max(0, T.krel + T.nk - 1 - T.off + p.win_l) / 128 + 1);
   const int n_m = (T.nk > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
   const int n_it = n_m * grp;                                          // tile iterations: GQA heads x query tiles
-  const bool early_out = (T.nk <= 0) || (*p.ctl.status != 0);
+  // (a status word already set by an earlier launch is not looked at: the first loads are in flight by now, and a
+  // kernel that runs after one that gave up does no harm)
+  const bool early_out = T.nk <= 0;
   if (tid == 0) TRACE(6, 0, 1);
 
   if (!early_out) {
@@ -217,15 +248,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (warp == 13) {
       // =================================================================== TMA producer
       if (lane == 0) {
-        tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_do);
-        mbar_arrive_expect_tx(&bars[BB_KV], 2 * TILE_BYTES + (FP4 ? 8192 + 1024 : 0));
-        tma_load_4d(sK, &tm_k, &bars[BB_KV], 0, hkv, T.k0, T.bat);
-        tma_load_4d(sV, &tm_v, &bars[BB_KV], 0, hkv, T.k0, T.bat);
-        if (FP4) {
-          tma_load_4d(sK4, &tm_k4, &bars[BB_KV], 0, hkv, T.k0, T.bat);
-          bulk_load(sSF, p.sfk4 + (((size_t)T.bat * p.h_kv + hkv) * (p.s_k / 128) + T.k0 / 128) * 1024, 1024, &bars[BB_KV]);
-        }
-        for (int it = 0; it < n_it; ++it) {
+        for (int it = 1; it < n_it; ++it) {      // K, V and iteration 0 were started during set-up
           const int st = it & 1, u = it >> 1;
           const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
           if (it >= 2 && !mbar_wait(&bars[BB_QEMPTY + st], (u & 1) ^ 1, p.ctl, abortp, 10)) break;

@@ -62,6 +62,7 @@ struct Tile {
   int off;    // causal alignment: key j (document-relative) is visible to query i iff j <= i + off
   int qrel;   // document-relative index of row q0
   int kofs;   // document-relative key of the first key row this CTA loads (a multiple of 128; > 0 under a left window)
+  int n[2];   // key tiles stage 0 / 1 walks: keys [kofs, kmax_i), n_i = ceil((kmax_i - kofs) / 128)
 };
 
 // barrier indices
@@ -116,7 +117,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   FTRACE_INIT();
   const int hkv = head / (p.h / p.h_kv);
 
-  if (tid == 0) {
+  // Set-up by the TMA thread itself, which then starts the first loads (Q and the first K / V tile) before the CTA-wide
+  // barrier: they fly while tensor memory is allocated and the other warps arrive.
+  if (tid == 8 * 32) {
     abort_s = 0;
     mbar_init(&bars[B_Q], 1);
     for (int i = 0; i < KV_STAGES; ++i) {
@@ -159,7 +162,31 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     t.kofs = 0;
     if (p.win_l >= 0 && t.nq > 0) t.kofs = (max(0, t.qrel + t.off - p.win_l) / 128) * 128;
     t.k0 += t.kofs;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int rows = min(128, t.nq - 128 * i);             // valid rows of the stage (<= 0: stage absent)
+      int kmax = t.sk;
+      if (p.win_r >= 0) kmax = min(t.sk, t.qrel + 128 * i + rows + t.off + p.win_r);
+      t.n[i] = (rows > 0 && kmax > t.kofs) ? (kmax - t.kofs + 127) / 128 : 0;
+    }
     tile_s = t;
+    if (t.nq > 0) {
+      tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+      const bool two = t.nq > 128;
+      mbar_arrive_expect_tx(&bars[B_Q], 2 * OP_BYTES + (FP4 ? (two ? 2048 : 1024) : 0));
+      tma_load_4d(sQ, &tm_q, &bars[B_Q], 0, head, t.q0, t.bat);
+      tma_load_4d(sQ + TILE_BYTES, &tm_q, &bars[B_Q], 0, head, t.q0 + 128, t.bat);
+      if (FP4)
+        bulk_load(sSF, p.sfq4 + (((size_t)t.bat * p.h + head) * (p.s_q / 128) + t.q0 / 128) * 1024, two ? 2048 : 1024, &bars[B_Q]);
+      if (max(t.n[0], t.n[1]) > 0) {      // key tile 0
+        mbar_arrive_expect_tx(&bars[B_KFULL], OP_BYTES + (FP4 ? 1024 : 0));
+        tma_load_4d(sK, &tm_k, &bars[B_KFULL], 0, hkv, t.k0, t.bat);
+        if (FP4)
+          bulk_load(sSF + 2048, p.sfk4 + (((size_t)t.bat * p.h_kv + hkv) * (p.s_k / 128) + t.k0 / 128) * 1024, 1024, &bars[B_KFULL]);
+        mbar_arrive_expect_tx(&bars[B_VFULL], TILE_BYTES);
+        tma_load_4d(sV, &tm_v, &bars[B_VFULL], 0, hkv, t.k0, t.bat);
+      }
+    }
   }
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 512);
@@ -172,33 +199,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const Tile T = tile_s;
   volatile int* abortp = &abort_s;
 
-  // keys visible to stage i: [kofs, kmax_i); tiles n_i = ceil((kmax_i - kofs) / 128)
-  int n_st[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int rows = min(128, T.nq - 128 * i);             // valid rows of the stage (<= 0: stage absent)
-    int kmax = T.sk;
-    if (p.win_r >= 0) kmax = min(T.sk, T.qrel + 128 * i + rows + T.off + p.win_r);
-    n_st[i] = (rows > 0 && kmax > T.kofs) ? (kmax - T.kofs + 127) / 128 : 0;
-  }
+  const int n_st[2] = {T.n[0], T.n[1]};
   const int n_max = max(n_st[0], n_st[1]);
-  const bool early_out = (T.nq <= 0) || (*p.ctl.status != 0);
+  // (a status word already set by an earlier launch is not looked at: the first loads are in flight by now, and a
+  // kernel that runs after one that gave up does no harm)
+  const bool early_out = T.nq <= 0;
 
   if (!early_out) {
     if (warp >= 8) fwd_reg_dealloc<72>();
     if (warp == 8) {
       // =================================================================== TMA producer
       if (lane == 0) {
-        tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-        const bool two = T.nq > 128;
-        mbar_arrive_expect_tx(&bars[B_Q], 2 * OP_BYTES + (FP4 ? (two ? 2048 : 1024) : 0));
-        tma_load_4d(sQ, &tm_q, &bars[B_Q], 0, head, T.q0, T.bat);
-        tma_load_4d(sQ + TILE_BYTES, &tm_q, &bars[B_Q], 0, head, T.q0 + 128, T.bat);
-        if (FP4) {
-          const uint8_t* src = p.sfq4 + (((size_t)T.bat * p.h + head) * (p.s_q / 128) + T.q0 / 128) * 1024;
-          bulk_load(sSF, src, two ? 2048 : 1024, &bars[B_Q]);
-        }
-        for (int j = 0; j < n_max; ++j) {
+        for (int j = 1; j < n_max; ++j) {       // Q and key tile 0 were started during set-up
           const int st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
           if (j >= KV_STAGES && !mbar_wait(&bars[B_KEMPTY + st], ph ^ 1, p.ctl, abortp, 10)) break;
           mbar_arrive_expect_tx(&bars[B_KFULL + st], OP_BYTES + (FP4 ? 1024 : 0));
