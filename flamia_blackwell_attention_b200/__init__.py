@@ -6,7 +6,7 @@ through the C ABI of include/flamia_b200.h; there is no CPU or PyTorch fallback.
 from .options import FP4AttnOptions, FP8AttnOptions, KernelTuning, TUNING_FIELDS
 from .plan import AttnPlan, resolve_fp4, resolve_fp8
 
-__all__ = ["flash_attn_fp4", "flash_attn_fp8", "FP4AttnOptions", "FP8AttnOptions", "KernelTuning", "TUNING_FIELDS",
+__all__ = ["flash_attn_fp4", "flash_attn_fp8", "check_status", "FP4AttnOptions", "FP8AttnOptions", "KernelTuning", "TUNING_FIELDS",
            "AttnPlan", "resolve_fp4", "resolve_fp8"]
 
 
@@ -16,4 +16,7 @@ def __getattr__(name):
     if name in ("flash_attn_fp4", "flash_attn_fp8"):
         from . import api
         return getattr(api, name)
+    if name == "check_status":
+        from ._routes import check_status
+        return check_status
     raise AttributeError(name)

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libflamia_b200.so")
 # status codes (csrc/sm100.cuh)
 FL_OK, FL_ERR_BAD_ARG, FL_ERR_CUDA, FL_ERR_UNSUPPORTED, FL_ERR_TOO_LARGE = 0, 1, 2, 3, 4
 FL_DEV_WAIT_TIMEOUT = 0x100
+FL_DEV_BAD_TABLE = 0x200
 ERR_NAMES = {1: "bad argument", 2: "CUDA error", 3: "unsupported configuration", 4: "size beyond the supported maximum"}
 
 FL_Q_HADAMARD, FL_Q_TOKEN_LOCAL, FL_Q_HADAMARD_NVFP4_ONLY = 1, 2, 4

@@ -19,26 +19,30 @@ from . import _routes
 
 _REG_LOCK = threading.Lock()
 _PLANS: list = []          # handle -> AttnPlan
+_PLAN_HANDLES: dict = {}   # AttnPlan (by value: plans are frozen) -> handle
 _ENTRIES: list = []        # backward entry handle -> (plan handle, docs meta)
+_ENTRY_HANDLES: dict = {}  # (plan handle, docs meta) -> backward entry handle
 
 
 def register_plan(plan) -> int:
+    """Handle of a plan. Equal plans share one handle, so the registry grows with the number of DISTINCT plans a
+    process resolves, not with the number of calls or of cache evictions."""
     with _REG_LOCK:
-        for i, p in enumerate(_PLANS):
-            if p is plan:
-                return i
-        _PLANS.append(plan)
-        return len(_PLANS) - 1
+        h = _PLAN_HANDLES.get(plan)
+        if h is None:
+            h = _PLAN_HANDLES[plan] = len(_PLANS)
+            _PLANS.append(plan)
+        return h
 
 
 def _register_entry(plan_id, docs_meta) -> int:
+    key = (plan_id, docs_meta)
     with _REG_LOCK:
-        key = (plan_id, docs_meta)
-        for i, e in enumerate(_ENTRIES):
-            if e == key:
-                return i
-        _ENTRIES.append(key)
-        return len(_ENTRIES) - 1
+        h = _ENTRY_HANDLES.get(key)
+        if h is None:
+            h = _ENTRY_HANDLES[key] = len(_ENTRIES)
+            _ENTRIES.append(key)
+        return h
 
 
 def _fwd_impl(q, k, v, docs: List[torch.Tensor], plan: int, docs_id: int):

@@ -9,12 +9,61 @@ No host synchronisation anywhere; everything is enqueued on the current stream.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib as L
 from . import kernels as K
 
 P_SHIFT_LOG2 = 8.0     # the backward recomputes P' = 2^8 P (its E4M3 P-hat then uses the normal range)
+
+
+def backward_scalars(softmax_scale, dq_boost=1.0):
+    """The eight kernel scalars of the reference's 8-bit backward (flash_attn/cute/device_scales.py:734-743, slots 0-7)
+    as this library uses them. Block-scaled operands carry their scales with the codes, so every operand descale is 1
+    and the scalars are constants: [0] softmax scale of S, [1] dP-sum scale, [2] dS boost 2^-8 (with P' = 2^8 P), [3] dV
+    scale 2^-8 (folded into the dV epilogue), [4] dK scale (the dK epilogue), [5] the f16 dQ pre-scale (per query tile on
+    the device: fl_dq_prescale; `dq_boost` stands for it here), [6] the D fold multiplier -2^-8 (applied by the dO
+    quantiser launch), [7] the dQ postprocess scale softmax_scale / pre-scale."""
+    import numpy as np
+    f = np.float32
+    p_shift = f(2.0 ** P_SHIFT_LOG2)
+    sm = f(softmax_scale)
+    return (sm, f(1.0), f(1.0) / p_shift, f(1.0) / p_shift, sm, f(dq_boost), -(f(1.0) / p_shift), sm / f(dq_boost))
+
+
+# --------------------------------------------------------------------------------------------------------------- status
+# Every device-side wait of the kernels is bounded; one that runs out writes 0x100 | site into the call's status word and
+# the kernel drains, leaving its outputs partly written. Reading the word costs a host synchronisation, so the hot path
+# never does it: the word of the most recent call per device is remembered here for check_status(), and the environment
+# variable FLAMIA_B200_CHECK_STATUS=1 makes every forward and backward check its own word (a debugging mode).
+_LAST_STATUS: dict = {}
+
+
+def _note_status(status):
+    _LAST_STATUS[status.device.index] = status
+    if os.environ.get("FLAMIA_B200_CHECK_STATUS", "0") not in ("", "0"):
+        check_status(status.device)
+
+
+def check_status(device=None) -> int:
+    """Synchronises `device` (default: the current one) and raises RuntimeError if the most recent flash_attn_fp8 /
+    flash_attn_fp4 call there (forward or backward) gave up a device-side wait; returns 0 otherwise."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    st = _LAST_STATUS.get(idx)
+    if st is None:
+        return 0
+    with torch.cuda.device(idx):
+        code = K.read_status(st)
+    if code:
+        what = f"a bounded wait ran out at site {code & 0xFF}" if code & L.FL_DEV_WAIT_TIMEOUT else \
+            (f"the document table is inconsistent (code {code:#x})" if code & L.FL_DEV_BAD_TABLE else f"code {code:#x}")
+        raise RuntimeError(f"flamia_blackwell_attention_b200: the last attention call on cuda:{idx} did not complete: "
+                           f"{what}; its outputs are not valid")
+    return 0
 
 
 # --------------------------------------------------------------------------------------------------------------- docs
@@ -154,6 +203,7 @@ def forward(plan, q, k, v, docs):
         lse_user = lse[0] if sh.aligned_varlen else lse.new_zeros(0)     # (h, total_q) on the aligned form only
     else:
         out_user, lse_user = out, lse
+    _note_status(status)
     return out_user, lse_user, state
 
 
@@ -184,7 +234,7 @@ def backward(plan, state, dout, docs_meta):
     b, s_q, h, d = out.shape
     acc = torch.empty(b, h, s_q, d, dtype=torch.float16, device=out.device)
     gq = K.quantize_fp8_blocks(gp, compute_d_with_output=out, shifted_log2_lse_from=lse, log2_lse_shift=P_SHIFT_LOG2,
-                               d_multiplier=-2.0 ** -P_SHIFT_LOG2, zero_accumulator=acc, output_tile_stats=True,
+                               d_multiplier=float(backward_scalars(plan.softmax_scale)[6]), zero_accumulator=acc, output_tile_stats=True,
                                token_local_exponents=tl)
     ks, ps = K.dq_prescale(gq["tile_stats"], vstats, kstats, causal_local=bw.dq_prescale == "causal_tile")
     had8 = f.qk_hadamard and not fp4           # only the 8-bit route's E4M3 codes are rotated
@@ -194,6 +244,7 @@ def backward(plan, state, dout, docs_meta):
                            token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all", window=f.window,
                            doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype)
+    _note_status(status)
     if docs is not None:
         tq = sh.tot_q if sh.varlen else sh.b * sh.s_q
         tk = sh.tot_k if sh.varlen else sh.b * sh.s_k

@@ -5,9 +5,9 @@ registered op lowbit_attn::fp8 / ::fp4, whose autograd node carries the plan han
 """
 from __future__ import annotations
 
-import collections
-import threading
+import functools
 import warnings
+from dataclasses import dataclass
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -18,44 +18,66 @@ from .plan import AttnPlan, _fail, resolve_fp4, resolve_fp8
 
 __all__ = ["flash_attn_fp4", "flash_attn_fp8"]
 
-_PLAN_CACHE_SIZE = 1024
-_PLAN_CACHE: "collections.OrderedDict" = collections.OrderedDict()
-_PLAN_LOCK = threading.Lock()
 _REPACK_WARNED = False
 REPACK_WARNING = (
-    "flash_attn_{entry} with cu_seqlens_q / cu_seqlens_k but without seqused_q / seqused_k: the documents are COPIED "
-    "into a buffer with every start rounded up to 128 tokens and unpacked afterwards (one extra read and write of q, k, "
-    "v, o and of dO, dQ, dK, dV). The zero-copy form lays each document out at a start that is a multiple of 128 "
-    "(cu_seqlens = those starts, total % 128 == 0) and passes its true length as seqused_q / seqused_k. (Warned once.)")
+    "flash_attn_{entry} got cu_seqlens_q / cu_seqlens_k without seqused_q / seqused_k. This library then gathers every "
+    "document into a padded buffer whose document starts are multiples of 128 and scatters the results back: one more "
+    "read and write of q, k, v, o and of dO, dQ, dK, dV. To avoid the copies, lay the documents out at starts that are "
+    "multiples of 128 yourself (cu_seqlens = those starts, total % 128 == 0) and pass the true lengths as seqused_q / "
+    "seqused_k. (Warned once.)")
 
 
-def _meta(t):
-    if t is None:
-        return None
-    if isinstance(t, torch.Tensor):
-        return (tuple(t.shape), t.dtype, bool(t.requires_grad), t.device.type)
-    return ("obj", type(t).__name__)
+@dataclass(frozen=True)
+class _TensorFacts:
+    """What plan resolution may look at in a tensor argument: nothing but metadata."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype
+    requires_grad: bool
+
+    @staticmethod
+    def of(t):
+        return _TensorFacts(tuple(t.shape), t.dtype, bool(t.requires_grad)) if isinstance(t, torch.Tensor) else t
+
+    def stand_in(self):
+        grad = self.requires_grad and self.dtype.is_floating_point
+        return torch.empty(self.shape, dtype=self.dtype, device="meta", requires_grad=grad)
+
+
+@dataclass(frozen=True)
+class _CallFacts:
+    """Hashable description of one call: everything a plan depends on and nothing else."""
+    entry: str
+    grad_mode: bool
+    dq_causal_prescale: bool
+    q: _TensorFacts
+    k: _TensorFacts
+    v: _TensorFacts
+    keywords: Tuple[Tuple[str, object], ...]
+
+
+@functools.lru_cache(maxsize=1024)
+def _plan_of(facts: _CallFacts) -> AttnPlan:
+    # plans are pure functions of argument values and tensor metadata, so they are resolved on meta stand-ins; a refusal
+    # raises out of here and is not remembered
+    resolve = resolve_fp8 if facts.entry == "fp8" else resolve_fp4
+    kw = {n: (x.stand_in() if isinstance(x, _TensorFacts) else x) for n, x in facts.keywords}
+    with torch.set_grad_enabled(facts.grad_mode):
+        return resolve(facts.q.stand_in(), facts.k.stand_in(), facts.v.stand_in(), **kw)
 
 
 def _cached_plan(resolve, q, k, v, kw) -> AttnPlan:
     from . import interface_bwd_fp4
+    entry = "fp8" if resolve is resolve_fp8 else "fp4"
+    if not all(isinstance(t, torch.Tensor) for t in (q, k, v)):
+        return resolve(q, k, v, **kw)           # the resolver words the refusal
+    facts = _CallFacts(entry, torch.is_grad_enabled(), bool(interface_bwd_fp4.DQ_CAUSAL_PRESCALE), _TensorFacts.of(q),
+                       _TensorFacts.of(k), _TensorFacts.of(v), tuple(sorted((n, _TensorFacts.of(x)) for n, x in kw.items())))
     try:
-        key = (resolve.__name__, torch.is_grad_enabled(), bool(interface_bwd_fp4.DQ_CAUSAL_PRESCALE), _meta(q), _meta(k),
-               _meta(v), tuple(sorted((n, _meta(x) if isinstance(x, torch.Tensor) else x) for n, x in kw.items())))
-        hash(key)
-    except TypeError:
-        return resolve(q, k, v, **kw)
-    with _PLAN_LOCK:
-        plan = _PLAN_CACHE.get(key)
-        if plan is not None:
-            _PLAN_CACHE.move_to_end(key)
-            return plan
-    plan = resolve(q, k, v, **kw)          # refusals raise here and are never cached
-    with _PLAN_LOCK:
-        _PLAN_CACHE[key] = plan
-        if len(_PLAN_CACHE) > _PLAN_CACHE_SIZE:
-            _PLAN_CACHE.popitem(last=False)
-    return plan
+        return _plan_of(facts)
+    except TypeError as exc:
+        if getattr(exc, "rule", None) is not None:
+            raise
+        return resolve(q, k, v, **kw)           # an unhashable argument (e.g. a callable object): resolve uncached
 
 
 def _run(plan, q, k, v, cu_q, cu_k, su_q, su_k, return_lse):
@@ -66,6 +88,15 @@ def _run(plan, q, k, v, cu_q, cu_k, su_q, su_k, return_lse):
     if sh.varlen and sh.tot_q != sh.tot_k:
         _fail("B8", NotImplementedError, "packed documents are self-attention documents here: q and k must share "
                                          "cu_seqlens (total_q == total_k)")
+    if sh.varlen:
+        # the kernels walk ONE document table (built from cu_seqlens_q / seqused_q): the key side must be the same
+        # tensor, otherwise a call with different key documents would silently run as self-attention over q's table
+        for a, b_, name in ((cu_q, cu_k, "cu_seqlens"), (su_q, su_k, "seqused")):
+            if a is None or b_ is None or a is b_:
+                continue
+            if tuple(a.shape) != tuple(b_.shape) or a.data_ptr() != b_.data_ptr():
+                _fail("B8", NotImplementedError, f"packed documents are self-attention documents here: pass the SAME tensor "
+                                                 f"as {name}_q and {name}_k (distinct query / key tables are not built)")
     if plan.fwd.ragged_documents and sh.s_q != sh.s_k:
         _fail("B8", NotImplementedError, "lengths that are no multiple of 128 run the batch rows as self-attention "
                                          f"documents: s_q must equal s_k; got {sh.s_q} and {sh.s_k}")

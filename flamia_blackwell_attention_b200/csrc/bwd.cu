@@ -179,15 +179,15 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       t.bat = bat_id; t.k0 = tile_id * 128; t.nk = min(128, p.s_k - t.k0); t.krel = t.k0; t.q0 = 0; t.sq = p.s_q;
       t.off = p.s_k - p.s_q;
     } else {
-      int x = tile_id, dsel = -1;
+      int x = tile_id, dsel = -1, len = 0, st = 0;
       for (int dI = 0; dI < p.n_docs; ++dI) {
-        const int nb = (p.doc_len[dI] + 127) / 128;
+        doc_entry(p.doc_start, p.doc_len, dI, p.s_k, p.ctl.status, st, len);
+        const int nb = (len + 127) / 128;
         if (x < nb) { dsel = dI; break; }
         x -= nb;
       }
       if (dsel < 0) { t.nk = 0; t.bat = 0; t.k0 = 0; t.krel = 0; t.q0 = 0; t.sq = 0; t.off = 0; }
       else {
-        const int len = p.doc_len[dsel], st = p.doc_start[dsel];
         t.bat = 0; t.k0 = st + x * 128; t.nk = min(128, len - x * 128); t.krel = x * 128; t.q0 = st; t.sq = len; t.off = 0;
       }
     }
@@ -575,6 +575,15 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             pf[j + 1] *= fmaf(__uint_as_float(pv[j + 1]), b4.y, d4.y);
             pf[j + 2] *= fmaf(__uint_as_float(pv[j + 2]), b4.z, d4.z);
             pf[j + 3] *= fmaf(__uint_as_float(pv[j + 3]), b4.w, d4.w);
+            if (!full) {
+              // masked entries hold P' = 0, but their dP^T or D'' may come from rows outside the document (padding or
+              // whatever the buffer held: possibly Inf / NaN), and 0 * NaN is NaN: select, do not multiply
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int qi = q_first + j + e;
+                pf[j + e] = (key_valid && qi >= vis_from && qi <= vis_to && qi < T.sq) ? pf[j + e] : 0.f;
+              }
+            }
             // the dK side carries f_Q(query) when the operands are token-local
             am = fmaxf(am, fmaxf(fmaxf(fabsf(pf[j] * q4.x), fabsf(pf[j + 1] * q4.y)),
                                  fmaxf(fabsf(pf[j + 2] * q4.z), fabsf(pf[j + 3] * q4.w))));

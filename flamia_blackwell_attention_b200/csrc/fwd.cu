@@ -144,15 +144,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       t.off = p.s_k - p.s_q; t.qrel = t.q0;
     } else {
       // documents sit at 128-aligned starts of one packed batch entry; block x -> (document, 256-row block)
-      int x = blk_id, dsel = -1, blk = 0;
+      int x = blk_id, dsel = -1, blk = 0, len = 0, st = 0;
       for (int dI = 0; dI < p.n_docs; ++dI) {
-        const int nb = (p.doc_len[dI] + 255) / 256;
+        doc_entry(p.doc_start, p.doc_len, dI, p.s_q, p.ctl.status, st, len);
+        const int nb = (len + 255) / 256;
         if (x < nb) { dsel = dI; blk = x; break; }
         x -= nb;
       }
       if (dsel < 0) { t.nq = 0; t.bat = 0; t.q0 = 0; t.k0 = 0; t.sk = 0; t.off = 0; t.qrel = 0; }
       else {
-        const int len = p.doc_len[dsel], st = p.doc_start[dsel];
         if (p.causal) blk = (len + 255) / 256 - 1 - blk;
         t.bat = 0; t.q0 = st + blk * 256; t.nq = min(256, len - blk * 256); t.k0 = st; t.sk = len; t.off = 0;
         t.qrel = blk * 256;

@@ -41,8 +41,12 @@ extern "C" int fl_bwd_static_acc(const fl_attn_args* args, const float* post_sca
   using namespace fl;
   if (!args || !post_scale || !dq) return FL_ERR_BAD_ARG;
   if (args->b <= 0 || args->h <= 0 || args->s_q <= 0 || args->d <= 0) return FL_ERR_BAD_ARG;
+  // each factor is checked against the limit first, so the product below cannot overflow
+  const long long lim = (long long)FL_STATIC_ACC_MAX_ELEMS;
+  if (args->b > lim || args->h > lim || args->s_q > lim || args->d > lim) return FL_ERR_TOO_LARGE;
+  if ((long long)args->b * args->h > lim || (long long)args->s_q * args->d > lim) return FL_ERR_TOO_LARGE;
   const long long elems = (long long)args->b * args->h * args->s_q * args->d;
-  if (elems > (long long)FL_STATIC_ACC_MAX_ELEMS) return FL_ERR_TOO_LARGE;
+  if (elems > lim) return FL_ERR_TOO_LARGE;
   void* acc = nullptr;
   int rc = static_acc_address(&acc);
   if (rc != FL_OK) return rc;

@@ -3,7 +3,7 @@
 //
 // Every wait in this library is bounded: a spin that exceeds its cycle budget records a code in the kernel's global
 // status word, raises the CTA's abort flag and returns false; the caller unwinds to the common exit where TMEM is
-// released. A kernel therefore always terminates and the host reads the status word through fl_last_status().
+// released. A kernel therefore always terminates and the host reads the status word through fl_read_status().
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -22,12 +22,29 @@ enum : int {
   FL_ERR_TOO_LARGE = 4,
   // device-side (written to the status word by a bounded wait): 0x100 | site
   FL_DEV_WAIT_TIMEOUT = 0x100,
+  // a packed-document table entry that does not fit the buffer (start negative, not a multiple of 128 or past the end,
+  // or start + length past the end): the entry is clamped, nothing out of bounds is touched, and this code is recorded
+  FL_DEV_BAD_TABLE = 0x200,
 };
 
 struct DevCtl {
   int* status;              // global status word (0 = ok)
   long long wait_cycles;    // budget of one wait
 };
+
+// One entry of a packed-document table, made safe: a start that is not a tile-aligned row of the buffer gives an empty
+// document, a length that runs past the buffer is cut; either way the status word says so.
+__device__ __forceinline__ void doc_entry(const int32_t* doc_start, const int32_t* doc_len, int i, int total, int* status,
+                                          int& start, int& len) {
+  start = doc_start[i];
+  len = doc_len[i];
+  const bool bad_start = start < 0 || (start & 127) != 0 || start >= total;
+  if (bad_start || len < 0 || len > total - start) {
+    atomicCAS(status, 0, FL_DEV_BAD_TABLE);
+    if (bad_start) { start = 0; len = 0; }
+    else len = max(0, min(len, total - start));
+  }
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -147,8 +147,11 @@ def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L
     dev = qc.device
     if status is None:
         status = new_status(dev)
-    out = torch.empty(b, s_q, h, d, dtype=out_dtype, device=dev)
-    lse = torch.empty(b, h, s_q, dtype=torch.float32, device=dev)
+    # documents: the kernel writes only the rows of its documents; padding rows and unused tail tiles must read as
+    # zeros afterwards (the backward prologue forms rowsum(O * dO) for every row of the buffer)
+    alloc = torch.empty if doc_start is None else torch.zeros
+    out = alloc(b, s_q, h, d, dtype=out_dtype, device=dev)
+    lse = alloc(b, h, s_q, dtype=torch.float32, device=dev)
     a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode,
                   flags=L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0, status=status, doc_start=doc_start,
                   doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local, window=window)
@@ -182,7 +185,8 @@ def dq_prescale(stats_do, stats_v, stats_k, *, causal_local=False, unit=1.0):
 
 
 def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torch.bfloat16):
-    """dq (b, s, h, d) = cast(acc (b, h, s, d) f16 * post_scale[b, s / 128] * mult), optionally rotated back."""
+    """dq (b, s, h, d) = cast(acc * post_scale[b, s / 128] * mult), optionally rotated back. acc is the f16 accumulator
+    in the backward kernel's layout: (b, h, d, s) at d = 128, (b, h, s, d) at d = 64."""
     dq = torch.empty(b, s, h, d, dtype=out_dtype, device=acc.device)
     L.check(L.load().fl_dq_post(L.ptr(acc), L.ptr(post_scale), float(mult), L.ptr(dq), b, s, h, d, int(bool(unrotate)),
                                 int(out_dtype == torch.float16), _stream()), "fl_dq_post")
@@ -193,7 +197,8 @@ def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax
              mode=L.FL_MODE_FP8, had_dk=False, status=None, doc_start=None, doc_len=None, wait_cycles=0,
              token_local=False, dq_rowlocal=False, window=None):
     """Backward main kernel on quantised operands. q / k / v / do: quantiser outputs (codes, fac). Adds the pre-scaled
-    dQ partials into dq_acc (b, h, s_q, d) f16 and returns (dk, dv, status), each (b, s_k, h_kv, d)."""
+    dQ partials into the f16 accumulator dq_acc of b * h * s_q * d elements ((b, h, d, s_q) at d = 128, (b, h, s_q, d)
+    at d = 64) and returns (dk, dv, status), each (b, s_k, h_kv, d)."""
     kc = k["codes"]
     b, s_k, h_kv, d = kc.shape
     dev = kc.device

@@ -3,7 +3,9 @@
  * Plain pointers and sizes only; every pointer is a CUDA device pointer unless stated otherwise; every function
  * enqueues on the given cudaStream_t (passed as void*), never synchronises the host, never allocates device memory,
  * and returns 0 or a positive FL_ERR_* code. Device-side problems (a bounded wait that ran out) are reported through
- * the int status word the caller passes in (0 = ok) and can be read with fl_read_status().
+ * the int status word the caller passes in (0 = ok) and can be read with fl_read_status(): 0x100 | site = that wait
+ * gave up and the kernel drained with its outputs partly written; 0x200 = an entry of the packed-document table did not
+ * fit the buffer and was clamped (nothing out of bounds was touched).
  *
  * The reference has no C ABI on this path: its boundary is Python over CuTe-DSL JIT kernels. Each entry point below
  * names the reference interface it replaces (paths inside the reference repository).
@@ -42,7 +44,8 @@ typedef struct fl_quant_args {
   uint8_t* sf4;         /* (b, h, s/128, d/64, 512) E4M3 scale atoms, rows = tokens, K = d/16 */
   float* d_out;         /* (b, h, s): d_multiplier * rowsum(O * dequant(codes)) in the fixed tree order */
   float* lse_log2;      /* (b, h, s): (lse == -inf ? 0 : lse * log2 e) - lse_shift */
-  void* zero_acc;       /* (b, h, s, d) f16 accumulator, zero-filled */
+  void* zero_acc;       /* f16 dQ accumulator of b * h * s * d elements, zero-filled (a flat fill: its layout is the backward's,
+                           (b, h, d, s) at d = 128 and (b, h, s, d) at d = 64, see fl_attn_args.dq_acc) */
   float* tile_stats;    /* (b, h, s/128, 2): amax and max row sum of squares of the values quantised */
   int32_t b, s, h, d;
   int32_t flags;
@@ -119,8 +122,10 @@ int fl_dq_prescale(const float* stats_do, const float* stats_v, const float* sta
                    int32_t nt_q, int32_t nt_k, int32_t causal_local, float unit, float* kernel_scale, float* post_scale,
                    void* stream);
 
-/* dQ postprocess: dq[b, s, h, :] = cast(acc[b, h, s, :] * post_scale[b, s/128] * mult) with optional Hadamard
- * back-rotation. Replaces flash_attn/cute/dq_postprocess_cute.py:46 DQPostprocess / bwd_2cta8_side.dq_postprocess_2cta8. */
+/* dQ postprocess: dq[b, s, h, c] = cast(acc(b, h, s, c) * post_scale[b, s/128] * mult) with optional Hadamard
+ * back-rotation, where acc(b, h, s, c) is element [b, h, c, s] of the (b, h, d, s) accumulator at d = 128 (the backward
+ * kernel produces transposed dQ tiles) and element [b, h, s, c] of the (b, h, s, d) accumulator at d = 64.
+ * Replaces flash_attn/cute/dq_postprocess_cute.py:46 DQPostprocess / bwd_2cta8_side.dq_postprocess_2cta8. */
 int fl_dq_post(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s, int32_t h,
                int32_t d, int32_t unrotate, int32_t out_f16, void* stream);
 

@@ -10,8 +10,10 @@ Restates, in plain PyTorch on the CPU, the two pieces the reference composes for
 
 qdq_attention() = quantise Q, K, V, dO with the quantiser oracle (token-block MXFP8, optionally NVFP4 for the S operands)
 -> dequantise -> fp32 attention. The roundings of P-hat and dS-hat inside the kernels are not emulated (fp32 softmax).
-Parity pin: the quantiser part is pinned byte-for-byte by tests/test_oracle_golden.py; the fp32 attention part is pinned
-against torch autograd in tests/test_oracle_attention.py.
+Parity pin: the quantiser part is pinned byte-for-byte by tests/test_oracle_golden.py; attention_fp32,
+attention_docs_fp32 and accuracy are pinned by tests/test_oracle_attention.py against tests/golden/attention_small.npz,
+written by tests/golden/make_golden_attention.py from the reference's own `reference`, `reference_docs`, `accuracy`
+and (rectangular / bottom-right causal cases) tests/cute/test_lowprec_api.py:1346 `_ref_bottom_right`, run on CPU.
 """
 from __future__ import annotations
 

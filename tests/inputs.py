@@ -72,3 +72,31 @@ def packed_doc_lengths(spec_total=16384, lo=128, hi=8192, seed=0):
     if len(out) > 1 and out[-1] < 16:
         out[-2] += out.pop()
     return out
+
+
+def br_inputs(b, sq, sk, h, hk, d, seed):
+    """(q, k, v, dO) bf16 with s_q != s_k, drawn in that order from one generator (the reference test's order,
+    tests/cute/test_lowprec_api.py:1390-1394)."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(b, sq, h, d, generator=g).to(torch.bfloat16)
+    k, v = (torch.randn(b, sk, hk, d, generator=g).to(torch.bfloat16) for _ in range(2))
+    do = torch.randn(b, sq, h, d, generator=g).to(torch.bfloat16)
+    return q, k, v, do
+
+
+def scale_stats(b, hq, hk, tq, tk, kind, seed):
+    """Per-tile statistics for the f16 dQ pre-scale tables: (max ||dO_q||^2 (b hq tq), max ||V_k||^2, max|K| (b hk tk)) with
+    the edge cases of the bound: zeros (the cap), overflow (the floor), tiny values."""
+    g = torch.Generator().manual_seed(seed)
+    dn = torch.rand(b * hq * tq, generator=g) * 300.0
+    vn = torch.rand(b * hk * tk, generator=g) * 200.0
+    km = torch.rand(b * hk * tk, generator=g) * 9.0
+    if kind == "zeros":
+        dn[: hq * tq] = 0.0          # first batch row: zero bound -> the cap 2^40
+    if kind == "huge":
+        dn *= 1e30
+        vn *= 1e30                  # an intermediate overflows -> the floor 2^-40
+    if kind == "tiny":
+        dn *= 1e-20
+        km *= 1e-12
+    return dn, vn, km
