@@ -1,11 +1,15 @@
 """Headline benchmark: causal-adjusted attention TFLOPS of one public fwd+bwd call (quantisation included) on the
-reference's headline cell b4 s4096 h16 d128 causal, MXFP8 route (flash_attn_fp8 defaults), synthetic seeded inputs.
+reference's headline cell b4 s4096 h16 d128 causal, synthetic seeded inputs: the MXFP8 route (flash_attn_fp8 defaults) is
+the line's `value`, the mixed NVFP4 / FP8 route (flash_attn_fp4 defaults) is reported in `routes.fp4` of the same line.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--route fp8|fp4] [--dense]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--dense] [--soak SECONDS]
 
 One process per GPU (torchrun for N > 1). The path has no collective: every rank runs its own slice of a global batch of
 4 N rows (weak scaling by (batch, head)); only the timing is reduced (max over ranks). Prints ONE JSON line on rank 0.
 FLOP rule (the reference benchmark's): fwd = 4 b h d pairs, pairs = s (s + 1) / 2 causal | s^2 dense; step = 3.5 x fwd.
+Timing protocol (the reference benchmark's `step` mode, benchmarks/benchmark_lowprec_attn.py:942-976): one step is captured
+in a CUDA graph; a batch = exactly K replays between two CUDA events; batches repeat until `--soak` seconds (2.5) have
+passed and the MEDIAN batch gives ms_per_step, so the figure is a sustained one with the clocks sampled inside it.
 """
 import argparse
 import json
@@ -136,14 +140,130 @@ def run_reference(args, rank, world):
         "gpu_launches": 0}))
 
 
+# DRAM read + write bytes of one backward-kernel launch, from the ncu capture summarised in
+# profiles/bwd_kernel_pipelined_b2_s4096_h16_d128.md (cell b2; traffic is proportional to the batch: independent (batch,
+# head) problems), per route, causal only
+NCU_BWD_TRAFFIC_B2 = {"fp8": 164.9e6, "fp4": 225.1e6}
+
+
+def measure_route(fn, route, causal, tensors, args, world, dist, K, clock_gpu=None):
+    """Sustained step time of one public fwd+bwd call + per-kernel CUDA-event times. Returns a dict (this rank's values)."""
+    import torch
+    import flamia_blackwell_attention_b200._routes as R
+    q, k, v, g = tensors
+    W = max(args.warmup, 3)
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        out = fn(q, k, v, causal=causal)
+        out.backward(g)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        step()
+    barrier()
+    # ---- the timed steps replay one captured step (8 launches + the status-word fill): no host launch gaps
+    run_step, mode = step, "eager"
+    if not args.no_graph:
+        try:
+            q.grad = k.grad = v.grad = None
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn(q, k, v, causal=causal).backward(g)
+            run_step, mode = graph.replay, "cuda graph replay"
+            for _ in range(3):
+                run_step()
+        except Exception as exc:      # capture is an optimisation of the launch path only
+            print(f"bench: graph capture failed ({exc!r}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+            run_step, mode = step, "eager"
+    barrier()
+    sampler = ClockSampler(clock_gpu) if clock_gpu is not None else None
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    batches = []
+    wall0 = time.time()
+    while True:
+        t0.record()
+        for _ in range(args.steps):
+            run_step()
+        t1.record()
+        torch.cuda.synchronize()
+        batches.append(t0.elapsed_time(t1) / args.steps)
+        if time.time() - wall0 >= args.soak:
+            break
+    wall1 = time.time()
+    clocks = sampler.stop((wall0, wall1)) if sampler else None
+    ms = sorted(batches)[len(batches) // 2]
+    # ---- per-kernel event pairs: eager steps right after the soak (event records cannot be timed inside a captured graph)
+    ev = {n: [] for n in ("fwd", "bwd", "quant", "dq_post")}
+    orig = {n: getattr(K, n) for n in ("attn_fwd", "attn_bwd", "quantize_fp8_blocks", "dq_post")}
+
+    def timed(name, f):
+        def w(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = f(*a, **kw)
+            e1.record()
+            ev[name].append((e0, e1))
+            return r
+        return w
+    K.attn_fwd, K.attn_bwd = timed("fwd", orig["attn_fwd"]), timed("bwd", orig["attn_bwd"])
+    K.quantize_fp8_blocks, K.dq_post = timed("quant", orig["quantize_fp8_blocks"]), timed("dq_post", orig["dq_post"])
+    n_ev = 20
+    try:
+        for _ in range(n_ev):
+            step()
+        torch.cuda.synchronize()
+    finally:
+        for n, f in orig.items():
+            setattr(K, n, f)
+    per = {n: sum(a.elapsed_time(b) for a, b in ev[n]) / n_ev for n in ev}      # ms per step (quant: its four launches)
+    R.check_status()          # a device-side wait that gave up anywhere above fails the run
+    return dict(ms=ms, mode=mode, batches=len(batches), clocks=clocks, k_fwd=per["fwd"], k_bwd=per["bwd"],
+                k_quant=per["quant"], k_dq_post=per["dq_post"], seconds=wall1 - wall0)
+
+
+def copy_probe(dev, tensors_host, n=6):
+    """Plain pinned-memory cudaMemcpyAsync rates of this rank, no kernels: (h2d GB/s, d2h GB/s), both directions at once as
+    in the end-to-end loop."""
+    import torch
+    d = [torch.empty_like(t, device=dev) for t in tensors_host]
+    back = [torch.empty_like(t).pin_memory() for t in tensors_host]
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    nbytes = sum(t.numel() * t.element_size() for t in tensors_host)
+    torch.cuda.synchronize()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    with torch.cuda.stream(s_in):
+        e[0].record(s_in)
+        for _ in range(n):
+            for a, b in zip(d, tensors_host):
+                a.copy_(b, non_blocking=True)
+        e[1].record(s_in)
+    with torch.cuda.stream(s_out):
+        e[2].record(s_out)
+        for _ in range(n):
+            for a, b in zip(back, d):
+                a.copy_(b, non_blocking=True)
+        e[3].record(s_out)
+    torch.cuda.synchronize()
+    return n * nbytes / (e[0].elapsed_time(e[1]) * 1e6), n * nbytes / (e[2].elapsed_time(e[3]) * 1e6)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--route", default="fp8", choices=["fp8", "fp4"])
+    ap.add_argument("--route", default="both", choices=["both", "fp8", "fp4"],
+                    help="both: fp8 is the line's value, fp4 rides in routes.fp4; fp8 / fp4: only that route")
     ap.add_argument("--dense", action="store_true")
+    ap.add_argument("--soak", type=float, default=2.5, help="seconds of repeated K-step batches per route")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of replaying one captured step")
     ap.add_argument("--profile-case", action="store_true",
@@ -165,17 +285,21 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    from flamia_blackwell_attention_b200 import flash_attn_fp4, flash_attn_fp8, kernels as K
+    import flamia_blackwell_attention_b200 as F
+    from flamia_blackwell_attention_b200 import kernels as K
+    import flamia_blackwell_attention_b200._routes as R
     from tests.inputs import attention_inputs
-    fn = flash_attn_fp8 if args.route == "fp8" else flash_attn_fp4
+    fns = {"fp8": F.flash_attn_fp8, "fp4": F.flash_attn_fp4}
     causal = not args.dense
     if args.profile_case:
+        fn = fns["fp4" if args.route == "fp4" else "fp8"]
         pq, pk, pv, pg = (t.to(dev) for t in attention_inputs(2, S, H, HKV, D, seed=0))
         pq.requires_grad_(True); pk.requires_grad_(True); pv.requires_grad_(True)
         for _ in range(args.warmup + args.steps):
             pq.grad = pk.grad = pv.grad = None
             fn(pq, pk, pv, causal=causal).backward(pg)
         torch.cuda.synchronize()
+        F.check_status()
         print(json.dumps({"profile_case": f"b2 s{S} h{H} d{D}", "steps": args.warmup + args.steps, "launches_per_step": 8}))
         return
     W = max(args.warmup, 3)
@@ -188,82 +312,25 @@ def main():
     q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
     torch.cuda.synchronize()
 
-    # per-kernel event pairs around the two tensor-core kernels (same stream as the launches)
-    ev = {"fwd": [], "bwd": []}
-    timing = {"on": False}
-    _fwd, _bwd = K.attn_fwd, K.attn_bwd
-
-    def timed(name, f):
-        def w(*a, **kw):
-            if not timing["on"]:
-                return f(*a, **kw)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            r = f(*a, **kw)
-            e1.record()
-            ev[name].append((e0, e1))
-            return r
-        return w
-    K.attn_fwd, K.attn_bwd = timed("fwd", _fwd), timed("bwd", _bwd)
-    import flamia_blackwell_attention_b200._routes as R
-    R.K = K
-
-    def step():
-        q.grad = k.grad = v.grad = None
-        out = fn(q, k, v, causal=causal)
-        out.backward(g)
-        return out
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local) if rank == 0 else None
-    for _ in range(W):
-        step()
-    barrier()
-    # per-kernel event pairs: a short eager pass (event records cannot be timed inside a captured graph)
-    timing["on"] = True
-    for _ in range(min(args.steps, 20)):
-        step()
-    torch.cuda.synchronize()
-    timing["on"] = False
-    k_fwd = sum(a.elapsed_time(b) for a, b in ev["fwd"]) / max(len(ev["fwd"]), 1)
-    k_bwd = sum(a.elapsed_time(b) for a, b in ev["bwd"]) / max(len(ev["bwd"]), 1)
-    # the timed steps replay one captured step (8 launches + the status-word fill): no host launch gaps between kernels
-    run_step, mode = step, "eager"
-    if not args.no_graph:
-        try:
-            q.grad = k.grad = v.grad = None
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                fn(q, k, v, causal=causal).backward(g)
-            run_step, mode = graph.replay, "cuda graph replay"
-            for _ in range(3):
-                run_step()
-        except Exception as exc:      # capture is an optimisation of the launch path only
-            print(f"bench: graph capture failed ({exc!r}); timing eager launches", file=sys.stderr)
-            torch.cuda.synchronize()
-            run_step, mode = step, "eager"
-    barrier()
-    wall0 = time.time()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        run_step()
-    t1.record()
-    barrier()
-    wall1 = time.time()
-    ms = t0.elapsed_time(t1) / args.steps
-    clocks = sampler.stop((wall0, wall1)) if sampler else None
+    main_route = "fp4" if args.route == "fp4" else "fp8"
+    res = {main_route: measure_route(fns[main_route], main_route, causal, (q, k, v, g), args, world, dist, K,
+                                     clock_gpu=local if rank == 0 else None)}
+    if args.route == "both":
+        res["fp4"] = measure_route(fns["fp4"], "fp4", causal, (q, k, v, g), args, world, dist, K,
+                                   clock_gpu=local if rank == 0 else None)
+    fn = fns[main_route]
 
     # ---- end to end through the public call with HOST buffers: every step copies q, k, v, dO in from pinned host memory
     # and O, dQ, dK, dV back out. Three streams (copy in, compute, copy out) and two device input sets: the copy-in of
     # step i + 1 and the copy-out of step i - 1 run beside the kernels of step i, so the steady state is bound by the slower
     # PCIe direction rather than by their sum.
     oh, dqh, dkh, dvh = (torch.empty_like(t).pin_memory() for t in (qh, qh, kh, vh))
-    main = torch.cuda.current_stream()
+    main_s = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     dev_in = [[torch.empty_like(t, device=dev) for t in (qh, kh, vh, gh)] for _ in range(2)]
     ev_in = [torch.cuda.Event() for _ in range(2)]
@@ -271,8 +338,8 @@ def main():
     ev_out = torch.cuda.Event()
 
     def e2e_run(n):
-        s_in.wait_stream(main)
-        s_out.wait_stream(main)
+        s_in.wait_stream(main_s)
+        s_out.wait_stream(main_s)
         for i in range(n + 1):
             if i < n:
                 with torch.cuda.stream(s_in):
@@ -283,21 +350,22 @@ def main():
                     ev_in[i % 2].record(s_in)
             if i >= 1:
                 j = i - 1
-                main.wait_event(ev_in[j % 2])
+                main_s.wait_event(ev_in[j % 2])
                 qd, kd, vd, gd = dev_in[j % 2]
                 qd = qd.detach().requires_grad_(True); kd = kd.detach().requires_grad_(True); vd = vd.detach().requires_grad_(True)
                 out = fn(qd, kd, vd, causal=causal)
                 out.backward(gd)
-                ev_used[j % 2].record(main)
-                res = (out.detach(), qd.grad, kd.grad, vd.grad)
+                ev_used[j % 2].record(main_s)
+                res_t = (out.detach(), qd.grad, kd.grad, vd.grad)
                 s_out.wait_event(ev_used[j % 2])
                 with torch.cuda.stream(s_out):
-                    for h_t, d_t in zip((oh, dqh, dkh, dvh), res):
+                    for h_t, d_t in zip((oh, dqh, dkh, dvh), res_t):
                         d_t.record_stream(s_out)
                         h_t.copy_(d_t, non_blocking=True)
                     ev_out.record(s_out)
-        main.wait_event(ev_out)
+        main_s.wait_event(ev_out)
 
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_run(3)
     barrier()
     n_e2e = max(4, min(args.steps, 20))
@@ -306,46 +374,77 @@ def main():
     t1.record()
     barrier()
     ms_e2e = t0.elapsed_time(t1) / n_e2e
-    status_ok = True
+    R.check_status()
+    barrier()
+    h2d_gbs, d2h_gbs = copy_probe(dev, (qh, kh, vh, gh))       # all ranks probe at the same time
 
-    tt = torch.tensor([ms, ms_e2e, k_fwd, k_bwd], device=dev, dtype=torch.float64)
+    keys = ("ms", "k_fwd", "k_bwd", "k_quant", "k_dq_post")
+    flat = [res[r][kk] for r in sorted(res) for kk in keys] + [ms_e2e, -h2d_gbs, -d2h_gbs]
+    tt = torch.tensor(flat, device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    ms, ms_e2e, k_fwd, k_bwd = tt.tolist()
+    flat = tt.tolist()
+    for i, r in enumerate(sorted(res)):
+        for j, kk in enumerate(keys):
+            res[r][kk] = flat[i * len(keys) + j]
+    ms_e2e, h2d_gbs, d2h_gbs = flat[-3], -flat[-2], -flat[-1]     # copy rates: the slowest rank's
     if rank == 0:
         f_fwd = flops_fwd(B, S, H, D, causal)
         f_step = 3.5 * f_fwd * world
-        value = f_step / (ms * 1e-3) / 1e12
-        e2e_val = f_step / (ms_e2e * 1e-3) / 1e12
-        sust, burst, hbm, how = _peaks()
-        peak = 2.0 * sust      # E4M3 tensor rate = 2 x the dense bf16 rate; the kernel is timed inside a long step
         f_bwd = 2.5 * f_fwd
-        # mixed route: the S recompute (1 of 5 backward GEMMs) runs at the E2M1 rate (2 x E4M3)
-        t_min = (f_bwd / (peak * 1e12)) if args.route == "fp8" else (0.2 * f_bwd / (2 * peak * 1e12) + 0.8 * f_bwd / (peak * 1e12))
-        achieved = f_bwd / (k_bwd * 1e-3) / 1e12
+        sust, burst, hbm, how = _peaks()
+
+        def route_block(r):
+            m = res[r]
+            # tensor roofline of the backward kernel: E4M3 products at 2 x, E2M1 products at 4 x the measured dense bf16
+            # rate. The kernel is timed alone with CUDA events (eager steps), so the denominator is the BURST figure.
+            f_e2m1 = 0.2 * f_bwd if r == "fp4" else 0.0        # mixed route: S recompute (1 of 5 GEMMs) in E2M1
+            t_min = f_e2m1 / (4 * burst * 1e12) + (f_bwd - f_e2m1) / (2 * burst * 1e12)
+            ach = f_bwd / (m["k_bwd"] * 1e-3) / 1e12
+            mhz = (m["clocks"] or {}).get("sm_mhz")
+            return {
+                "value": f_step / (m["ms"] * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": m["ms"],
+                "timing": f"median of {m['batches']} batches of {args.steps} steps over {m['seconds']:.2f} s, {m['mode']}",
+                "ms_x_sm_mhz": (m["ms"] * mhz) if mhz else None,
+                "ms_fwd_kernel": m["k_fwd"], "ms_bwd_kernel": m["k_bwd"], "ms_quant_launches": m["k_quant"],
+                "ms_dq_post": m["k_dq_post"],
+                "tflops_fwd_kernel": f_fwd / (m["k_fwd"] * 1e-3) / 1e12, "tflops_bwd_kernel": ach,
+                "published_reference_ms": ({"fp8": 0.865, "fp4": 0.866} if causal else {"fp8": 1.416, "fp4": None})[r],
+                "roofline": {"bound": "tensor", "kernel": "bwd_kernel_pipelined", "achieved": ach,
+                             "peak": f_bwd / t_min / 1e12, "unit": "TFLOP/s", "frac": t_min / (m["k_bwd"] * 1e-3),
+                             "traffic": NCU_BWD_TRAFFIC_B2[r] * B / 2 if causal else None,
+                             "note": f"peak = 2 x (E4M3) / 4 x (E2M1) the {burst} TF/s dense bf16 burst figure ({how}); the "
+                                     f"kernel is event-timed alone, hence burst; of {how}. traffic: ncu dram read + write "
+                                     "of the b2 cell scaled by the batch"},
+                "clocks": m["clocks"],
+            }
+        blocks = {r: route_block(r) for r in res}
+        top = blocks[main_route]
+        n_timed = sum(res[r]["batches"] for r in res) * args.steps
         line = {
-            "metric": "attention fwd+bwd step TFLOPS (causal-adjusted), " + ("MXFP8" if args.route == "fp8" else "NVFP4/FP8"),
-            "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": W, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3" if args.route == "fp8" else "e2m1+e4m3",
-            "data": "synthetic",
-            "config": {"workload": f"b{B} s{S} h{H} d{D} {'causal' if causal else 'dense'} fwd+bwd per GPU, flash_attn_{args.route} "
+            "metric": "attention fwd+bwd step TFLOPS (causal-adjusted), " + ("MXFP8" if main_route == "fp8" else "NVFP4/FP8"),
+            "value": top["value"], "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": W,
+            "ms_per_step": top["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e4m3" if main_route == "fp8" else "e2m1+e4m3", "data": "synthetic",
+            "config": {"workload": f"b{B} s{S} h{H} d{D} {'causal' if causal else 'dense'} fwd+bwd per GPU, flash_attn_{main_route} "
                                    "defaults (token-block scales, Hadamard on), quantisation included",
                        "global_batch": B * world, "seq_len": S, "parallelism": f"batch-sharded x{world}, no collective",
-                       "l2": "inputs 268 MB per step > 126 MB L2, no flush needed", "launch": mode,
-                       "published_reference_ms": 0.865 if causal else 1.416},
-            "ms_fwd_kernel": k_fwd, "ms_bwd_kernel": k_bwd,
-            "tflops_fwd_kernel": f_fwd / (k_fwd * 1e-3) / 1e12, "tflops_bwd_kernel": achieved,
-            "roofline": {"bound": "tensor", "kernel": "bwd_kernel_pipelined", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": (t_min / (k_bwd * 1e-3)),
-                         # dram read + write bytes of one launch: 151.4 MB captured by ncu on the b2 cell of
-                         # --profile-case, scaled by the batch (traffic is proportional to b); fp8 route, causal
-                         "traffic": 151.4e6 * B / 2 if (args.route == "fp8" and causal) else None,
-                         "note": f"peak = 2 x {sust} TF/s dense bf16 sustained ({how}); of {how}"},
-            "e2e": {"value": e2e_val, "unit": "TFLOPS", "ms_per_step": ms_e2e,
+                       "l2": "inputs 268 MB per step > 126 MB L2, no flush needed", "launch": res[main_route]["mode"],
+                       "timing": top["timing"], "published_reference_ms": top["published_reference_ms"]},
+            "ms_fwd_kernel": top["ms_fwd_kernel"], "ms_bwd_kernel": top["ms_bwd_kernel"],
+            "ms_quant_launches": top["ms_quant_launches"], "ms_dq_post": top["ms_dq_post"],
+            "tflops_fwd_kernel": top["tflops_fwd_kernel"], "tflops_bwd_kernel": top["tflops_bwd_kernel"],
+            "roofline": top["roofline"],
+            "routes": {r: blocks[r] for r in blocks if r != main_route},
+            "e2e": {"value": f_step / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (qh, kh, vh, gh)),
-                    "d2h_bytes_per_step": sum(t.numel() * t.element_size() for t in (oh, dqh, dkh, dvh))},
-            "gpu_launches": 8 * args.steps,
-            "clocks": clocks,
+                    "d2h_bytes_per_step": sum(t.numel() * t.element_size() for t in (oh, dqh, dkh, dvh)),
+                    "copy_probe": {"h2d_gbs_slowest_rank": h2d_gbs, "d2h_gbs_slowest_rank": d2h_gbs,
+                                   "what": "pinned cudaMemcpyAsync of the same buffers, both directions at once on every "
+                                           "rank, no kernels: the ceiling of the end-to-end figure"}},
+            "gpu_launches": 8 * n_timed,
+            "clocks": top["clocks"],
+            "status_word": 0,
         }
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1

@@ -12,6 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libflamia_b200.so")
 
 # status codes (csrc/sm100.cuh)
+ABI_VERSION = 3
 FL_OK, FL_ERR_BAD_ARG, FL_ERR_CUDA, FL_ERR_UNSUPPORTED, FL_ERR_TOO_LARGE = 0, 1, 2, 3, 4
 FL_DEV_WAIT_TIMEOUT = 0x100
 FL_DEV_BAD_TABLE = 0x200
@@ -27,7 +28,8 @@ vp, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 class QuantArgs(C.Structure):
     _fields_ = [(n, vp) for n in ("x", "o", "lse", "codes", "codes_t", "e_tab", "fac", "sf_tok", "sf_dim",
                                   "token_factors", "x4", "sf4", "d_out", "lse_log2", "zero_acc", "tile_stats")] + \
-               [(n, i32) for n in ("b", "s", "h", "d", "flags", "in_f16")] + [("lse_shift", f32), ("d_multiplier", f32)]
+               [(n, i32) for n in ("b", "s", "h", "d", "flags", "in_f16")] + [("lse_shift", f32), ("d_multiplier", f32),
+                                                                            ("status", vp), ("wait_cycles", i64)]
 
 
 class AttnArgs(C.Structure):

@@ -181,10 +181,10 @@ def forward(plan, q, k, v, docs):
     # rotation: the 8-bit route rotates the E4M3 codes; the mixed route rotates only the NVFP4 S operands
     qk_kw = dict(apply_hadamard_rotation=f.qk_hadamard, hadamard_rotation_scope="nvfp4_copy" if fp4 else "all",
                  also_make_nvfp4_copy=fp4, token_local_exponents=tl)
-    qq = K.quantize_fp8_blocks(qp, **qk_kw)
-    kq = K.quantize_fp8_blocks(kp, output_tile_stats=need_bwd, **qk_kw)
-    vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl)
     status = K.new_status(q.device)
+    qq = K.quantize_fp8_blocks(qp, status=status, **qk_kw)
+    kq = K.quantize_fp8_blocks(kp, output_tile_stats=need_bwd, status=status, **qk_kw)
+    vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl, status=status)
     out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=q.dtype, mode=mode,
                              status=status, token_local=tl, window=f.window,
                              doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
@@ -235,7 +235,7 @@ def backward(plan, state, dout, docs_meta):
     acc = torch.empty(b, h, s_q, d, dtype=torch.float16, device=out.device)
     gq = K.quantize_fp8_blocks(gp, compute_d_with_output=out, shifted_log2_lse_from=lse, log2_lse_shift=P_SHIFT_LOG2,
                                d_multiplier=float(backward_scalars(plan.softmax_scale)[6]), zero_accumulator=acc, output_tile_stats=True,
-                               token_local_exponents=tl)
+                               token_local_exponents=tl, status=status)
     ks, ps = K.dq_prescale(gq["tile_stats"], vstats, kstats, causal_local=bw.dq_prescale == "causal_tile")
     had8 = f.qk_hadamard and not fp4           # only the 8-bit route's E4M3 codes are rotated
     dk, dv, _ = K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks,

@@ -1,25 +1,28 @@
 // Fused block-scaled quantiser (token-block MXFP8, optional NVFP4 S-operand copy, optional Hadamard rotation) and the
 // fused backward prologue (D = rowsum(O * dequant(dO)), shifted log2 LSE, zeroed f16 dQ accumulator).
 //
-// Replaces the reference's quantize_fp8_blocks launch (flash_attn/cute/quant/fp8.py:2512, kernel_stream :1639) and the
-// fused NVFP4 copy (flash_attn/cute/quant/_fp8_nvfp4.py:121-158). Outputs are byte-identical to the reference's eager
-// definitions (tests/cute/quant_reference.py:714-798, 270-369).
+// Replaces the reference's quantize_fp8_blocks launch (flash_attn/cute/quant/fp8.py:2512, kernel_stream :1639; its input
+// staging :262-300) and the fused NVFP4 copy (flash_attn/cute/quant/_fp8_nvfp4.py:121-158). Outputs are byte-identical to
+// the reference's eager definitions (tests/cute/quant_reference.py:714-798, 270-369).
 //
-// One CTA (512 threads) per (128-token tile, head, batch). Four lanes share a token row: lane q of the row holds the
-// 16-byte chunks c = 4 j + q (8 elements each), so every global access of a row is 64 contiguous bytes per instruction
-// and no staging through shared memory is needed. Element index i = 32 j + 8 q + e: the Hadamard levels 1, 2, 4 and
-// 32, 64 are in-thread, levels 8, 16 are two lane exchanges; the same order of operations as the one-thread-per-row
-// butterfly, hence the same bits. The kernel is HBM-bound (2 B read + 1 B written per element, plus optional copies).
+// Persistent CTAs (512 threads) walk the (128-token tile, head) pairs of the tensor, heads fastest, so the CTAs running
+// at any moment read one contiguous stretch of the (b, s, h, d) input. Each CTA keeps STAGES tiles in flight: one thread
+// issues the TMA loads of tile t + STAGES (plain cp.async.bulk.tensor, never multicast) as soon as every thread has read
+// tile t out of its stage, so the memory system stays busy while the butterflies and conversions of the current tile run.
+// Four lanes share a token row: lane q of the row holds the 16-byte chunks c = 4 j + q (8 elements each); element index
+// i = 32 j + 8 q + e, so the Hadamard levels 1, 2, 4 and 32, 64 are in-thread and levels 8, 16 are two lane exchanges:
+// the same order of operations as a one-thread-per-row butterfly, hence the same bits. The butterflies run as packed
+// f32x2 instructions on register pairs (chunk j, chunk j + 2): one issue slot per two additions, same rounding.
+// Bound: HBM (2 B read + 1 B written per element, plus the optional copies).
 #include "flamia_internal.h"
 
 namespace fl {
 
-static constexpr int QT = 128;       // tokens per tile
-static constexpr int QTHREADS = 512; // four lanes per token
+static constexpr int QT = 128;        // tokens per tile
+static constexpr int QTHREADS = 512;  // four lanes per token
+static constexpr int QSTAGES = 3;
 
 struct QuantParams {
-  const uint16_t* x;
-  const uint16_t* o;      // prologue: forward output (same layout as x) or null
   const float* lse;       // (b, h, s) or null
   uint8_t* codes;         // (b, s, h, d)
   uint8_t* codes_t;       // (b, h, d, s) or null
@@ -34,21 +37,36 @@ struct QuantParams {
   float* lse_log2;        // (b, h, s) or null
   uint16_t* zero_acc;     // f16 accumulator of b * h * s * d elements or null
   float* tile_stats;      // (b, h, s/128, 2): [amax of the values quantised, max row sum of squares] or null
-  int b, s, h, d;
-  int flags;
+  int b, s, h;
+  int n_tiles;            // b * (s / 128) * h
+  int token_local;
   int in_f16;
   float lse_shift, d_multiplier;
+  DevCtl ctl;
 };
 
-__device__ __forceinline__ float in_to_f32(uint32_t v16, int f16) {
-  return f16 ? __half2float(__ushort_as_half((uint16_t)v16)) : __uint_as_float(v16 << 16);
-}
 __device__ __forceinline__ float flush_sub(float v) { return fabsf(v) < 1.17549435e-38f ? v * 0.0f : v; }
-// a * b rounded to nearest with subnormal inputs and results flushed to zero (the product and its flush in one instruction)
-__device__ __forceinline__ float mul_ftz(float a, float b) {
-  float r;
-  asm("mul.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-  return r;
+// packed pairs: a + b, a - b, and a * b with subnormal inputs and results flushed to zero (the product and its flush in
+// one instruction); each half rounds exactly as the scalar instruction does
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2_ftz(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
 }
 
 // UE8M0 round-up selector: smallest e with 448 * 2^e >= amax; byte 0 when fp32(amax * fp32(1/448)) is subnormal / zero
@@ -67,281 +85,401 @@ __device__ __forceinline__ float e4m3_byte_to_f32(uint32_t c) {
   return (c & 0x80) ? -v : v;
 }
 
-template <int D>
-__global__ void __launch_bounds__(QTHREADS) quant_blocks_kernel(const QuantParams p) {
+// MODE bits: 1 = the E4M3 codes are of the rotated rows, 2 = also write the NVFP4 copy, 4 = rotate only the NVFP4 copy
+template <int D, int MODE, bool PRO>
+__global__ void __launch_bounds__(QTHREADS, PRO ? 1 : 2)
+quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_o,
+                    const QuantParams p) {
+  constexpr bool ROT = (MODE & 1) != 0, NV4 = (MODE & 2) != 0, ROT4 = (MODE & 4) != 0;
   constexpr int NJ = D / 32;                     // 16-byte chunks per lane
   constexpr int NE = 8 * NJ;                     // elements per lane
-  __shared__ float s_wmax[16];                   // per-warp (8 rows) maximum
-  __shared__ float s_wsq[16];                    // per-warp maximum row sum of squares
-  __shared__ __align__(16) uint8_t s_codes[QT * (D + 16)];   // channel-major copy only
+  constexpr int TILE_B = QT * D * 2;             // bytes of one 16-bit input tile
+  constexpr int STAGE_B = PRO ? 2 * TILE_B : TILE_B;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* s_codes = smem + QSTAGES * STAGE_B;   // channel-major copy only (present when codes_t is asked for)
+  __shared__ __align__(8) uint64_t full[QSTAGES];
+  __shared__ float s_wmax[2][16];                // per-warp (8 rows) maximum, double-buffered by tile parity
+  __shared__ float s_wsq[2][16];                 // per-warp maximum row sum of squares
+  __shared__ __align__(16) uint32_t s_sign[4][4][4];   // [lane of the row][chunk][word]: sign bits of the rotation
+  __shared__ int abort_s;
 
-  const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int r = tid >> 2, q = tid & 3;           // token row of the tile, lane of the row
-  const int t0 = tile * QT;
-  const size_t row_stride = (size_t)p.h * D;     // elements between consecutive tokens
-  const size_t row_off = ((size_t)bat * p.s + t0 + r) * row_stride + (size_t)head * D;
-  const bool prologue = p.d_out != nullptr && p.o != nullptr;
+  // lane -> (row of the warp's eight, lane of the row). The two rows of a quarter warp differ in bit 2, so that with
+  // the 128-byte swizzle their 16-byte chunks fall into different bank groups (conflict-free 128-bit loads).
+  const int q = lane & 3;
+  const int r = warp * 8 + ((lane >> 2) & 1) * 4 + (lane >> 3);      // token row of the tile
+  const int G = gridDim.x;
+  const int ntile = p.s / QT;
+  volatile int* abortp = &abort_s;
 
-  float x[NE];
-  auto load_row = [&](const uint16_t* base, float* dst) {
-    const uint4* src = reinterpret_cast<const uint4*>(base + row_off) + q;
-    uint4 v[NJ];
+  auto issue = [&](int L, int st) {              // one thread: the loads of linear tile L into stage st
+    const int head = L % p.h, tile = (L / p.h) % ntile, bat = L / (p.h * ntile);
+    uint8_t* dst = smem + st * STAGE_B;
+    mbar_arrive_expect_tx(&full[st], STAGE_B);
+    tma_load_4d(dst, &tm_x, &full[st], 0, head, tile * QT, bat);
+    if (D == 128) tma_load_4d(dst + TILE_B / 2, &tm_x, &full[st], 64, head, tile * QT, bat);
+    if (PRO) {
+      tma_load_4d(dst + TILE_B, &tm_o, &full[st], 0, head, tile * QT, bat);
+      if (D == 128) tma_load_4d(dst + TILE_B + TILE_B / 2, &tm_o, &full[st], 64, head, tile * QT, bat);
+    }
+  };
+  if (tid == 0) {
+    abort_s = 0;
+    for (int i = 0; i < QSTAGES; ++i) mbar_init(&full[i], 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_x);
+    if (PRO) tma_prefetch_desc(&tm_o);
+    for (int i = 0; i < QSTAGES; ++i)
+      if (blockIdx.x + i * G < p.n_tiles) issue(blockIdx.x + i * G, i);
+  }
+  if ((ROT || ROT4) && tid < 16) {               // sign words: bit 15 / 31 of word k = sign of element 2 k / 2 k + 1
+    constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
+    const int qq = tid >> 2, j = tid & 3;
+    const uint32_t m = (NEG[j] >> (8 * qq)) & 0xFF;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) v[j] = src[4 * j];
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+    for (int k = 0; k < 4; ++k) s_sign[qq][j][k] = (((m >> (2 * k)) & 1) << 15) | (((m >> (2 * k + 1)) & 1) << 31);
+  }
+  __syncthreads();
+
+  // raw 16-byte chunk j of this thread's row (global chunk 4 j + q) from a staged tile
+  auto lds_chunk = [&](uint32_t tile_addr, int j) -> uint4 {
+    const int g = 4 * j + q;
+    const uint32_t box = (D == 128) ? (uint32_t)(g >> 3) * (TILE_B / 2) : 0u;
+    return lds_u4(tile_addr + box + r * 128 + (((g & 7) ^ (r & 7)) << 4));
+  };
+  auto to_f32 = [&](const uint4& v, float* dst) {      // 8 elements of one chunk
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    if (p.in_f16) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        dst[8 * j + 2 * k] = in_to_f32(w[k] & 0xFFFF, p.in_f16);
-        dst[8 * j + 2 * k + 1] = in_to_f32(w[k] >> 16, p.in_f16);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+        dst[2 * k] = f.x;
+        dst[2 * k + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        dst[2 * k] = __uint_as_float(w[k] << 16);
+        dst[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
       }
     }
   };
-  load_row(p.x, x);
-  if (p.zero_acc) {   // this tile's share of the accumulator: 128 * D f16 = 32 D 16-byte chunks, contiguous
-    uint4* z = reinterpret_cast<uint4*>(p.zero_acc + (((size_t)bat * p.h + head) * p.s + t0) * D);
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int i = tid; i < QT * D / 8; i += QTHREADS) z[i] = zero;
-  }
-
-  const bool rotate = (p.flags & (FL_Q_HADAMARD | FL_Q_HADAMARD_NVFP4_ONLY)) != 0;
-  const bool rot_only4 = (p.flags & FL_Q_HADAMARD_NVFP4_ONLY) != 0;
-  const bool want4 = p.x4 != nullptr;
-
-  // (y * signs) H_128 / sqrt(128): butterfly levels 1, 2, ..., 64 with (a, b) -> (a + b, a - b)
-  auto rotate_row = [&](float* y) {
+  // (y * signs) H_128 / sqrt(128): butterfly levels 1, 2, ..., 64 with (a, b) -> (a + b, a - b), then the scaling with
+  // subnormal results flushed. Reads the staged tile, leaves the rotated row in y.
+  auto load_rotated = [&](uint32_t tile_addr, float* y) {
     if constexpr (D == 128) {
-      constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
+      float t[32];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint32_t m = NEG[j] >> (8 * q);
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-          if ((m >> e) & 1) y[8 * j + e] = -y[8 * j + e];
+        uint4 v = lds_chunk(tile_addr, j);
+        const uint4 sg = *reinterpret_cast<const uint4*>(&s_sign[q][j][0]);
+        v.x ^= sg.x; v.y ^= sg.y; v.z ^= sg.z; v.w ^= sg.w;
+        to_f32(v, t + 8 * j);
       }
+      uint64_t Y[16];                              // Y[8 jp + e] = (element (jp, e), element (jp + 2, e))
 #pragma unroll
-      for (int hs = 1; hs < 8; hs <<= 1) {       // element bits 0..2: inside one chunk
+      for (int k = 0; k < 16; ++k) Y[k] = pack2(t[k], t[k + 16]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if ((i & hs) == 0) {
-            const float a = y[i], b2 = y[i + hs];
-            y[i] = __fadd_rn(a, b2);
-            y[i + hs] = __fsub_rn(a, b2);
+      for (int hs = 1; hs < 8; hs <<= 1) {         // element bits 0..2: inside one chunk
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          if ((k & hs) == 0) {
+            const uint64_t a = Y[k], b2 = Y[k + hs];
+            Y[k] = add2(a, b2);
+            Y[k + hs] = sub2(a, b2);
           }
       }
 #pragma unroll
-      for (int lb = 1; lb < 4; lb <<= 1) {       // element bits 3, 4 = the lane of the row
+      for (int lb = 1; lb < 4; lb <<= 1) {         // element bits 3, 4 = the lane of the row
         // low lane: y + other; high lane: other - y. Both are other + (+-1) y: one fma (the product is exact)
         const float sg = (q & lb) ? -1.0f : 1.0f;
+        const uint64_t sg2 = pack2(sg, sg);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float other = __shfl_xor_sync(0xFFFFFFFFu, y[i], lb);
-          y[i] = __fmaf_rn(y[i], sg, other);
+        for (int k = 0; k < 16; ++k) {
+          float lo, hi;
+          unpack2(Y[k], lo, hi);
+          const uint64_t other = pack2(__shfl_xor_sync(0xFFFFFFFFu, lo, lb), __shfl_xor_sync(0xFFFFFFFFu, hi, lb));
+          Y[k] = fma2(Y[k], sg2, other);
         }
       }
 #pragma unroll
-      for (int jb = 1; jb < 4; jb <<= 1) {       // element bits 5, 6 = the chunk index j
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (((i >> 3) & jb) == 0) {
-            const float a = y[i], b2 = y[i + 8 * jb];
-            y[i] = __fadd_rn(a, b2);
-            y[i + 8 * jb] = __fsub_rn(a, b2);
-          }
+      for (int k = 0; k < 8; ++k) {                // element bit 5 = chunk bit 0
+        const uint64_t a = Y[k], b2 = Y[k + 8];
+        Y[k] = add2(a, b2);
+        Y[k + 8] = sub2(a, b2);
       }
+      const uint64_t c2 = pack2(0.08838834764831845f, 0.08838834764831845f);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) y[i] = mul_ftz(y[i], 0.08838834764831845f);   // scaled and flushed
-    }
-  };
-
-  // NVFP4 copy of y: per 16 along d (two neighbouring lanes): SF = E4M3_rn(amax * f32(1/6)); codes = E2M1_rn(ftz(y * m)),
-  // m = 1 / SF | +inf (SF rounds to 0, amax > 0) | 0
-  auto nvfp4_row = [&](const float* y) {
-    uint32_t sfpack = 0;                         // this lane's scale bytes: chunk j in byte j
-    uint8_t* x4row = p.x4 + (((size_t)bat * p.s + t0 + r) * p.h + head) * (D / 2);
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      float am = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float a = fabsf(flush_sub(y[8 * j + e]));
-        am = (a > am) ? a : am;                  // a NaN never wins
-      }
-      const float oth = __shfl_xor_sync(0xFFFFFFFFu, am, 1);
-      am = (oth > am) ? oth : am;
-      const float u = __fmul_rn(am, 1.0f / 6.0f);
-      const uint32_t sfb = cvt_e4m3x2(u, 0.f) & 0xFF;
-      const float sfv = e4m3_byte_to_f32(sfb);
-      const float m = sfv > 0.f ? __frcp_rn(sfv) : (u > 0.f ? __int_as_float(0x7F800000) : 0.f);
-      uint32_t packed = 0;
-#pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        const float a0 = flush_sub(__fmul_rn(flush_sub(y[8 * j + e]), m));
-        const float a1 = flush_sub(__fmul_rn(flush_sub(y[8 * j + e + 1]), m));
-        uint16_t c2;
-        asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}" : "=h"(c2) : "f"(a1), "f"(a0));
-        packed |= (uint32_t)(c2 & 0xFF) << (e * 4);
-      }
-      *reinterpret_cast<uint32_t*>(x4row + (4 * j + q) * 4) = packed;
-      sfpack |= sfb << (8 * j);
-    }
-    // group g = 2 j + (q >> 1): atom g / 4 = j / 2, byte g % 4 = 2 (j & 1) + (q >> 1); lane 0 of the row assembles
-    const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, sfpack, 2);
-    if (p.sf4 && q == 0) {
-      uint8_t* atom = p.sf4 + ((((size_t)bat * p.h + head) * (p.s / QT) + tile) * (D / 64)) * 512;
-#pragma unroll
-      for (int a = 0; a < D / 64; ++a) {
-        const uint32_t lo0 = (sfpack >> (16 * a)) & 0xFF, lo1 = (sfpack >> (16 * a + 8)) & 0xFF;
-        const uint32_t hi0 = (hi >> (16 * a)) & 0xFF, hi1 = (hi >> (16 * a + 8)) & 0xFF;
-        *reinterpret_cast<uint32_t*>(atom + a * 512 + (r & 31) * 16 + (r >> 5) * 4) = lo0 | (hi0 << 8) | (lo1 << 16) | (hi1 << 24);
+      for (int k = 0; k < 16; ++k) {               // element bit 6 = chunk bit 1: the two halves of a pair
+        float lo, hi;
+        unpack2(Y[k], lo, hi);
+        const uint64_t s2 = mul2_ftz(pack2(__fadd_rn(lo, hi), __fsub_rn(lo, hi)), c2);   // scaled and flushed
+        unpack2(s2, y[k], y[k + 16]);
       }
     }
   };
+  auto load_plain = [&](uint32_t tile_addr, float* y) {
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) to_f32(lds_chunk(tile_addr, j), y + 8 * j);
+  };
 
-  if (want4 && rotate && rot_only4) {   // NVFP4 codes of the rotated row, E4M3 codes of the row as read
-    rotate_row(x);
-    nvfp4_row(x);
-    load_row(p.x, x);
-  } else if (rotate) {
-    rotate_row(x);
-  }
-  if (want4 && !(rotate && rot_only4)) nvfp4_row(x);
+  int it = 0;
+  for (int L = blockIdx.x; L < p.n_tiles; L += G, ++it) {
+    const int st = it % QSTAGES, par = it & 1;
+    const int head = L % p.h, tile = (L / p.h) % ntile, bat = L / (p.h * ntile);
+    const int t0 = tile * QT;
+    const size_t row_off = (((size_t)bat * p.s + t0 + r) * p.h + head) * D;     // this row in a (b, s, h, D) tensor
+    const size_t bh = (size_t)bat * p.h + head;
+    const size_t ri = bh * p.s + t0 + r;
+    const uint32_t tile_addr = smem_u32(smem + st * STAGE_B);
+    bool ok = mbar_wait(&full[st], (it / QSTAGES) & 1, p.ctl, abortp, 50);
 
-  // ---- exponents: per token (4 lanes) and per 32-token block (4 warps)
-  float amax = 0.f, sumsq = 0.f;
-#pragma unroll
-  for (int i = 0; i < NE; ++i) {
-    x[i] = mul_ftz(x[i], 1.0f);      // subnormal -> zero of the same sign (rotated rows were flushed by their scaling)
-    amax = fmaxf(amax, fabsf(x[i]));
-  }
-  if (p.tile_stats) {     // the row norm is only wanted with the tile statistics (K, V, dO)
-#pragma unroll
-    for (int i = 0; i < NE; ++i) sumsq = fmaf(x[i], x[i], sumsq);
-  }
-  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));      // the token's maximum
-  sumsq += __shfl_xor_sync(0xFFFFFFFFu, sumsq, 1);
-  sumsq += __shfl_xor_sync(0xFFFFFFFFu, sumsq, 2);
-  float wmax = amax, wsq = sumsq;
-#pragma unroll
-  for (int o = 4; o < 32; o <<= 1) {
-    wmax = fmaxf(wmax, __shfl_xor_sync(0xFFFFFFFFu, wmax, o));
-    wsq = fmaxf(wsq, __shfl_xor_sync(0xFFFFFFFFu, wsq, o));
-  }
-  if (lane == 0) { s_wmax[warp] = wmax; s_wsq[warp] = wsq; }
-  __syncthreads();
-  const int blk = r >> 5;                                         // 32-token block of the tile
-  const float bmax = fmaxf(fmaxf(s_wmax[4 * blk], s_wmax[4 * blk + 1]), fmaxf(s_wmax[4 * blk + 2], s_wmax[4 * blk + 3]));
-  const uint32_t bbyte = ue8m0_byte(bmax);
-  const bool tl = (p.flags & FL_Q_TOKEN_LOCAL) != 0;
-  const uint32_t tbyte = tl ? ue8m0_byte(amax) : bbyte;
-  const float inv = tbyte ? pow2_from_field(254 - (int)tbyte) : 0.f;
-  const float scale = tbyte ? pow2_from_field((int)tbyte) : 0.f;
+    if (p.zero_acc) {   // this tile's share of the accumulator: 128 * D f16 = 32 D 16-byte chunks, contiguous
+      uint4* z = reinterpret_cast<uint4*>(p.zero_acc + (bh * p.s + t0) * D);
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+      for (int i = tid; i < QT * D / 8; i += QTHREADS) z[i] = zero;
+    }
 
-  uint32_t cw[2 * NJ];
+    // NVFP4 copy of y: per 16 along d (two neighbouring lanes): SF = E4M3_rn(amax * f32(1/6)); codes = E2M1_rn(ftz(y * m)),
+    // m = 1 / SF | +inf (SF rounds to 0, amax > 0) | 0
+    auto nvfp4_row = [&](const float* y) {
+      uint32_t sfpack = 0;                         // this lane's scale bytes: chunk j in byte j
+      uint8_t* x4row = p.x4 + row_off / 2;
 #pragma unroll
-  for (int i = 0; i < 2 * NJ; ++i)
-    cw[i] = cvt_e4m3x4(__fmul_rn(x[4 * i], inv), __fmul_rn(x[4 * i + 1], inv), __fmul_rn(x[4 * i + 2], inv),
-                       __fmul_rn(x[4 * i + 3], inv));
-  {
-    uint8_t* crow = p.codes + row_off;
+      for (int j = 0; j < NJ; ++j) {
+        float am = 0.f;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j)
-      *reinterpret_cast<uint2*>(crow + (4 * j + q) * 8) = make_uint2(cw[2 * j], cw[2 * j + 1]);
-  }
+        for (int e = 0; e < 8; ++e) {
+          const float a = fabsf(flush_sub(y[8 * j + e]));
+          am = (a > am) ? a : am;                  // a NaN never wins
+        }
+        const float oth = __shfl_xor_sync(0xFFFFFFFFu, am, 1);
+        am = (oth > am) ? oth : am;
+        const float u = __fmul_rn(am, 1.0f / 6.0f);
+        const uint32_t sfb = cvt_e4m3x2(u, 0.f) & 0xFF;
+        const float sfv = e4m3_byte_to_f32(sfb);
+        const float m = sfv > 0.f ? __frcp_rn(sfv) : (u > 0.f ? __int_as_float(0x7F800000) : 0.f);
+        uint32_t packed = 0;
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const float a0 = flush_sub(__fmul_rn(flush_sub(y[8 * j + e]), m));
+          const float a1 = flush_sub(__fmul_rn(flush_sub(y[8 * j + e + 1]), m));
+          uint16_t c2;
+          asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}" : "=h"(c2) : "f"(a1), "f"(a0));
+          packed |= (uint32_t)(c2 & 0xFF) << (e * 4);
+        }
+        *reinterpret_cast<uint32_t*>(x4row + (4 * j + q) * 4) = packed;
+        sfpack |= sfb << (8 * j);
+      }
+      // group g = 2 j + (q >> 1): atom g / 4 = j / 2, byte g % 4 = 2 (j & 1) + (q >> 1); lane 0 of the row assembles
+      const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, sfpack, 2);
+      if (p.sf4 && q == 0) {
+        uint8_t* atom = p.sf4 + ((bh * ntile + tile) * (D / 64)) * 512;
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a) {
+          const uint32_t lo0 = (sfpack >> (16 * a)) & 0xFF, lo1 = (sfpack >> (16 * a + 8)) & 0xFF;
+          const uint32_t hi0 = (hi >> (16 * a)) & 0xFF, hi1 = (hi >> (16 * a + 8)) & 0xFF;
+          *reinterpret_cast<uint32_t*>(atom + a * 512 + (r & 31) * 16 + (r >> 5) * 4) = lo0 | (hi0 << 8) | (lo1 << 16) | (hi1 << 24);
+        }
+      }
+    };
 
-  const size_t bh = (size_t)bat * p.h + head;
-  const size_t ri = bh * p.s + t0 + r;
-  // ---- prologue: D in the fixed tree order (column bits 1 (fma), 2, 3, 0, 6, 5, 4), shifted log2 LSE
-  if (prologue) {
-    float o[NE];
-    load_row(p.o, o);
-    float v[4 * NJ];                               // columns with bit 1 clear: index (j, e bit 2, e bit 0)
+    float x[NE];
+    if (ROT4) {          // NVFP4 codes of the rotated row, E4M3 codes of the row as read
+      load_rotated(tile_addr, x);
+      nvfp4_row(x);
+      load_plain(tile_addr, x);
+    } else if (ROT) {
+      load_rotated(tile_addr, x);
+      if (NV4) nvfp4_row(x);
+    } else {
+      load_plain(tile_addr, x);
+      if (NV4) nvfp4_row(x);
+    }
+    uint4 o_raw[NJ];     // prologue: the forward output's row, kept as read until the codes exist
+    if (PRO) {
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
+      for (int j = 0; j < NJ; ++j) o_raw[j] = lds_chunk(tile_addr + TILE_B, j);
+    }
+
+    // ---- exponents: per token (4 lanes) and per 32-token block (4 warps)
+    float amax = 0.f, sumsq = 0.f;
+    if (!ROT || ROT4) {  // subnormal -> zero of the same sign (rotated rows were flushed by their scaling)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int e = ((k >> 1) << 2) | (k & 1);   // 0, 1, 4, 5
-        const float a0 = __fmul_rn(e4m3_byte_to_f32((cw[2 * j + (e >> 2)] >> (8 * (e & 3))) & 0xFF), scale);
-        const float a2 = __fmul_rn(e4m3_byte_to_f32((cw[2 * j + ((e + 2) >> 2)] >> (8 * ((e + 2) & 3))) & 0xFF), scale);
-        v[4 * j + k] = __fmaf_rn(a0, o[8 * j + e], __fmul_rn(a2, o[8 * j + e + 2]));
+      for (int i = 0; i < NE; i += 2) {
+        const uint64_t f2 = mul2_ftz(pack2(x[i], x[i + 1]), pack2(1.0f, 1.0f));
+        unpack2(f2, x[i], x[i + 1]);
       }
     }
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {                 // bit 2
-      v[4 * j + 0] = __fadd_rn(v[4 * j + 0], v[4 * j + 2]);
-      v[4 * j + 1] = __fadd_rn(v[4 * j + 1], v[4 * j + 3]);
-    }
+    for (int i = 0; i < NE; i += 2) amax = fmaxf(fmaxf(amax, fabsf(x[i])), fabsf(x[i + 1]));
+    if (p.tile_stats) {     // the row norm is only wanted with the tile statistics (K, V, dO)
+      float sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {                 // bit 3 = lane bit 0
-      v[4 * j + 0] = __fadd_rn(v[4 * j + 0], __shfl_xor_sync(0xFFFFFFFFu, v[4 * j + 0], 1));
-      v[4 * j + 1] = __fadd_rn(v[4 * j + 1], __shfl_xor_sync(0xFFFFFFFFu, v[4 * j + 1], 1));
+      for (int i = 0; i < NE; ++i) sq[i & 3] = fmaf(x[i], x[i], sq[i & 3]);
+      sumsq = (sq[0] + sq[1]) + (sq[2] + sq[3]);
     }
-    float w4[4];
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));      // the token's maximum
+    sumsq += __shfl_xor_sync(0xFFFFFFFFu, sumsq, 1);
+    sumsq += __shfl_xor_sync(0xFFFFFFFFu, sumsq, 2);
+    float wmax = amax, wsq = sumsq;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) w4[j] = j < NJ ? __fadd_rn(v[4 * (j < NJ ? j : 0) + 0], v[4 * (j < NJ ? j : 0) + 1]) : 0.f;   // bit 0
-    const float w2a = __fadd_rn(w4[0], w4[2]), w2b = __fadd_rn(w4[1], w4[3]);                  // bit 6
-    float w1 = __fadd_rn(w2a, w2b);                                                            // bit 5
-    w1 = __fadd_rn(w1, __shfl_xor_sync(0xFFFFFFFFu, w1, 2));                                   // bit 4 = lane bit 1
-    if (q == 0) p.d_out[ri] = __fmul_rn(w1, p.d_multiplier);
-  }
-  if (p.lse && p.lse_log2 && q == 0) {
-    const float l = p.lse[ri];
-    p.lse_log2[ri] = __fsub_rn((l == -INFINITY) ? 0.f : __fmul_rn(l, 1.4426950408889634f), p.lse_shift);
-  }
+    for (int o = 4; o < 32; o <<= 1) {
+      wmax = fmaxf(wmax, __shfl_xor_sync(0xFFFFFFFFu, wmax, o));
+      wsq = fmaxf(wsq, __shfl_xor_sync(0xFFFFFFFFu, wsq, o));
+    }
+    if (lane == 0) { s_wmax[par][warp] = wmax; s_wsq[par][warp] = wsq; }
+    // every thread has read the stage: it can take tile it + STAGES. A wait that ran out leaves the loop here, all
+    // threads together.
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (!ok) break;
+    if (tid == 0 && L + QSTAGES * G < p.n_tiles) issue(L + QSTAGES * G, st);
 
-  // ---- side tables
-  const int ntile = p.s / QT;
-  const uint32_t b0 = ue8m0_byte(fmaxf(fmaxf(s_wmax[0], s_wmax[1]), fmaxf(s_wmax[2], s_wmax[3])));
-  const uint32_t b1 = ue8m0_byte(fmaxf(fmaxf(s_wmax[4], s_wmax[5]), fmaxf(s_wmax[6], s_wmax[7])));
-  const uint32_t b2 = ue8m0_byte(fmaxf(fmaxf(s_wmax[8], s_wmax[9]), fmaxf(s_wmax[10], s_wmax[11])));
-  const uint32_t b3 = ue8m0_byte(fmaxf(fmaxf(s_wmax[12], s_wmax[13]), fmaxf(s_wmax[14], s_wmax[15])));
-  if ((tid & 127) == 0) {                          // one thread per 32-token block
-    if (p.e_tab) {
-      uint8_t* e = p.e_tab + (bh * (p.s / 32) + tile * 4 + blk) * (D / 32);
-#pragma unroll
-      for (int g = 0; g < D / 32; ++g) e[g] = (uint8_t)bbyte;
-    }
-    if (p.fac) {
-      const uint32_t tm = max(max(b0, b1), max(b2, b3));
-      const uint32_t e0 = bbyte ? bbyte : tm;
-      p.fac[bh * (p.s / 32) + tile * 4 + blk] = e0 ? pow2_from_field((int)e0) : 1.0f;
-    }
-  }
-  if (q == 0) {
-    if (p.token_factors) p.token_factors[ri] = tbyte ? scale : 1.0f;
-    if (p.sf_tok)
-      *reinterpret_cast<uint32_t*>(p.sf_tok + (bh * ntile + tile) * 512 + (r & 31) * 16 + (r >> 5) * 4) = tbyte * 0x01010101u;
-  }
-  if (p.sf_dim && tid < 128)
-    *reinterpret_cast<uint32_t*>(p.sf_dim + (bh * ntile + tile) * 512 + tid * 4) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
-  if (p.tile_stats && tid == 0) {
-    float a = 0.f, sq = 0.f;
-#pragma unroll
-    for (int w = 0; w < 16; ++w) { a = fmaxf(a, s_wmax[w]); sq = fmaxf(sq, s_wsq[w]); }
-    p.tile_stats[(bh * ntile + tile) * 2] = a;
-    p.tile_stats[(bh * ntile + tile) * 2 + 1] = sq;
-  }
+    const float* wm = s_wmax[par];
+    const int blk = r >> 5;                                         // 32-token block of the tile
+    const float bmax = fmaxf(fmaxf(wm[4 * blk], wm[4 * blk + 1]), fmaxf(wm[4 * blk + 2], wm[4 * blk + 3]));
+    const uint32_t bbyte = ue8m0_byte(bmax);
+    const bool tl = p.token_local != 0;
+    const uint32_t tbyte = tl ? ue8m0_byte(amax) : bbyte;
+    const float inv = tbyte ? pow2_from_field(254 - (int)tbyte) : 0.f;
+    const float scale = tbyte ? pow2_from_field((int)tbyte) : 0.f;
 
-  // ---- channel-major copy (b, h, d, s): through shared memory, thread c gathers column c
-  if (p.codes_t) {
-    constexpr int CROWB = D + 16;
+    uint32_t cw[2 * NJ];
+    {
+      const uint64_t inv2 = pack2(inv, inv);
 #pragma unroll
-    for (int j = 0; j < NJ; ++j)
-      *reinterpret_cast<uint2*>(s_codes + r * CROWB + (4 * j + q) * 8) = make_uint2(cw[2 * j], cw[2 * j + 1]);
-    __syncthreads();
-    for (int i = tid; i < D * 8; i += QTHREADS) {  // (channel, 16-token group)
-      const int c = i >> 3, rg = (i & 7) * 16;
-      uint32_t w[4];
+      for (int i = 0; i < 2 * NJ; ++i) {
+        float a0, a1, a2, a3;
+        unpack2(mul2(pack2(x[4 * i], x[4 * i + 1]), inv2), a0, a1);
+        unpack2(mul2(pack2(x[4 * i + 2], x[4 * i + 3]), inv2), a2, a3);
+        cw[i] = cvt_e4m3x4(a0, a1, a2, a3);
+      }
+      uint8_t* crow = p.codes + row_off;
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        w[k] = (uint32_t)s_codes[(rg + 4 * k) * CROWB + c] | ((uint32_t)s_codes[(rg + 4 * k + 1) * CROWB + c] << 8) |
-               ((uint32_t)s_codes[(rg + 4 * k + 2) * CROWB + c] << 16) | ((uint32_t)s_codes[(rg + 4 * k + 3) * CROWB + c] << 24);
-      *reinterpret_cast<uint4*>(p.codes_t + (bh * D + c) * (size_t)p.s + t0 + rg) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int j = 0; j < NJ; ++j)
+        *reinterpret_cast<uint2*>(crow + (4 * j + q) * 8) = make_uint2(cw[2 * j], cw[2 * j + 1]);
+    }
+
+    // ---- prologue: D in the fixed tree order (column bits 1 (fma), 2, 3, 0, 6, 5, 4), shifted log2 LSE
+    if (PRO) {
+      float o[NE];
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) to_f32(o_raw[j], o + 8 * j);
+      float v[4 * NJ];                               // columns with bit 1 clear: index (j, e bit 2, e bit 0)
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int e = ((k >> 1) << 2) | (k & 1);   // 0, 1, 4, 5
+          const float a0 = __fmul_rn(e4m3_byte_to_f32((cw[2 * j + (e >> 2)] >> (8 * (e & 3))) & 0xFF), scale);
+          const float a2 = __fmul_rn(e4m3_byte_to_f32((cw[2 * j + ((e + 2) >> 2)] >> (8 * ((e + 2) & 3))) & 0xFF), scale);
+          v[4 * j + k] = __fmaf_rn(a0, o[8 * j + e], __fmul_rn(a2, o[8 * j + e + 2]));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {                 // bit 2
+        v[4 * j + 0] = __fadd_rn(v[4 * j + 0], v[4 * j + 2]);
+        v[4 * j + 1] = __fadd_rn(v[4 * j + 1], v[4 * j + 3]);
+      }
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {                 // bit 3 = lane bit 0
+        v[4 * j + 0] = __fadd_rn(v[4 * j + 0], __shfl_xor_sync(0xFFFFFFFFu, v[4 * j + 0], 1));
+        v[4 * j + 1] = __fadd_rn(v[4 * j + 1], __shfl_xor_sync(0xFFFFFFFFu, v[4 * j + 1], 1));
+      }
+      float w4[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w4[j] = j < NJ ? __fadd_rn(v[4 * (j < NJ ? j : 0) + 0], v[4 * (j < NJ ? j : 0) + 1]) : 0.f;   // bit 0
+      const float w2a = __fadd_rn(w4[0], w4[2]), w2b = __fadd_rn(w4[1], w4[3]);                  // bit 6
+      float w1 = __fadd_rn(w2a, w2b);                                                            // bit 5
+      w1 = __fadd_rn(w1, __shfl_xor_sync(0xFFFFFFFFu, w1, 2));                                   // bit 4 = lane bit 1
+      if (q == 0 && p.d_out) p.d_out[ri] = __fmul_rn(w1, p.d_multiplier);
+    }
+    if (p.lse && p.lse_log2 && q == 0) {
+      const float l = p.lse[ri];
+      p.lse_log2[ri] = __fsub_rn((l == -INFINITY) ? 0.f : __fmul_rn(l, 1.4426950408889634f), p.lse_shift);
+    }
+
+    // ---- side tables
+    const uint32_t b0 = ue8m0_byte(fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3])));
+    const uint32_t b1 = ue8m0_byte(fmaxf(fmaxf(wm[4], wm[5]), fmaxf(wm[6], wm[7])));
+    const uint32_t b2 = ue8m0_byte(fmaxf(fmaxf(wm[8], wm[9]), fmaxf(wm[10], wm[11])));
+    const uint32_t b3 = ue8m0_byte(fmaxf(fmaxf(wm[12], wm[13]), fmaxf(wm[14], wm[15])));
+    if ((tid & 127) == 0) {                          // one thread per 32-token block (tid 128 k: row 32 k, lane 0 of it)
+      if (p.e_tab) {
+        uint8_t* e = p.e_tab + (bh * (p.s / 32) + tile * 4 + blk) * (D / 32);
+#pragma unroll
+        for (int g = 0; g < D / 32; ++g) e[g] = (uint8_t)bbyte;
+      }
+      if (p.fac) {
+        const uint32_t tm = max(max(b0, b1), max(b2, b3));
+        const uint32_t e0 = bbyte ? bbyte : tm;
+        p.fac[bh * (p.s / 32) + tile * 4 + blk] = e0 ? pow2_from_field((int)e0) : 1.0f;
+      }
+    }
+    if (q == 0) {
+      if (p.token_factors) p.token_factors[ri] = tbyte ? scale : 1.0f;
+      if (p.sf_tok)
+        *reinterpret_cast<uint32_t*>(p.sf_tok + (bh * ntile + tile) * 512 + (r & 31) * 16 + (r >> 5) * 4) = tbyte * 0x01010101u;
+    }
+    if (p.sf_dim && tid < 128)
+      *reinterpret_cast<uint32_t*>(p.sf_dim + (bh * ntile + tile) * 512 + tid * 4) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    if (p.tile_stats && tid == 0) {
+      float a = 0.f, sq = 0.f;
+#pragma unroll
+      for (int w = 0; w < 16; ++w) { a = fmaxf(a, wm[w]); sq = fmaxf(sq, s_wsq[par][w]); }
+      p.tile_stats[(bh * ntile + tile) * 2] = a;
+      p.tile_stats[(bh * ntile + tile) * 2 + 1] = sq;
+    }
+
+    // ---- channel-major copy (b, h, d, s): through shared memory, thread c gathers column c
+    if (p.codes_t) {
+      constexpr int CROWB = D + 16;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j)
+        *reinterpret_cast<uint2*>(s_codes + r * CROWB + (4 * j + q) * 8) = make_uint2(cw[2 * j], cw[2 * j + 1]);
+      __syncthreads();
+      for (int i = tid; i < D * 8; i += QTHREADS) {  // (channel, 16-token group)
+        const int c = i >> 3, rg = (i & 7) * 16;
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          w[k] = (uint32_t)s_codes[(rg + 4 * k) * CROWB + c] | ((uint32_t)s_codes[(rg + 4 * k + 1) * CROWB + c] << 8) |
+                 ((uint32_t)s_codes[(rg + 4 * k + 2) * CROWB + c] << 16) | ((uint32_t)s_codes[(rg + 4 * k + 3) * CROWB + c] << 24);
+        *reinterpret_cast<uint4*>(p.codes_t + (bh * D + c) * (size_t)p.s + t0 + rg) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      __syncthreads();                               // the staging rows are rewritten by the next tile
     }
   }
+  // a CTA that gave up must not exit while loads into its shared memory may still land
+  if (abort_s) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+}
+
+static int sm_count() {
+  static int n[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!n[dev]) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev] = v;
+  }
+  return n[dev];
+}
+
+template <int D, int MODE, bool PRO>
+static int launch_quant(const CUtensorMap& mx, const CUtensorMap& mo, const QuantParams& p, bool want_t, cudaStream_t st) {
+  constexpr int TILE_B = QT * D * 2;
+  const int smem = QSTAGES * (PRO ? 2 : 1) * TILE_B + 1024 + (want_t ? QT * (D + 16) : 0);
+  auto kern = quant_blocks_kernel<D, MODE, PRO>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
+  const int per_sm = (PRO || want_t) ? 1 : 2;
+  const int grid = min(p.n_tiles, sm_count() * per_sm);
+  kern<<<grid, QTHREADS, smem, st>>>(mx, mo, p);
+  return FL_OK;
 }
 
 }  // namespace fl
@@ -353,17 +491,42 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   if (a->d != 64 && a->d != 128) return FL_ERR_UNSUPPORTED;
   if ((a->flags & (FL_Q_HADAMARD | FL_Q_HADAMARD_NVFP4_ONLY)) && a->d != 128) return FL_ERR_UNSUPPORTED;
   if ((a->flags & FL_Q_HADAMARD) && (a->flags & FL_Q_TOKEN_LOCAL)) return FL_ERR_UNSUPPORTED;
+  if ((a->flags & FL_Q_HADAMARD_NVFP4_ONLY) && !a->x4) return FL_ERR_BAD_ARG;
   if (a->h > 65535 || a->b > 65535) return FL_ERR_TOO_LARGE;
+  const long long n_tiles = (long long)a->b * (a->s / 128) * a->h;
+  if (n_tiles > 0x7FFFFFFF) return FL_ERR_TOO_LARGE;
+  const bool pro = a->d_out != nullptr && a->o != nullptr;
+  const bool rot = (a->flags & FL_Q_HADAMARD) != 0, rot4 = (a->flags & FL_Q_HADAMARD_NVFP4_ONLY) != 0;
+  const bool nv4 = a->x4 != nullptr;
+  if (pro && (rot || rot4 || nv4)) return FL_ERR_UNSUPPORTED;     // the prologue rides on the dO launch, which does neither
   QuantParams p;
-  p.x = (const uint16_t*)a->x; p.o = (const uint16_t*)a->o; p.lse = a->lse;
-  p.codes = a->codes; p.codes_t = a->codes_t; p.e_tab = a->e_tab; p.fac = a->fac; p.sf_tok = a->sf_tok;
+  p.lse = a->lse; p.codes = a->codes; p.codes_t = a->codes_t; p.e_tab = a->e_tab; p.fac = a->fac; p.sf_tok = a->sf_tok;
   p.sf_dim = a->sf_dim; p.token_factors = a->token_factors; p.x4 = a->x4; p.sf4 = a->sf4; p.d_out = a->d_out;
   p.lse_log2 = a->lse_log2; p.zero_acc = (uint16_t*)a->zero_acc; p.tile_stats = a->tile_stats;
-  p.b = a->b; p.s = a->s; p.h = a->h; p.d = a->d; p.flags = a->flags; p.in_f16 = a->in_f16;
+  p.b = a->b; p.s = a->s; p.h = a->h; p.n_tiles = (int)n_tiles;
+  p.token_local = (a->flags & FL_Q_TOKEN_LOCAL) ? 1 : 0;
+  p.in_f16 = a->in_f16;
   p.lse_shift = a->lse_shift; p.d_multiplier = a->d_multiplier;
-  dim3 grid(a->s / 128, a->h, a->b);
+  p.ctl.status = a->status;
+  p.ctl.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kDefaultWaitCycles;
+  CUtensorMap mx, mo;
+  int rc;
+  if ((rc = make_rows_map_16(&mx, a->x, a->b, a->s, a->h, a->d, 128))) return rc;
+  if ((rc = make_rows_map_16(&mo, pro ? a->o : a->x, a->b, a->s, a->h, a->d, 128))) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  if (a->d == 128) quant_blocks_kernel<128><<<grid, QTHREADS, 0, st>>>(p);
-  else quant_blocks_kernel<64><<<grid, QTHREADS, 0, st>>>(p);
+  const bool wt = a->codes_t != nullptr;
+  if (a->d == 64) {
+    if (pro) rc = launch_quant<64, 0, true>(mx, mo, p, wt, st);
+    else rc = nv4 ? launch_quant<64, 2, false>(mx, mo, p, wt, st) : launch_quant<64, 0, false>(mx, mo, p, wt, st);
+  } else if (pro) {
+    rc = launch_quant<128, 0, true>(mx, mo, p, wt, st);
+  } else if (rot4) {
+    rc = launch_quant<128, 6, false>(mx, mo, p, wt, st);
+  } else if (rot) {
+    rc = nv4 ? launch_quant<128, 3, false>(mx, mo, p, wt, st) : launch_quant<128, 1, false>(mx, mo, p, wt, st);
+  } else {
+    rc = nv4 ? launch_quant<128, 2, false>(mx, mo, p, wt, st) : launch_quant<128, 0, false>(mx, mo, p, wt, st);
+  }
+  if (rc) return rc;
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

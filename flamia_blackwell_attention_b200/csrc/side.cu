@@ -49,84 +49,95 @@ __global__ void dq_prescale_kernel(const float* __restrict__ st_do, const float*
 }
 
 // ------------------------------------------------------------------------------------------------ dQ postprocess
-// dq[b, q, h, :] = cast(f32(acc[b, h, q, :]) * post[b, q / 128] * mult), optionally rotated back:
-// (y H_128 / sqrt(128)) * signs in the quantiser's butterfly order. Replaces the reference's DQPostprocess
-// (flash_attn/cute/dq_postprocess_cute.py:46-124).
-template <int D>
-__global__ void __launch_bounds__(128) dq_post_kernel(const __half* __restrict__ acc, const float* __restrict__ post,
-                                                      uint16_t* __restrict__ dq, int s, int h, float mult, int unrotate,
-                                                      int out_f16, int acc_t) {
-  extern __shared__ __align__(16) uint8_t sm[];
-  constexpr int ROWB = D * 2 + 16;
+// dq[b, q, h, :] = cast(f32(acc) * post[b, q / 128] * mult), optionally rotated back: (y H_128 / sqrt(128)) * signs in the
+// quantiser's butterfly order. Replaces the reference's DQPostprocess (flash_attn/cute/dq_postprocess_cute.py:46-124).
+// HBM-bound: 2 B read + 2 B written per element.
+__device__ __forceinline__ uint32_t cvt_out2(float a, float b, int out_f16) {
+  if (out_f16) { __half2 hh = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&hh); }
+  return pack_bf16x2(a, b);
+}
+
+// head dim 64: the accumulator is (b, h, s, 64); a straight scaled copy into the (b, s, h, 64) gradient
+__global__ void __launch_bounds__(128) dq_post_rows64_kernel(const __half* __restrict__ acc, const float* __restrict__ post,
+                                                             uint16_t* __restrict__ dq, int s, int h, float mult,
+                                                             int out_f16) {
+  constexpr int D = 64, CPR = D / 8;
   const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z, tid = threadIdx.x;
   const int t0 = tile * 128;
   const __half* src = acc + (((size_t)bat * h + head) * s + t0) * D;
   const float sc = post[(size_t)bat * (s / 128) + tile] * mult;
   uint16_t* dst = dq + (((size_t)bat * s + t0) * h + head) * D;
   const size_t row_stride = (size_t)h * D;
-  constexpr int CPR = D / 8;
-  auto cvt2 = [&](float a, float b) -> uint32_t {
-    if (out_f16) { __half2 hh = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&hh); }
-    return pack_bf16x2(a, b);
-  };
-  if (!unrotate && !acc_t) {
-    for (int i = tid; i < 128 * CPR; i += 128) {
-      const int r = i / CPR, c = i % CPR;
-      uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
-      const __half2* hv = reinterpret_cast<const __half2*>(&v);
-      uint32_t w[4];
+  for (int i = tid; i < 128 * CPR; i += 128) {
+    const int r = i / CPR, c = i % CPR;
+    uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
+    const __half2* hv = reinterpret_cast<const __half2*>(&v);
+    uint32_t w[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __half22float2(hv[j]);
-        w[j] = cvt2(f.x * sc, f.y * sc);
-      }
-      *reinterpret_cast<uint4*>(dst + (size_t)r * row_stride + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __half22float2(hv[j]);
+      w[j] = cvt_out2(f.x * sc, f.y * sc, out_f16);
     }
-    return;
+    *reinterpret_cast<uint4*>(dst + (size_t)r * row_stride + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
   }
-  if constexpr (D == 128) {
+}
+
+// head dim 128: the accumulator is (b, h, 128, s) (the backward produces transposed dQ tiles). One CTA per (128-token tile,
+// head): the 128 x 128 f16 tile comes in as two TMA boxes of 64 tokens (128-byte rows, 128 B swizzle), thread t gathers
+// token t's column from shared memory, optionally rotates it back, and the rows leave through a padded staging buffer
+// as coalesced 16-byte stores.
+__global__ void __launch_bounds__(128) dq_post_t128_kernel(const __grid_constant__ CUtensorMap tm_acc,
+                                                           const float* __restrict__ post, uint16_t* __restrict__ dq,
+                                                           int s, int h, float mult, int unrotate, int out_f16) {
+  constexpr int D = 128, ROWB = D * 2 + 16, CPR = D / 8;
+  extern __shared__ __align__(1024) uint8_t sm_raw[];
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sm_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* s_in = sm;                  // 2 boxes x 128 head-dim rows x 128 B
+  uint8_t* s_out = sm + 32768;         // 128 token rows x (256 + 16) B
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_s;
+  const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z, tid = threadIdx.x;
+  const int t0 = tile * 128;
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+    mbar_arrive_expect_tx(&bar, 32768);
+    tma_load_4d(s_in, &tm_acc, &bar, t0, 0, head, bat);
+    tma_load_4d(s_in + 16384, &tm_acc, &bar, t0 + 64, 0, head, bat);
+  }
+  const float sc = post[(size_t)bat * (s / 128) + tile] * mult;
+  __syncthreads();
+  const DevCtl ctl = {nullptr, kDefaultWaitCycles};
+  bool ok = mbar_wait(&bar, 0, ctl, &abort_s, 60);
+  ok = __syncthreads_and(ok ? 1 : 0) != 0;
+  if (ok) {
     float y[128];
-    if (acc_t) {
-      // (b, h, d, s) accumulator: this thread's token is one f16 in each of the 128 head-dim rows (a warp reads 64
-      // contiguous bytes per row)
-      const __half* col = acc + ((size_t)bat * h + head) * D * (size_t)s + t0 + tid;
+    {
+      const int tt = tid & 63;
+      const uint32_t base = smem_u32(s_in) + (tid >> 6) * 16384 + (tt & 7) * 2;
 #pragma unroll
-      for (int c = 0; c < 128; ++c) y[c] = __half2float(col[(size_t)c * s]) * sc;
-    } else {
-      for (int i = tid; i < 128 * CPR; i += 128) {
-        const int r = i / CPR, c = i % CPR;
-        *reinterpret_cast<uint4*>(sm + r * ROWB + c * 16) = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
-      }
-      __syncthreads();
-      const uint8_t* rowp = sm + tid * ROWB;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        uint4 v = *reinterpret_cast<const uint4*>(rowp + c * 16);
-        const __half2* hv = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = __half22float2(hv[j]);
-          y[c * 8 + 2 * j] = f.x * sc;
-          y[c * 8 + 2 * j + 1] = f.y * sc;
-        }
+      for (int c = 0; c < 128; ++c) {
+        uint16_t hv;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(hv) : "r"(base + c * 128 + ((((uint32_t)tt >> 3) ^ (c & 7)) << 4)));
+        y[c] = __half2float(__ushort_as_half(hv)) * sc;
       }
     }
     if (unrotate) {
 #pragma unroll
-    for (int hs = 1; hs < 128; hs <<= 1) {
+      for (int hs = 1; hs < 128; hs <<= 1) {
 #pragma unroll
-      for (int i = 0; i < 128; ++i) {
-        if ((i & hs) == 0) {
-          float a = y[i], b2 = y[i + hs];
-          y[i] = __fadd_rn(a, b2);
-          y[i + hs] = __fsub_rn(a, b2);
+        for (int i = 0; i < 128; ++i) {
+          if ((i & hs) == 0) {
+            float a = y[i], b2 = y[i + hs];
+            y[i] = __fadd_rn(a, b2);
+            y[i + hs] = __fsub_rn(a, b2);
+          }
         }
       }
     }
-    }
     constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
-    __syncthreads();
-    uint8_t* rowo = sm + tid * ROWB;
+    uint8_t* rowo = s_out + tid * ROWB;
 #pragma unroll
     for (int c = 0; c < 16; ++c) {
       uint32_t w[4];
@@ -140,15 +151,19 @@ __global__ void __launch_bounds__(128) dq_post_kernel(const __half* __restrict__
           if ((NEG[i0 >> 5] >> (i0 & 31)) & 1) a = -a;
           if ((NEG[i1 >> 5] >> (i1 & 31)) & 1) b2 = -b2;
         }
-        w[j] = cvt2(a, b2);
+        w[j] = cvt_out2(a, b2, out_f16);
       }
       *reinterpret_cast<uint4*>(rowo + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     __syncthreads();
+    uint16_t* dst = dq + (((size_t)bat * s + t0) * h + head) * D;
+    const size_t row_stride = (size_t)h * D;
     for (int i = tid; i < 128 * CPR; i += 128) {
       const int r = i / CPR, c = i % CPR;
-      *reinterpret_cast<uint4*>(dst + (size_t)r * row_stride + c * 8) = *reinterpret_cast<const uint4*>(sm + r * ROWB + c * 16);
+      *reinterpret_cast<uint4*>(dst + (size_t)r * row_stride + c * 8) = *reinterpret_cast<const uint4*>(s_out + r * ROWB + c * 16);
     }
+  } else {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);     // loads into this CTA's shared memory may still land
   }
 }
 
@@ -190,15 +205,19 @@ extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, float mul
   using namespace fl;
   if (!dq_acc || !post_scale || !dq || b <= 0 || s <= 0 || (s % 128) || h <= 0) return FL_ERR_BAD_ARG;
   if ((d != 64 && d != 128) || (unrotate && d != 128)) return FL_ERR_UNSUPPORTED;
+  if (h > 65535 || b > 65535) return FL_ERR_TOO_LARGE;
   dim3 grid(s / 128, h, b);
   cudaStream_t st = (cudaStream_t)stream;
   if (d == 128) {
-    const int sm = 128 * 272;
-    if (cudaFuncSetAttribute(dq_post_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 272) != cudaSuccess)
+    CUtensorMap macc;
+    int rc = make_acc_t_map_16(&macc, dq_acc, b, h, d, s);
+    if (rc) return rc;
+    const int sm = 32768 + 128 * 272 + 1024;
+    if (cudaFuncSetAttribute(dq_post_t128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sm) != cudaSuccess)
       return FL_ERR_CUDA;
-    dq_post_kernel<128><<<grid, 128, sm, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16, 1);
+    dq_post_t128_kernel<<<grid, 128, sm, st>>>(macc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16);
   } else {
-    dq_post_kernel<64><<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, 0, out_f16, 0);
+    dq_post_rows64_kernel<<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, out_f16);
   }
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

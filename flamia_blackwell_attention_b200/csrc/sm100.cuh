@@ -40,7 +40,7 @@ __device__ __forceinline__ void doc_entry(const int32_t* doc_start, const int32_
   len = doc_len[i];
   const bool bad_start = start < 0 || (start & 127) != 0 || start >= total;
   if (bad_start || len < 0 || len > total - start) {
-    atomicCAS(status, 0, FL_DEV_BAD_TABLE);
+    if (status) atomicCAS(status, 0, FL_DEV_BAD_TABLE);
     if (bad_start) { start = 0; len = 0; }
     else len = max(0, min(len, total - start));
   }
@@ -81,7 +81,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       if (*abort) return false;
       if (clock64() - t0 > ctl.wait_cycles) {
         *abort = 1;
-        atomicCAS(ctl.status, 0, FL_DEV_WAIT_TIMEOUT | site);
+        if (ctl.status) atomicCAS(ctl.status, 0, FL_DEV_WAIT_TIMEOUT | site);
         return false;
       }
     }

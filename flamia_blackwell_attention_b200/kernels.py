@@ -37,7 +37,7 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
                         make_channel_major_copy=False, output_exponent_table=True, output_token_block_factors=True,
                         output_sf_atoms=False, also_make_nvfp4_copy=False, compute_d_with_output=None,
                         shifted_log2_lse_from=None, log2_lse_shift=0.0, d_multiplier=1.0, zero_accumulator=None,
-                        output_tile_stats=False):
+                        output_tile_stats=False, status=None, wait_cycles=0):
     """Token-block MXFP8 quantiser of x (b, s, h, d) bf16 / f16 (s % 128 == 0, d in {64, 128}).
     Returns a dict: codes (b,s,h,d) float8_e4m3fn; e (b,h,s/32,d/32) uint8; fac (b,h,s/32) f32; optionally codes_t,
     sf_tok_raw, sf_dim_raw, token_factors, x4 / sf4_raw (NVFP4 copy), D, lse_log2, tile_stats.
@@ -104,6 +104,7 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
         out["tile_stats"] = torch.empty(b, h, s // 128, 2, dtype=torch.float32, device=dev)
         a.tile_stats = L.ptr(out["tile_stats"])
     a.lse_shift, a.d_multiplier = float(log2_lse_shift), float(d_multiplier)
+    a.status, a.wait_cycles = L.ptr(status), int(wait_cycles)      # status: the call's device status word or None
     L.check(L.load().fl_quant_blocks(C.byref(a), _stream()), "fl_quant_blocks")
     out["codes"] = out["codes"].view(torch.float8_e4m3fn)
     if "codes_t" in out:

@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define FL_ABI_VERSION 2
+#define FL_ABI_VERSION 3
 
 /* fl_quant_args.flags */
 #define FL_Q_HADAMARD 1            /* rotate rows by diag(signs) H_128 / sqrt(128) before quantising (d = 128) */
@@ -30,7 +30,7 @@ extern "C" {
  * flash_attn/cute/quant/_fp8_nvfp4.py:121-158, and the fused backward preprocess (compute_d_with_output,
  * shifted_log2_lse_from, zero_accumulator: quant/fp8.py:1980-2032). Any output pointer may be NULL = not produced. */
 typedef struct fl_quant_args {
-  const void* x;        /* (b, s, h, d) bf16 (in_f16 = 0) or f16 (1), contiguous; s % 128 == 0; d = 64 | 128 */
+  const void* x;        /* (b, s, h, d) bf16 (in_f16 = 0) or f16 (1), contiguous, 16-byte aligned; s % 128 == 0; d = 64 | 128 */
   const void* o;        /* prologue: forward output, same layout / dtype as x */
   const float* lse;     /* (b, h, s) natural-log LSE */
   uint8_t* codes;       /* (b, s, h, d) E4M3 */
@@ -52,6 +52,8 @@ typedef struct fl_quant_args {
   int32_t in_f16;
   float lse_shift;
   float d_multiplier;
+  int32_t* status;      /* device int, 0 on entry, or NULL: a wait of the kernel's load pipeline that gave up writes a code */
+  int64_t wait_cycles;  /* budget of one device-side wait in SM clocks; 0 = default (2^31) */
 } fl_quant_args;
 
 int fl_quant_blocks(const fl_quant_args* args, void* stream);

@@ -1,0 +1,258 @@
+"""GPU: run-time contracts of the public call and robustness of the document forms.
+
+  * the f16 dQ pre-scale tables of fl_dq_prescale, bit for bit against the pinned scale oracle (row and causal-tile modes,
+    unit != 1, zero / overflowing / tiny statistics);
+  * packed and ragged documents stay finite when the caching allocator hands out memory full of NaN;
+  * a document table that does not fit its buffer is clamped and reported through the status word;
+  * check_status() raises for a status word that records a wait that ran out;
+  * distinct query / key document tables are refused;
+  * the backward runs on another thread with the plan of ITS forward (two plans interleaved);
+  * a captured CUDA graph of the public fwd+bwd call replays to the eager result (O, LSE, dK, dV bitwise);
+  * causal safety: future K / V / dO rows do not move earlier rows of O, LSE and dQ.
+The last three follow the reference's tests/cute/test_lowprec_api.py:831-883, :977-1000 and
+tests/cute/test_lowprec_causal_safe_v.py.
+"""
+import threading
+import warnings
+
+import numpy as np
+import pytest
+import torch
+
+from inputs import attention_inputs, scale_stats
+from oracle import attention_oracle as A
+from oracle import scales_oracle as S
+
+pytestmark = pytest.mark.gpu
+
+
+# ------------------------------------------------------------------------------------------------ dQ pre-scale tables
+@pytest.mark.parametrize("kind", ["plain", "zeros", "huge", "tiny"])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 3, 3), (1, 2, 2, 5, 5), (3, 8, 1, 2, 4)])
+@pytest.mark.parametrize("unit", [1.0, 256.0])
+def test_dq_prescale_tables_bitwise(kind, shape, unit):
+    from flamia_blackwell_attention_b200 import kernels as K
+    b, hq, hk, tq, tk = shape
+    dn, vn, km = scale_stats(b, hq, hk, tq, tk, kind, seed=b * 100 + tq)
+    st_do = torch.zeros(b, hq, tq, 2)
+    st_v = torch.zeros(b, hk, tk, 2)
+    st_k = torch.zeros(b, hk, tk, 2)
+    st_do[..., 1] = dn.view(b, hq, tq)      # max row sum of squares of dO
+    st_v[..., 1] = vn.view(b, hk, tk)       # max row sum of squares of V
+    st_k[..., 0] = km.view(b, hk, tk)       # amax of K
+    for mode in ("row", "causal_tile"):
+        if mode == "causal_tile" and tq != tk:
+            continue
+        ks, ps = K.dq_prescale(st_do.cuda(), st_v.cuda(), st_k.cuda(), causal_local=mode == "causal_tile", unit=unit)
+        fn = S.dq_prescale_rows if mode == "row" else S.dq_prescale_causal_tiles
+        want_k, want_p = fn(dn.numpy(), vn.numpy(), km.numpy(), b, hq, hk, tq, tk, unit=unit, base=1.0, num=1.0)
+        assert np.array_equal(ks.cpu().numpy().reshape(-1).view(np.uint32), want_k.view(np.uint32)), (mode, kind)
+        assert np.array_equal(ps.cpu().numpy().reshape(-1).view(np.uint32), want_p.view(np.uint32)), (mode, kind)
+
+
+# ------------------------------------------------------------------------------------------------ NaN-filled allocator
+def _poison_allocator(nbytes=192 << 20):
+    """Allocate, fill with NaN bit patterns (as f32 and as bf16) and free: the caching allocator hands these blocks out
+    again to the next torch.empty calls."""
+    blocks = [torch.full((nbytes // 16,), float("nan"), dtype=torch.float32, device="cuda") for _ in range(3)]
+    blocks += [torch.full((nbytes // 64,), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(8)]
+    torch.cuda.synchronize()
+    del blocks
+
+
+@pytest.mark.parametrize("form", ["ragged", "packed", "aligned"])
+@pytest.mark.parametrize("route", ["fp8", "fp4"])
+def test_documents_stay_finite_on_poisoned_memory(form, route):
+    import flamia_blackwell_attention_b200 as F
+    if route == "fp4" and form == "ragged":
+        pytest.skip("flash_attn_fp4 takes lengths that are multiples of 128 on the batched form")
+    fn = F.flash_attn_fp8 if route == "fp8" else F.flash_attn_fp4
+    h, d = 2, 128
+    kw = dict(causal=True)
+    if form == "ragged":
+        q, k, v, g = attention_inputs(2, 300, h, h, d, seed=81)
+    else:
+        lens = [300, 128, 77, 515]
+        if form == "aligned":
+            starts, total = [0, 384, 512, 640], 1280 + 256       # two unused tail tiles
+            su = torch.tensor(lens, dtype=torch.int32, device="cuda")
+            kw.update(seqused_q=su, seqused_k=su)
+        else:
+            starts, total = [sum(lens[:i]) for i in range(4)], sum(lens)
+        q, k, v, g = (t[0] for t in attention_inputs(1, total, h, h, d, seed=82))
+        cu = torch.tensor(starts + [total], dtype=torch.int32, device="cuda")
+        kw.update(cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens))
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    gc = g.cuda()
+    _poison_allocator()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = fn(qc, kc, vc, **kw)
+        _poison_allocator()
+        out.backward(gc)
+    torch.cuda.synchronize()
+    if form == "aligned":      # rows between documents are the caller's padding: only document rows are defined
+        rows = torch.zeros(total, dtype=torch.bool)
+        for s0, n in zip(starts, lens):
+            rows[s0:s0 + n] = True
+        rows = rows.cuda()
+        for name, t in (("o", out), ("dq", qc.grad), ("dk", kc.grad), ("dv", vc.grad)):
+            assert torch.isfinite(t[rows]).all(), (form, route, name)
+    else:
+        for name, t in (("o", out), ("dq", qc.grad), ("dk", kc.grad), ("dv", vc.grad)):
+            assert torch.isfinite(t).all(), (form, route, name)
+    assert F.check_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ status word
+def test_document_table_that_does_not_fit_is_clamped_and_reported():
+    """seqused beyond the end of the buffer: the kernels cut the document at the buffer's end, touch nothing outside it
+    and leave FL_DEV_BAD_TABLE in the status word, which check_status() turns into an error."""
+    import flamia_blackwell_attention_b200 as F
+    from flamia_blackwell_attention_b200 import _lib as L
+    h, d, total = 2, 128, 512
+    q, k, v, g = (t[0] for t in attention_inputs(1, total, h, h, d, seed=83))
+    cu = torch.tensor([0, 256, total], dtype=torch.int32, device="cuda")
+    su = torch.tensor([200, 900], dtype=torch.int32, device="cuda")          # the second document claims 900 of 256 rows
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = F.flash_attn_fp8(qc, kc, vc, causal=True, cu_seqlens_q=cu, cu_seqlens_k=cu, seqused_q=su, seqused_k=su,
+                           max_seqlen_q=256, max_seqlen_k=256)
+    out.backward(g.cuda())
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="document table"):
+        F.check_status()
+    assert torch.isfinite(out[:200]).all() and torch.isfinite(out[256:]).all()
+    # the first document is untouched by its neighbour's bad entry
+    ro, *_ = A.attention_fp32(q[None, :200].float(), k[None, :200].float(), v[None, :200].float(), None, True)
+    assert A.accuracy(out[:200].float().cpu(), ro[0])["rel_l2"] < 7e-2
+    assert L.FL_DEV_BAD_TABLE == 0x200
+
+
+def test_check_status_raises_for_a_wait_that_ran_out():
+    import flamia_blackwell_attention_b200 as F
+    from flamia_blackwell_attention_b200 import _routes
+    q, k, v, _ = (t.cuda() for t in attention_inputs(1, 256, 2, 2, 128, seed=84))
+    with torch.no_grad():
+        F.flash_attn_fp8(q, k, v, causal=True)
+    assert F.check_status() == 0
+    _routes._note_status(torch.tensor([0x100 | 23], dtype=torch.int32, device="cuda"))    # what a kernel would leave
+    with pytest.raises(RuntimeError, match="site 23"):
+        F.check_status()
+    with torch.no_grad():
+        F.flash_attn_fp8(q, k, v, causal=True)
+    assert F.check_status() == 0
+
+
+def test_distinct_key_table_is_refused():
+    import flamia_blackwell_attention_b200 as F
+    q, k, v, _ = (t[0].cuda() for t in attention_inputs(1, 512, 2, 2, 128, seed=85))
+    cu_q = torch.tensor([0, 200, 512], dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0, 300, 512], dtype=torch.int32, device="cuda")
+    with pytest.raises(NotImplementedError) as e:
+        F.flash_attn_fp8(q, k, v, causal=True, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, max_seqlen_q=312, max_seqlen_k=312)
+    assert e.value.rule == "B8"
+
+
+# ------------------------------------------------------------------------------------------------ threads and graphs
+def _eager(fn, q, k, v, g, **kw):
+    qc, kc, vc = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    out, lse = fn(qc, kc, vc, return_lse=True, **kw)
+    out.backward(g)
+    torch.cuda.synchronize()
+    return out.detach(), lse, qc.grad, kc.grad, vc.grad
+
+
+def _cos(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float(a @ b / (a.norm() * b.norm() + 1e-30))
+
+
+def test_backward_on_another_thread_uses_the_plan_of_its_forward():
+    """forward A (row-local dQ side), forward B (defaults), backward B, backward A, each backward on a fresh thread: every
+    gradient equals the one of the same call made alone on the main thread."""
+    import flamia_blackwell_attention_b200 as F
+    q, k, v, g = (t.cuda() for t in attention_inputs(1, 512, 4, 2, 128, seed=86))
+    opt_a = F.FP8AttnOptions(ds_dq_rowlocal="all")
+    alone_a = _eager(F.flash_attn_fp8, q, k, v, g, causal=True, options=opt_a)
+    alone_b = _eager(F.flash_attn_fp8, q, k, v, g, causal=True)
+    assert not torch.equal(alone_a[2], alone_b[2])          # the two plans do differ in dQ
+    leaves = {}
+
+    def fwd(tag, **kw):
+        leaves[tag] = tuple(t.detach().clone().requires_grad_(True) for t in (q, k, v))
+        return F.flash_attn_fp8(*leaves[tag], causal=True, **kw)
+    o_a = fwd("a", options=opt_a)
+    o_b = fwd("b")
+    for o in (o_b, o_a):
+        t = threading.Thread(target=lambda o=o: o.backward(g))
+        t.start()
+        t.join()
+    torch.cuda.synchronize()
+    for tag, alone in (("a", alone_a), ("b", alone_b)):
+        qg, kg, vg = (t.grad for t in leaves[tag])
+        assert torch.equal(kg, alone[3]) and torch.equal(vg, alone[4]), tag
+        assert _cos(qg, alone[2]) > 0.99999, tag           # f16 partial sums are added in arrival order
+
+
+@pytest.mark.parametrize("route", ["fp8", "fp4"])
+def test_graph_replay_equals_eager(route):
+    import flamia_blackwell_attention_b200 as F
+    fn = F.flash_attn_fp8 if route == "fp8" else F.flash_attn_fp4
+    q, k, v, g = (t.cuda() for t in attention_inputs(2, 512, 4, 2, 128, seed=87))
+    eager = _eager(fn, q, k, v, g, causal=True)
+    sq, sk, sv = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn(sq, sk, sv, causal=True).backward(g)
+            sq.grad = sk.grad = sv.grad = None
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        go, glse = fn(sq, sk, sv, causal=True, return_lse=True)
+        go.backward(g)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(go, eager[0]) and torch.equal(glse, eager[1])
+    assert torch.equal(sk.grad, eager[3]) and torch.equal(sv.grad, eager[4])
+    assert _cos(sq.grad, eager[2]) > 0.99999
+    assert F.check_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ causal safety
+@pytest.mark.parametrize("route,opts", [("fp8", None), ("fp8", "token_local"), ("fp4", None)])
+def test_future_rows_do_not_move_earlier_rows(route, opts):
+    """Causal calls: K, V and dO rows from K0 on (K0 a multiple of 128, so no visible row shares a scale block with them)
+    are replaced by large values; O, LSE and dQ of the rows before K0 must not move: O and LSE bitwise, dQ up to the
+    arrival order of its f16 partial sums. With the causal dQ pre-scale the scale of an earlier query tile is sized from
+    the keys it may see only, so dQ keeps its rounding too."""
+    import flamia_blackwell_attention_b200 as F
+    import flamia_blackwell_attention_b200.interface_bwd_fp4 as I
+    fn = F.flash_attn_fp8 if route == "fp8" else F.flash_attn_fp4
+    kw = dict(causal=True)
+    if opts == "token_local":
+        kw["options"] = F.FP8AttnOptions(operand_scaling="token_local", ds_dq_rowlocal="all")
+    s, k0 = 1024, 640
+    q, k, v, g = (t.cuda() for t in attention_inputs(1, s, 4, 2, 128, seed=88))
+    k2, v2, g2 = k.clone(), v.clone(), g.clone()
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    for t in (k2, v2, g2):
+        t[:, k0:k0 + 40] = torch.randn(t[:, k0:k0 + 40].shape, generator=gen, device="cuda").sign().to(t.dtype) * 60.0
+    old = I.DQ_CAUSAL_PRESCALE
+    I.DQ_CAUSAL_PRESCALE = route == "fp8"
+    try:
+        base = _eager(fn, q, k, v, g, **kw)
+        again = _eager(fn, q, k, v, g, **kw)
+        pert = _eager(fn, q, k2, v2, g2, **kw)
+    finally:
+        I.DQ_CAUSAL_PRESCALE = old
+    assert not torch.equal(base[0][:, k0:], pert[0][:, k0:])                 # the probe is not blind
+    assert torch.equal(base[0][:, :k0], pert[0][:, :k0])
+    assert torch.equal(base[1][..., :k0], pert[1][..., :k0])
+    if route == "fp8":
+        noise = float((base[2][:, :k0].float() - again[2][:, :k0].float()).abs().max())
+        moved = float((base[2][:, :k0].float() - pert[2][:, :k0].float()).abs().max())
+        ulp = float(base[2][:, :k0].float().abs().max()) * 2.0 ** -7
+        assert moved <= max(noise, ulp), (moved, noise, ulp)
