@@ -20,7 +20,7 @@ ERR_NAMES = {1: "bad argument", 2: "CUDA error", 3: "unsupported configuration",
 
 FL_Q_HADAMARD, FL_Q_TOKEN_LOCAL, FL_Q_HADAMARD_NVFP4_ONLY = 1, 2, 4
 FL_MODE_FP8, FL_MODE_FP4 = 0, 1
-FL_A_CAUSAL, FL_A_OUT_F16, FL_A_TOKEN_LOCAL, FL_A_DQ_ROWLOCAL, FL_A_HAD_DQ, FL_A_HAD_DK = 1, 2, 4, 8, 16, 32
+FL_A_CAUSAL, FL_A_OUT_F16, FL_A_TOKEN_LOCAL, FL_A_DQ_ROWLOCAL, FL_A_HAD_DQ, FL_A_HAD_DK, FL_A_P_GROUP = 1, 2, 4, 8, 16, 32, 64
 
 vp, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 

@@ -186,7 +186,7 @@ def forward(plan, q, k, v, docs):
     kq = K.quantize_fp8_blocks(kp, output_tile_stats=need_bwd, status=status, **qk_kw)
     vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl, status=status)
     out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=q.dtype, mode=mode,
-                             status=status, token_local=tl, window=f.window,
+                             status=status, token_local=tl, window=f.window, p_group=f.p_hat_frame == "group",
                              doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     state = [out, lse, qq["codes"], qq["fac"], kq["codes"], kq["fac"], vq["codes"], vq["fac"], status]
     if need_bwd:

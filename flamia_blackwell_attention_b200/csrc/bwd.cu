@@ -1,9 +1,14 @@
 // Backward main kernel for sm_100a (head_dim 128 or 64): dK, dV and the pre-scaled f16 dQ accumulator from block-scaled
-// operands, software-pipelined over 64-query half tiles.
+// operands, software-pipelined over 64-query half tiles, on a persistent grid.
 //
 // Replaces the reference's FlashAttentionBackwardSm100FP4 (flash_attn/cute/flash_bwd_sm100_fp4.py:82; driver
-// flash_attn/cute/interface_bwd_fp4.py:1207) for the E4M3 backward. One CTA per (128-key tile, kv head, batch | document);
-// it walks the query tiles that see the key tile (x the query heads of the GQA group), each as two 64-query halves
+// flash_attn/cute/interface_bwd_fp4.py:1207) for the E4M3 backward. One CTA per SM walks a static list of work items
+// (128-key tile, kv head, batch | document): under the causal mask the items are ordered longest first and dealt out in
+// zigzag rounds (round k gives CTA c item k G + c or k G + G - 1 - c), so every CTA gets nearly the same number of query
+// tiles. All pipelines run ACROSS items: the K / V tiles of the next item are loaded into a second buffer while the
+// current item's last query tiles are processed, the first S^T / dP^T products of the next item are issued while the
+// compute warpgroups write the current item's dK / dV, and barriers, tensor memory and tensor maps are set up once per CTA.
+// An item walks the query tiles that see its key tile (x the query heads of the GQA group), each as two 64-query halves
 // x = 0, 1 that run one step apart, so the tensor core works on one half while the other half's elementwise math runs:
 //   S^T_x  = K Q_x^T                  kind::f8f6f4, N = 64 (token-block factors folded into the exponent argument)
 //   P'     = 2^(S^T c - lse_log2) = 2^8 P        -> P-hat = E4M3(P')                   [tensor memory]
@@ -22,6 +27,9 @@
 //   warps 8-11 dQ reduction (thread = head-dim row)      warp 12 UMMA issuer      warp 13 TMA producer
 // TMEM: [0,64) / [64,128) S^T_x, then P-hat +0, dS-hat +16, six scale tiles +32..+56; [128,256) dV;
 //       [256,320) / [320,384) dP^T_x, then dQ^T_x; [384,512) dK.  Every wait is bounded (sm100.cuh).
+// Item epilogue: the compute warpgroups read dV (warpgroup 0) / dK (warpgroup 1) out of tensor memory, release the
+// accumulators to the next item's products, and write their rows through the finished item's K / V tile buffers (dead by
+// then) with TMA stores, 64 columns at a time; only then may the producer refill those buffers (two items ahead).
 // FL_MODE_FP4 (the mixed route): S^T_x is recomputed at the forward's precision, K4 Q4_x^T with
 // kind::mxf4nvf4.block_scale.scale_vec::4X on the NVFP4 copies; everything after P' is the E4M3 path above. The 16 scale
 // columns of that product (tcgen05.cp of the K and Q atoms) are parked in the half's own dP^T columns: they are free
@@ -59,38 +67,32 @@ struct BwdParams {
   int win_l, win_r;      // sliding window sides, -1 = unlimited (causal: the right side is 0)
   int out_f16;
   int had_dk;
+  int n_items;           // work items: key tiles x kv heads x batch rows (documents: tile slots x kv heads)
+  int n_tile;            // key tiles per batch row (documents: tile slots of the packed buffer)
+  int zigzag;            // deal the items out in zigzag rounds (causal: they are ordered longest first)
   DevCtl ctl;
 };
 
 struct BTile {
   int bat;    // batch coordinate of the tensor maps (0 for packed documents)
+  int hkv;    // kv head
   int k0;     // first key row of the tile (row index inside the batch entry)
-  int nk;     // valid keys of the tile (<= 128)
+  int nk;     // valid keys of the tile (<= 128; 0 = an empty tile slot)
   int krel;   // document-relative index of key row k0
   int q0;     // first query row of the document (row index inside the batch entry)
   int sq;     // queries of the document
   int off;    // causal alignment: key j (document-relative) is visible to query i iff j <= i + off
+  int m_lo;   // first query tile that sees this key tile
+  int n_m;    // number of query tiles that see it
 };
 
-enum { BB_KV = 0, BB_QFULL = 1, BB_QEMPTY = 3, BB_S = 5, BB_DP = 7, BB_P = 9, BB_DS = 11, BB_EX = 13, BB_DQF = 15,
-       BB_DQE = 17, BB_R1 = 19, BB_R2 = 20, BB_ACC = 21, BB_EP = 22, BB_COUNT = 24 };
+// barriers; [2] = one per half, stage or buffer
+enum { BB_KV = 0, BB_KVE = 2, BB_QFULL = 4, BB_QEMPTY = 6, BB_S = 8, BB_DP = 10, BB_P = 12, BB_DS = 14, BB_EX = 16,
+       BB_DQF = 18, BB_DQE = 20, BB_EP = 22, BB_EPI = 24, BB_R1 = 26, BB_R2 = 27, BB_ACC = 28, BB_ACCFREE = 29,
+       BB_COUNT = 30 };
 // TMEM columns; the per-half regions are at + 64 * x
 enum { TC_S = 0, TO_P = 0, TO_DS = 16, TO_SFA_P = 32, TO_SFB_DO = 36, TO_SFA_DK = 40, TO_SFB_Q = 44, TO_SFA_DQ = 48,
        TO_SFB_DQ = 52, TC_DV = 128, TC_DP = 256, TC_DK = 384 };
-
-// Timeline tracing of one CTA (development aid, compiled out unless FL_TRACE is defined): clock64 stamps per role, step
-// and event into a caller-provided buffer of [8 roles][256 steps][8 events] int64.
-#ifdef FL_TRACE
-__device__ long long* g_trace = nullptr;
-#define TRACE_INIT() long long* const trace_p = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? g_trace : nullptr
-#define TRACE(role, step, ev)                                                                                     \
-  do {                                                                                                            \
-    if (trace_p && (step) < 256) trace_p[(((role) * 256) + (step)) * 8 + (ev)] = clock64();                       \
-  } while (0)
-#else
-#define TRACE_INIT()
-#define TRACE(role, step, ev)
-#endif
 
 __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
   uint32_t r;
@@ -116,6 +118,42 @@ __device__ __forceinline__ uint32_t exp448(uint32_t bits) {
 }
 __device__ __forceinline__ float pow2_inv(uint32_t ebyte) { return __uint_as_float((uint32_t)(254 - (int)ebyte) << 23); }
 
+// k-th work item of CTA c on a grid of G CTAs (>= n_items: the CTA is done)
+__device__ __forceinline__ int bwd_item(int k, int G, int c, int zigzag) {
+  return k * G + ((zigzag && (k & 1)) ? (G - 1 - c) : c);
+}
+
+// Work item L -> its key tile. Causal: tiles slowest, so that the item index orders the items longest first (a key tile
+// near the start of the sequence is seen by the most query tiles). Otherwise tiles fastest: the CTAs that run at the same
+// time work on one head and share its Q / dO tiles in L2.
+__device__ __forceinline__ void bwd_decode(const BwdParams& p, int L, BTile& t) {
+  if (p.doc_start == nullptr) {
+    int tile, rem;
+    if (p.causal) { tile = L / (p.h_kv * p.b); rem = L % (p.h_kv * p.b); }
+    else { tile = L % p.n_tile; rem = L / p.n_tile; }
+    t.hkv = rem % p.h_kv; t.bat = rem / p.h_kv;
+    t.k0 = tile * 128; t.nk = min(128, p.s_k - t.k0); t.krel = t.k0; t.q0 = 0; t.sq = p.s_q; t.off = p.s_k - p.s_q;
+  } else {
+    // documents sit at 128-aligned starts of one packed batch entry; tile slot x -> (document, key tile of it)
+    int x = L / p.h_kv, dsel = -1, len = 0, st = 0;
+    t.hkv = L % p.h_kv;
+    for (int dI = 0; dI < p.n_docs; ++dI) {
+      doc_entry(p.doc_start, p.doc_len, dI, p.s_k, p.ctl.status, st, len);
+      const int nb = (len + 127) / 128;
+      if (x < nb) { dsel = dI; break; }
+      x -= nb;
+    }
+    if (dsel < 0) { t.nk = 0; t.bat = 0; t.k0 = 0; t.krel = 0; t.q0 = 0; t.sq = 0; t.off = 0; }
+    else { t.bat = 0; t.k0 = st + x * 128; t.nk = min(128, len - x * 128); t.krel = x * 128; t.q0 = st; t.sq = len; t.off = 0; }
+  }
+  // query tiles that see this key tile: the first query that sees its first key, the last one that sees its last key
+  int m_hi = (t.sq + 127) / 128, m_lo = 0;
+  if (p.win_r >= 0 && t.krel - t.off - p.win_r > 0) m_lo = (t.krel - t.off - p.win_r) / 128;
+  if (p.win_l >= 0) m_hi = min(m_hi, max(0, t.krel + t.nk - 1 - t.off + p.win_l) / 128 + 1);
+  t.m_lo = m_lo;
+  t.n_m = (t.nk > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
+}
+
 template <int D, bool FP4, int VAR>
 __global__ void __launch_bounds__(512, 1)
 bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -128,97 +166,50 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   constexpr uint32_t OP_SBO = 8 * D;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;                                  // 1 tile
-  uint8_t* sV = sK + TILE_BYTES;                       // 1 tile
-  uint8_t* sQ = sV + TILE_BYTES;                       // 2 stages
+  uint8_t* sK = smem;                                  // 2 buffers (items alternate)
+  uint8_t* sV = sK + 2 * TILE_BYTES;                   // 2 buffers
+  uint8_t* sQ = sV + 2 * TILE_BYTES;                   // 2 stages
   uint8_t* sDO = sQ + 2 * TILE_BYTES;                  // 2 stages
   uint8_t* sDS = sDO + 2 * TILE_BYTES;                 // per half: 128 key rows x 64 query bytes, 64 B swizzle
   uint8_t* sDQ = sDS + 2 * 8192;                       // per half: 128 head-dim rows x 64 queries f16, 128 B swizzle
   float* sVec = reinterpret_cast<float*>(sDQ + 2 * 16384);   // 2 stages x {lse_log2[128], D''[128]}
-  // FP4 only: NVFP4 K tile (8 KB), two Q4 stages (8 KB each), scale atoms K 1 KB + Q 2 x 1 KB
-  uint8_t* sK4 = reinterpret_cast<uint8_t*>(sVec) + 2048;
-  uint8_t* sQ4 = sK4 + 8192;
+  // d = 64 only: the gradient rows' way out (2 x 16 KB; at d = 128 the finished item's K / V buffers serve)
+  uint8_t* sOut64 = reinterpret_cast<uint8_t*>(sVec) + 2048;
+  // FP4 only: NVFP4 K tiles (2 x 8 KB), Q4 stages (2 x 8 KB), scale atoms K 2 x 1 KB + Q 2 x 1 KB
+  uint8_t* sK4 = sOut64 + (D == 64 ? 2 * 16384 : 0);
+  uint8_t* sQ4 = sK4 + 2 * 8192;
   uint8_t* sSF = sQ4 + 2 * 8192;
   __shared__ __align__(8) uint64_t bars[BB_COUNT];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
-  __shared__ BTile tile_s;
+  __shared__ BTile tile_s[2];                          // the items in flight (written by the producer, item k in slot k & 1)
   __shared__ uint32_t sE[2][4];                        // [half][key block] = exponent bytes of the half's two query blocks
   __shared__ uint32_t sEP[2][128];                     // VAR 2: [half][key row] = P-hat exponent bytes of the two query blocks
   __shared__ __align__(4) uint8_t sEQ[2][64][4];       // VAR >= 1: [half][query][key block] = dQ-side dS-hat exponents
   constexpr bool RL = VAR >= 1, TL = VAR == 2;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // causal: grid = (kv heads, batch rows, key tiles), so key tiles with the same number of query tiles are dispatched
-  // together, longest first. Otherwise grid = (key tiles, kv heads, batch rows): the CTAs of one head run together and
-  // share its Q / dO tiles in L2.
-  const int hkv = p.causal ? blockIdx.x : blockIdx.y;
-  const int tile_id = p.causal ? blockIdx.z : blockIdx.x, bat_id = p.causal ? blockIdx.y : blockIdx.z;
+  const int G = gridDim.x, cta = blockIdx.x;
   const int grp = p.h / p.h_kv;
-  TRACE_INIT();
-  if (tid == 0) TRACE(6, 0, 0);
 
-  // Set-up by the TMA thread itself, which then starts the first loads (K, V and the first Q / dO tile) before the CTA-wide
-  // barrier: they fly while tensor memory is allocated and the other warps arrive (~1300 clocks earlier first scores).
   if (tid == 13 * 32) {
     abort_s = 0;
-    mbar_init(&bars[BB_KV], 1);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[BB_KV + i], 1); mbar_init(&bars[BB_KVE + i], 2);      // released by one thread of each compute warpgroup
       mbar_init(&bars[BB_QFULL + i], 1); mbar_init(&bars[BB_QEMPTY + i], 1);
       mbar_init(&bars[BB_S + i], 1); mbar_init(&bars[BB_DP + i], 1);
       mbar_init(&bars[BB_P + i], 4); mbar_init(&bars[BB_DS + i], 4); mbar_init(&bars[BB_EX + i], 4);      // one arrival per warp
       mbar_init(&bars[BB_DQF + i], 1); mbar_init(&bars[BB_DQE + i], 4);
-      mbar_init(&bars[BB_EP + i], 4);
+      mbar_init(&bars[BB_EP + i], 4); mbar_init(&bars[BB_EPI + i], 4);
     }
     mbar_init(&bars[BB_R1], 4);
     mbar_init(&bars[BB_R2], 4);
     mbar_init(&bars[BB_ACC], 1);
+    mbar_init(&bars[BB_ACCFREE], 8);
     fence_barrier_init();
-    BTile t;
-    if (p.doc_start == nullptr) {
-      t.bat = bat_id; t.k0 = tile_id * 128; t.nk = min(128, p.s_k - t.k0); t.krel = t.k0; t.q0 = 0; t.sq = p.s_q;
-      t.off = p.s_k - p.s_q;
-    } else {
-      int x = tile_id, dsel = -1, len = 0, st = 0;
-      for (int dI = 0; dI < p.n_docs; ++dI) {
-        doc_entry(p.doc_start, p.doc_len, dI, p.s_k, p.ctl.status, st, len);
-        const int nb = (len + 127) / 128;
-        if (x < nb) { dsel = dI; break; }
-        x -= nb;
-      }
-      if (dsel < 0) { t.nk = 0; t.bat = 0; t.k0 = 0; t.krel = 0; t.q0 = 0; t.sq = 0; t.off = 0; }
-      else {
-        t.bat = 0; t.k0 = st + x * 128; t.nk = min(128, len - x * 128); t.krel = x * 128; t.q0 = st; t.sq = len; t.off = 0;
-      }
-    }
-    tile_s = t;
-    int mh = (t.sq + 127) / 128, ml = 0;      // as below: the query tiles that see this key tile
-    if (p.win_r >= 0 && t.krel - t.off - p.win_r > 0) ml = (t.krel - t.off - p.win_r) / 128;
-    if (p.win_l >= 0) mh = min(mh, max(0, t.krel + t.nk - 1 - t.off + p.win_l) / 128 + 1);
-    if (t.nk > 0) {
-      tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_do);
-      mbar_arrive_expect_tx(&bars[BB_KV], 2 * TILE_BYTES + (FP4 ? 8192 + 1024 : 0));
-      tma_load_4d(sK, &tm_k, &bars[BB_KV], 0, hkv, t.k0, t.bat);
-      tma_load_4d(sV, &tm_v, &bars[BB_KV], 0, hkv, t.k0, t.bat);
-      if (FP4) {
-        tma_load_4d(sK4, &tm_k4, &bars[BB_KV], 0, hkv, t.k0, t.bat);
-        bulk_load(sSF, p.sfk4 + (((size_t)t.bat * p.h_kv + hkv) * (p.s_k / 128) + t.k0 / 128) * 1024, 1024, &bars[BB_KV]);
-      }
-      if (mh > ml) {       // iteration 0: first head of the group, first query tile
-        const int head = hkv * grp, m = ml;
-        mbar_arrive_expect_tx(&bars[BB_QFULL + 0], 2 * TILE_BYTES + 1024 + (FP4 ? 8192 + 1024 : 0));
-        tma_load_4d(sQ, &tm_q, &bars[BB_QFULL + 0], 0, head, t.q0 + m * 128, t.bat);
-        if (FP4) {
-          tma_load_4d(sQ4, &tm_q4, &bars[BB_QFULL + 0], 0, head, t.q0 + m * 128, t.bat);
-          bulk_load(sSF + 1024, p.sfq4 + (((size_t)t.bat * p.h + head) * (p.s_q / 128) + (t.q0 + m * 128) / 128) * 1024, 1024,
-                    &bars[BB_QFULL + 0]);
-        }
-        tma_load_4d(sDO, &tm_do, &bars[BB_QFULL + 0], 0, head, t.q0 + m * 128, t.bat);
-        const size_t ro = ((size_t)t.bat * p.h + head) * p.s_q + t.q0 + m * 128;
-        bulk_load(sVec, p.lse_log2 + ro, 512, &bars[BB_QFULL + 0]);
-        bulk_load(sVec + 128, p.d_rows + ro, 512, &bars[BB_QFULL + 0]);
-      }
-    }
+    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_acc); tma_prefetch_desc(&tm_dk); tma_prefetch_desc(&tm_dv);
+    if (FP4) { tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k4); }
   }
   if (warp == 0) {
     tmem_alloc(&tmem_base_s, 512);
@@ -228,168 +219,194 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const BTile T = tile_s;
   volatile int* abortp = &abort_s;
+  // (a status word already set by an earlier launch is not looked at: a kernel that runs after one that gave up does no harm)
 
-  // query tiles that see this key tile: the first query that sees its first key, the last one that sees its last key
-  int m_hi = (T.sq + 127) / 128;
-  int m_lo = 0;
-  if (p.win_r >= 0 && T.krel - T.off - p.win_r > 0) m_lo = (T.krel - T.off - p.win_r) / 128;
-  if (p.win_l >= 0) m_hi = min(m_hi, max(0, T.krel + T.nk - 1 - T.off + p.win_l) / 128 + 1);
-  const int n_m = (T.nk > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
-  const int n_it = n_m * grp;                                          // tile iterations: GQA heads x query tiles
-  // (a status word already set by an earlier launch is not looked at: the first loads are in flight by now, and a
-  // kernel that runs after one that gave up does no harm)
-  const bool early_out = T.nk <= 0;
-  if (tid == 0) TRACE(6, 0, 1);
-
-  if (!early_out) {
-    if (warp >= 12) reg_dealloc<80>();     // register budget per warpgroup: 176 / 176 / 80 / 80 (x 128 threads = 64 K)
-    if (warp == 13) {
-      // =================================================================== TMA producer
-      if (lane == 0) {
-        for (int it = 1; it < n_it; ++it) {      // K, V and iteration 0 were started during set-up
-          const int st = it & 1, u = it >> 1;
-          const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
-          if (it >= 2 && !mbar_wait(&bars[BB_QEMPTY + st], (u & 1) ^ 1, p.ctl, abortp, 10)) break;
-          mbar_arrive_expect_tx(&bars[BB_QFULL + st], 2 * TILE_BYTES + 1024 + (FP4 ? 8192 + 1024 : 0));
-          tma_load_4d(sQ + st * TILE_BYTES, &tm_q, &bars[BB_QFULL + st], 0, head, T.q0 + m * 128, T.bat);
+  if (warp >= 12) reg_dealloc<80>();     // register budget per warpgroup: 176 / 176 / 80 / 80 (x 128 threads = 64 K)
+  if (warp == 13) {
+    // =================================================================== TMA producer
+    if (lane == 0) {
+      int gi = 0;                          // query-tile iterations issued so far, over all items
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        const int L = bwd_item(k, G, cta, p.zigzag);
+        if (L >= p.n_items) break;
+        const int kb = k & 1;
+        // the buffers of item k - 2 (and its slot of tile_s) are free once both compute warpgroups have written its
+        // gradient rows out of them
+        if (k >= 2 && !(ok = mbar_wait(&bars[BB_KVE + kb], ((k >> 1) - 1) & 1, p.ctl, abortp, 11))) break;
+        BTile t;
+        bwd_decode(p, L, t);
+        tile_s[kb] = t;
+        if (t.nk > 0) {
+          mbar_arrive_expect_tx(&bars[BB_KV + kb], 2 * TILE_BYTES + (FP4 ? 8192 + 1024 : 0));
+          tma_load_4d(sK + kb * TILE_BYTES, &tm_k, &bars[BB_KV + kb], 0, t.hkv, t.k0, t.bat);
+          tma_load_4d(sV + kb * TILE_BYTES, &tm_v, &bars[BB_KV + kb], 0, t.hkv, t.k0, t.bat);
           if (FP4) {
-            tma_load_4d(sQ4 + st * 8192, &tm_q4, &bars[BB_QFULL + st], 0, head, T.q0 + m * 128, T.bat);
-            bulk_load(sSF + 1024 + st * 1024,
-                      p.sfq4 + (((size_t)T.bat * p.h + head) * (p.s_q / 128) + (T.q0 + m * 128) / 128) * 1024, 1024,
+            tma_load_4d(sK4 + kb * 8192, &tm_k4, &bars[BB_KV + kb], 0, t.hkv, t.k0, t.bat);
+            bulk_load(sSF + kb * 1024, p.sfk4 + (((size_t)t.bat * p.h_kv + t.hkv) * (p.s_k / 128) + t.k0 / 128) * 1024, 1024,
+                      &bars[BB_KV + kb]);
+          }
+        } else {
+          mbar_arrive(&bars[BB_KV + kb]);  // an empty tile slot: the phase still completes, every role moves on
+        }
+        const int n_it = t.n_m * grp;
+        for (int it = 0; it < n_it; ++it, ++gi) {
+          const int st = gi & 1;
+          const int head = t.hkv * grp + it / t.n_m, m = t.m_lo + it % t.n_m;
+          if (gi >= 2 && !(ok = mbar_wait(&bars[BB_QEMPTY + st], ((gi >> 1) - 1) & 1, p.ctl, abortp, 10))) break;
+          mbar_arrive_expect_tx(&bars[BB_QFULL + st], 2 * TILE_BYTES + 1024 + (FP4 ? 8192 + 1024 : 0));
+          tma_load_4d(sQ + st * TILE_BYTES, &tm_q, &bars[BB_QFULL + st], 0, head, t.q0 + m * 128, t.bat);
+          if (FP4) {
+            tma_load_4d(sQ4 + st * 8192, &tm_q4, &bars[BB_QFULL + st], 0, head, t.q0 + m * 128, t.bat);
+            bulk_load(sSF + 2048 + st * 1024,
+                      p.sfq4 + (((size_t)t.bat * p.h + head) * (p.s_q / 128) + (t.q0 + m * 128) / 128) * 1024, 1024,
                       &bars[BB_QFULL + st]);
           }
-          tma_load_4d(sDO + st * TILE_BYTES, &tm_do, &bars[BB_QFULL + st], 0, head, T.q0 + m * 128, T.bat);
-          const size_t ro = ((size_t)T.bat * p.h + head) * p.s_q + T.q0 + m * 128;
+          tma_load_4d(sDO + st * TILE_BYTES, &tm_do, &bars[BB_QFULL + st], 0, head, t.q0 + m * 128, t.bat);
+          const size_t ro = ((size_t)t.bat * p.h + head) * p.s_q + t.q0 + m * 128;
           bulk_load(sVec + st * 256, p.lse_log2 + ro, 512, &bars[BB_QFULL + st]);
           bulk_load(sVec + st * 256 + 128, p.d_rows + ro, 512, &bars[BB_QFULL + st]);
         }
       }
-    } else if (warp == 12) {
-      // =================================================================== UMMA issuer
-      // The whole warp stays converged through the waits and the descriptor arithmetic (warp-uniform values); one elected
-      // lane issues. Descriptors are built once; the loop only adds byte offsets.
-      {
-        constexpr uint32_t ID_N64 = idesc_f8(128, 64, 0, 0);
-        const uint32_t tm = __shfl_sync(0xFFFFFFFFu, tmem, 0);
-        const int n_steps = 2 * __shfl_sync(0xFFFFFFFFu, n_it, 0);
-        const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
-                       ds_addr = smem_u32(sDS);
-        const uint64_t dK_k = smem_desc(k_addr, 16, OP_SBO, OP_SWZ), dV_k = smem_desc(v_addr, 16, OP_SBO, OP_SWZ),
-                       dQ0 = smem_desc(q_addr, 16, OP_SBO, OP_SWZ), dDO0 = smem_desc(do_addr, 16, OP_SBO, OP_SWZ),
-                       dDS_A = smem_desc(ds_addr, 8192, 512, SWZ_64),   // d = 64: dS-hat as A, next M block 8 KB further
-                       dDS0 = smem_desc(ds_addr, 16, 512, SWZ_64);
-        const uint64_t dK4 = smem_desc(smem_u32(sK4), 16, 512, SWZ_64), dQ40 = smem_desc(smem_u32(sQ4), 16, 512, SWZ_64),
-                       dSF0 = smem_desc(smem_u32(sSF), 0, 128, SWZ_NONE);
-        bool ok = mbar_wait(&bars[BB_KV], 0, p.ctl, abortp, 20);
-        for (int t = 0; ok && t <= n_steps; ++t) {
-          if (t < n_steps) {
-            // ---- front end of step t: S^T_x and dP^T_x
-            const int it = t >> 1, x = t & 1, st = it & 1;
-            if (x == 0 && !(ok = mbar_wait(&bars[BB_QFULL + st], (it >> 1) & 1, p.ctl, abortp, 21))) break;
-            tc_fence_after();
-            const uint64_t qx = desc_adv(dQ0, st * TILE_BYTES + x * 64 * D), dox = desc_adv(dDO0, st * TILE_BYTES + x * 64 * D);
-            if (FP4) {
-              // the scale columns go into the half's dP^T region: its previous dQ^T must have been read out first
-              if (it > 0 && !(ok = mbar_wait(&bars[BB_DQE + x], (it - 1) & 1, p.ctl, abortp, 22))) break;
-              tc_fence_after();
-            }
-            if (elect_one()) {
-              if (FP4) {
-                const uint32_t park = tm + TC_DP + 64 * x;
-                const uint64_t q4x = desc_adv(dQ40, st * 8192 + x * 4096);
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                  tmem_cp_sf_atom(park + 4 * k, desc_adv(dSF0, 512 * k));
-                  tmem_cp_sf_atom(park + 8 + 4 * k, desc_adv(dSF0, 1024 + st * 1024 + 512 * k));
-                }
-#pragma unroll
-                for (int k = 0; k < 2; ++k)   // K = 64 elements = 32 bytes per instruction
-                  umma_nvf4_ss(tm + TC_S + 64 * x, desc_adv(dK4, 32 * k), desc_adv(q4x, 32 * k),
-                               idesc_bs(128, 64, 1, 1, 0, 0, 0, 0, 0), park + 4 * k, park + 8 + 4 * k + 2 * x, k > 0);
-              } else {
-#pragma unroll
-                for (int k = 0; k < D / 32; ++k)
-                  umma_f8_ss(tm + TC_S + 64 * x, desc_adv(dK_k, 32 * k), desc_adv(qx, 32 * k), ID_N64, k > 0);
-              }
-              tc_commit(&bars[BB_S + x]);
-              TRACE(0, t, 0);
-            }
-            __syncwarp();
-            // the half's dP^T columns hold its previous dQ^T until the reduction warps have read it
-            if (!FP4 && it > 0 && !(ok = mbar_wait(&bars[BB_DQE + x], (it - 1) & 1, p.ctl, abortp, 22))) break;
-            tc_fence_after();
-            if (elect_one()) {
-#pragma unroll
-              for (int k = 0; k < D / 32; ++k)
-                umma_f8_ss(tm + TC_DP + 64 * x, desc_adv(dV_k, 32 * k), desc_adv(dox, 32 * k), ID_N64, k > 0);
-              tc_commit(&bars[BB_DP + x]);
-              TRACE(0, t, 1);
-            }
-            __syncwarp();
-          }
-          if (t >= 1) {
-            // ---- back end of step t - 1: dV, dK, dQ^T of half y
-            const int tb = t - 1, it = tb >> 1, y = tb & 1, st = it & 1;
-            const uint32_t sx = tm + TC_S + 64 * y;
-            const uint64_t qy = desc_adv(dQ0, st * TILE_BYTES + y * 64 * D), doy = desc_adv(dDO0, st * TILE_BYTES + y * 64 * D);
-            const uint32_t accum = tb > 0;
-            if (!(ok = mbar_wait(&bars[BB_P + y], it & 1, p.ctl, abortp, 23))) break;
-            tc_fence_after();
-            if (elect_one()) {
-              TRACE(0, tb, 2);
-#pragma unroll
-              for (int kk = 0; kk < 2; ++kk)     // K = 64 queries: two instructions of 32
-                umma_mxf8_ts(tm + TC_DV, sx + TO_P + 8 * kk, desc_adv(doy, kk * 32 * D),
-                             idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), sx + TO_SFA_P, sx + TO_SFB_DO, accum | kk);
-              TRACE(0, tb, 3);
-            }
-            __syncwarp();
-            if (!(ok = mbar_wait(&bars[BB_DS + y], it & 1, p.ctl, abortp, 24))) break;
-            tc_fence_after();
-            if (elect_one()) {
-              TRACE(0, tb, 4);
-#pragma unroll
-              for (int kk = 0; kk < 2; ++kk)
-                umma_mxf8_ts(tm + TC_DK, sx + TO_DS + 8 * kk, desc_adv(qy, kk * 32 * D),
-                             idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), sx + TO_SFA_DK, sx + TO_SFB_Q, accum | kk);
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {   // K = 128 keys
-                if (D == 128)      // A = K tile (M = head dim), B = dS-hat half (N = 64 queries)
-                  umma_mxf8_ss(tm + TC_DP + 64 * y, desc_adv(dK_k, kk * 32 * D), desc_adv(dDS0, y * 8192 + kk * 2048),
-                               idesc_bs(128, 64, 0, 0, 1, 1, 1, kk, kk), sx + TO_SFA_DQ, sx + TO_SFB_DQ, kk > 0);
-                else               // A = dS-hat half (M = 64 queries + 64 unused rows), B = K tile (N = head dim)
-                  umma_mxf8_ss(tm + TC_DP + 64 * y, desc_adv(dDS_A, y * 8192 + kk * 2048), desc_adv(dK_k, kk * 32 * D),
-                               idesc_bs(128, 64, 0, 0, 1, 1, 1, kk, kk), sx + TO_SFB_DQ, sx + TO_SFA_DQ, kk > 0);
-              }
-              tc_commit(&bars[BB_DQF + y]);
-              TRACE(0, tb, 5);
-              if (y == 1) tc_commit(&bars[BB_QEMPTY + st]);
-            }
-            __syncwarp();
-          }
-        }
-        if (ok && elect_one()) tc_commit(&bars[BB_ACC]);
-        __syncwarp();
-      }
-    } else if (warp >= 8 && warp < 12) {
-      reg_dealloc<80>();
-      // =================================================================== dQ reduction (thread = head-dim row)
-      const int r = tid & 127;
-      const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-      bool ok = true;
+    }
+  } else if (warp == 12) {
+    // =================================================================== UMMA issuer
+    // The whole warp stays converged through the waits and the descriptor arithmetic (warp-uniform values); one elected
+    // lane issues. Descriptors are built once; the loops only add byte offsets.
+    constexpr uint32_t ID_N64 = idesc_f8(128, 64, 0, 0);
+    const uint32_t tm = __shfl_sync(0xFFFFFFFFu, tmem, 0);
+    const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
+                   ds_addr = smem_u32(sDS);
+    const uint64_t dQ0 = smem_desc(q_addr, 16, OP_SBO, OP_SWZ), dDO0 = smem_desc(do_addr, 16, OP_SBO, OP_SWZ),
+                   dDS_A = smem_desc(ds_addr, 8192, 512, SWZ_64),   // d = 64: dS-hat as A, next M block 8 KB further
+                   dDS0 = smem_desc(ds_addr, 16, 512, SWZ_64);
+    const uint32_t k4_addr = smem_u32(sK4);
+    const uint64_t dQ40 = smem_desc(smem_u32(sQ4), 16, 512, SWZ_64), dSF0 = smem_desc(smem_u32(sSF), 0, 128, SWZ_NONE);
+    int gi = 0;
+    bool ok = true;
+    for (int k = 0; ok; ++k) {
+      const int L = bwd_item(k, G, cta, p.zigzag);
+      if (L >= p.n_items) break;
+      const int kb = k & 1;
+      if (!(ok = mbar_wait(&bars[BB_KV + kb], (k >> 1) & 1, p.ctl, abortp, 20))) break;
+      const int n_it = tile_s[kb].n_m * grp;
       const int n_steps = 2 * n_it;
-      for (int t = 0; t < n_steps; ++t) {
-        const int it = t >> 1, y = t & 1;
-        const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
-        // the staging buffer of this half was last read by the reduction of step t - 2
+      const uint64_t dK_k = smem_desc(k_addr + kb * TILE_BYTES, 16, OP_SBO, OP_SWZ),
+                     dV_k = smem_desc(v_addr + kb * TILE_BYTES, 16, OP_SBO, OP_SWZ),
+                     dK4 = smem_desc(k4_addr + kb * 8192, 16, 512, SWZ_64);
+      for (int t = 0; ok && t <= n_steps; ++t) {
+        if (t < n_steps) {
+          // ---- front end of step t: S^T_x and dP^T_x
+          const int g = gi + (t >> 1), x = t & 1, st = g & 1;
+          if (x == 0 && !(ok = mbar_wait(&bars[BB_QFULL + st], (g >> 1) & 1, p.ctl, abortp, 21))) break;
+          tc_fence_after();
+          const uint64_t qx = desc_adv(dQ0, st * TILE_BYTES + x * 64 * D), dox = desc_adv(dDO0, st * TILE_BYTES + x * 64 * D);
+          if (FP4) {
+            // the scale columns go into the half's dP^T region: its previous dQ^T must have been read out first
+            if (g > 0 && !(ok = mbar_wait(&bars[BB_DQE + x], (g - 1) & 1, p.ctl, abortp, 22))) break;
+            tc_fence_after();
+          }
+          if (elect_one()) {
+            if (FP4) {
+              const uint32_t park = tm + TC_DP + 64 * x;
+              const uint64_t q4x = desc_adv(dQ40, st * 8192 + x * 4096);
+#pragma unroll
+              for (int kk = 0; kk < 2; ++kk) {
+                tmem_cp_sf_atom(park + 4 * kk, desc_adv(dSF0, kb * 1024 + 512 * kk));
+                tmem_cp_sf_atom(park + 8 + 4 * kk, desc_adv(dSF0, 2048 + st * 1024 + 512 * kk));
+              }
+#pragma unroll
+              for (int kk = 0; kk < 2; ++kk)   // K = 64 elements = 32 bytes per instruction
+                umma_nvf4_ss(tm + TC_S + 64 * x, desc_adv(dK4, 32 * kk), desc_adv(q4x, 32 * kk),
+                             idesc_bs(128, 64, 1, 1, 0, 0, 0, 0, 0), park + 4 * kk, park + 8 + 4 * kk + 2 * x, kk > 0);
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < D / 32; ++kk)
+                umma_f8_ss(tm + TC_S + 64 * x, desc_adv(dK_k, 32 * kk), desc_adv(qx, 32 * kk), ID_N64, kk > 0);
+            }
+            tc_commit(&bars[BB_S + x]);
+          }
+          __syncwarp();
+          // the half's dP^T columns hold its previous dQ^T until the reduction warps have read it
+          if (!FP4 && g > 0 && !(ok = mbar_wait(&bars[BB_DQE + x], (g - 1) & 1, p.ctl, abortp, 22))) break;
+          tc_fence_after();
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < D / 32; ++kk)
+              umma_f8_ss(tm + TC_DP + 64 * x, desc_adv(dV_k, 32 * kk), desc_adv(dox, 32 * kk), ID_N64, kk > 0);
+            tc_commit(&bars[BB_DP + x]);
+          }
+          __syncwarp();
+        }
+        if (t >= 1) {
+          // ---- back end of step t - 1: dV, dK, dQ^T of half y
+          const int tb = t - 1, g = gi + (tb >> 1), y = tb & 1, st = g & 1;
+          const uint32_t sx = tm + TC_S + 64 * y;
+          const uint64_t qy = desc_adv(dQ0, st * TILE_BYTES + y * 64 * D), doy = desc_adv(dDO0, st * TILE_BYTES + y * 64 * D);
+          const uint32_t accum = tb > 0;
+          // the first products of an item overwrite dV / dK: the previous item's rows must have left tensor memory
+          if (tb == 0 && k > 0 && !(ok = mbar_wait(&bars[BB_ACCFREE], (k - 1) & 1, p.ctl, abortp, 25))) break;
+          if (!(ok = mbar_wait(&bars[BB_P + y], g & 1, p.ctl, abortp, 23))) break;
+          tc_fence_after();
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk)     // K = 64 queries: two instructions of 32
+              umma_mxf8_ts(tm + TC_DV, sx + TO_P + 8 * kk, desc_adv(doy, kk * 32 * D),
+                           idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), sx + TO_SFA_P, sx + TO_SFB_DO, accum | kk);
+          }
+          __syncwarp();
+          if (!(ok = mbar_wait(&bars[BB_DS + y], g & 1, p.ctl, abortp, 24))) break;
+          tc_fence_after();
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk)
+              umma_mxf8_ts(tm + TC_DK, sx + TO_DS + 8 * kk, desc_adv(qy, kk * 32 * D),
+                           idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk), sx + TO_SFA_DK, sx + TO_SFB_Q, accum | kk);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {   // K = 128 keys
+              if (D == 128)      // A = K tile (M = head dim), B = dS-hat half (N = 64 queries)
+                umma_mxf8_ss(tm + TC_DP + 64 * y, desc_adv(dK_k, kk * 32 * D), desc_adv(dDS0, y * 8192 + kk * 2048),
+                             idesc_bs(128, 64, 0, 0, 1, 1, 1, kk, kk), sx + TO_SFA_DQ, sx + TO_SFB_DQ, kk > 0);
+              else               // A = dS-hat half (M = 64 queries + 64 unused rows), B = K tile (N = head dim)
+                umma_mxf8_ss(tm + TC_DP + 64 * y, desc_adv(dDS_A, y * 8192 + kk * 2048), desc_adv(dK_k, kk * 32 * D),
+                             idesc_bs(128, 64, 0, 0, 1, 1, 1, kk, kk), sx + TO_SFB_DQ, sx + TO_SFA_DQ, kk > 0);
+            }
+            tc_commit(&bars[BB_DQF + y]);
+            if (y == 1) tc_commit(&bars[BB_QEMPTY + st]);
+          }
+          __syncwarp();
+        }
+      }
+      if (!ok) break;
+      // an item without query tiles issues nothing, but its accumulator hand-over still takes place once
+      if (n_steps == 0 && k > 0 && !(ok = mbar_wait(&bars[BB_ACCFREE], (k - 1) & 1, p.ctl, abortp, 25))) break;
+      if (elect_one()) tc_commit(&bars[BB_ACC]);       // every product of the item has completed when this arrives
+      __syncwarp();
+      gi += n_it;
+    }
+  } else if (warp >= 8 && warp < 12) {
+    reg_dealloc<80>();
+    // =================================================================== dQ reduction (thread = head-dim row)
+    const int r = tid & 127;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    bool ok = true;
+    int gi = 0, gt = 0;                     // iterations and half steps so far, over all items
+    for (int k = 0; ok; ++k) {
+      const int L = bwd_item(k, G, cta, p.zigzag);
+      if (L >= p.n_items) break;
+      const int kb = k & 1;
+      if (!(ok = mbar_wait(&bars[BB_KV + kb], (k >> 1) & 1, p.ctl, abortp, 43))) break;
+      const BTile T = tile_s[kb];
+      const int n_it = T.n_m * grp;
+      for (int t = 0; t < 2 * n_it; ++t, ++gt) {
+        const int it = t >> 1, y = t & 1, g = gi + it;
+        const int head = T.hkv * grp + it / T.n_m, m = T.m_lo + it % T.n_m;
+        // the staging buffer of this half was last read by the reduction of step gt - 2
         if (tid == 256) tma_store_wait_read<1>();
         mbar_arrive_warp(&bars[BB_R1]);
-        if (!(ok = mbar_wait(&bars[BB_R1], t & 1, p.ctl, abortp, 41))) break;
-        if (r == 0) TRACE(3, t, 0);
-        if (!(ok = mbar_wait(&bars[BB_DQF + y], it & 1, p.ctl, abortp, 40))) break;
-        if (r == 0) TRACE(3, t, 1);
+        if (!(ok = mbar_wait(&bars[BB_R1], gt & 1, p.ctl, abortp, 41))) break;
+        if (!(ok = mbar_wait(&bars[BB_DQF + y], g & 1, p.ctl, abortp, 40))) break;
         tc_fence_after();
         const uint32_t rowp = smem_u32(sDQ) + y * 16384 + r * 128;
         // d = 128: thread = head-dim row of dQ^T, 64 query columns. d = 64: thread = query row (the first 64 lanes; the
@@ -414,25 +431,40 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         tc_fence_before();
         mbar_arrive_warp(&bars[BB_DQE + y]);
-        if (r == 0) TRACE(3, t, 2);
         fence_proxy_async();
         mbar_arrive_warp(&bars[BB_R2]);
-        if (!(ok = mbar_wait(&bars[BB_R2], t & 1, p.ctl, abortp, 42))) break;
+        if (!(ok = mbar_wait(&bars[BB_R2], gt & 1, p.ctl, abortp, 42))) break;
         if (tid == 256) {
           if (D == 128) tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, T.q0 + m * 128 + 64 * y, 0, head, T.bat);
           else tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, 0, T.q0 + m * 128 + 64 * y, head, T.bat);
           tma_store_commit();
         }
       }
-      if (tid == 256) tma_store_wait<0>();
-    } else if (warp < 8) {
-      reg_alloc<176>();
-      // =================================================================== compute (thread = key row, 64 query columns)
-      const int x = warp >> 2;                         // the half this warpgroup owns
-      const int wq = warp & 3;                         // lane quadrant = 32-key block of the tile
-      const int r = wq * 32 + lane;                    // key row of the tile = TMEM lane
-      const uint32_t lane_base = tmem + ((uint32_t)(wq * 32) << 16);
-      const uint32_t t_sx = lane_base + TC_S + 64 * x, t_dpx = lane_base + TC_DP + 64 * x;
+      gi += n_it;
+    }
+    if (tid == 256) tma_store_wait<0>();
+  } else if (warp < 8) {
+    reg_alloc<176>();
+    // =================================================================== compute (thread = key row, 64 query columns)
+    const int x = warp >> 2;                         // the half this warpgroup owns
+    const int wq = warp & 3;                         // lane quadrant = 32-key block of the tile
+    const int r = wq * 32 + lane;                    // key row of the tile = TMEM lane
+    const uint32_t lane_base = tmem + ((uint32_t)(wq * 32) << 16);
+    const uint32_t t_sx = lane_base + TC_S + 64 * x, t_dpx = lane_base + TC_DP + 64 * x;
+    const uint32_t ds_row = smem_u32(sDS) + x * 8192 + r * 64;
+    bool ok = true;
+    int gi = 0, epi = 0;                             // iterations so far; uses of the epilogue barrier so far
+    for (int k = 0; ok; ++k) {
+      const int L = bwd_item(k, G, cta, p.zigzag);
+      if (L >= p.n_items) break;
+      const int kb = k & 1;
+      if (!(ok = mbar_wait(&bars[BB_KV + kb], (k >> 1) & 1, p.ctl, abortp, 39))) break;
+      // token-local variant: short of registers, so the tile is read from its slot where needed (the slot stays valid until
+      // this item's buffers are released); otherwise a register copy
+      const BTile Tcopy = tile_s[kb];
+      const BTile& T = TL ? tile_s[kb] : Tcopy;
+      const int hkv = T.hkv, n_m = T.n_m, m_lo = T.m_lo;
+      const int n_it = n_m * grp;
       const int krel = T.krel + r;
       const bool key_valid = r < T.nk;
       const size_t bh_k = (size_t)T.bat * p.h_kv + hkv;
@@ -444,15 +476,13 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       uint32_t ek_word = TL ? 0x7F7F7F7Fu : 0u;        // UE8M0 bytes of the tile's four key blocks (unit when token-local)
       if (!TL) {
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb)
-          ek_word |= ((__float_as_uint(p.fac_k[bh_k * (p.s_k / 32) + T.k0 / 32 + kb]) >> 23) & 0xFF) << (8 * kb);
+        for (int kbk = 0; kbk < 4; ++kbk)
+          ek_word |= ((__float_as_uint(p.fac_k[bh_k * (p.s_k / 32) + T.k0 / 32 + kbk]) >> 23) & 0xFF) << (8 * kbk);
       }
-      const uint32_t ds_row = smem_u32(sDS) + x * 8192 + r * 64;
       const int vis_from = p.win_r >= 0 ? (krel - T.off - p.win_r) : 0;    // queries in [vis_from, vis_to] see this key
       const int vis_to = p.win_l >= 0 ? (krel - T.off + p.win_l) : 0x7FFFFFFF;
-      bool ok = true;
       for (int it = 0; it < n_it; ++it) {
-        const int st = it & 1, u = it >> 1;
+        const int g = gi + it, st = g & 1, u = g >> 1;
         const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
         const size_t bh_q = (size_t)T.bat * p.h + head;
         const int qb0 = (T.q0 + m * 128) / 32 + 2 * x;                     // first of the half's two 32-query blocks
@@ -476,9 +506,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const bool full = key_valid && (q_first >= vis_from) && (q_first + 63 <= vis_to) && (q_first + 64 <= T.sq);
 
         // ---- P' = 2^(s c - lse2)
-        if (r == 0) TRACE(1 + x, it, 0);
-        if (!(ok = mbar_wait(&bars[BB_S + x], it & 1, p.ctl, abortp, 31))) break;
-        if (r == 0) TRACE(1 + x, it, 1);
+        if (!(ok = mbar_wait(&bars[BB_S + x], g & 1, p.ctl, abortp, 31))) break;
         tc_fence_after();
         uint32_t pv[64];
         FL_TMEM_LD_32(t_sx, pv);
@@ -531,7 +559,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           // every lane quadrant holds the whole A scale tile: column = key block, lane = row of the block
           sEP[x][r] = ep[0] | (ep[1] << 8);
           mbar_arrive_warp(&bars[BB_EP + x]);
-          if (!(ok = mbar_wait(&bars[BB_EP + x], it & 1, p.ctl, abortp, 37))) break;
+          if (!(ok = mbar_wait(&bars[BB_EP + x], g & 1, p.ctl, abortp, 37))) break;
           uint32_t sf[8] = {sEP[x][lane], sEP[x][32 + lane], sEP[x][64 + lane], sEP[x][96 + lane],
                             0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu};
           FL_TMEM_ST_8(t_sx + TO_SFA_P, sf);
@@ -547,11 +575,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_wait_st();
         tc_fence_before();
         mbar_arrive_warp(&bars[BB_P + x]);
-        if (r == 0) TRACE(1 + x, it, 2);
 
         // ---- dS = P' (b dP + D''), block exponent per (this warp's 32 keys, 32 queries)
-        if (!(ok = mbar_wait(&bars[BB_DP + x], it & 1, p.ctl, abortp, 32))) break;
-        if (r == 0) TRACE(1 + x, it, 3);
+        if (!(ok = mbar_wait(&bars[BB_DP + x], g & 1, p.ctl, abortp, 32))) break;
         tc_fence_after();
         FL_TMEM_LD_32(t_dpx, pv);
         FL_TMEM_LD_32(t_dpx + 32, (pv + 32));
@@ -575,21 +601,22 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             pf[j + 1] *= fmaf(__uint_as_float(pv[j + 1]), b4.y, d4.y);
             pf[j + 2] *= fmaf(__uint_as_float(pv[j + 2]), b4.z, d4.z);
             pf[j + 3] *= fmaf(__uint_as_float(pv[j + 3]), b4.w, d4.w);
-            if (!full) {
-              // masked entries hold P' = 0, but their dP^T or D'' may come from rows outside the document (padding or
-              // whatever the buffer held: possibly Inf / NaN), and 0 * NaN is NaN: select, do not multiply
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int qi = q_first + j + e;
-                pf[j + e] = (key_valid && qi >= vis_from && qi <= vis_to && qi < T.sq) ? pf[j + e] : 0.f;
-              }
-            }
             // the dK side carries f_Q(query) when the operands are token-local
             am = fmaxf(am, fmaxf(fmaxf(fabsf(pf[j] * q4.x), fabsf(pf[j + 1] * q4.y)),
                                  fmaxf(fabsf(pf[j + 2] * q4.z), fabsf(pf[j + 3] * q4.w))));
           }
           const uint32_t wm = warp_max_u32(__float_as_uint(am));          // non-negative floats order as integers
           ebyte[qh] = exp448(wm);                                          // 448 * 2^(e-127) >= amax
+        }
+        if (!full) {      // diagonal / tail tiles only
+          // masked entries hold P' = 0, but their dP^T or D'' may come from rows outside the document (padding or whatever
+          // the buffer held: possibly Inf / NaN), and 0 * NaN is NaN: select again after the multiply. (The maxima above
+          // ignore NaN, so the block exponents are those of the visible entries.)
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            const int qi = q_first + j;
+            pf[j] = (key_valid && qi >= vis_from && qi <= vis_to && qi < T.sq) ? pf[j] : 0.f;
+          }
         }
         if (lane == 0) sE[x][wq] = ebyte[0] | (ebyte[1] << 8);
         if (!RL) mbar_arrive_warp(&bars[BB_EX + x]);
@@ -637,9 +664,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4)
           sts128(ds_row + ((q4 ^ ((r >> 1) & 3)) << 4), dsw[4 * q4], dsw[4 * q4 + 1], dsw[4 * q4 + 2], dsw[4 * q4 + 3]);
-        if (r == 0) TRACE(1 + x, it, 4);
-        if (!(ok = mbar_wait(&bars[BB_EX + x], it & 1, p.ctl, abortp, 36))) break;
-        if (r == 0) TRACE(1 + x, it, 5);
+        if (!(ok = mbar_wait(&bars[BB_EX + x], g & 1, p.ctl, abortp, 36))) break;
         {
           // dK:   A[key lane, column = key block]  bytes = the half's two query blocks;  B = Q's exponents
           // dQ^T: A[head-dim lane] = K's exponents (+ pre-scale) per key block; B[query lane, column = query block of
@@ -663,19 +688,19 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         fence_proxy_async();             // the dS-hat tile in shared memory is read by the tensor core (async proxy)
         tc_fence_before();
         mbar_arrive_warp(&bars[BB_DS + x]);
-        if (r == 0) TRACE(1 + x, it, 6);
       }
-      // ---- epilogue: warpgroup 0 writes dV, warpgroup 1 writes dK (full rows)
-      if (r == 0) TRACE(6, 0, 2 + 3 * x);
-      if (ok) ok = mbar_wait(&bars[BB_ACC], 0, p.ctl, abortp, 33);
-      if (r == 0) TRACE(6, 0, 3 + 3 * x);
-      if (ok) {
-        tc_fence_after();
+      if (!ok) break;
+      gi += n_it;
+
+      // ---- item epilogue: warpgroup 0 writes dV, warpgroup 1 writes dK (full rows)
+      if (!(ok = mbar_wait(&bars[BB_ACC], k & 1, p.ctl, abortp, 33))) break;
+      tc_fence_after();
+      {
         const uint32_t t_acc = lane_base + (x == 0 ? TC_DV : TC_DK);
         const float mult = (x == 0) ? 0.00390625f : p.softmax_scale;       // dV carries 2^8 (P'), dK the softmax scale
         float y[D];
         if (n_it > 0) {                  // (CTA-uniform: the tensor-memory loads are warp-collective)
-          uint32_t v[D];                 // all four loads in flight, one wait
+          uint32_t v[D];                 // all loads in flight, one wait
 #pragma unroll
           for (int cc = 0; cc < D / 32; ++cc) FL_TMEM_LD_32(t_acc + 32 * cc, (v + 32 * cc));
           tc_wait_ld();
@@ -686,6 +711,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
           for (int e = 0; e < D; ++e) y[e] = 0.f;
         }
+        // the accumulators are in registers: the next item's products may overwrite them
+        tc_fence_before();
+        mbar_arrive_warp(&bars[BB_ACCFREE]);
         if (D == 128 && x == 1 && p.had_dk) {       // dK of rotated operands: (y H / sqrt(128)) * signs
 #pragma unroll
           for (int hs = 1; hs < D; hs <<= 1) {
@@ -705,54 +733,56 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if ((NEG[i >> 5] >> (i & 31)) & 1) y[i] = -y[i];
           }
         }
-        // rows -> shared memory (two boxes of 64 elements, 128 B swizzle) -> one TMA store per box: a thread's own 256-byte
-        // row written straight to global memory costs 32 separate 128-byte lines per warp instruction
-        uint8_t* stage = (x == 0) ? sQ : sDO;            // the operand stages are dead: every product has completed
+        // rows -> shared memory (boxes of 64 elements, 128 B swizzle) -> one TMA store per box: a thread's own row
+        // written straight to global memory costs 32 separate 128-byte lines per warp instruction. The way out at
+        // d = 128 is the finished item's K (warpgroup 0) / V (warpgroup 1) buffer: every product that read it has completed.
+        uint8_t* stage = (D == 128) ? ((x == 0 ? sK : sV) + kb * TILE_BYTES) : (sOut64 + x * 16384);
         const uint32_t srow = smem_u32(stage) + r * 128;
+        const CUtensorMap* tm_out = (x == 0) ? &tm_dv : &tm_dk;
 #pragma unroll
-        for (int c8 = 0; c8 < D / 8; ++c8) {
-          uint32_t w[4];
+        for (int pass = 0; pass < D / 64; ++pass) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float a = y[8 * c8 + 2 * e], b2 = y[8 * c8 + 2 * e + 1];
-            if (p.out_f16) {
-              __half2 hh = __floats2half2_rn(a, b2);
-              w[e] = *reinterpret_cast<uint32_t*>(&hh);
-            } else {
-              w[e] = pack_bf16x2(a, b2);
+          for (int c8 = 0; c8 < 8; ++c8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float a = y[64 * pass + 8 * c8 + 2 * e], b2 = y[64 * pass + 8 * c8 + 2 * e + 1];
+              if (p.out_f16) {
+                __half2 hh = __floats2half2_rn(a, b2);
+                w[e] = *reinterpret_cast<uint32_t*>(&hh);
+              } else {
+                w[e] = pack_bf16x2(a, b2);
+              }
             }
+            sts128(srow + ((c8 ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
           }
-          sts128(srow + (c8 >> 3) * 16384 + (((c8 & 7) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+          fence_proxy_async();
+          mbar_arrive_warp(&bars[BB_EPI + x]);            // the warpgroup's four warps have written their rows
+          if (!(ok = mbar_wait(&bars[BB_EPI + x], epi & 1, p.ctl, abortp, 38))) break;
+          ++epi;
+          if (r == 0 && T.nk > 0) {
+            tma_store_4d(tm_out, stage, 64 * pass, hkv, T.k0, T.bat);
+            tma_store_commit();
+            tma_store_wait_read<0>();    // the shared-memory source must outlive the copy; the writes complete with the grid
+          }
+          mbar_arrive_warp(&bars[BB_EPI + x]);            // the buffer has been read: the next pass / the producer may take it
+          if (!(ok = mbar_wait(&bars[BB_EPI + x], epi & 1, p.ctl, abortp, 38))) break;
+          ++epi;
         }
-        fence_proxy_async();
-        mbar_arrive_warp(&bars[BB_EX + x]);              // the warpgroup's four warps; phase n_it of that barrier
-        if (mbar_wait(&bars[BB_EX + x], n_it & 1, p.ctl, abortp, 38) && r == 0) {
-          const CUtensorMap* tm_out = (x == 0) ? &tm_dv : &tm_dk;
-          tma_store_4d(tm_out, stage, 0, hkv, T.k0, T.bat);
-          if (D == 128) tma_store_4d(tm_out, stage + 16384, 64, hkv, T.k0, T.bat);
-          tma_store_commit();
-          tma_store_wait_read<0>();      // the shared-memory source must outlive the copy; the writes complete with the grid
-        }
+        if (!ok) break;
+        if (r == 0) mbar_arrive(&bars[BB_KVE + kb]);
       }
     }
   }
-  if (tid == 0 || tid == 128) TRACE(6, 0, 4 + 3 * (tid >> 7));
   if (abort_s) {
     for (int it = 0; it < 200; ++it) __nanosleep(1000);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
-  if (tid == 0) TRACE(6, 1, 0);
 }
 
 }  // namespace fl
-
-#ifdef FL_TRACE
-extern "C" int fl_debug_set_trace(void* buf) {
-  return cudaMemcpyToSymbol(fl::g_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
-}
-#endif
 
 extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   using namespace fl;
@@ -804,8 +834,14 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.ctl.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kDefaultWaitCycles;
   const int ntile = a->doc_start ? (a->s_k / 128 + a->n_docs) : a->s_k / 128;
   const int nb = a->doc_start ? 1 : a->b;
-  dim3 grid = p.causal ? dim3(a->h_kv, nb, ntile) : dim3(ntile, a->h_kv, nb);
-  const int smem = 6 * 128 * a->d + 2 * 8192 + 2 * 16384 + 2048 + 1024 + (fp4 ? 3 * 8192 + 3 * 1024 : 0);
+  p.n_tile = ntile;
+  const long long n_items = (long long)ntile * a->h_kv * nb;
+  if (n_items > 0x3FFFFFFF) return FL_ERR_TOO_LARGE;
+  p.n_items = (int)n_items;
+  p.zigzag = (p.causal && !a->doc_start) ? 1 : 0;
+  const int grid = (int)(n_items < sm_count() ? n_items : sm_count());     // one persistent CTA per SM
+  const int smem = 8 * 128 * a->d + 2 * 8192 + 2 * 16384 + 2048 + (a->d == 64 ? 2 * 16384 : 0) + 1024 +
+                   (fp4 ? 4 * 8192 + 4 * 1024 : 0);
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
     kern<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, mdk, mdv, p);

@@ -22,6 +22,9 @@ int make_acc_map_16(CUtensorMap* m, const void* base, int b, int heads, int s, i
 
 int make_acc_t_map_16(CUtensorMap* m, const void* base, int b, int heads, int d, int s);
 
+// multiprocessors of the current device (cached per device): the size of a persistent grid
+int sm_count();
+
 static constexpr long long kDefaultWaitCycles = 1ll << 31;
 
 }  // namespace fl

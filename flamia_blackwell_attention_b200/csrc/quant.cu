@@ -458,18 +458,6 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   }
 }
 
-static int sm_count() {
-  static int n[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (!n[dev]) {
-    int v = 0;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
-    n[dev] = v;
-  }
-  return n[dev];
-}
-
 template <int D, int MODE, bool PRO>
 static int launch_quant(const CUtensorMap& mx, const CUtensorMap& mo, const QuantParams& p, bool want_t, cudaStream_t st) {
   constexpr int TILE_B = QT * D * 2;

@@ -141,8 +141,9 @@ def attn_args(q, k, v, *, causal, softmax_scale, mode=L.FL_MODE_FP8, flags=0, st
 
 
 def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L.FL_MODE_FP8, status=None,
-             doc_start=None, doc_len=None, wait_cycles=0, token_local=False, window=None):
-    """Forward kernel on quantised operands. Returns (out (b, s_q, h, d), lse (b, h, s_q) float32, status)."""
+             doc_start=None, doc_len=None, wait_cycles=0, token_local=False, window=None, p_group=False):
+    """Forward kernel on quantised operands. Returns (out (b, s_q, h, d), lse (b, h, s_q) float32, status).
+    p_group: group-frame P-hat (one UE8M0 exponent per query row and 32 keys) instead of the row frame."""
     qc = q["codes"]
     b, s_q, h, d = qc.shape
     dev = qc.device
@@ -154,7 +155,8 @@ def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L
     out = alloc(b, s_q, h, d, dtype=out_dtype, device=dev)
     lse = alloc(b, h, s_q, dtype=torch.float32, device=dev)
     a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode,
-                  flags=L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0, status=status, doc_start=doc_start,
+                  flags=(L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0) | (L.FL_A_P_GROUP if p_group else 0),
+                  status=status, doc_start=doc_start,
                   doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local, window=window)
     a.out, a.lse = L.ptr(out), L.ptr(lse)
     L.check(L.load().fl_fwd(C.byref(a), _stream()), "fl_fwd")

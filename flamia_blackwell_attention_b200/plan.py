@@ -54,7 +54,7 @@ class FwdSpec:
     qk_format: str         # e4m3 | nvfp4
     pv_operand: str        # e4m3
     operand_scaling: str   # token_block | token_local
-    p_hat_frame: str       # row
+    p_hat_frame: str       # row | group
     softmax_exp: str       # exp2
     qk_hadamard: bool
     causal: bool
@@ -239,11 +239,11 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
 
 
 def _finish(entry, route, qk_format, shape, log_rows, opts, *, softmax_scale, causal, return_lse, had, scaling, rowlocal,
-            ragged, dq_causal, window_size=(None, None)):
+            ragged, dq_causal, window_size=(None, None), p_frame="row"):
     sc = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(shape.d)
     # sliding window (left, right): None / -1 = unlimited on that side; causal caps the right side at 0 in the kernels
     win = tuple(None if (w is None or w < 0) else int(w) for w in tuple(window_size))
-    fwd = FwdSpec("fwd_sm100", qk_format, "e4m3", scaling, "row", "exp2", had, bool(causal), shape.varlen,
+    fwd = FwdSpec("fwd_sm100", qk_format, "e4m3", scaling, p_frame, "exp2", had, bool(causal), shape.varlen,
                   shape.aligned_varlen, ragged, bool(return_lse), None if win == (None, None) else win)
     bwd = BwdSpec("1cta" if shape.requires_grad else "none", scaling, "block_32x32", rowlocal, "row", "e4m3", False,
                   "causal_tile" if dq_causal else "row")
@@ -273,9 +273,6 @@ def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     if o.forward_kernel == "upstream":
         _fail(16, ValueError, "flash_attn_fp8: operand_scaling='auto' resolves to token blocks, which cannot serve this "
                               "call: forward_kernel='upstream'")
-    if o.p_hat_frame == "group":
-        _fail("B6", NotImplementedError, "p_hat_frame='group' is not built on the 8-bit entry: the row frame is its "
-                                         "default")
     shape = _shape_of("fp8", q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k, max_seqlen_q, max_seqlen_k)
     rows = []
 
@@ -286,14 +283,27 @@ def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
                                              score_mod=score_mod, score_mod_bwd=score_mod_bwd, mask_mod=mask_mod,
                                              seqused_k=seqused_k, deterministic=deterministic, qk_hadamard=qk_hadamard,
                                              opts=o)
-    log("p_hat_frame", "row", "auto: the 8-bit default" if o.p_hat_frame == "auto" else "explicit")
+    p_frame = _p_frame("fp8", o, shape, scaling, default="row")
+    log("p_hat_frame", p_frame, "auto: the 8-bit default" if o.p_hat_frame == "auto" else "explicit")
     log("backward_kernel", "1cta", "the 1-CTA backward (key-stationary, GQA in the same accumulators)")
     from . import interface_bwd_fp4
     dq_causal = bool(interface_bwd_fp4.DQ_CAUSAL_PRESCALE) and bool(causal) and not shape.varlen and shape.s_q == shape.s_k
     log("dq_prescale", "causal_tile" if dq_causal else "row", "per query tile from the prefix of key tiles"
         if dq_causal else "one power of two per batch row / document")
     return _finish("fp8", "fp8", "e4m3", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
-                   return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=dq_causal, window_size=window_size)
+                   return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=dq_causal,
+                   window_size=window_size, p_frame=p_frame)
+
+
+def _p_frame(entry, o, shape, scaling, default):
+    """The frame of the E4M3 P-hat: 'row' (one frame per query row) or 'group' (one UE8M0 exponent per row and 32 keys)."""
+    frame = default if o.p_hat_frame == "auto" else o.p_hat_frame
+    if frame == "group" and (shape.d != 128 or scaling == "token_local"):
+        if o.p_hat_frame == "auto":
+            return "row"
+        _fail("B6", NotImplementedError, f"p_hat_frame='group' is built for head_dim 128 with token-block operands (flash_attn_{entry})"
+                                         "")
+    return frame
 
 
 def resolve_fp4(q, k, v, *, softmax_scale=None, causal=False, window_size=(None, None), softcap=0.0, score_mod=None,
@@ -336,9 +346,6 @@ def resolve_fp4(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     }.items():
         if name in non_default_fields(o):
             _fail(rule, ValueError, msg + f"; got {name}={getattr(o, name)!r}")
-    if o.p_hat_frame == "group":
-        _fail("B6", NotImplementedError, "p_hat_frame='group' (one UE8M0 per 32 keys of P-hat) is not built: the "
-                                         "forward uses the row frame")
     shape = _shape_of("fp4", q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k, max_seqlen_q, max_seqlen_k)
     if shape.d != 128:
         _fail("E13", NotImplementedError, f"flash_attn_fp4 serves head_dim 128 here; got {shape.d}")
@@ -355,7 +362,10 @@ def resolve_fp4(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
                                              opts=o)
     if scaling == "token_local":
         _fail("B6", NotImplementedError, "operand_scaling='token_local' is built on flash_attn_fp8 only")
-    log("p_hat_frame", "row", "the row-frame E4M3 P-hat (the group frame is not built)")
+    p_frame = _p_frame("fp4", o, shape, scaling, default="group")
+    log("p_hat_frame", p_frame, "auto: one UE8M0 exponent per query row and 32 keys of P-hat" if o.p_hat_frame == "auto"
+        else "explicit")
     log("backward_kernel", "1cta", "the 1-CTA backward; S recomputed from the forward's NVFP4 codes")
     return _finish("fp4", "fp4.e4m3_pv", "nvfp4", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
-                   return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=False, window_size=window_size)
+                   return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=False,
+                   window_size=window_size, p_frame=p_frame)

@@ -68,6 +68,7 @@ int fl_quant_blocks(const fl_quant_args* args, void* stream);
 #define FL_A_DQ_ROWLOCAL 8   /* backward: the dQ side of dS-hat gets one exponent per query row of each 32-key block */
 #define FL_A_HAD_DQ 16       /* backward: dQ accumulator holds rotated rows (post kernel rotates back) */
 #define FL_A_HAD_DK 32       /* backward: rotate dK back in the epilogue */
+#define FL_A_P_GROUP 64      /* forward: group-frame P-hat (one UE8M0 exponent per query row and 32 keys) instead of the row frame */
 
 /* One attention problem. Operands are the quantiser's outputs; q / k / v / dO codes are (b, s, heads, d) E4M3. */
 typedef struct fl_attn_args {

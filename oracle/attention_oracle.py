@@ -134,10 +134,12 @@ def qdq_attention(q, k, v, g=None, *, causal=False, softmax_scale=None, fp4_qk=F
 
 
 def accuracy(x, ref):
-    """cosine, norm ratio, max / mean relative error with the floor 1e-3 * max|ref|, and relative L2 error."""
+    """cosine, norm ratio, max / mean relative error with the floor 1e-3 * max|ref| (the reference benchmark's four figures),
+    plus the relative L2 error and the largest absolute error in units of max|ref| (`max_abs`)."""
     p, r = x.detach().float().flatten().double(), ref.detach().float().flatten().double()
     floor = max(float(r.abs().max()) * 1e-3, 1e-30)
     rel = (p - r).abs() / r.abs().clamp_min(floor)
     return dict(cos=float(p @ r / (p.norm() * r.norm() + 1e-30)), norm_ratio=float(p.norm() / (r.norm() + 1e-30)),
                 max_rel_err=float(rel.max()), mean_rel_err=float(rel.mean()),
-                rel_l2=float((p - r).norm() / (r.norm() + 1e-30)))
+                rel_l2=float((p - r).norm() / (r.norm() + 1e-30)),
+                max_abs=float((p - r).abs().max() / (r.abs().max() + 1e-30)))

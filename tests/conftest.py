@@ -25,3 +25,19 @@ def pytest_collection_modifyitems(config, items):
     for it in items:
         if "gpu" in it.keywords:
             it.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _device_status_is_clean(request):
+    """After every GPU test: no kernel of the library gave up a device-side wait (the status word of the last call)."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return
+        import flamia_blackwell_attention_b200 as F
+    except Exception:
+        return
+    F.check_status()

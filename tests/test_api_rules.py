@@ -76,7 +76,8 @@ RULES = [
     ("rB4c", R8, dict(seqused_k=_I32(1)), {}, NotImplementedError, "B4", "batched seqused_k"),
     ("rB5", R8, dict(deterministic=True), {}, NotImplementedError, "B5", "deterministic=True"),
     ("rB6", R8, dict(options=O8(ds_scaling="row_local")), {}, NotImplementedError, "B6", "ds_scaling='row_local'"),
-    ("rB6b", R8, dict(options=O8(p_hat_frame="group")), {}, NotImplementedError, "B6", "p_hat_frame='group'"),
+    ("rB6b", R8, dict(options=O8(p_hat_frame="group", operand_scaling="token_local", ds_dq_rowlocal="all")), {},
+     NotImplementedError, "B6", "p_hat_frame='group'"),
     ("rB7", R8, dict(q_quantized=(1, 1.0), k_quantized=(1, 1.0)), {}, NotImplementedError, "B7", "pre-quantised Q / K"),
 ]
 

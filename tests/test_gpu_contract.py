@@ -126,6 +126,9 @@ def test_document_table_that_does_not_fit_is_clamped_and_reported():
     ro, *_ = A.attention_fp32(q[None, :200].float(), k[None, :200].float(), v[None, :200].float(), None, True)
     assert A.accuracy(out[:200].float().cpu(), ro[0])["rel_l2"] < 7e-2
     assert L.FL_DEV_BAD_TABLE == 0x200
+    with torch.no_grad():      # a clean call: the status word of the last call is fine again
+        F.flash_attn_fp8(qc[:256].detach()[None], kc[:256].detach()[None], vc[:256].detach()[None], causal=True)
+    assert F.check_status() == 0
 
 
 def test_check_status_raises_for_a_wait_that_ran_out():
