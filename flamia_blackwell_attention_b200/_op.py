@@ -47,12 +47,15 @@ def _register_entry(plan_id, docs_meta) -> int:
 
 def _fwd_impl(q, k, v, docs: List[torch.Tensor], plan: int, docs_id: int):
     p = _PLANS[plan]
+    seqused_k = None
+    if p.fwd.seqused_k:           # batched form: docs = [seqused_k]
+        seqused_k, docs = docs[0], []
     cu_q = docs[0] if len(docs) > 0 else None
     cu_k = docs[1] if len(docs) > 1 else None
     su_q = docs[2] if len(docs) > 2 else None
     su_k = docs[3] if len(docs) > 3 else None
     d = _routes.docs_of(p, q, cu_q, cu_k, su_q, su_k)
-    out, lse, state = _routes.forward(p, q, k, v, d)
+    out, lse, state = _routes.forward(p, q, k, v, d, seqused_k)
     meta = None if d is None else (d.capacity, d.aligned)
     entry = _register_entry(plan, meta)
     # batched form: the kernels' O / LSE ARE the op's outputs (the autograd node saves those itself, an op output may not
@@ -72,7 +75,7 @@ def _fake_fwd(q, k, v, docs, plan, docs_id):
     sh = p.shape
     is_docs = sh.varlen or p.fwd.ragged_documents
     lse_shape = (sh.h, sh.tot_q) if sh.aligned_varlen else ((0,) if is_docs else (sh.b, sh.h, sh.s_q))
-    n_docs = int(docs[0].shape[0]) - 1 if len(docs) > 0 else 0
+    n_docs = int(docs[0].shape[0]) - 1 if (len(docs) > 0 and not p.fwd.seqused_k) else 0
     spec = _routes.state_spec(p, n_docs, q.dtype)
     # as _fwd_impl: the batched form hands O / LSE out as the op's outputs, documents keep the padded ones in the state
     state = [q.new_empty(shape, dtype=dt) for shape, dt in (spec if is_docs else spec[2:])]

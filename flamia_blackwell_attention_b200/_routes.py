@@ -158,14 +158,17 @@ def state_spec(plan, n_docs=0, dtype=torch.bfloat16):
                  ((b, s_k, hk, d // 2), u8), ((b, hk, s_k // 128, d // 64, 32, 4, 4), u8)]
     if tl:
         spec += [((b, h, s_q), f32), ((b, hk, s_k), f32), ((b, hk, s_k), f32)]
+    if f.seqused_k:
+        spec += [((b,), i32)]
     if docs:
         spec += [((n,), i32), ((n,), i32)] + ([] if sh.aligned_varlen else [((cap,), i32)])
     return spec
 
 
 # --------------------------------------------------------------------------------------------------------------- forward
-def forward(plan, q, k, v, docs):
-    """Returns (out, lse, state): out / lse in the caller's layout, state = the tensors the backward needs."""
+def forward(plan, q, k, v, docs, seqused_k=None):
+    """Returns (out, lse, state): out / lse in the caller's layout, state = the tensors the backward needs.
+    seqused_k: the batched form's (b,) int32 valid-key counts, or None."""
     sh, f = plan.shape, plan.fwd
     fp4 = plan.entry == "fp4"
     mode = L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8
@@ -187,7 +190,7 @@ def forward(plan, q, k, v, docs):
     vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl, status=status)
     out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=q.dtype, mode=mode,
                              status=status, token_local=tl, window=f.window, p_group=f.p_hat_frame == "group",
-                             doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
+                             seqused_k=seqused_k, doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     state = [out, lse, qq["codes"], qq["fac"], kq["codes"], kq["fac"], vq["codes"], vq["fac"], status]
     if need_bwd:
         state += [kq["tile_stats"], vq["tile_stats"]]
@@ -195,6 +198,8 @@ def forward(plan, q, k, v, docs):
         state += [qq["x4"], qq["sf4_raw"], kq["x4"], kq["sf4_raw"]]
     if tl:
         state += [qq["token_factors"], kq["token_factors"], vq["token_factors"]]
+    if seqused_k is not None:
+        state += [seqused_k]
     if docs is not None:
         state += [docs.start, docs.len] + ([] if docs.row_map is None else [docs.row_map])
         out_user = docs.unpack(out, sh.tot_q if sh.varlen else sh.b * sh.s_q)
@@ -220,6 +225,7 @@ def backward(plan, state, dout, docs_meta):
         qq["x4"], qq["sf4_raw"], kq["x4"], kq["sf4_raw"] = (next(it) for _ in range(4))
     if tl:
         qq["token_factors"], kq["token_factors"], vq["token_factors"] = (next(it) for _ in range(3))
+    seqused_k = next(it) if f.seqused_k else None
     docs = None
     if docs_meta is not None:
         docs = object.__new__(Docs)
@@ -241,7 +247,7 @@ def backward(plan, state, dout, docs_meta):
     dk, dv, _ = K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks,
                            causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=out.dtype,
                            mode=L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8, had_dk=had8, status=status,
-                           token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all", window=f.window,
+                           token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all", window=f.window, seqused_k=seqused_k,
                            doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype)
     _note_status(status)

@@ -103,7 +103,8 @@ def _run(plan, q, k, v, cu_q, cu_k, su_q, su_k, return_lse):
     if sh.varlen and not sh.aligned_varlen and not _REPACK_WARNED:
         _REPACK_WARNED = True
         warnings.warn(REPACK_WARNING.format(entry=plan.entry), UserWarning, stacklevel=3)
-    docs = [t for t in (cu_q, cu_k, su_q, su_k) if t is not None] if sh.varlen else []
+    docs = [t for t in (cu_q, cu_k, su_q, su_k) if t is not None] if sh.varlen else \
+        ([su_k.contiguous()] if plan.fwd.seqused_k else [])
     out, lse = _op.op_apply(plan, q, k, v, docs)
     if return_lse:
         if lse.numel() == 0:

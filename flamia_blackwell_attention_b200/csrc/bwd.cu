@@ -59,6 +59,7 @@ struct BwdParams {
   void* dv;
   const int32_t* doc_start;
   const int32_t* doc_len;
+  const int32_t* seqused_k;   // batched form: valid keys per batch row, or null
   int n_docs;
   int b, s_q, s_k, h, h_kv;
   float scale_log2;
@@ -77,7 +78,8 @@ struct BTile {
   int bat;    // batch coordinate of the tensor maps (0 for packed documents)
   int hkv;    // kv head
   int k0;     // first key row of the tile (row index inside the batch entry)
-  int nk;     // valid keys of the tile (<= 128; 0 = an empty tile slot)
+  int nk;     // key rows of the tile inside the document / batch row (<= 128; 0 = an empty tile slot)
+  int nv;     // of those, the keys that take part (fewer under seqused_k; <= 0: none, the tile's gradients are zero)
   int krel;   // document-relative index of key row k0
   int q0;     // first query row of the document (row index inside the batch entry)
   int sq;     // queries of the document
@@ -133,6 +135,7 @@ __device__ __forceinline__ void bwd_decode(const BwdParams& p, int L, BTile& t) 
     else { tile = L % p.n_tile; rem = L / p.n_tile; }
     t.hkv = rem % p.h_kv; t.bat = rem / p.h_kv;
     t.k0 = tile * 128; t.nk = min(128, p.s_k - t.k0); t.krel = t.k0; t.q0 = 0; t.sq = p.s_q; t.off = p.s_k - p.s_q;
+    t.nv = p.seqused_k ? min(t.nk, p.seqused_k[t.bat] - t.k0) : t.nk;
   } else {
     // documents sit at 128-aligned starts of one packed batch entry; tile slot x -> (document, key tile of it)
     int x = L / p.h_kv, dsel = -1, len = 0, st = 0;
@@ -145,13 +148,14 @@ __device__ __forceinline__ void bwd_decode(const BwdParams& p, int L, BTile& t) 
     }
     if (dsel < 0) { t.nk = 0; t.bat = 0; t.k0 = 0; t.krel = 0; t.q0 = 0; t.sq = 0; t.off = 0; }
     else { t.bat = 0; t.k0 = st + x * 128; t.nk = min(128, len - x * 128); t.krel = x * 128; t.q0 = st; t.sq = len; t.off = 0; }
+    t.nv = t.nk;
   }
   // query tiles that see this key tile: the first query that sees its first key, the last one that sees its last key
   int m_hi = (t.sq + 127) / 128, m_lo = 0;
   if (p.win_r >= 0 && t.krel - t.off - p.win_r > 0) m_lo = (t.krel - t.off - p.win_r) / 128;
   if (p.win_l >= 0) m_hi = min(m_hi, max(0, t.krel + t.nk - 1 - t.off + p.win_l) / 128 + 1);
   t.m_lo = m_lo;
-  t.n_m = (t.nk > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
+  t.n_m = (t.nv > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
 }
 
 template <int D, bool FP4, int VAR>
@@ -466,7 +470,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const int hkv = T.hkv, n_m = T.n_m, m_lo = T.m_lo;
       const int n_it = n_m * grp;
       const int krel = T.krel + r;
-      const bool key_valid = r < T.nk;
+      const bool key_valid = r < T.nv;
       const size_t bh_k = (size_t)T.bat * p.h_kv + hkv;
       const int kblk = (T.k0 + r) / 32;
       // token-local: this key's own factors; otherwise its 32-key block's
@@ -800,6 +804,7 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
   if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
   if (a->doc_start && (a->b != 1 || a->n_docs <= 0 || !a->doc_len || a->s_q != a->s_k)) return FL_ERR_BAD_ARG;
+  if (a->seqused_k && a->doc_start) return FL_ERR_UNSUPPORTED;      // documents carry their own lengths
   CUtensorMap mq, mk, mv, mdo, macc, mq4, mk4, mdk, mdv;
   int rc;
   if ((rc = make_rows_map(&mq, a->q_codes, a->b, a->s_q, a->h, a->d, 128))) return rc;
@@ -822,6 +827,7 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.d_rows = a->d_rows; p.dq_scale = a->dq_scale; p.dk = a->dk; p.dv = a->dv;
   p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;
+  p.seqused_k = a->seqused_k;
   p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;

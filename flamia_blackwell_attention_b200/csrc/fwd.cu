@@ -59,6 +59,7 @@ struct FwdParams {
   float* lse;
   const int32_t* doc_start;
   const int32_t* doc_len;
+  const int32_t* seqused_k;   // batched form: valid keys per batch row, or null
   int n_docs;
   int b, s_q, s_k, h, h_kv;
   float scale_log2;
@@ -112,6 +113,7 @@ __device__ __forceinline__ void fwd_decode(const FwdParams& p, int L, Tile& t) {
     else { blk = L % p.n_blk; rem = L / p.n_blk; }
     t.head = rem % p.h; t.bat = rem / p.h;
     t.q0 = blk * 256; t.nq = min(256, p.s_q - t.q0); t.k0 = 0; t.sk = p.s_k;
+    if (p.seqused_k) t.sk = max(0, min(p.s_k, p.seqused_k[t.bat]));      // keys past it are masked like a document's end
     t.off = p.s_k - p.s_q; t.qrel = t.q0;
   } else {
     // documents sit at 128-aligned starts of one packed batch entry; block slot x -> (document, 256-row block)
@@ -651,6 +653,7 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
   if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
   if (a->doc_start && (a->b != 1 || a->n_docs <= 0 || !a->doc_len || a->s_q != a->s_k)) return FL_ERR_BAD_ARG;
+  if (a->seqused_k && a->doc_start) return FL_ERR_UNSUPPORTED;      // documents carry their own lengths
   CUtensorMap mq, mk, mv, mo;
   int rc;
   if ((rc = make_rows_map(&mq, fp4 ? a->q4 : a->q_codes, a->b, a->s_q, a->h, fp4 ? a->d / 2 : a->d, 128))) return rc;
@@ -661,6 +664,7 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.lse = a->lse;
   p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;
+  p.seqused_k = a->seqused_k;
   p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.causal = (a->flags & FL_A_CAUSAL) ? 1 : 0;

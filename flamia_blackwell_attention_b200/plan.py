@@ -140,6 +140,10 @@ def _shape_of(entry, q, k, v, cu_q, cu_k, seqused_q, seqused_k, max_q, max_k):
                      bool(varlen), bool(aligned), bool(rg), int(tot_q), int(tot_k))
 
 
+def scaling_request(o):
+    return getattr(o, "operand_scaling", "auto")
+
+
 def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score_mod_bwd, mask_mod, seqused_k,
             deterministic, qk_hadamard, opts, two_cta_fields=True):
     """Rules shared by both entries; returns (qk_hadamard, operand_scaling, ds_dq_rowlocal, ragged)."""
@@ -161,8 +165,17 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
     if softcap:
         _fail("B4", NotImplementedError, "softcap is not built yet")
     if seqused_k is not None and not shape.aligned_varlen:
-        _fail("B4", NotImplementedError, "batched seqused_k is not built yet: use the aligned varlen form "
-                                         "(cu_seqlens + seqused_q + seqused_k)")
+        if shape.varlen:
+            _fail("B9", ValueError, f"flash_attn_{entry}: the aligned varlen form takes seqused_q AND seqused_k")
+        if shape.s_q % 128 or shape.s_k % 128:
+            _fail("B4", NotImplementedError, "batched seqused_k with lengths that are no multiple of 128 is not built "
+                                             f"(those run as documents); got {shape.s_q} / {shape.s_k}")
+        if scaling_request(o) == "token_local":
+            _fail("B4", NotImplementedError, "batched seqused_k with operand_scaling='token_local' is not built")
+        if isinstance(seqused_k, torch.Tensor) and (seqused_k.dim() != 1 or seqused_k.shape[0] != shape.b or
+                                                    seqused_k.dtype != torch.int32):
+            _fail("B9", ValueError, f"flash_attn_{entry}: seqused_k is an int32 tensor of shape (batch,); got "
+                                    f"{tuple(seqused_k.shape)} {seqused_k.dtype}")
     if deterministic:
         _fail("B5", NotImplementedError, "deterministic=True (ordered dQ reduction) is not built: the f16 dQ partials "
                                          "are reduce-added in arrival order")
@@ -239,12 +252,13 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
 
 
 def _finish(entry, route, qk_format, shape, log_rows, opts, *, softmax_scale, causal, return_lse, had, scaling, rowlocal,
-            ragged, dq_causal, window_size=(None, None), p_frame="row"):
+            ragged, dq_causal, window_size=(None, None), p_frame="row", seqused_k=False):
     sc = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(shape.d)
     # sliding window (left, right): None / -1 = unlimited on that side; causal caps the right side at 0 in the kernels
     win = tuple(None if (w is None or w < 0) else int(w) for w in tuple(window_size))
     fwd = FwdSpec("fwd_sm100", qk_format, "e4m3", scaling, p_frame, "exp2", had, bool(causal), shape.varlen,
-                  shape.aligned_varlen, ragged, bool(return_lse), None if win == (None, None) else win)
+                  shape.aligned_varlen, ragged, bool(return_lse), None if win == (None, None) else win,
+                  seqused_k=bool(seqused_k))
     bwd = BwdSpec("1cta" if shape.requires_grad else "none", scaling, "block_32x32", rowlocal, "row", "e4m3", False,
                   "causal_tile" if dq_causal else "row")
     return AttnPlan(entry, route, sc, shape, fwd, bwd, opts.tuning, False, False, tuple(log_rows), opts)
@@ -292,7 +306,8 @@ def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
         if dq_causal else "one power of two per batch row / document")
     return _finish("fp8", "fp8", "e4m3", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
                    return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=dq_causal,
-                   window_size=window_size, p_frame=p_frame)
+                   window_size=window_size, p_frame=p_frame,
+                   seqused_k=seqused_k is not None and not shape.aligned_varlen)
 
 
 def _p_frame(entry, o, shape, scaling, default):
@@ -368,4 +383,5 @@ def resolve_fp4(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     log("backward_kernel", "1cta", "the 1-CTA backward; S recomputed from the forward's NVFP4 codes")
     return _finish("fp4", "fp4.e4m3_pv", "nvfp4", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
                    return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=False,
-                   window_size=window_size, p_frame=p_frame)
+                   window_size=window_size, p_frame=p_frame,
+                   seqused_k=seqused_k is not None and not shape.aligned_varlen)

@@ -107,6 +107,10 @@ typedef struct fl_attn_args {
    * a zero-filled struct means no window. FL_A_CAUSAL caps the right side at 0. */
   int32_t window_left_p1;
   int32_t window_right_p1;
+  /* Batched form only: (b) int32, the number of valid keys of each batch row (keys at or past it are masked; dK / dV rows
+   * there come back zero), or NULL. The reference's batched seqused_k (flash_attn/cute/lowprec/api.py:270). The causal
+   * alignment keeps using s_k - s_q. */
+  const int32_t* seqused_k;
 } fl_attn_args;
 
 /* Forward: O = softmax(scale Q K^T + mask) V, LSE.

@@ -26,13 +26,14 @@ from . import quant_oracle as Q
 
 
 def attention_fp32(q, k, v, g=None, causal=False, softmax_scale=None, chunk=1024, q_grad=None, k_grad=None,
-                   window=None):
+                   window=None, seqused_k=None):
     """q (b, s_q, h, d), k / v (b, s_k, h_kv, d) float32 CPU tensors -> (o, lse, dq, dk, dv); lse (b, h, s_q) in nats.
     Causal: key j visible to query i iff j <= i + (s_k - s_q). g = dO or None (forward only).
     q_grad / k_grad: the copies of Q / K used as operands of dK = dS^T Q and dQ = dS K when they differ from the S
     operands (the mixed route: S from the NVFP4 copies, gradient GEMMs from the E4M3 copies).
     window = (left, right), None = unlimited: key j visible iff i + off - left <= j <= i + off + right (causal caps the
-    right side at 0)."""
+    right side at 0). seqused_k: per batch row the number of valid keys (keys at or past it are masked; the causal
+    alignment keeps using s_k - s_q), as tests/cute/test_lowprec_api.py:1346 `_ref_bottom_right` of the reference."""
     q, k, v = q.float(), k.float(), v.float()
     qg = q if q_grad is None else q_grad.float()
     kg = k if k_grad is None else k_grad.float()
@@ -64,6 +65,8 @@ def attention_fp32(q, k, v, g=None, causal=False, softmax_scale=None, chunk=1024
                         S = S.masked_fill(cc > rr + off + wr, float("-inf"))
                     if wl is not None:
                         S = S.masked_fill(cc < rr + off - wl, float("-inf"))
+                if seqused_k is not None:
+                    S = S.masked_fill(torch.arange(sk)[None, :] >= int(seqused_k[bi]), float("-inf"))
                 L = torch.logsumexp(S, -1)
                 lse[bi, hi, r0:r0 + chunk] = L
                 P = torch.exp(S - torch.where(torch.isinf(L), torch.zeros_like(L), L)[:, None])
@@ -112,7 +115,7 @@ def _qdq4(x, rotate=False):
 
 
 def qdq_attention(q, k, v, g=None, *, causal=False, softmax_scale=None, fp4_qk=False, rotate_qk=False,
-                  token_local=False, window=None):
+                  token_local=False, window=None, seqused_k=None):
     """The quantise-dequantise emulation: MXFP8 (token-block) Q, K, V, dO -> fp32 attention. fp4_qk: the S operands are
     the NVFP4 codes of Q, K instead (the mixed route's forward and S recompute; dP / dV / dK / dQ keep the E4M3 copies --
     emulated here by using the NVFP4 values for S and the E4M3 values for the gradient GEMMs' Q / K operands).
@@ -125,12 +128,12 @@ def qdq_attention(q, k, v, g=None, *, causal=False, softmax_scale=None, fp4_qk=F
     v8 = _qdq8(v, False, token_local)
     g8 = _qdq8(g, False, token_local) if g is not None else None
     if not fp4_qk:
-        return attention_fp32(q8, k8, v8, g8, causal, softmax_scale, window=window)
+        return attention_fp32(q8, k8, v8, g8, causal, softmax_scale, window=window, seqused_k=seqused_k)
     q4, k4 = back(_qdq4(q, rotate_qk)), back(_qdq4(k, rotate_qk))
     # forward and P from the 4-bit S operands; with rotation on only the 4-bit copies are rotated on this route, so the
     # E4M3 copies for the gradient GEMMs are those of the unrotated rows
     q8u, k8u = (q8, k8) if not rotate_qk else (_qdq8(q, False, token_local), _qdq8(k, False, token_local))
-    return attention_fp32(q4, k4, v8, g8, causal, softmax_scale, q_grad=q8u, k_grad=k8u, window=window)
+    return attention_fp32(q4, k4, v8, g8, causal, softmax_scale, q_grad=q8u, k_grad=k8u, window=window, seqused_k=seqused_k)
 
 
 def accuracy(x, ref):

@@ -55,6 +55,7 @@ BR_CASES = {     # name -> (b, s_q, s_k, h, hk, d, causal)
     "sq_gt_sk_causal": (1, 128, 64, 2, 2, 32, True),
     "sq_lt_sk_dense": (2, 32, 96, 2, 1, 16, False),
 }
+SEQUSED_CASE = dict(shape=(2, 64, 128, 2, 1, 32), causal=True, seqused=[100, 37])   # (b, s_q, s_k, h, hk, d)
 DOC_CASE = dict(lens=[37, 128, 91], h=2, hk=1, d=32)
 
 
@@ -77,6 +78,10 @@ def main():
         o, lse, dq, dk, dv = ref_bottom_right(q, k, v, do, causal)
         for key, t in (("o", o), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
             out[f"br.{name}.{key}"] = t.contiguous().numpy()
+    q, k, v, do = br_inputs(*SEQUSED_CASE["shape"], seed=34)
+    o, lse, dq, dk, dv = ref_bottom_right(q, k, v, do, SEQUSED_CASE["causal"], seqused=torch.tensor(SEQUSED_CASE["seqused"]))
+    for key, t in (("o", o), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+        out[f"seqused.{key}"] = t.contiguous().numpy()
     lens, h, hk, d = DOC_CASE["lens"], DOC_CASE["h"], DOC_CASE["hk"], DOC_CASE["d"]
     tot = sum(lens)
     q, k, v, g = (t[0] for t in attention_inputs(1, tot, h, hk, d, seed=45))

@@ -319,3 +319,22 @@ def test_extreme_input_families(dist):
         assert torch.isfinite(t).all(), (dist, name)
         if torch.isfinite(r).all() and float(r.abs().max()) > 0:
             assert A.accuracy(t, r)["rel_l2"] < 6e-2, (dist, name, A.accuracy(t, r))
+
+
+@pytest.mark.parametrize("route,causal,sq,sk", [("fp8", True, 512, 512), ("fp8", False, 256, 640), ("fp4", True, 384, 384)])
+def test_batched_seqused_k(route, causal, sq, sk):
+    """seqused_k on the batched form: keys at or past seqused_k[b] are masked, their dK / dV rows come back zero, rows that
+    see no key give a zero output row (tests/cute/test_lowprec_api.py:1346 of the reference states the semantics)."""
+    import flamia_blackwell_attention_b200 as F
+    fn = F.flash_attn_fp8 if route == "fp8" else F.flash_attn_fp4
+    s = max(sq, sk)
+    q, k, v, g = attention_inputs(3, s, 4, 2, 128, seed=91)
+    q, g, k, v = q[:, :sq], g[:, :sq], k[:, :sk], v[:, :sk]
+    used = [sk, 200, 129]
+    su = torch.tensor(used, dtype=torch.int32, device="cuda")
+    o, dq, dk, dv, _ = _step(fn, q, k, v, g, causal=causal, seqused_k=su)
+    ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=causal, rotate_qk=True, fp4_qk=route == "fp4", seqused_k=used)
+    _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))
+    for b_, n in enumerate(used):
+        assert float(dk[b_, n:].abs().max() if n < sk else 0.0) == 0.0 and float(dv[b_, n:].abs().max() if n < sk else 0.0) == 0.0
+    assert torch.isfinite(o).all() and torch.isfinite(dq).all()

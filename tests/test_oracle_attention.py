@@ -65,6 +65,16 @@ def test_attention_fp32_bottom_right_and_rectangular(name):
         _close(np.nan_to_num(t.numpy(), neginf=0.0), np.nan_to_num(want, neginf=0.0), f"{name}.{key}")
 
 
+def test_attention_fp32_batched_seqused_k():
+    q, k, v, do = br_inputs(2, 64, 128, 2, 1, 32, seed=34)
+    o, lse, dq, dk, dv = A.attention_fp32(q, k, v, do, causal=True, seqused_k=[100, 37])
+    for key, t in (("o", o), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+        want = GOLD[f"seqused.{key}"]
+        if key == "lse":
+            assert np.array_equal(np.isneginf(t.numpy()), np.isneginf(want))
+        _close(np.nan_to_num(t.numpy(), neginf=0.0), np.nan_to_num(want, neginf=0.0), f"seqused.{key}")
+
+
 def test_attention_docs_fp32_matches_reference_docs():
     lens, h, hk, d = [37, 128, 91], 2, 1, 32
     q, k, v, g = (t[0] for t in attention_inputs(1, sum(lens), h, hk, d, seed=45))
