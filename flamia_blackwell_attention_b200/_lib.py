@@ -38,7 +38,7 @@ class AttnArgs(C.Structure):
                                   "dv", "doc_start", "doc_len")] + \
                [(n, i32) for n in ("n_docs", "b", "s_q", "s_k", "h", "h_kv", "d")] + [("softmax_scale", f32)] + \
                [(n, i32) for n in ("mode", "flags")] + [("status", vp), ("wait_cycles", i64)] + \
-               [(n, i32) for n in ("window_left_p1", "window_right_p1")] + [("seqused_k", vp)]
+               [(n, i32) for n in ("window_left_p1", "window_right_p1")] + [("seqused_k", vp), ("softcap", f32)]
 
 
 EXPORTS = {

@@ -190,7 +190,8 @@ def forward(plan, q, k, v, docs, seqused_k=None):
     vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl, status=status)
     out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=q.dtype, mode=mode,
                              status=status, token_local=tl, window=f.window, p_group=f.p_hat_frame == "group",
-                             seqused_k=seqused_k, doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
+                             seqused_k=seqused_k, softcap=f.softcap,
+                             doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     state = [out, lse, qq["codes"], qq["fac"], kq["codes"], kq["fac"], vq["codes"], vq["fac"], status]
     if need_bwd:
         state += [kq["tile_stats"], vq["tile_stats"]]
@@ -248,6 +249,7 @@ def backward(plan, state, dout, docs_meta):
                            causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=out.dtype,
                            mode=L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8, had_dk=had8, status=status,
                            token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all", window=f.window, seqused_k=seqused_k,
+                           softcap=f.softcap,
                            doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype)
     _note_status(status)

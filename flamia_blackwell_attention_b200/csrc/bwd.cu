@@ -64,6 +64,7 @@ struct BwdParams {
   int b, s_q, s_k, h, h_kv;
   float scale_log2;
   float softmax_scale;
+  float cap_a, cap_b;    // soft cap c: x = cap_a tanh(s * factor * cap_b) in log2 units, cap_a = c log2 e, cap_b = 1 / cap_a
   int causal;
   int win_l, win_r;      // sliding window sides, -1 = unlimited (causal: the right side is 0)
   int out_f16;
@@ -158,7 +159,7 @@ __device__ __forceinline__ void bwd_decode(const BwdParams& p, int L, BTile& t) 
   t.n_m = (t.nv > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
 }
 
-template <int D, bool FP4, int VAR>
+template <int D, bool FP4, int VAR, bool SC>
 __global__ void __launch_bounds__(512, 1)
 bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -176,13 +177,17 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint8_t* sDO = sQ + 2 * TILE_BYTES;                  // 2 stages
   uint8_t* sDS = sDO + 2 * TILE_BYTES;                 // per half: 128 key rows x 64 query bytes, 64 B swizzle
   uint8_t* sDQ = sDS + 2 * 8192;                       // per half: 128 head-dim rows x 64 queries f16, 128 B swizzle
-  float* sVec = reinterpret_cast<float*>(sDQ + 2 * 16384);   // 2 stages x {lse_log2[128], D''[128]}
+  // 2 stages x {lse_log2[128], D''[128]}, then 2 stages x {f_Q[4], f_dO[4] of the query tile's 32-row blocks, dQ pre-scale}:
+  // the per-iteration scalars travel with the tile (read from global memory at the top of an iteration they cost a
+  // memory latency on the compute warpgroups' critical path)
+  float* sVec = reinterpret_cast<float*>(sDQ + 2 * 16384);
   // d = 64 only: the gradient rows' way out (2 x 16 KB; at d = 128 the finished item's K / V buffers serve)
   uint8_t* sOut64 = reinterpret_cast<uint8_t*>(sVec) + 2048;
   // FP4 only: NVFP4 K tiles (2 x 8 KB), Q4 stages (2 x 8 KB), scale atoms K 2 x 1 KB + Q 2 x 1 KB
   uint8_t* sK4 = sOut64 + (D == 64 ? 2 * 16384 : 0);
   uint8_t* sQ4 = sK4 + 2 * 8192;
   uint8_t* sSF = sQ4 + 2 * 8192;
+  float* sFac = reinterpret_cast<float*>(sK4 + (FP4 ? 4 * 8192 + 4 * 1024 : 0));   // 2 stages x 16 floats, after everything else
   __shared__ __align__(8) uint64_t bars[BB_COUNT];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
@@ -226,7 +231,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   volatile int* abortp = &abort_s;
   // (a status word already set by an earlier launch is not looked at: a kernel that runs after one that gave up does no harm)
 
-  if (warp >= 12) reg_dealloc<80>();     // register budget per warpgroup: 176 / 176 / 80 / 80 (x 128 threads = 64 K)
+  if (warp >= 12) reg_dealloc<72>();     // register budget per warpgroup: 184 / 184 / 72 / 72 (x 128 threads = 64 K)
   if (warp == 13) {
     // =================================================================== TMA producer
     if (lane == 0) {
@@ -259,7 +264,16 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           const int st = gi & 1;
           const int head = t.hkv * grp + it / t.n_m, m = t.m_lo + it % t.n_m;
           if (gi >= 2 && !(ok = mbar_wait(&bars[BB_QEMPTY + st], ((gi >> 1) - 1) & 1, p.ctl, abortp, 10))) break;
-          mbar_arrive_expect_tx(&bars[BB_QFULL + st], 2 * TILE_BYTES + 1024 + (FP4 ? 8192 + 1024 : 0));
+          // token-local factors are per query and read by the compute threads themselves; otherwise four block factors
+          // of Q and of dO (16 bytes each, 16-byte aligned: the tile starts at a multiple of four blocks)
+          constexpr bool TLF = VAR == 2;
+          sFac[st * 16 + 8] = p.dq_scale[(size_t)t.bat * (p.s_q / 128) + t.q0 / 128 + m];
+          mbar_arrive_expect_tx(&bars[BB_QFULL + st], 2 * TILE_BYTES + 1024 + (TLF ? 0 : 32) + (FP4 ? 8192 + 1024 : 0));
+          if (!TLF) {
+            const size_t fo = ((size_t)t.bat * p.h + head) * (p.s_q / 32) + (t.q0 + m * 128) / 32;
+            bulk_load(sFac + st * 16, p.fac_q + fo, 16, &bars[BB_QFULL + st]);
+            bulk_load(sFac + st * 16 + 4, p.fac_do + fo, 16, &bars[BB_QFULL + st]);
+          }
           tma_load_4d(sQ + st * TILE_BYTES, &tm_q, &bars[BB_QFULL + st], 0, head, t.q0 + m * 128, t.bat);
           if (FP4) {
             tma_load_4d(sQ4 + st * 8192, &tm_q4, &bars[BB_QFULL + st], 0, head, t.q0 + m * 128, t.bat);
@@ -390,7 +404,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       gi += n_it;
     }
   } else if (warp >= 8 && warp < 12) {
-    reg_dealloc<80>();
+    reg_dealloc<72>();
     // =================================================================== dQ reduction (thread = head-dim row)
     const int r = tid & 127;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -448,7 +462,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     if (tid == 256) tma_store_wait<0>();
   } else if (warp < 8) {
-    reg_alloc<176>();
+    reg_alloc<184>();
     // =================================================================== compute (thread = key row, 64 query columns)
     const int x = warp >> 2;                         // the half this warpgroup owns
     const int wq = warp & 3;                         // lane quadrant = 32-key block of the tile
@@ -489,13 +503,14 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int g = gi + it, st = g & 1, u = g >> 1;
         const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
         const size_t bh_q = (size_t)T.bat * p.h + head;
-        const int qb0 = (T.q0 + m * 128) / 32 + 2 * x;                     // first of the half's two 32-query blocks
-        const float fq0 = TL ? 1.f : p.fac_q[bh_q * (p.s_q / 32) + qb0], fq1 = TL ? 1.f : p.fac_q[bh_q * (p.s_q / 32) + qb0 + 1];
-        const float fd0 = TL ? 1.f : p.fac_do[bh_q * (p.s_q / 32) + qb0], fd1 = TL ? 1.f : p.fac_do[bh_q * (p.s_q / 32) + qb0 + 1];
+        if (!(ok = mbar_wait(&bars[BB_QFULL + st], u & 1, p.ctl, abortp, 30))) break;   // factors, lse / D'' vectors visible
+        // the half's two 32-query blocks' factors and the tile's dQ pre-scale, staged by the producer
+        const float fq0 = TL ? 1.f : sFac[st * 16 + 2 * x], fq1 = TL ? 1.f : sFac[st * 16 + 2 * x + 1];
+        const float fd0 = TL ? 1.f : sFac[st * 16 + 4 + 2 * x], fd1 = TL ? 1.f : sFac[st * 16 + 4 + 2 * x + 1];
         // token-local: the 64 per-query factors of the half (same addresses for every thread: broadcast loads)
         const float4* fq_vec = reinterpret_cast<const float4*>(p.fac_q + (TL ? bh_q * p.s_q + T.q0 + m * 128 + 64 * x : 0));
         const float4* fdo_vec = reinterpret_cast<const float4*>(p.fac_do + (TL ? bh_q * p.s_q + T.q0 + m * 128 + 64 * x : 0));
-        const float bsc = p.dq_scale[(size_t)T.bat * (p.s_q / 128) + T.q0 / 128 + m];
+        const float bsc = sFac[st * 16 + 8];
         // FP4: the block scales of S were applied by the tensor core; only the softmax scale remains
         const float c[2] = {FP4 ? p.scale_log2 : fk * fq0, FP4 ? p.scale_log2 : fk * fq1}, b8[2] = {fv8 * fd0, fv8 * fd1};
         // token-local: fq0 = fq1 = fd0 = fd1 = 1, i.e. unit scale bytes for the Q and dO operands
@@ -504,7 +519,6 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // K's exponent bytes with the power-of-two f16 pre-scale of this query tile folded in (A scale of dQ^T)
         const uint32_t lb = (uint32_t)((int)((__float_as_uint(bsc) >> 23) & 0xFF) - 127) & 0xFF;
         const uint32_t ekb_word = __vadd4(ek_word, lb * 0x01010101u);
-        if (!(ok = mbar_wait(&bars[BB_QFULL + st], u & 1, p.ctl, abortp, 30))) break;   // lse / D'' vectors visible
         const uint32_t v_lse = smem_u32(sVec) + (st * 256 + 64 * x) * 4, v_dpp = v_lse + 512;
         const int q_first = m * 128 + 64 * x;                              // document-relative query of column 0
         const bool full = key_valid && (q_first >= vis_from) && (q_first + 63 <= vis_to) && (q_first + 64 <= T.sq);
@@ -517,10 +531,31 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         FL_TMEM_LD_32(t_sx + 32, (pv + 32));
         tc_wait_ld();
         float pf[64];
+        uint32_t pw_sc[SC ? 16 : 1];
 #pragma unroll
         for (int j4 = 0; j4 < 16; ++j4) {
           const float4 l4 = lds128(v_lse + 16 * j4);
           const float cc = c[j4 >> 3];
+          if (SC) {
+            // soft cap: x = cap_a tanh(s c cap_b); P-hat is taken from P' right here, and what stays in pf is
+            // P' (1 - tanh^2), the factor dS needs (the reference's score_mod_bwd, flash_attn/cute/utils.py:178-187)
+            const float l[4] = {l4.x, l4.y, l4.z, l4.w};
+            float pp[4], df[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float th = tanh_fast(__uint_as_float(pv[4 * j4 + e]) * (cc * p.cap_b));
+              pp[e] = ex2(fmaf(p.cap_a, th, -l[e]));
+              df[e] = fmaf(-th, th, 1.0f);
+              if (!full) {
+                const int qi = q_first + 4 * j4 + e;
+                pp[e] = (key_valid && qi >= vis_from && qi <= vis_to && qi < T.sq) ? pp[e] : 0.f;
+              }
+            }
+            pw_sc[j4] = cvt_e4m3x4(pp[0], pp[1], pp[2], pp[3]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pf[4 * j4 + e] = pp[e] * df[e];
+            continue;
+          }
           float4 c4 = make_float4(cc, cc, cc, cc);
           if (TL) {
             const float4 f4 = __ldg(fq_vec + j4);
@@ -531,7 +566,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           pf[4 * j4 + 2] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 2]), c4.z, -l4.z));
           pf[4 * j4 + 3] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 3]), c4.w, -l4.w));
         }
-        if (!full) {      // diagonal / tail tiles only
+        if (!SC && !full) {      // diagonal / tail tiles only
 #pragma unroll
           for (int j = 0; j < 64; ++j) {
             const int qi = q_first + j;
@@ -570,7 +605,8 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         } else {
           uint32_t pw[16];
 #pragma unroll
-          for (int w = 0; w < 16; ++w) pw[w] = cvt_e4m3x4(pf[4 * w], pf[4 * w + 1], pf[4 * w + 2], pf[4 * w + 3]);
+          for (int w = 0; w < 16; ++w)
+            pw[w] = SC ? pw_sc[w] : cvt_e4m3x4(pf[4 * w], pf[4 * w + 1], pf[4 * w + 2], pf[4 * w + 3]);
           FL_TMEM_ST_16(t_sx + TO_P, pw);
           // scale tiles of the dV product: A = 1, B = dO's exponent per 32 queries (bytes = the half's two K steps)
           uint32_t sf[8] = {0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, edo2, edo2, edo2, edo2};
@@ -831,6 +867,10 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  const bool sc = a->softcap > 0.f;
+  if (sc && (tl || rl)) return FL_ERR_UNSUPPORTED;     // soft cap: the default dS-hat route only
+  p.cap_a = sc ? a->softcap * 1.4426950408889634f : 0.f;
+  p.cap_b = sc ? 1.0f / p.cap_a : 0.f;
   p.causal = (a->flags & FL_A_CAUSAL) ? 1 : 0;
   p.win_l = a->window_left_p1 - 1;
   p.win_r = p.causal ? 0 : a->window_right_p1 - 1;
@@ -847,16 +887,24 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.zigzag = (p.causal && !a->doc_start) ? 1 : 0;
   const int grid = (int)(n_items < sm_count() ? n_items : sm_count());     // one persistent CTA per SM
   const int smem = 8 * 128 * a->d + 2 * 8192 + 2 * 16384 + 2048 + (a->d == 64 ? 2 * 16384 : 0) + 1024 +
-                   (fp4 ? 4 * 8192 + 4 * 1024 : 0);
+                   (fp4 ? 4 * 8192 + 4 * 1024 : 0) + 128;
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
     kern<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, mdk, mdv, p);
     return FL_OK;
   };
-  if (a->d == 64) rc = launch(bwd_kernel_pipelined<64, false, 0>);
-  else if (fp4) rc = rl ? launch(bwd_kernel_pipelined<128, true, 1>) : launch(bwd_kernel_pipelined<128, true, 0>);
-  else if (tl) rc = launch(bwd_kernel_pipelined<128, false, 2>);
-  else rc = rl ? launch(bwd_kernel_pipelined<128, false, 1>) : launch(bwd_kernel_pipelined<128, false, 0>);
+  if (sc) {
+    if (a->d == 64) rc = launch(bwd_kernel_pipelined<64, false, 0, true>);
+    else rc = fp4 ? launch(bwd_kernel_pipelined<128, true, 0, true>) : launch(bwd_kernel_pipelined<128, false, 0, true>);
+  } else if (a->d == 64) {
+    rc = launch(bwd_kernel_pipelined<64, false, 0, false>);
+  } else if (fp4) {
+    rc = rl ? launch(bwd_kernel_pipelined<128, true, 1, false>) : launch(bwd_kernel_pipelined<128, true, 0, false>);
+  } else if (tl) {
+    rc = launch(bwd_kernel_pipelined<128, false, 2, false>);
+  } else {
+    rc = rl ? launch(bwd_kernel_pipelined<128, false, 1, false>) : launch(bwd_kernel_pipelined<128, false, 0, false>);
+  }
   if (rc) return rc;
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

@@ -8,6 +8,7 @@
 //                folded into the softmax scale (exact); P.V = kind::mxf8f6f4.block_scale with V's UE8M0 exponent per
 //                32 keys as the B scale.
 //   FL_MODE_FP4: S = NVFP4 x NVFP4 (kind::mxf4nvf4.block_scale.scale_vec::4X), same P.V.
+//   softcap c:   score = scale q.k becomes c tanh(score / c) before masking (flash_attn/cute/utils.py:167-175).
 //   FL_A_TOKEN_LOCAL (the reference's "fold forward", flash_attn/cute/lowprec/_routes.py:749-786): every token of Q, K,
 //                V has its own power-of-two factor; f_Q f_K multiplies each score, log2 f_V(key) is added to the exponent
 //                argument of P-hat (so P.V runs with unit scales) and the row sum takes P / f_V(key) back out.
@@ -63,6 +64,7 @@ struct FwdParams {
   int n_docs;
   int b, s_q, s_k, h, h_kv;
   float scale_log2;
+  float cap_a, cap_b;    // soft cap c: x = cap_a tanh(s * factor * cap_b) in log2 units, cap_a = c log2 e, cap_b = 1 / cap_a
   int causal;
   int win_l, win_r;      // sliding window sides, -1 = unlimited (causal: the right side is 0)
   int out_f16;
@@ -145,7 +147,7 @@ __device__ __forceinline__ void fwd_decode(const FwdParams& p, int L, Tile& t) {
   }
 }
 
-template <int D, bool FP4, bool TL, bool GF>
+template <int D, bool FP4, bool TL, bool GF, bool SC>
 __global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const FwdParams p) {
@@ -408,14 +410,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       constexpr float P_OFF = GF ? P_LOG2_448 : P_LOG2_OFFSET;
 
       float m_used = -INFINITY, l_sum = 0.f;
+      // The four K / V block factors of a key tile are loaded one tile ahead: read at the top of their own tile they cost
+      // a global-memory latency on the softmax threads' critical path (the scores are usually there already).
+      const float4* fk_t = reinterpret_cast<const float4*>(fk_row);
+      const float4* fv_t = reinterpret_cast<const float4*>(fv_row);
+      float4 fk_nxt = make_float4(1.f, 1.f, 1.f, 1.f), fv_nxt = fk_nxt;
+      if (!TL && n_i > 0) { fk_nxt = __ldg(fk_t); fv_nxt = __ldg(fv_t); }
       for (int j = 0; j < n_i; ++j, ++cs) {
         float c[4];
         uint32_t sfv = 0;
+        const float4 fk_cur = fk_nxt, fv_cur = fv_nxt;
+        if (!TL && j + 1 < n_i) { fk_nxt = __ldg(fk_t + j + 1); fv_nxt = __ldg(fv_t + j + 1); }
+        if (!TL) {
+          const float fkv[4] = {fk_cur.x, fk_cur.y, fk_cur.z, fk_cur.w}, fvv[4] = {fv_cur.x, fv_cur.y, fv_cur.z, fv_cur.w};
 #pragma unroll
-        for (int kbk = 0; kbk < 4; ++kbk) {
-          if (TL) continue;
-          c[kbk] = FP4 ? fq : fq * fk_row[j * 4 + kbk];      // FP4: the block scales were applied by the tensor core
-          sfv |= ((__float_as_uint(fv_row[j * 4 + kbk]) >> 23) & 0xFF) << (8 * kbk);
+          for (int kbk = 0; kbk < 4; ++kbk) {
+            c[kbk] = FP4 ? fq : fq * fkv[kbk];               // FP4: the block scales were applied by the tensor core
+            sfv |= ((__float_as_uint(fvv[kbk]) >> 23) & 0xFF) << (8 * kbk);
+          }
         }
         // token-local: the tile's 128 per-key factors (same addresses for every thread: broadcast loads through L1;
         // staging them in shared memory was twice as slow: 384 broadcast reads per thread and tile saturate the
@@ -452,6 +464,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             s[4 * e4 + 2] = fmaf(s[4 * e4 + 2], fq * k4.z, lg(v4.z));
             s[4 * e4 + 3] = fmaf(s[4 * e4 + 3], fq * k4.w, lg(v4.w));
           }
+        }
+        if (SC) {   // soft cap: the capped score in log2 units; the factors are used up here
+#pragma unroll
+          for (int e = 0; e < 128; ++e) s[e] = p.cap_a * tanh_fast(s[e] * (c[e >> 5] * p.cap_b));
+#pragma unroll
+          for (int kbk = 0; kbk < 4; ++kbk) c[kbk] = 1.f;
         }
         const int kb0 = T.kofs + j * 128;                       // document-relative key of column 0
         const bool need_mask = (kb0 + 127 > col_limit) || (kb0 < col_first);    // only on boundary tiles
@@ -689,11 +707,22 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
     kern<<<grid, 384, smem, st>>>(mq, mk, mv, mo, p);
     return FL_OK;
   };
-  if (fp4) rc = gf ? launch(fwd_kernel<128, true, false, true>) : launch(fwd_kernel<128, true, false, false>);
-  else if (a->d == 128)
-    rc = tl ? launch(fwd_kernel<128, false, true, false>)
-            : (gf ? launch(fwd_kernel<128, false, false, true>) : launch(fwd_kernel<128, false, false, false>));
-  else rc = tl ? launch(fwd_kernel<64, false, true, false>) : launch(fwd_kernel<64, false, false, false>);
+  const bool sc = a->softcap > 0.f;
+  if (sc && tl) return FL_ERR_UNSUPPORTED;
+  p.cap_a = sc ? a->softcap * 1.4426950408889634f : 0.f;
+  p.cap_b = sc ? 1.0f / p.cap_a : 0.f;
+  if (sc) {
+    if (fp4) rc = gf ? launch(fwd_kernel<128, true, false, true, true>) : launch(fwd_kernel<128, true, false, false, true>);
+    else if (a->d == 128) rc = gf ? launch(fwd_kernel<128, false, false, true, true>) : launch(fwd_kernel<128, false, false, false, true>);
+    else rc = launch(fwd_kernel<64, false, false, false, true>);
+  } else if (fp4) {
+    rc = gf ? launch(fwd_kernel<128, true, false, true, false>) : launch(fwd_kernel<128, true, false, false, false>);
+  } else if (a->d == 128) {
+    rc = tl ? launch(fwd_kernel<128, false, true, false, false>)
+            : (gf ? launch(fwd_kernel<128, false, false, true, false>) : launch(fwd_kernel<128, false, false, false, false>));
+  } else {
+    rc = tl ? launch(fwd_kernel<64, false, true, false, false>) : launch(fwd_kernel<64, false, false, false, false>);
+  }
   if (rc) return rc;
   return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
 }

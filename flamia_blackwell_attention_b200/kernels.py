@@ -113,7 +113,7 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
 
 
 def attn_args(q, k, v, *, causal, softmax_scale, mode=L.FL_MODE_FP8, flags=0, status=None, doc_start=None, doc_len=None,
-              wait_cycles=0, token_local=False, window=None, seqused_k=None):
+              wait_cycles=0, token_local=False, window=None, seqused_k=None, softcap=0.0):
     """AttnArgs from quantiser outputs q / k / v (dicts with codes, fac [, x4, sf4_raw, token_factors])."""
     qc, kc, vc = q["codes"], k["codes"], v["codes"]
     b, s_q, h, d = qc.shape
@@ -138,11 +138,13 @@ def attn_args(q, k, v, *, causal, softmax_scale, mode=L.FL_MODE_FP8, flags=0, st
         a.window_left_p1 = 0 if window[0] is None else int(window[0]) + 1
         a.window_right_p1 = 0 if window[1] is None else int(window[1]) + 1
     a.seqused_k = L.ptr(seqused_k)      # batched form: (b,) int32 valid keys per batch row, or None
+    a.softcap = float(softcap or 0.0)
     return a
 
 
 def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L.FL_MODE_FP8, status=None,
-             doc_start=None, doc_len=None, wait_cycles=0, token_local=False, window=None, p_group=False, seqused_k=None):
+             doc_start=None, doc_len=None, wait_cycles=0, token_local=False, window=None, p_group=False, seqused_k=None,
+             softcap=0.0):
     """Forward kernel on quantised operands. Returns (out (b, s_q, h, d), lse (b, h, s_q) float32, status).
     p_group: group-frame P-hat (one UE8M0 exponent per query row and 32 keys) instead of the row frame."""
     qc = q["codes"]
@@ -158,7 +160,8 @@ def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L
     a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode,
                   flags=(L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0) | (L.FL_A_P_GROUP if p_group else 0),
                   status=status, doc_start=doc_start,
-                  doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local, window=window, seqused_k=seqused_k)
+                  doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local, window=window, seqused_k=seqused_k,
+                  softcap=softcap)
     a.out, a.lse = L.ptr(out), L.ptr(lse)
     L.check(L.load().fl_fwd(C.byref(a), _stream()), "fl_fwd")
     return out, lse, status
@@ -199,7 +202,7 @@ def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torc
 
 def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax_scale, out_dtype=torch.bfloat16,
              mode=L.FL_MODE_FP8, had_dk=False, status=None, doc_start=None, doc_len=None, wait_cycles=0,
-             token_local=False, dq_rowlocal=False, window=None, seqused_k=None):
+             token_local=False, dq_rowlocal=False, window=None, seqused_k=None, softcap=0.0):
     """Backward main kernel on quantised operands. q / k / v / do: quantiser outputs (codes, fac). Adds the pre-scaled
     dQ partials into the f16 accumulator dq_acc of b * h * s_q * d elements ((b, h, d, s_q) at d = 128, (b, h, s_q, d)
     at d = 64) and returns (dk, dv, status), each (b, s_k, h_kv, d)."""
@@ -214,7 +217,7 @@ def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax
         (L.FL_A_DQ_ROWLOCAL if dq_rowlocal else 0)
     a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode, flags=flags, status=status,
                   doc_start=doc_start, doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local, window=window,
-                  seqused_k=seqused_k)
+                  seqused_k=seqused_k, softcap=softcap)
     a.do_codes, a.fac_do = L.ptr(do["codes"]), L.ptr(do["token_factors" if token_local else "fac"])
     a.lse_log2, a.d_rows, a.dq_acc, a.dq_scale = L.ptr(lse_log2), L.ptr(d_rows), L.ptr(dq_acc), L.ptr(dq_scale)
     a.dk, a.dv = L.ptr(dk), L.ptr(dv)

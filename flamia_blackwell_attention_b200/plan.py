@@ -163,7 +163,12 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
         if w is not None and (not isinstance(w, int) or w < -1):
             _fail(28, ValueError, f"window_size entries are None, -1 (unlimited) or a non-negative int; got {window_size}")
     if softcap:
-        _fail("B4", NotImplementedError, "softcap is not built yet")
+        if not isinstance(softcap, (int, float)) or softcap < 0:
+            _fail(28, ValueError, f"softcap is a non-negative float (0 = off); got {softcap!r}")
+        if scaling_request(o) == "token_local" or o.ds_dq_rowlocal == "all":
+            _fail("B4", NotImplementedError, "softcap is built on the default route (token-block operands, shared "
+                                             "dS-hat exponents), not with operand_scaling='token_local' / "
+                                             "ds_dq_rowlocal='all'")
     if seqused_k is not None and not shape.aligned_varlen:
         if shape.varlen:
             _fail("B9", ValueError, f"flash_attn_{entry}: the aligned varlen form takes seqused_q AND seqused_k")
@@ -252,13 +257,13 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
 
 
 def _finish(entry, route, qk_format, shape, log_rows, opts, *, softmax_scale, causal, return_lse, had, scaling, rowlocal,
-            ragged, dq_causal, window_size=(None, None), p_frame="row", seqused_k=False):
+            ragged, dq_causal, window_size=(None, None), p_frame="row", seqused_k=False, softcap=0.0):
     sc = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(shape.d)
     # sliding window (left, right): None / -1 = unlimited on that side; causal caps the right side at 0 in the kernels
     win = tuple(None if (w is None or w < 0) else int(w) for w in tuple(window_size))
     fwd = FwdSpec("fwd_sm100", qk_format, "e4m3", scaling, p_frame, "exp2", had, bool(causal), shape.varlen,
                   shape.aligned_varlen, ragged, bool(return_lse), None if win == (None, None) else win,
-                  seqused_k=bool(seqused_k))
+                  softcap=float(softcap or 0.0), seqused_k=bool(seqused_k))
     bwd = BwdSpec("1cta" if shape.requires_grad else "none", scaling, "block_32x32", rowlocal, "row", "e4m3", False,
                   "causal_tile" if dq_causal else "row")
     return AttnPlan(entry, route, sc, shape, fwd, bwd, opts.tuning, False, False, tuple(log_rows), opts)
@@ -307,7 +312,7 @@ def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     return _finish("fp8", "fp8", "e4m3", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
                    return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=dq_causal,
                    window_size=window_size, p_frame=p_frame,
-                   seqused_k=seqused_k is not None and not shape.aligned_varlen)
+                   seqused_k=seqused_k is not None and not shape.aligned_varlen, softcap=softcap)
 
 
 def _p_frame(entry, o, shape, scaling, default):
@@ -384,4 +389,4 @@ def resolve_fp4(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     return _finish("fp4", "fp4.e4m3_pv", "nvfp4", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
                    return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=False,
                    window_size=window_size, p_frame=p_frame,
-                   seqused_k=seqused_k is not None and not shape.aligned_varlen)
+                   seqused_k=seqused_k is not None and not shape.aligned_varlen, softcap=softcap)

@@ -111,6 +111,10 @@ typedef struct fl_attn_args {
    * there come back zero), or NULL. The reference's batched seqused_k (flash_attn/cute/lowprec/api.py:270). The causal
    * alignment keeps using s_k - s_q. */
   const int32_t* seqused_k;
+  /* Soft cap of the scaled scores: c > 0 turns score = softmax_scale q.k into c tanh(score / c) before masking, and dS takes
+   * the factor 1 - tanh^2 (the reference's softcap, flash_attn/cute/utils.py:167-187); 0 = off. Default P-hat route only
+   * (no token-local / row-local variants). */
+  float softcap;
 } fl_attn_args;
 
 /* Forward: O = softmax(scale Q K^T + mask) V, LSE.

@@ -26,14 +26,16 @@ from . import quant_oracle as Q
 
 
 def attention_fp32(q, k, v, g=None, causal=False, softmax_scale=None, chunk=1024, q_grad=None, k_grad=None,
-                   window=None, seqused_k=None):
+                   window=None, seqused_k=None, softcap=0.0):
     """q (b, s_q, h, d), k / v (b, s_k, h_kv, d) float32 CPU tensors -> (o, lse, dq, dk, dv); lse (b, h, s_q) in nats.
     Causal: key j visible to query i iff j <= i + (s_k - s_q). g = dO or None (forward only).
     q_grad / k_grad: the copies of Q / K used as operands of dK = dS^T Q and dQ = dS K when they differ from the S
     operands (the mixed route: S from the NVFP4 copies, gradient GEMMs from the E4M3 copies).
     window = (left, right), None = unlimited: key j visible iff i + off - left <= j <= i + off + right (causal caps the
     right side at 0). seqused_k: per batch row the number of valid keys (keys at or past it are masked; the causal
-    alignment keeps using s_k - s_q), as tests/cute/test_lowprec_api.py:1346 `_ref_bottom_right` of the reference."""
+    alignment keeps using s_k - s_q), as tests/cute/test_lowprec_api.py:1346 `_ref_bottom_right` of the reference.
+    softcap c > 0: the scaled scores become c tanh(score / c) before masking, and dS takes the factor 1 - tanh^2
+    (flash_attn/cute/utils.py:167-187, tests/cute/test_lowprec_api.py:1118 `_ref_attn`)."""
     q, k, v = q.float(), k.float(), v.float()
     qg = q if q_grad is None else q_grad.float()
     kg = k if k_grad is None else k_grad.float()
@@ -55,6 +57,11 @@ def attention_fp32(q, k, v, g=None, causal=False, softmax_scale=None, chunk=1024
             Qm, Km, Vm = q[bi, :, hi], kr[bi, :, hi], vr[bi, :, hi]
             for r0 in range(0, sq, chunk):
                 S = (Qm[r0:r0 + chunk] @ Km.T) * sc
+                dcap = None
+                if softcap:
+                    th = torch.tanh(S / float(softcap))
+                    S = float(softcap) * th
+                    dcap = 1.0 - th * th
                 wl, wr = (None, None) if window is None else window
                 if causal:
                     wr = 0
@@ -76,6 +83,8 @@ def attention_fp32(q, k, v, g=None, causal=False, softmax_scale=None, chunk=1024
                 if bwd:
                     dO = g[bi, r0:r0 + chunk, hi].float()
                     dS = P * (dO @ Vm.T - (dO * O).sum(-1, keepdim=True))
+                    if dcap is not None:
+                        dS = dS * dcap
                     dq[bi, r0:r0 + chunk, hi] = (dS @ kgr[bi, :, hi]) * sc
                     dk[bi, :, hi] += (dS.T @ qg[bi, r0:r0 + chunk, hi]) * sc
                     dv[bi, :, hi] += P.T @ dO
@@ -115,7 +124,7 @@ def _qdq4(x, rotate=False):
 
 
 def qdq_attention(q, k, v, g=None, *, causal=False, softmax_scale=None, fp4_qk=False, rotate_qk=False,
-                  token_local=False, window=None, seqused_k=None):
+                  token_local=False, window=None, seqused_k=None, softcap=0.0):
     """The quantise-dequantise emulation: MXFP8 (token-block) Q, K, V, dO -> fp32 attention. fp4_qk: the S operands are
     the NVFP4 codes of Q, K instead (the mixed route's forward and S recompute; dP / dV / dK / dQ keep the E4M3 copies --
     emulated here by using the NVFP4 values for S and the E4M3 values for the gradient GEMMs' Q / K operands).
@@ -128,12 +137,13 @@ def qdq_attention(q, k, v, g=None, *, causal=False, softmax_scale=None, fp4_qk=F
     v8 = _qdq8(v, False, token_local)
     g8 = _qdq8(g, False, token_local) if g is not None else None
     if not fp4_qk:
-        return attention_fp32(q8, k8, v8, g8, causal, softmax_scale, window=window, seqused_k=seqused_k)
+        return attention_fp32(q8, k8, v8, g8, causal, softmax_scale, window=window, seqused_k=seqused_k, softcap=softcap)
     q4, k4 = back(_qdq4(q, rotate_qk)), back(_qdq4(k, rotate_qk))
     # forward and P from the 4-bit S operands; with rotation on only the 4-bit copies are rotated on this route, so the
     # E4M3 copies for the gradient GEMMs are those of the unrotated rows
     q8u, k8u = (q8, k8) if not rotate_qk else (_qdq8(q, False, token_local), _qdq8(k, False, token_local))
-    return attention_fp32(q4, k4, v8, g8, causal, softmax_scale, q_grad=q8u, k_grad=k8u, window=window, seqused_k=seqused_k)
+    return attention_fp32(q4, k4, v8, g8, causal, softmax_scale, q_grad=q8u, k_grad=k8u, window=window, seqused_k=seqused_k,
+                          softcap=softcap)
 
 
 def accuracy(x, ref):

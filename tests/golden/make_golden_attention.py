@@ -6,7 +6,8 @@ definitions on CPU. Run once where the reference is mounted:
 What is executed, unmodified, from the reference checkout:
   * benchmarks/benchmark_lowprec_attn.py   `reference` (chunked fp32 attention fwd + bwd), `accuracy`
   * benchmarks/benchmark_packed_docs.py    `reference_docs` (fp32 attention per packed document)
-  * tests/cute/test_lowprec_api.py         `_ref_bottom_right` (s_q != s_k, bottom-right causal, autograd)
+  * tests/cute/test_lowprec_api.py         `_ref_bottom_right` (s_q != s_k, bottom-right causal, seqused_k, autograd) and
+                                           `_ref_attn` (softcap and window; gradients by autograd through it)
   * flash_attn/cute/device_scales.py       `_bwd1_fp8_host`, `_bwd1_fp4_host`, `_bwd2_host` (numpy float32 kernel scalars) and
                                            the Triton kernel `_dq_tile_table` (per-row / per-tile / per-query-row f16 dQ
                                            pre-scale) under Triton's CPU interpreter
@@ -66,7 +67,8 @@ def main():
     reference, accuracy = functions_of(os.path.join(root, "benchmarks", "benchmark_lowprec_attn.py"),
                                        ["reference", "accuracy"])
     (reference_docs,) = functions_of(os.path.join(root, "benchmarks", "benchmark_packed_docs.py"), ["reference_docs"])
-    (ref_bottom_right,) = functions_of(os.path.join(root, "tests", "cute", "test_lowprec_api.py"), ["_ref_bottom_right"])
+    ref_bottom_right, ref_attn = functions_of(os.path.join(root, "tests", "cute", "test_lowprec_api.py"),
+                                              ["_ref_bottom_right", "_ref_attn"])
     out = {}
     for name, (b, s, h, hk, d, causal, window, chunk) in ATTN_CASES.items():
         q, k, v, g = (t.float() for t in attention_inputs(b, s, h, hk, d, seed=21))
@@ -82,6 +84,14 @@ def main():
     o, lse, dq, dk, dv = ref_bottom_right(q, k, v, do, SEQUSED_CASE["causal"], seqused=torch.tensor(SEQUSED_CASE["seqused"]))
     for key, t in (("o", o), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
         out[f"seqused.{key}"] = t.contiguous().numpy()
+    # softcap (with a causal window): _ref_attn is MHA only
+    q, k, v, g = attention_inputs(1, 96, 2, 2, 32, seed=52)
+    q = (q.float() * 3.0).to(torch.bfloat16)           # scores large enough for the cap to bite
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    oc = ref_attn(qf, kf, vf, True, window=(40, 0), softcap=2.0)
+    oc.backward(g.float())
+    for key, t in (("o", oc.detach()), ("dq", qf.grad), ("dk", kf.grad), ("dv", vf.grad)):
+        out[f"softcap.{key}"] = t.contiguous().numpy()
     lens, h, hk, d = DOC_CASE["lens"], DOC_CASE["h"], DOC_CASE["hk"], DOC_CASE["d"]
     tot = sum(lens)
     q, k, v, g = (t[0] for t in attention_inputs(1, tot, h, hk, d, seed=45))

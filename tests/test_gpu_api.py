@@ -338,3 +338,24 @@ def test_batched_seqused_k(route, causal, sq, sk):
     for b_, n in enumerate(used):
         assert float(dk[b_, n:].abs().max() if n < sk else 0.0) == 0.0 and float(dv[b_, n:].abs().max() if n < sk else 0.0) == 0.0
     assert torch.isfinite(o).all() and torch.isfinite(dq).all()
+
+
+@pytest.mark.parametrize("route,d,causal,window", [("fp8", 128, True, None), ("fp8", 64, False, None), ("fp4", 128, True, (200, 0)),
+                                                   ("fp8", 128, True, (100, 0))])
+def test_softcap(route, d, causal, window):
+    """softcap c: score -> c tanh(score / c) before masking, dS takes 1 - tanh^2 (flash_attn/cute/utils.py:167-187 of the
+    reference). Scores are made large enough (Q x 3) for the cap to bite."""
+    import flamia_blackwell_attention_b200 as F
+    fn = F.flash_attn_fp8 if route == "fp8" else F.flash_attn_fp4
+    q, k, v, g = attention_inputs(2, 512, 4, 2, d, seed=93)
+    q = (q.float() * 3.0).to(torch.bfloat16)
+    kw = dict(causal=causal, softcap=2.0)
+    if window is not None:
+        kw["window_size"] = window
+    o, dq, dk, dv, _ = _step(fn, q, k, v, g, **kw)
+    ro, _, rdq, rdk, rdv = A.qdq_attention(q, k, v, g, causal=causal, rotate_qk=d == 128, fp4_qk=route == "fp4", window=window,
+                                           softcap=2.0)
+    _check((o, dq, dk, dv), (ro, rdq, rdk, rdv))
+    # the cap does something: the uncapped result differs
+    o2, *_ = _step(fn, q, k, v, g, causal=causal, **({} if window is None else dict(window_size=window)))
+    assert A.accuracy(o2, ro)["rel_l2"] > 0.05

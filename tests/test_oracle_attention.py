@@ -75,6 +75,14 @@ def test_attention_fp32_batched_seqused_k():
         _close(np.nan_to_num(t.numpy(), neginf=0.0), np.nan_to_num(want, neginf=0.0), f"seqused.{key}")
 
 
+def test_attention_fp32_softcap_and_window():
+    q, k, v, g = attention_inputs(1, 96, 2, 2, 32, seed=52)
+    q = (q.float() * 3.0).to(torch.bfloat16)
+    o, _lse, dq, dk, dv = A.attention_fp32(q, k, v, g, causal=True, window=(40, 0), softcap=2.0)
+    for key, t in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
+        _close(t.numpy(), GOLD[f"softcap.{key}"], f"softcap.{key}")
+
+
 def test_attention_docs_fp32_matches_reference_docs():
     lens, h, hk, d = [37, 128, 91], 2, 1, 32
     q, k, v, g = (t[0] for t in attention_inputs(1, sum(lens), h, hk, d, seed=45))
