@@ -177,17 +177,13 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint8_t* sDO = sQ + 2 * TILE_BYTES;                  // 2 stages
   uint8_t* sDS = sDO + 2 * TILE_BYTES;                 // per half: 128 key rows x 64 query bytes, 64 B swizzle
   uint8_t* sDQ = sDS + 2 * 8192;                       // per half: 128 head-dim rows x 64 queries f16, 128 B swizzle
-  // 2 stages x {lse_log2[128], D''[128]}, then 2 stages x {f_Q[4], f_dO[4] of the query tile's 32-row blocks, dQ pre-scale}:
-  // the per-iteration scalars travel with the tile (read from global memory at the top of an iteration they cost a
-  // memory latency on the compute warpgroups' critical path)
-  float* sVec = reinterpret_cast<float*>(sDQ + 2 * 16384);
+  float* sVec = reinterpret_cast<float*>(sDQ + 2 * 16384);   // 2 stages x {lse_log2[128], D''[128]}
   // d = 64 only: the gradient rows' way out (2 x 16 KB; at d = 128 the finished item's K / V buffers serve)
   uint8_t* sOut64 = reinterpret_cast<uint8_t*>(sVec) + 2048;
   // FP4 only: NVFP4 K tiles (2 x 8 KB), Q4 stages (2 x 8 KB), scale atoms K 2 x 1 KB + Q 2 x 1 KB
   uint8_t* sK4 = sOut64 + (D == 64 ? 2 * 16384 : 0);
   uint8_t* sQ4 = sK4 + 2 * 8192;
   uint8_t* sSF = sQ4 + 2 * 8192;
-  float* sFac = reinterpret_cast<float*>(sK4 + (FP4 ? 4 * 8192 + 4 * 1024 : 0));   // 2 stages x 16 floats, after everything else
   __shared__ __align__(8) uint64_t bars[BB_COUNT];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
@@ -231,7 +227,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   volatile int* abortp = &abort_s;
   // (a status word already set by an earlier launch is not looked at: a kernel that runs after one that gave up does no harm)
 
-  if (warp >= 12) reg_dealloc<72>();     // register budget per warpgroup: 184 / 184 / 72 / 72 (x 128 threads = 64 K)
+  if (warp >= 12) reg_dealloc<80>();     // register budget per warpgroup: 176 / 176 / 80 / 80 (x 128 threads = 64 K)
   if (warp == 13) {
     // =================================================================== TMA producer
     if (lane == 0) {
@@ -264,16 +260,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           const int st = gi & 1;
           const int head = t.hkv * grp + it / t.n_m, m = t.m_lo + it % t.n_m;
           if (gi >= 2 && !(ok = mbar_wait(&bars[BB_QEMPTY + st], ((gi >> 1) - 1) & 1, p.ctl, abortp, 10))) break;
-          // token-local factors are per query and read by the compute threads themselves; otherwise four block factors
-          // of Q and of dO (16 bytes each, 16-byte aligned: the tile starts at a multiple of four blocks)
-          constexpr bool TLF = VAR == 2;
-          sFac[st * 16 + 8] = p.dq_scale[(size_t)t.bat * (p.s_q / 128) + t.q0 / 128 + m];
-          mbar_arrive_expect_tx(&bars[BB_QFULL + st], 2 * TILE_BYTES + 1024 + (TLF ? 0 : 32) + (FP4 ? 8192 + 1024 : 0));
-          if (!TLF) {
-            const size_t fo = ((size_t)t.bat * p.h + head) * (p.s_q / 32) + (t.q0 + m * 128) / 32;
-            bulk_load(sFac + st * 16, p.fac_q + fo, 16, &bars[BB_QFULL + st]);
-            bulk_load(sFac + st * 16 + 4, p.fac_do + fo, 16, &bars[BB_QFULL + st]);
-          }
+          mbar_arrive_expect_tx(&bars[BB_QFULL + st], 2 * TILE_BYTES + 1024 + (FP4 ? 8192 + 1024 : 0));
           tma_load_4d(sQ + st * TILE_BYTES, &tm_q, &bars[BB_QFULL + st], 0, head, t.q0 + m * 128, t.bat);
           if (FP4) {
             tma_load_4d(sQ4 + st * 8192, &tm_q4, &bars[BB_QFULL + st], 0, head, t.q0 + m * 128, t.bat);
@@ -404,7 +391,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       gi += n_it;
     }
   } else if (warp >= 8 && warp < 12) {
-    reg_dealloc<72>();
+    reg_dealloc<80>();
     // =================================================================== dQ reduction (thread = head-dim row)
     const int r = tid & 127;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -462,7 +449,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     if (tid == 256) tma_store_wait<0>();
   } else if (warp < 8) {
-    reg_alloc<184>();
+    reg_alloc<176>();
     // =================================================================== compute (thread = key row, 64 query columns)
     const int x = warp >> 2;                         // the half this warpgroup owns
     const int wq = warp & 3;                         // lane quadrant = 32-key block of the tile
@@ -503,14 +490,13 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int g = gi + it, st = g & 1, u = g >> 1;
         const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
         const size_t bh_q = (size_t)T.bat * p.h + head;
-        if (!(ok = mbar_wait(&bars[BB_QFULL + st], u & 1, p.ctl, abortp, 30))) break;   // factors, lse / D'' vectors visible
-        // the half's two 32-query blocks' factors and the tile's dQ pre-scale, staged by the producer
-        const float fq0 = TL ? 1.f : sFac[st * 16 + 2 * x], fq1 = TL ? 1.f : sFac[st * 16 + 2 * x + 1];
-        const float fd0 = TL ? 1.f : sFac[st * 16 + 4 + 2 * x], fd1 = TL ? 1.f : sFac[st * 16 + 4 + 2 * x + 1];
+        const int qb0 = (T.q0 + m * 128) / 32 + 2 * x;                     // first of the half's two 32-query blocks
+        const float fq0 = TL ? 1.f : p.fac_q[bh_q * (p.s_q / 32) + qb0], fq1 = TL ? 1.f : p.fac_q[bh_q * (p.s_q / 32) + qb0 + 1];
+        const float fd0 = TL ? 1.f : p.fac_do[bh_q * (p.s_q / 32) + qb0], fd1 = TL ? 1.f : p.fac_do[bh_q * (p.s_q / 32) + qb0 + 1];
         // token-local: the 64 per-query factors of the half (same addresses for every thread: broadcast loads)
         const float4* fq_vec = reinterpret_cast<const float4*>(p.fac_q + (TL ? bh_q * p.s_q + T.q0 + m * 128 + 64 * x : 0));
         const float4* fdo_vec = reinterpret_cast<const float4*>(p.fac_do + (TL ? bh_q * p.s_q + T.q0 + m * 128 + 64 * x : 0));
-        const float bsc = sFac[st * 16 + 8];
+        const float bsc = p.dq_scale[(size_t)T.bat * (p.s_q / 128) + T.q0 / 128 + m];
         // FP4: the block scales of S were applied by the tensor core; only the softmax scale remains
         const float c[2] = {FP4 ? p.scale_log2 : fk * fq0, FP4 ? p.scale_log2 : fk * fq1}, b8[2] = {fv8 * fd0, fv8 * fd1};
         // token-local: fq0 = fq1 = fd0 = fd1 = 1, i.e. unit scale bytes for the Q and dO operands
@@ -519,6 +505,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // K's exponent bytes with the power-of-two f16 pre-scale of this query tile folded in (A scale of dQ^T)
         const uint32_t lb = (uint32_t)((int)((__float_as_uint(bsc) >> 23) & 0xFF) - 127) & 0xFF;
         const uint32_t ekb_word = __vadd4(ek_word, lb * 0x01010101u);
+        if (!(ok = mbar_wait(&bars[BB_QFULL + st], u & 1, p.ctl, abortp, 30))) break;   // lse / D'' vectors visible
         const uint32_t v_lse = smem_u32(sVec) + (st * 256 + 64 * x) * 4, v_dpp = v_lse + 512;
         const int q_first = m * 128 + 64 * x;                              // document-relative query of column 0
         const bool full = key_valid && (q_first >= vis_from) && (q_first + 63 <= vis_to) && (q_first + 64 <= T.sq);
@@ -531,14 +518,14 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         FL_TMEM_LD_32(t_sx + 32, (pv + 32));
         tc_wait_ld();
         float pf[64];
-        uint32_t pw_sc[SC ? 16 : 1];
+        [[maybe_unused]] uint32_t pw_sc[SC ? 16 : 1];
+        if constexpr (SC) {
+          // soft cap: x = cap_a tanh(s c cap_b); P-hat is taken from P' right here, and what stays in pf is
+          // P' (1 - tanh^2), the factor dS needs (the reference's score_mod_bwd, flash_attn/cute/utils.py:178-187)
 #pragma unroll
-        for (int j4 = 0; j4 < 16; ++j4) {
-          const float4 l4 = lds128(v_lse + 16 * j4);
-          const float cc = c[j4 >> 3];
-          if (SC) {
-            // soft cap: x = cap_a tanh(s c cap_b); P-hat is taken from P' right here, and what stays in pf is
-            // P' (1 - tanh^2), the factor dS needs (the reference's score_mod_bwd, flash_attn/cute/utils.py:178-187)
+          for (int j4 = 0; j4 < 16; ++j4) {
+            const float4 l4 = lds128(v_lse + 16 * j4);
+            const float cc = c[j4 >> 3];
             const float l[4] = {l4.x, l4.y, l4.z, l4.w};
             float pp[4], df[4];
 #pragma unroll
@@ -554,17 +541,22 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             pw_sc[j4] = cvt_e4m3x4(pp[0], pp[1], pp[2], pp[3]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) pf[4 * j4 + e] = pp[e] * df[e];
-            continue;
           }
-          float4 c4 = make_float4(cc, cc, cc, cc);
-          if (TL) {
-            const float4 f4 = __ldg(fq_vec + j4);
-            c4 = make_float4(fk * f4.x, fk * f4.y, fk * f4.z, fk * f4.w);
+        } else {
+#pragma unroll
+          for (int j4 = 0; j4 < 16; ++j4) {
+            const float4 l4 = lds128(v_lse + 16 * j4);
+            const float cc = c[j4 >> 3];
+            float4 c4 = make_float4(cc, cc, cc, cc);
+            if (TL) {
+              const float4 f4 = __ldg(fq_vec + j4);
+              c4 = make_float4(fk * f4.x, fk * f4.y, fk * f4.z, fk * f4.w);
+            }
+            pf[4 * j4 + 0] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 0]), c4.x, -l4.x));
+            pf[4 * j4 + 1] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 1]), c4.y, -l4.y));
+            pf[4 * j4 + 2] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 2]), c4.z, -l4.z));
+            pf[4 * j4 + 3] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 3]), c4.w, -l4.w));
           }
-          pf[4 * j4 + 0] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 0]), c4.x, -l4.x));
-          pf[4 * j4 + 1] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 1]), c4.y, -l4.y));
-          pf[4 * j4 + 2] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 2]), c4.z, -l4.z));
-          pf[4 * j4 + 3] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 3]), c4.w, -l4.w));
         }
         if (!SC && !full) {      // diagonal / tail tiles only
 #pragma unroll
@@ -605,8 +597,10 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         } else {
           uint32_t pw[16];
 #pragma unroll
-          for (int w = 0; w < 16; ++w)
-            pw[w] = SC ? pw_sc[w] : cvt_e4m3x4(pf[4 * w], pf[4 * w + 1], pf[4 * w + 2], pf[4 * w + 3]);
+          for (int w = 0; w < 16; ++w) {
+            if constexpr (SC) pw[w] = pw_sc[w];
+            else pw[w] = cvt_e4m3x4(pf[4 * w], pf[4 * w + 1], pf[4 * w + 2], pf[4 * w + 3]);
+          }
           FL_TMEM_ST_16(t_sx + TO_P, pw);
           // scale tiles of the dV product: A = 1, B = dO's exponent per 32 queries (bytes = the half's two K steps)
           uint32_t sf[8] = {0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, edo2, edo2, edo2, edo2};
@@ -887,7 +881,7 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.zigzag = (p.causal && !a->doc_start) ? 1 : 0;
   const int grid = (int)(n_items < sm_count() ? n_items : sm_count());     // one persistent CTA per SM
   const int smem = 8 * 128 * a->d + 2 * 8192 + 2 * 16384 + 2048 + (a->d == 64 ? 2 * 16384 : 0) + 1024 +
-                   (fp4 ? 4 * 8192 + 4 * 1024 : 0) + 128;
+                   (fp4 ? 4 * 8192 + 4 * 1024 : 0);
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
     kern<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, mdk, mdv, p);

@@ -410,24 +410,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       constexpr float P_OFF = GF ? P_LOG2_448 : P_LOG2_OFFSET;
 
       float m_used = -INFINITY, l_sum = 0.f;
-      // The four K / V block factors of a key tile are loaded one tile ahead: read at the top of their own tile they cost
-      // a global-memory latency on the softmax threads' critical path (the scores are usually there already).
-      const float4* fk_t = reinterpret_cast<const float4*>(fk_row);
-      const float4* fv_t = reinterpret_cast<const float4*>(fv_row);
-      float4 fk_nxt = make_float4(1.f, 1.f, 1.f, 1.f), fv_nxt = fk_nxt;
-      if (!TL && n_i > 0) { fk_nxt = __ldg(fk_t); fv_nxt = __ldg(fv_t); }
       for (int j = 0; j < n_i; ++j, ++cs) {
         float c[4];
         uint32_t sfv = 0;
-        const float4 fk_cur = fk_nxt, fv_cur = fv_nxt;
-        if (!TL && j + 1 < n_i) { fk_nxt = __ldg(fk_t + j + 1); fv_nxt = __ldg(fv_t + j + 1); }
-        if (!TL) {
-          const float fkv[4] = {fk_cur.x, fk_cur.y, fk_cur.z, fk_cur.w}, fvv[4] = {fv_cur.x, fv_cur.y, fv_cur.z, fv_cur.w};
 #pragma unroll
-          for (int kbk = 0; kbk < 4; ++kbk) {
-            c[kbk] = FP4 ? fq : fq * fkv[kbk];               // FP4: the block scales were applied by the tensor core
-            sfv |= ((__float_as_uint(fvv[kbk]) >> 23) & 0xFF) << (8 * kbk);
-          }
+        for (int kbk = 0; kbk < 4; ++kbk) {
+          if (TL) continue;
+          c[kbk] = FP4 ? fq : fq * fk_row[j * 4 + kbk];      // FP4: the block scales were applied by the tensor core
+          sfv |= ((__float_as_uint(fv_row[j * 4 + kbk]) >> 23) & 0xFF) << (8 * kbk);
         }
         // token-local: the tile's 128 per-key factors (same addresses for every thread: broadcast loads through L1;
         // staging them in shared memory was twice as slow: 384 broadcast reads per thread and tile saturate the
