@@ -3,10 +3,11 @@ backward, behind the public interface of the reference's flash_attn.cute.lowprec
 plan resolution, torch custom ops). The compute path is hand-written CUDA for sm_100a in libflamia_b200.so, reached
 through the C ABI of include/flamia_b200.h; there is no CPU or PyTorch fallback.
 """
+from .docmaps import DocMaps
 from .options import FP4AttnOptions, FP8AttnOptions, KernelTuning, TUNING_FIELDS
 from .plan import AttnPlan, resolve_fp4, resolve_fp8
 
-__all__ = ["flash_attn_fp4", "flash_attn_fp8", "check_status", "FP4AttnOptions", "FP8AttnOptions", "KernelTuning", "TUNING_FIELDS",
+__all__ = ["flash_attn_fp4", "flash_attn_fp8", "check_status", "DocMaps", "FP4AttnOptions", "FP8AttnOptions", "KernelTuning", "TUNING_FIELDS",
            "AttnPlan", "resolve_fp4", "resolve_fp8"]
 
 

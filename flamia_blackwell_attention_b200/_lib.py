@@ -29,7 +29,8 @@ class QuantArgs(C.Structure):
     _fields_ = [(n, vp) for n in ("x", "o", "lse", "codes", "codes_t", "e_tab", "fac", "sf_tok", "sf_dim",
                                   "token_factors", "x4", "sf4", "d_out", "lse_log2", "zero_acc", "tile_stats")] + \
                [(n, i32) for n in ("b", "s", "h", "d", "flags", "in_f16")] + [("lse_shift", f32), ("d_multiplier", f32),
-                                                                            ("status", vp), ("wait_cycles", i64)]
+                                                                            ("status", vp), ("wait_cycles", i64),
+                                                                            ("slot_src", vp), ("slot_rows", vp), ("src_rows", i32)]
 
 
 class AttnArgs(C.Structure):
@@ -53,6 +54,7 @@ EXPORTS = {
     "fl_unpack_rows": (i32, [vp, vp, vp, i32, i32, vp]),
     "fl_selftest_mma": (i32, [i32, vp, vp, vp, vp, vp, vp, i64, vp]),
     "fl_read_status": (i32, [vp, C.POINTER(i32), vp]),
+    "fl_last_cuda_error": (i32, [C.c_char_p, i32]),
 }
 
 _lib = None
@@ -76,7 +78,12 @@ def load():
 
 def check(rc: int, what: str):
     if rc != 0:
-        raise RuntimeError(f"{what} failed: {ERR_NAMES.get(rc, rc)} (code {rc})")
+        detail = ""
+        if rc == FL_ERR_CUDA:
+            buf = C.create_string_buffer(256)
+            load().fl_last_cuda_error(buf, 256)
+            detail = ": " + buf.value.decode(errors="replace")
+        raise RuntimeError(f"{what} failed: {ERR_NAMES.get(rc, rc)} (code {rc}){detail}")
 
 
 def ptr(t):

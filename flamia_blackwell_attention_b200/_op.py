@@ -50,11 +50,14 @@ def _fwd_impl(q, k, v, docs: List[torch.Tensor], plan: int, docs_id: int):
     seqused_k = None
     if p.fwd.seqused_k:           # batched form: docs = [seqused_k]
         seqused_k, docs = docs[0], []
-    cu_q = docs[0] if len(docs) > 0 else None
-    cu_k = docs[1] if len(docs) > 1 else None
-    su_q = docs[2] if len(docs) > 2 else None
-    su_k = docs[3] if len(docs) > 3 else None
-    d = _routes.docs_of(p, q, cu_q, cu_k, su_q, su_k)
+    if len(docs) == 6:            # precomputed maps: cu, start, len, row_map, slot_src, slot_rows
+        d = _routes.Docs.from_tables(docs[1], docs[2], docs[3], docs[4], docs[5], docs[3].numel())
+    else:
+        cu_q = docs[0] if len(docs) > 0 else None
+        cu_k = docs[1] if len(docs) > 1 else None
+        su_q = docs[2] if len(docs) > 2 else None
+        su_k = docs[3] if len(docs) > 3 else None
+        d = _routes.docs_of(p, q, cu_q, cu_k, su_q, su_k)
     out, lse, state = _routes.forward(p, q, k, v, d, seqused_k)
     meta = None if d is None else (d.capacity, d.aligned)
     entry = _register_entry(plan, meta)
@@ -76,7 +79,7 @@ def _fake_fwd(q, k, v, docs, plan, docs_id):
     is_docs = sh.varlen or p.fwd.ragged_documents
     lse_shape = (sh.h, sh.tot_q) if sh.aligned_varlen else ((0,) if is_docs else (sh.b, sh.h, sh.s_q))
     n_docs = int(docs[0].shape[0]) - 1 if (len(docs) > 0 and not p.fwd.seqused_k) else 0
-    spec = _routes.state_spec(p, n_docs, q.dtype)
+    spec = _routes.state_spec(p, n_docs, q.dtype, capacity=int(docs[3].numel()) if len(docs) == 6 else None)
     # as _fwd_impl: the batched form hands O / LSE out as the op's outputs, documents keep the padded ones in the state
     state = [q.new_empty(shape, dtype=dt) for shape, dt in (spec if is_docs else spec[2:])]
     state.append(torch.empty((), dtype=torch.int64))

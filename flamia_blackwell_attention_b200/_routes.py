@@ -69,13 +69,16 @@ def check_status(device=None) -> int:
 # --------------------------------------------------------------------------------------------------------------- docs
 class Docs:
     """Packed documents laid out at 128-aligned starts of one padded buffer. Built on the device without a host sync:
-    the padded capacity is the host-known bound total + 127 * n_docs rounded up to 128."""
+    the padded capacity is the host-known bound total + 127 * n_docs rounded up to 128. The quantisers read the packed
+    rows in place through the slot tables (slot_src / slot_rows: first source row and number of real rows of every
+    128-row slot of the buffer); outputs are scattered back through row_map."""
 
-    def __init__(self, cu, lens, total, aligned):
+    def __init__(self, cu, lens, total, aligned, capacity=None):
         dev = cu.device
         self.n = int(lens.numel())
         self.len = lens.to(torch.int32).contiguous()
         self.aligned = aligned
+        self.slot_src = self.slot_rows = None
         if aligned:
             self.start = cu[:-1].to(torch.int32).contiguous()
             self.capacity = int(total)
@@ -84,12 +87,29 @@ class Docs:
         padded = ((self.len + 127) // 128) * 128
         ends = torch.cumsum(padded, 0)
         self.start = (ends - padded).to(torch.int32).contiguous()
-        self.capacity = ((int(total) + 127 * self.n + 127) // 128) * 128
+        self.capacity = int(capacity) if capacity is not None else ((int(total) + 127 * self.n + 127) // 128) * 128
         rows = torch.arange(self.capacity, device=dev, dtype=torch.int32)
         doc = torch.searchsorted(ends.to(torch.int32), rows, right=True).clamp_(max=self.n - 1)
         off = rows - self.start[doc]
         src = cu[:-1].to(torch.int32)[doc] + off
-        self.row_map = torch.where((off >= 0) & (off < self.len[doc]), src, torch.full_like(src, -1)).contiguous()
+        live = (off >= 0) & (off < self.len[doc])
+        self.row_map = torch.where(live, src, torch.full_like(src, -1)).contiguous()
+        first = slice(0, self.capacity, 128)
+        self.slot_src = self.row_map[first].contiguous()                     # a slot's first row is real or the slot is empty
+        self.slot_rows = torch.where(live[first], (self.len[doc] - off)[first].clamp(max=128),
+                                     torch.zeros_like(off[first])).to(torch.int32).contiguous()
+
+    @classmethod
+    def from_tables(cls, start, lens, row_map, slot_src, slot_rows, capacity):
+        """A Docs over precomputed tables (DocMaps): nothing is computed."""
+        d = object.__new__(cls)
+        d.n, d.len, d.start, d.aligned = int(lens.numel()), lens, start, False
+        d.capacity, d.row_map, d.slot_src, d.slot_rows = int(capacity), row_map, slot_src, slot_rows
+        return d
+
+    def slots(self):
+        """The quantisers' packed-source argument, or None on the aligned form (the rows are in place already)."""
+        return None if self.aligned else (self.slot_src, self.slot_rows, self.capacity)
 
     def pack(self, x):
         """(total, h, d) -> (1, capacity, h, d) with zero padding rows."""
@@ -128,7 +148,7 @@ def docs_of(plan, q, cu_q, cu_k, seqused_q, seqused_k):
     return None
 
 
-def state_spec(plan, n_docs=0, dtype=torch.bfloat16):
+def state_spec(plan, n_docs=0, dtype=torch.bfloat16, capacity=None):
     """Shapes and dtypes of the tensors forward() returns as `state`, in order, from the plan alone (n_docs = number of
     documents of a packed call). The fake implementations of the registered ops are built from this, and a GPU test
     checks it against the real state."""
@@ -143,7 +163,7 @@ def state_spec(plan, n_docs=0, dtype=torch.bfloat16):
             n, cap = n_docs, sh.tot_q
         else:
             n, tot = (n_docs, sh.tot_q) if sh.varlen else (sh.b, sh.b * sh.s_q)
-            cap = ((tot + 127 * n + 127) // 128) * 128
+            cap = capacity if capacity is not None else ((tot + 127 * n + 127) // 128) * 128
         b, s_q, s_k = 1, cap, cap
     else:
         b, s_q, s_k = sh.b, sh.s_q, sh.s_k
@@ -161,7 +181,7 @@ def state_spec(plan, n_docs=0, dtype=torch.bfloat16):
     if f.seqused_k:
         spec += [((b,), i32)]
     if docs:
-        spec += [((n,), i32), ((n,), i32)] + ([] if sh.aligned_varlen else [((cap,), i32)])
+        spec += [((n,), i32), ((n,), i32)] + ([] if sh.aligned_varlen else [((cap,), i32), ((cap // 128,), i32), ((cap // 128,), i32)])
     return spec
 
 
@@ -173,21 +193,24 @@ def forward(plan, q, k, v, docs, seqused_k=None):
     fp4 = plan.entry == "fp4"
     mode = L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8
     tl = f.operand_scaling == "token_local"
+    slots = None
     if docs is not None:
-        qv = q.reshape(sh.b * sh.s_q, sh.h, sh.d) if q.dim() == 4 else q
-        kv = k.reshape(-1, sh.h_kv, sh.d) if k.dim() == 4 else k
-        vv = v.reshape(-1, sh.h_kv, sh.d) if v.dim() == 4 else v
-        qp, kp, vp = docs.pack(qv), docs.pack(kv), docs.pack(vv)
+        qp = q.reshape(sh.b * sh.s_q, sh.h, sh.d) if q.dim() == 4 else q
+        kp = k.reshape(-1, sh.h_kv, sh.d) if k.dim() == 4 else k
+        vp = v.reshape(-1, sh.h_kv, sh.d) if v.dim() == 4 else v
+        slots = docs.slots()                  # repacked documents: the quantisers gather the packed rows themselves
+        if slots is None:
+            qp, kp, vp = qp.unsqueeze(0), kp.unsqueeze(0), vp.unsqueeze(0)
     else:
         qp, kp, vp = q, k, v
     need_bwd = plan.bwd.kernel != "none"
     # rotation: the 8-bit route rotates the E4M3 codes; the mixed route rotates only the NVFP4 S operands
     qk_kw = dict(apply_hadamard_rotation=f.qk_hadamard, hadamard_rotation_scope="nvfp4_copy" if fp4 else "all",
-                 also_make_nvfp4_copy=fp4, token_local_exponents=tl)
+                 also_make_nvfp4_copy=fp4, token_local_exponents=tl, packed_slots=slots)
     status = K.new_status(q.device)
     qq = K.quantize_fp8_blocks(qp, status=status, **qk_kw)
     kq = K.quantize_fp8_blocks(kp, output_tile_stats=need_bwd, status=status, **qk_kw)
-    vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl, status=status)
+    vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl, status=status, packed_slots=slots)
     out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=q.dtype, mode=mode,
                              status=status, token_local=tl, window=f.window, p_group=f.p_hat_frame == "group",
                              seqused_k=seqused_k, softcap=f.softcap,
@@ -202,7 +225,7 @@ def forward(plan, q, k, v, docs, seqused_k=None):
     if seqused_k is not None:
         state += [seqused_k]
     if docs is not None:
-        state += [docs.start, docs.len] + ([] if docs.row_map is None else [docs.row_map])
+        state += [docs.start, docs.len] + ([] if docs.row_map is None else [docs.row_map, docs.slot_src, docs.slot_rows])
         out_user = docs.unpack(out, sh.tot_q if sh.varlen else sh.b * sh.s_q)
         if not sh.varlen:
             out_user = out_user.reshape(sh.b, sh.s_q, sh.h, sh.d)
@@ -233,16 +256,18 @@ def backward(plan, state, dout, docs_meta):
         docs.start, docs.len = next(it), next(it)
         docs.capacity, docs.aligned = docs_meta
         docs.n = int(docs.len.numel())
-        docs.row_map = None if docs.aligned else next(it)
-        g = dout.reshape(-1, sh.h, sh.d) if dout.dim() == 4 else dout
-        gp = docs.pack(g.contiguous())
+        docs.row_map, docs.slot_src, docs.slot_rows = (None, None, None) if docs.aligned else (next(it), next(it), next(it))
+        gp = (dout.reshape(-1, sh.h, sh.d) if dout.dim() == 4 else dout).contiguous()
+        if docs.aligned:
+            gp = gp.unsqueeze(0)
     else:
         gp = dout.contiguous()
     b, s_q, h, d = out.shape
     acc = torch.empty(b, h, s_q, d, dtype=torch.float16, device=out.device)
     gq = K.quantize_fp8_blocks(gp, compute_d_with_output=out, shifted_log2_lse_from=lse, log2_lse_shift=P_SHIFT_LOG2,
                                d_multiplier=float(backward_scalars(plan.softmax_scale)[6]), zero_accumulator=acc, output_tile_stats=True,
-                               token_local_exponents=tl, status=status)
+                               token_local_exponents=tl, status=status,
+                               packed_slots=None if docs is None else docs.slots())
     ks, ps = K.dq_prescale(gq["tile_stats"], vstats, kstats, causal_local=bw.dq_prescale == "causal_tile")
     had8 = f.qk_hadamard and not fp4           # only the 8-bit route's E4M3 codes are rotated
     dk, dv, _ = K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks,

@@ -80,7 +80,21 @@ def _cached_plan(resolve, q, k, v, kw) -> AttnPlan:
         return resolve(q, k, v, **kw)           # an unhashable argument (e.g. a callable object): resolve uncached
 
 
-def _run(plan, q, k, v, cu_q, cu_k, su_q, su_k, return_lse):
+def _doc_maps_args(maps, q, cu_q, cu_k, su_q, su_k):
+    """doc_maps= stands for the varlen arguments: the plan is resolved as for cu_seqlens = maps.cu."""
+    from .docmaps import DocMaps
+    if not isinstance(maps, DocMaps):
+        _fail("B9", TypeError, f"doc_maps must be a DocMaps; got {type(maps).__name__}")
+    if cu_q is not None or cu_k is not None or su_q is not None or su_k is not None:
+        _fail("B9", ValueError, "doc_maps carries the documents: do not pass cu_seqlens_* / seqused_* with it")
+    if isinstance(q, torch.Tensor) and (q.dim() != 3 or q.shape[0] != maps.total):
+        _fail("B9", ValueError, f"doc_maps describes {maps.total} packed rows; q is {tuple(q.shape)}")
+    if isinstance(q, torch.Tensor) and q.is_cuda and maps.device != q.device:
+        _fail("B9", ValueError, f"doc_maps is on {maps.device}, q on {q.device}: move the maps with .to(device)")
+    return maps.cu, maps.cu, maps.max_seqlen, maps.max_seqlen
+
+
+def _run(plan, q, k, v, cu_q, cu_k, su_q, su_k, return_lse, doc_maps=None):
     global _REPACK_WARNED
     if not q.is_cuda:
         raise RuntimeError(f"flash_attn_{plan.entry}: q, k, v must be CUDA tensors (this library has no CPU path)")
@@ -100,11 +114,14 @@ def _run(plan, q, k, v, cu_q, cu_k, su_q, su_k, return_lse):
     if plan.fwd.ragged_documents and sh.s_q != sh.s_k:
         _fail("B8", NotImplementedError, "lengths that are no multiple of 128 run the batch rows as self-attention "
                                          f"documents: s_q must equal s_k; got {sh.s_q} and {sh.s_k}")
-    if sh.varlen and not sh.aligned_varlen and not _REPACK_WARNED:
+    if sh.varlen and not sh.aligned_varlen and doc_maps is None and not _REPACK_WARNED:
         _REPACK_WARNED = True
         warnings.warn(REPACK_WARNING.format(entry=plan.entry), UserWarning, stacklevel=3)
-    docs = [t for t in (cu_q, cu_k, su_q, su_k) if t is not None] if sh.varlen else \
-        ([su_k.contiguous()] if plan.fwd.seqused_k else [])
+    if doc_maps is not None:
+        docs = doc_maps.tensors()           # cu, start, len, row_map, slot_src, slot_rows: nothing is computed per call
+    else:
+        docs = [t for t in (cu_q, cu_k, su_q, su_k) if t is not None] if sh.varlen else \
+            ([su_k.contiguous()] if plan.fwd.seqused_k else [])
     out, lse = _op.op_apply(plan, q, k, v, docs)
     if return_lse:
         if lse.numel() == 0:
@@ -132,7 +149,8 @@ def flash_attn_fp8(q, k, v, *, softmax_scale: Optional[float] = None, causal: bo
     E4M3 Q, K, V, dO with one UE8M0 exponent per 32 tokens x the whole head dim; qk_hadamard=None turns the random-sign
     Hadamard rotation of Q / K on at d = 128. Every unserved combination raises with a `.rule` before any launch."""
     if doc_maps is not None:
-        _fail("B8", NotImplementedError, "doc_maps (precomputed document maps) are not built: pass cu_seqlens_*")
+        cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k = _doc_maps_args(doc_maps, q, cu_seqlens_q, cu_seqlens_k,
+                                                                                seqused_q, seqused_k)
     if q_descale is not None or k_descale is not None or v_descale is not None or grad_proxies is not None or \
             (isinstance(q, torch.Tensor) and q.dtype == torch.float8_e4m3fn):
         _fail("B7", NotImplementedError, "FA3-style pre-quantised E4M3 inputs (q_descale / k_descale / v_descale / "
@@ -145,7 +163,7 @@ def flash_attn_fp8(q, k, v, *, softmax_scale: Optional[float] = None, causal: bo
         max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, seqused_k=seqused_k, seqused_q=seqused_q,
         deterministic=deterministic, return_lse=return_lse, qk_hadamard=qk_hadamard, q_quantized=q_quantized,
         k_quantized=k_quantized, q_scale_fused=q_scale_fused, options=options))
-    return _run(plan, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k, return_lse)
+    return _run(plan, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k, return_lse, doc_maps)
 
 
 def flash_attn_fp4(q, k, v, *, softmax_scale: Optional[float] = None, causal: bool = False,
@@ -163,7 +181,8 @@ def flash_attn_fp4(q, k, v, *, softmax_scale: Optional[float] = None, causal: bo
     as flash_attn_fp8; d = 128. With qk_hadamard on (default) the NVFP4 codes are of the rotated rows, the E4M3 copies of
     the rows as given."""
     if doc_maps is not None:
-        _fail("B8", NotImplementedError, "doc_maps (precomputed document maps) are not built: pass cu_seqlens_*")
+        cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k = _doc_maps_args(doc_maps, q, cu_seqlens_q, cu_seqlens_k,
+                                                                                seqused_q, seqused_k)
     if q_descale is not None or k_descale is not None or v_descale is not None or \
             any(isinstance(t, torch.Tensor) and t.dtype == torch.float8_e4m3fn for t in (q, k, v)):
         _fail("B7", TypeError, "flash_attn_fp4 takes bf16 / f16 inputs: pre-quantised E4M3 inputs are a flash_attn_fp8 "
@@ -176,4 +195,4 @@ def flash_attn_fp4(q, k, v, *, softmax_scale: Optional[float] = None, causal: bo
         max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, seqused_k=seqused_k, seqused_q=seqused_q,
         deterministic=deterministic, return_lse=return_lse, pv_precision=pv_precision, backward=backward,
         causal_safety=causal_safety, qk_hadamard=qk_hadamard, options=options))
-    return _run(plan, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k, return_lse)
+    return _run(plan, q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k, return_lse, doc_maps)

@@ -883,7 +883,8 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   const int smem = 8 * 128 * a->d + 2 * 8192 + 2 * 16384 + 2048 + (a->d == 64 ? 2 * 16384 : 0) + 1024 +
                    (fp4 ? 4 * 8192 + 4 * 1024 : 0);
   auto launch = [&](auto kern) -> int {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
+    if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); e != cudaSuccess)
+      return cuda_fail((int)e, "fl_bwd: cudaFuncSetAttribute");
     kern<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, mdk, mdv, p);
     return FL_OK;
   };
@@ -900,5 +901,5 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
     rc = rl ? launch(bwd_kernel_pipelined<128, false, 1, false>) : launch(bwd_kernel_pipelined<128, false, 0, false>);
   }
   if (rc) return rc;
-  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+  return launch_result("fl_bwd: kernel launch");
 }

@@ -22,6 +22,11 @@ int make_acc_map_16(CUtensorMap* m, const void* base, int b, int heads, int s, i
 
 int make_acc_t_map_16(CUtensorMap* m, const void* base, int b, int heads, int d, int s);
 
+// FL_ERR_CUDA with the failing call and its CUDA code remembered for fl_last_cuda_error() (per host thread)
+int cuda_fail(int cuda_code, const char* where);
+// the result of a kernel launch just made: FL_OK, or cuda_fail() of cudaGetLastError()
+int launch_result(const char* where);
+
 // multiprocessors of the current device (cached per device): the size of a persistent grid
 int sm_count();
 

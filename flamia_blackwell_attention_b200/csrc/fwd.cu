@@ -693,7 +693,8 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   const int smem = 4 * Q_STRIDE + 2 * KV_STAGES * 128 * a->d + 1024 + (fp4 ? 4096 + KV_STAGES * 1024 : 0);
   cudaStream_t st = (cudaStream_t)stream;
   auto launch = [&](auto kern) -> int {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
+    if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); e != cudaSuccess)
+      return cuda_fail((int)e, "fl_fwd: cudaFuncSetAttribute");
     kern<<<grid, 384, smem, st>>>(mq, mk, mv, mo, p);
     return FL_OK;
   };
@@ -714,5 +715,5 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
     rc = tl ? launch(fwd_kernel<64, false, true, false, false>) : launch(fwd_kernel<64, false, false, false, false>);
   }
   if (rc) return rc;
-  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+  return launch_result("fl_fwd: kernel launch");
 }

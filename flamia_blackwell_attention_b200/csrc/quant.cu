@@ -38,6 +38,8 @@ struct QuantParams {
   uint16_t* zero_acc;     // f16 accumulator of b * h * s * d elements or null
   float* tile_stats;      // (b, h, s/128, 2): [amax of the values quantised, max row sum of squares] or null
   int b, s, h;
+  const int32_t* slot_src;   // packed source: first source row of each 128-row slot of the output (-1: an empty slot), or null
+  const int32_t* slot_rows;  // packed source: valid rows of each slot (the rest of the slot reads as zero)
   int n_tiles;            // b * (s / 128) * h
   int token_local;
   int in_f16;
@@ -116,9 +118,14 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   auto issue = [&](int L, int st) {              // one thread: the loads of linear tile L into stage st
     const int head = L % p.h, tile = (L / p.h) % ntile, bat = L / (p.h * ntile);
     uint8_t* dst = smem + st * STAGE_B;
-    mbar_arrive_expect_tx(&full[st], STAGE_B);
-    tma_load_4d(dst, &tm_x, &full[st], 0, head, tile * QT, bat);
-    if (D == 128) tma_load_4d(dst + TILE_B / 2, &tm_x, &full[st], 64, head, tile * QT, bat);
+    // packed source (documents stored back to back): the slot's rows start at an arbitrary row of the (1, total, h, d)
+    // tensor; only the innermost TMA coordinate has an alignment rule. An empty slot loads nothing of x.
+    const int xrow = p.slot_src ? p.slot_src[tile] : tile * QT;
+    mbar_arrive_expect_tx(&full[st], (xrow >= 0 ? TILE_B : 0) + (PRO ? TILE_B : 0));
+    if (xrow >= 0) {
+      tma_load_4d(dst, &tm_x, &full[st], 0, head, xrow, bat);
+      if (D == 128) tma_load_4d(dst + TILE_B / 2, &tm_x, &full[st], 64, head, xrow, bat);
+    }
     if (PRO) {
       tma_load_4d(dst + TILE_B, &tm_o, &full[st], 0, head, tile * QT, bat);
       if (D == 128) tma_load_4d(dst + TILE_B + TILE_B / 2, &tm_o, &full[st], 64, head, tile * QT, bat);
@@ -143,10 +150,18 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   __syncthreads();
 
   // raw 16-byte chunk j of this thread's row (global chunk 4 j + q) from a staged tile
+  bool row_live = true;                          // packed source: false for the rows of a slot past its document's end
   auto lds_chunk = [&](uint32_t tile_addr, int j) -> uint4 {
     const int g = 4 * j + q;
     const uint32_t box = (D == 128) ? (uint32_t)(g >> 3) * (TILE_B / 2) : 0u;
     return lds_u4(tile_addr + box + r * 128 + (((g & 7) ^ (r & 7)) << 4));
+  };
+  // the same for a chunk of x: rows that do not belong to the slot's document (or an empty slot, whose stage holds
+  // whatever was there) read as zero
+  auto lds_chunk_x = [&](uint32_t tile_addr, int j) -> uint4 {
+    uint4 v = lds_chunk(tile_addr, j);
+    if (!row_live) v = make_uint4(0, 0, 0, 0);
+    return v;
   };
   auto to_f32 = [&](const uint4& v, float* dst) {      // 8 elements of one chunk
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -172,7 +187,7 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       float t[32];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        uint4 v = lds_chunk(tile_addr, j);
+        uint4 v = lds_chunk_x(tile_addr, j);
         const uint4 sg = *reinterpret_cast<const uint4*>(&s_sign[q][j][0]);
         v.x ^= sg.x; v.y ^= sg.y; v.z ^= sg.z; v.w ^= sg.w;
         to_f32(v, t + 8 * j);
@@ -221,7 +236,7 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   };
   auto load_plain = [&](uint32_t tile_addr, float* y) {
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) to_f32(lds_chunk(tile_addr, j), y + 8 * j);
+    for (int j = 0; j < NJ; ++j) to_f32(lds_chunk_x(tile_addr, j), y + 8 * j);
   };
 
   int it = 0;
@@ -234,6 +249,7 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const size_t ri = bh * p.s + t0 + r;
     const uint32_t tile_addr = smem_u32(smem + st * STAGE_B);
     bool ok = mbar_wait(&full[st], (it / QSTAGES) & 1, p.ctl, abortp, 50);
+    if (p.slot_rows) row_live = r < p.slot_rows[tile];
 
     if (p.zero_acc) {   // this tile's share of the accumulator: 128 * D f16 = 32 D 16-byte chunks, contiguous
       uint4* z = reinterpret_cast<uint4*>(p.zero_acc + (bh * p.s + t0) * D);
@@ -463,7 +479,8 @@ static int launch_quant(const CUtensorMap& mx, const CUtensorMap& mo, const Quan
   constexpr int TILE_B = QT * D * 2;
   const int smem = QSTAGES * (PRO ? 2 : 1) * TILE_B + 1024 + (want_t ? QT * (D + 16) : 0);
   auto kern = quant_blocks_kernel<D, MODE, PRO>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FL_ERR_CUDA;
+  if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); e != cudaSuccess)
+      return cuda_fail((int)e, "fl_quant_blocks: cudaFuncSetAttribute");
   const int per_sm = (PRO || want_t) ? 1 : 2;
   const int grid = min(p.n_tiles, sm_count() * per_sm);
   kern<<<grid, QTHREADS, smem, st>>>(mx, mo, p);
@@ -492,6 +509,9 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   p.sf_dim = a->sf_dim; p.token_factors = a->token_factors; p.x4 = a->x4; p.sf4 = a->sf4; p.d_out = a->d_out;
   p.lse_log2 = a->lse_log2; p.zero_acc = (uint16_t*)a->zero_acc; p.tile_stats = a->tile_stats;
   p.b = a->b; p.s = a->s; p.h = a->h; p.n_tiles = (int)n_tiles;
+  p.slot_src = a->slot_src; p.slot_rows = a->slot_rows;
+  const bool packed = a->slot_src != nullptr;
+  if (packed && (!a->slot_rows || a->b != 1 || a->src_rows <= 0)) return FL_ERR_BAD_ARG;
   p.token_local = (a->flags & FL_Q_TOKEN_LOCAL) ? 1 : 0;
   p.in_f16 = a->in_f16;
   p.lse_shift = a->lse_shift; p.d_multiplier = a->d_multiplier;
@@ -499,7 +519,7 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   p.ctl.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kDefaultWaitCycles;
   CUtensorMap mx, mo;
   int rc;
-  if ((rc = make_rows_map_16(&mx, a->x, a->b, a->s, a->h, a->d, 128))) return rc;
+  if ((rc = make_rows_map_16(&mx, a->x, a->b, packed ? a->src_rows : a->s, a->h, a->d, 128))) return rc;
   if ((rc = make_rows_map_16(&mo, pro ? a->o : a->x, a->b, a->s, a->h, a->d, 128))) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const bool wt = a->codes_t != nullptr;
@@ -516,5 +536,5 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
     rc = nv4 ? launch_quant<128, 2, false>(mx, mo, p, wt, st) : launch_quant<128, 0, false>(mx, mo, p, wt, st);
   }
   if (rc) return rc;
-  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+  return launch_result("fl_quant_blocks: kernel launch");
 }

@@ -195,7 +195,7 @@ extern "C" int fl_dq_prescale(const float* stats_do, const float* stats_v, const
     return FL_ERR_BAD_ARG;
   dq_prescale_kernel<<<dim3(nt_q, b), 128, 0, (cudaStream_t)stream>>>(stats_do, stats_v, stats_k, h, h_kv, nt_q, nt_k,
                                                                       causal_local, unit, kernel_scale, post_scale);
-  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+  return launch_result("fl_dq_prescale: kernel launch");
 }
 
 // The accumulator layout follows the backward kernel that filled it: (b, h, d, s) for head_dim 128 (pipelined kernel,
@@ -213,13 +213,13 @@ extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, float mul
     int rc = make_acc_t_map_16(&macc, dq_acc, b, h, d, s);
     if (rc) return rc;
     const int sm = 32768 + 128 * 272 + 1024;
-    if (cudaFuncSetAttribute(dq_post_t128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sm) != cudaSuccess)
-      return FL_ERR_CUDA;
+    if (cudaError_t e = cudaFuncSetAttribute(dq_post_t128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); e != cudaSuccess)
+      return cuda_fail((int)e, "fl_dq_post: cudaFuncSetAttribute");
     dq_post_t128_kernel<<<grid, 128, sm, st>>>(macc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16);
   } else {
     dq_post_rows64_kernel<<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, out_f16);
   }
-  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+  return launch_result("fl_dq_post: kernel launch");
 }
 
 extern "C" int fl_pack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n_dst_rows, int32_t row_bytes,
@@ -230,7 +230,7 @@ extern "C" int fl_pack_rows(const void* src, void* dst, const int32_t* row_map, 
   const size_t n = (size_t)n_dst_rows * chunks;
   pack_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, row_map,
                                                                                   n_dst_rows, chunks);
-  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+  return launch_result("fl_pack_rows: kernel launch");
 }
 
 extern "C" int fl_unpack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n_src_rows, int32_t row_bytes,
@@ -241,5 +241,5 @@ extern "C" int fl_unpack_rows(const void* src, void* dst, const int32_t* row_map
   const size_t n = (size_t)n_src_rows * chunks;
   unpack_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst,
                                                                                     row_map, n_src_rows, chunks);
-  return cudaGetLastError() == cudaSuccess ? FL_OK : FL_ERR_CUDA;
+  return launch_result("fl_unpack_rows: kernel launch");
 }

@@ -37,8 +37,11 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
                         make_channel_major_copy=False, output_exponent_table=True, output_token_block_factors=True,
                         output_sf_atoms=False, also_make_nvfp4_copy=False, compute_d_with_output=None,
                         shifted_log2_lse_from=None, log2_lse_shift=0.0, d_multiplier=1.0, zero_accumulator=None,
-                        output_tile_stats=False, status=None, wait_cycles=0):
+                        output_tile_stats=False, status=None, wait_cycles=0, packed_slots=None):
     """Token-block MXFP8 quantiser of x (b, s, h, d) bf16 / f16 (s % 128 == 0, d in {64, 128}).
+    packed_slots = (slot_src, slot_rows, padded_rows): x is a packed (total, h, d) tensor of documents stored back to back
+    and the outputs are those of the 128-aligned buffer (1, padded_rows, h, d): slot_src[i] = first row of x of output
+    rows [128 i, 128 i + 128) (-1 = empty), slot_rows[i] = how many of them are real. Nothing is copied.
     Returns a dict: codes (b,s,h,d) float8_e4m3fn; e (b,h,s/32,d/32) uint8; fac (b,h,s/32) f32; optionally codes_t,
     sf_tok_raw, sf_dim_raw, token_factors, x4 / sf4_raw (NVFP4 copy), D, lse_log2, tile_stats.
     hadamard_rotation_scope: "all" (codes and NVFP4 copy of the rotated rows) | "nvfp4_copy" (only the NVFP4 copy)."""
@@ -46,11 +49,17 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
     if x.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError("x must be bf16 or f16")
     x = x.contiguous()
-    b, s, h, d = x.shape
+    a = L.QuantArgs()
+    if packed_slots is not None:
+        slot_src, slot_rows, padded_rows = packed_slots
+        assert x.dim() == 3 and padded_rows % 128 == 0 and slot_src.numel() == padded_rows // 128
+        (total, h, d), b, s = x.shape, 1, int(padded_rows)
+        a.slot_src, a.slot_rows, a.src_rows = L.ptr(slot_src), L.ptr(slot_rows), int(total)
+    else:
+        b, s, h, d = x.shape
     dev = x.device
     u8 = dict(dtype=torch.uint8, device=dev)
     out = {}
-    a = L.QuantArgs()
     a.x = L.ptr(x)
     a.b, a.s, a.h, a.d = b, s, h, d
     a.in_f16 = int(x.dtype == torch.float16)
@@ -85,7 +94,7 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
     keep = []
     if compute_d_with_output is not None:
         o = compute_d_with_output.contiguous()
-        assert o.shape == x.shape and o.dtype == x.dtype
+        assert tuple(o.shape) == (b, s, h, d) and o.dtype == x.dtype
         keep.append(o)
         a.o = L.ptr(o)
         out["D"] = torch.empty(b, h, s, dtype=torch.float32, device=dev)

@@ -54,6 +54,13 @@ typedef struct fl_quant_args {
   float d_multiplier;
   int32_t* status;      /* device int, 0 on entry, or NULL: a wait of the kernel's load pipeline that gave up writes a code */
   int64_t wait_cycles;  /* budget of one device-side wait in SM clocks; 0 = default (2^31) */
+  /* Packed source (documents stored back to back, b = 1): x is (src_rows, h, d) and the outputs are the 128-aligned buffer
+   * of s rows; slot_src[i] = first row of x that goes to rows [128 i, 128 i + 128) of the outputs (-1: the slot is
+   * empty), slot_rows[i] = how many of them are real (the others quantise as zeros). Replaces the row gather of
+   * flash_attn/cute/lp_docmaps.py (the quantisers read Q / K / V / dO through the row map). NULL = x has the outputs' rows. */
+  const int32_t* slot_src;
+  const int32_t* slot_rows;
+  int32_t src_rows;
 } fl_quant_args;
 
 int fl_quant_blocks(const fl_quant_args* args, void* stream);
@@ -176,6 +183,11 @@ int fl_selftest_mma(int32_t which, const uint8_t* a, const uint8_t* b, const uin
 
 /* Copies the device status word to the host (synchronises the stream). */
 int fl_read_status(const int32_t* status, int32_t* host_value, void* stream);
+
+/* Detail of the last FL_ERR_CUDA this host thread got from the library: writes "<failing call>: <CUDA error name and
+ * text>" into text (a host buffer of text_bytes bytes, may be null) and returns the CUDA error code (10000 + CUresult
+ * for a driver call, -1 where there is no code, 0 if no call has failed). No reference counterpart. */
+int fl_last_cuda_error(char* text, int32_t text_bytes);
 
 int fl_abi_version(void);
 

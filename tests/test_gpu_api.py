@@ -88,6 +88,8 @@ def test_fp8_packed_documents(aligned):
     if aligned:
         su = torch.tensor(lens, dtype=torch.int32, device="cuda")
         kw.update(seqused_q=su, seqused_k=su)
+    from flamia_blackwell_attention_b200 import api
+    api._REPACK_WARNED = False                   # the notice is given once per process: make this call the first
     with pytest.warns(UserWarning) if not aligned else _nullcontext():
         o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, **kw)
     for s0, n in zip(starts, lens):

