@@ -184,6 +184,9 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint8_t* sK4 = sOut64 + (D == 64 ? 2 * 16384 : 0);
   uint8_t* sQ4 = sK4 + 2 * 8192;
   uint8_t* sSF = sQ4 + 2 * 8192;
+  // d = 128, 8-bit route: a second way out for the gradient rows (2 x 16 KB), see the item epilogue
+  constexpr bool EPI2 = (D == 128) && !FP4;
+  uint8_t* sOut2 = sOut64;
   __shared__ __align__(8) uint64_t bars[BB_COUNT];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
@@ -459,6 +462,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t ds_row = smem_u32(sDS) + x * 8192 + r * 64;
     bool ok = true;
     int gi = 0, epi = 0;                             // iterations so far; uses of the epilogue barrier so far
+    int pending_kve = -1;                            // the K / V buffer whose gradient stores are still to be confirmed
     for (int k = 0; ok; ++k) {
       const int L = bwd_item(k, G, cta, p.zigzag);
       if (L >= p.n_items) break;
@@ -489,6 +493,11 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       for (int it = 0; it < n_it; ++it) {
         const int g = gi + it, st = g & 1, u = g >> 1;
         const int head = hkv * grp + it / n_m, m = m_lo + it % n_m;
+        if (it == 1 && pending_kve >= 0) {
+          // the previous item's gradient stores have long read their shared-memory source: its K / V buffer goes back
+          if (r == 0) { tma_store_wait_read<0>(); mbar_arrive(&bars[BB_KVE + pending_kve]); }
+          pending_kve = -1;
+        }
         const size_t bh_q = (size_t)T.bat * p.h + head;
         const int qb0 = (T.q0 + m * 128) / 32 + 2 * x;                     // first of the half's two 32-query blocks
         const float fq0 = TL ? 1.f : p.fac_q[bh_q * (p.s_q / 32) + qb0], fq1 = TL ? 1.f : p.fac_q[bh_q * (p.s_q / 32) + qb0 + 1];
@@ -547,15 +556,24 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int j4 = 0; j4 < 16; ++j4) {
             const float4 l4 = lds128(v_lse + 16 * j4);
             const float cc = c[j4 >> 3];
-            float4 c4 = make_float4(cc, cc, cc, cc);
             if (TL) {
               const float4 f4 = __ldg(fq_vec + j4);
-              c4 = make_float4(fk * f4.x, fk * f4.y, fk * f4.z, fk * f4.w);
+              const float4 c4 = make_float4(fk * f4.x, fk * f4.y, fk * f4.z, fk * f4.w);
+              pf[4 * j4 + 0] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 0]), c4.x, -l4.x));
+              pf[4 * j4 + 1] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 1]), c4.y, -l4.y));
+              pf[4 * j4 + 2] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 2]), c4.z, -l4.z));
+              pf[4 * j4 + 3] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 3]), c4.w, -l4.w));
+            } else {
+              // two columns per instruction: t = lse2 - s c, P' = 2^-t
+              const uint64_t nc2 = pack2(-cc, -cc);
+              float t0, t1, t2, t3;
+              unpack2(fma2(pack2(__uint_as_float(pv[4 * j4 + 0]), __uint_as_float(pv[4 * j4 + 1])), nc2, pack2(l4.x, l4.y)), t0, t1);
+              unpack2(fma2(pack2(__uint_as_float(pv[4 * j4 + 2]), __uint_as_float(pv[4 * j4 + 3])), nc2, pack2(l4.z, l4.w)), t2, t3);
+              pf[4 * j4 + 0] = ex2_neg(t0);
+              pf[4 * j4 + 1] = ex2_neg(t1);
+              pf[4 * j4 + 2] = ex2_neg(t2);
+              pf[4 * j4 + 3] = ex2_neg(t3);
             }
-            pf[4 * j4 + 0] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 0]), c4.x, -l4.x));
-            pf[4 * j4 + 1] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 1]), c4.y, -l4.y));
-            pf[4 * j4 + 2] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 2]), c4.z, -l4.z));
-            pf[4 * j4 + 3] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 3]), c4.w, -l4.w));
           }
         }
         if (!SC && !full) {      // diagonal / tail tiles only
@@ -631,13 +649,23 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
               b4 = make_float4(fv8 * f4.x, fv8 * f4.y, fv8 * f4.z, fv8 * f4.w);
               q4 = __ldg(fq_vec + qh * 8 + j4);
             }
-            pf[j + 0] *= fmaf(__uint_as_float(pv[j + 0]), b4.x, d4.x);
-            pf[j + 1] *= fmaf(__uint_as_float(pv[j + 1]), b4.y, d4.y);
-            pf[j + 2] *= fmaf(__uint_as_float(pv[j + 2]), b4.z, d4.z);
-            pf[j + 3] *= fmaf(__uint_as_float(pv[j + 3]), b4.w, d4.w);
-            // the dK side carries f_Q(query) when the operands are token-local
-            am = fmaxf(am, fmaxf(fmaxf(fabsf(pf[j] * q4.x), fabsf(pf[j + 1] * q4.y)),
-                                 fmaxf(fabsf(pf[j + 2] * q4.z), fabsf(pf[j + 3] * q4.w))));
+            if (TL) {
+              pf[j + 0] *= fmaf(__uint_as_float(pv[j + 0]), b4.x, d4.x);
+              pf[j + 1] *= fmaf(__uint_as_float(pv[j + 1]), b4.y, d4.y);
+              pf[j + 2] *= fmaf(__uint_as_float(pv[j + 2]), b4.z, d4.z);
+              pf[j + 3] *= fmaf(__uint_as_float(pv[j + 3]), b4.w, d4.w);
+              // the dK side carries f_Q(query) when the operands are token-local
+              am = fmaxf(am, fmaxf(fmaxf(fabsf(pf[j] * q4.x), fabsf(pf[j + 1] * q4.y)),
+                                   fmaxf(fabsf(pf[j + 2] * q4.z), fabsf(pf[j + 3] * q4.w))));
+            } else {
+              // two columns per instruction
+              const uint64_t b2 = pack2(b8[qh], b8[qh]);
+              const uint64_t u01 = fma2(pack2(__uint_as_float(pv[j + 0]), __uint_as_float(pv[j + 1])), b2, pack2(d4.x, d4.y));
+              const uint64_t u23 = fma2(pack2(__uint_as_float(pv[j + 2]), __uint_as_float(pv[j + 3])), b2, pack2(d4.z, d4.w));
+              unpack2(mul2(pack2(pf[j + 0], pf[j + 1]), u01), pf[j + 0], pf[j + 1]);
+              unpack2(mul2(pack2(pf[j + 2], pf[j + 3]), u23), pf[j + 2], pf[j + 3]);
+              am = fmax3_abs(fmax3_abs(am, pf[j], pf[j + 1]), pf[j + 2], pf[j + 3]);
+            }
           }
           const uint32_t wm = warp_max_u32(__float_as_uint(am));          // non-negative floats order as integers
           ebyte[qh] = exp448(wm);                                          // 448 * 2^(e-127) >= amax
@@ -666,7 +694,15 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
               const float4 f4 = __ldg(fq_vec + qh * 8 + w);
               q4 = make_float4(f4.x * inv, f4.y * inv, f4.z * inv, f4.w * inv);   // powers of two: exact, in range
             }
-            dsw[qh * 8 + w] = cvt_e4m3x4(pf[j0] * q4.x, pf[j0 + 1] * q4.y, pf[j0 + 2] * q4.z, pf[j0 + 3] * q4.w);
+            if (TL) {
+              dsw[qh * 8 + w] = cvt_e4m3x4(pf[j0] * q4.x, pf[j0 + 1] * q4.y, pf[j0 + 2] * q4.z, pf[j0 + 3] * q4.w);
+            } else {
+              const uint64_t inv2 = pack2(inv, inv);
+              float a0, a1, a2, a3;
+              unpack2(mul2(pack2(pf[j0], pf[j0 + 1]), inv2), a0, a1);
+              unpack2(mul2(pack2(pf[j0 + 2], pf[j0 + 3]), inv2), a2, a3);
+              dsw[qh * 8 + w] = cvt_e4m3x4(a0, a1, a2, a3);
+            }
           }
         }
         FL_TMEM_ST_16(t_sx + TO_DS, dsw);
@@ -732,55 +768,77 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       {
         const uint32_t t_acc = lane_base + (x == 0 ? TC_DV : TC_DK);
         const float mult = (x == 0) ? 0.00390625f : p.softmax_scale;       // dV carries 2^8 (P'), dK the softmax scale
-        float y[D];
+        const float mk = key_valid ? mult : 0.f;       // rows past the end of the document store zeros
+        uint32_t v[D];
         if (n_it > 0) {                  // (CTA-uniform: the tensor-memory loads are warp-collective)
-          uint32_t v[D];                 // all loads in flight, one wait
 #pragma unroll
-          for (int cc = 0; cc < D / 32; ++cc) FL_TMEM_LD_32(t_acc + 32 * cc, (v + 32 * cc));
+          for (int cc = 0; cc < D / 32; ++cc) FL_TMEM_LD_32(t_acc + 32 * cc, (v + 32 * cc));   // all loads in flight, one wait
           tc_wait_ld();
-          const float mk = key_valid ? mult : 0.f;     // rows past the end of the document store zeros
-#pragma unroll
-          for (int e = 0; e < D; ++e) y[e] = __uint_as_float(v[e]) * mk;
         } else {                         // no query tile saw this key tile
 #pragma unroll
-          for (int e = 0; e < D; ++e) y[e] = 0.f;
+          for (int e = 0; e < D; ++e) v[e] = 0;
         }
         // the accumulators are in registers: the next item's products may overwrite them
         tc_fence_before();
         mbar_arrive_warp(&bars[BB_ACCFREE]);
+        // pairs of neighbouring columns in one 64-bit register: every step below is one instruction per pair
+        uint64_t Y[D / 2];
         if (D == 128 && x == 1 && p.had_dk) {       // dK of rotated operands: (y H / sqrt(128)) * signs
 #pragma unroll
-          for (int hs = 1; hs < D; hs <<= 1) {
+          for (int i = 0; i < D / 2; ++i) {         // butterfly level 1: the two halves of a pair
+            const float a = __uint_as_float(v[2 * i]), b2 = __uint_as_float(v[2 * i + 1]);
+            Y[i] = pack2(a + b2, a - b2);
+          }
 #pragma unroll
-            for (int i = 0; i < D; ++i) {
+          for (int hs = 1; hs < D / 2; hs <<= 1) {  // levels 2 .. D / 2: whole pairs
+#pragma unroll
+            for (int i = 0; i < D / 2; ++i) {
               if ((i & hs) == 0) {
-                const float a = y[i], b2 = y[i + hs];
-                y[i] = a + b2;
-                y[i + hs] = a - b2;
+                const uint64_t a = Y[i], b2 = Y[i + hs];
+                Y[i] = add2(a, b2);
+                Y[i + hs] = sub2(a, b2);
               }
             }
           }
           constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
+          const float cp = 0.08838834764831845f * mk, cn = -cp;
 #pragma unroll
-          for (int i = 0; i < D; ++i) {
-            y[i] *= 0.08838834764831845f;
-            if ((NEG[i >> 5] >> (i & 31)) & 1) y[i] = -y[i];
+          for (int i = 0; i < D / 2; ++i) {
+            const bool n0 = (NEG[(2 * i) >> 5] >> ((2 * i) & 31)) & 1, n1 = (NEG[(2 * i + 1) >> 5] >> ((2 * i + 1) & 31)) & 1;
+            Y[i] = mul2(Y[i], pack2(n0 ? cn : cp, n1 ? cn : cp));
           }
+        } else {
+          const uint64_t mk2 = pack2(mk, mk);
+#pragma unroll
+          for (int i = 0; i < D / 2; ++i) Y[i] = mul2(pack2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), mk2);
         }
         // rows -> shared memory (boxes of 64 elements, 128 B swizzle) -> one TMA store per box: a thread's own row
-        // written straight to global memory costs 32 separate 128-byte lines per warp instruction. The way out at
-        // d = 128 is the finished item's K (warpgroup 0) / V (warpgroup 1) buffer: every product that read it has completed.
-        uint8_t* stage = (D == 128) ? ((x == 0 ? sK : sV) + kb * TILE_BYTES) : (sOut64 + x * 16384);
-        const uint32_t srow = smem_u32(stage) + r * 128;
+        // written straight to global memory costs 32 separate 128-byte lines per warp instruction. At d = 128 the first
+        // box goes through the finished item's K (warpgroup 0) / V (warpgroup 1) buffer: every product that read it has
+        // completed. The second box has a buffer of its own where shared memory allows (the 8-bit route), so that both
+        // stores are issued together and nobody waits for them here: the thread that issued them confirms that they have
+        // read their source, and only then hands the K / V buffer back to the producer, one query tile into the next item.
+        if (pending_kve >= 0) {          // (an item with fewer than two query tiles came in between)
+          if (r == 0) { tma_store_wait_read<0>(); mbar_arrive(&bars[BB_KVE + pending_kve]); }
+          pending_kve = -1;
+          mbar_arrive_warp(&bars[BB_EPI + x]);
+          if (!(ok = mbar_wait(&bars[BB_EPI + x], epi & 1, p.ctl, abortp, 38))) break;
+          ++epi;
+        }
+        uint8_t* stage0 = (D == 128) ? ((x == 0 ? sK : sV) + kb * TILE_BYTES) : (sOut64 + x * 16384);
+        uint8_t* stage1 = EPI2 ? (sOut2 + x * 16384) : stage0;
         const CUtensorMap* tm_out = (x == 0) ? &tm_dv : &tm_dk;
 #pragma unroll
         for (int pass = 0; pass < D / 64; ++pass) {
+          uint8_t* stage = pass == 0 ? stage0 : stage1;
+          const uint32_t srow = smem_u32(stage) + r * 128;
 #pragma unroll
           for (int c8 = 0; c8 < 8; ++c8) {
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float a = y[64 * pass + 8 * c8 + 2 * e], b2 = y[64 * pass + 8 * c8 + 2 * e + 1];
+              float a, b2;
+              unpack2(Y[32 * pass + 4 * c8 + e], a, b2);
               if (p.out_f16) {
                 __half2 hh = __floats2half2_rn(a, b2);
                 w[e] = *reinterpret_cast<uint32_t*>(&hh);
@@ -790,23 +848,30 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             sts128(srow + ((c8 ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
           }
+          const bool last = pass + 1 == D / 64;
+          if (EPI2 && !last) continue;                    // both boxes are announced together
           fence_proxy_async();
           mbar_arrive_warp(&bars[BB_EPI + x]);            // the warpgroup's four warps have written their rows
           if (!(ok = mbar_wait(&bars[BB_EPI + x], epi & 1, p.ctl, abortp, 38))) break;
           ++epi;
           if (r == 0 && T.nk > 0) {
+            if (EPI2) tma_store_4d(tm_out, stage0, 0, hkv, T.k0, T.bat);
             tma_store_4d(tm_out, stage, 64 * pass, hkv, T.k0, T.bat);
             tma_store_commit();
-            tma_store_wait_read<0>();    // the shared-memory source must outlive the copy; the writes complete with the grid
+            if (!last) tma_store_wait_read<0>();          // the one buffer is written again by the next pass
           }
-          mbar_arrive_warp(&bars[BB_EPI + x]);            // the buffer has been read: the next pass / the producer may take it
-          if (!(ok = mbar_wait(&bars[BB_EPI + x], epi & 1, p.ctl, abortp, 38))) break;
-          ++epi;
+          if (!last) {
+            mbar_arrive_warp(&bars[BB_EPI + x]);
+            if (!(ok = mbar_wait(&bars[BB_EPI + x], epi & 1, p.ctl, abortp, 38))) break;
+            ++epi;
+          }
         }
         if (!ok) break;
-        if (r == 0) mbar_arrive(&bars[BB_KVE + kb]);
+        pending_kve = kb;
       }
     }
+    // the shared-memory sources of the last stores must outlive the copies (the writes complete with the grid)
+    if (r == 0) tma_store_wait_read<0>();
   }
   if (abort_s) {
     for (int it = 0; it < 200; ++it) __nanosleep(1000);
@@ -880,7 +945,7 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.n_items = (int)n_items;
   p.zigzag = (p.causal && !a->doc_start) ? 1 : 0;
   const int grid = (int)(n_items < sm_count() ? n_items : sm_count());     // one persistent CTA per SM
-  const int smem = 8 * 128 * a->d + 2 * 8192 + 2 * 16384 + 2048 + (a->d == 64 ? 2 * 16384 : 0) + 1024 +
+  const int smem = 8 * 128 * a->d + 2 * 8192 + 2 * 16384 + 2048 + ((a->d == 64 || !fp4) ? 2 * 16384 : 0) + 1024 +
                    (fp4 ? 4 * 8192 + 4 * 1024 : 0);
   auto launch = [&](auto kern) -> int {
     if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); e != cudaSuccess)

@@ -50,19 +50,9 @@ struct QuantParams {
 __device__ __forceinline__ float flush_sub(float v) { return fabsf(v) < 1.17549435e-38f ? v * 0.0f : v; }
 // packed pairs: a + b, a - b, and a * b with subnormal inputs and results flushed to zero (the product and its flush in
 // one instruction); each half rounds exactly as the scalar instruction does
-__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
 __device__ __forceinline__ uint64_t mul2_ftz(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("mul.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
 __device__ __forceinline__ uint4 lds_u4(uint32_t addr) {

@@ -333,6 +333,18 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+// max(a, |b|, |c|)
+__device__ __forceinline__ float fmax3_abs(float a, float b, float c) {
+  float d;
+  asm("{\n\t.reg .f32 x, y;\n\tabs.f32 x, %2;\n\tabs.f32 y, %3;\n\tmax.f32 %0, %1, x, y;\n\t}" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^(-x)
+__device__ __forceinline__ float ex2_neg(float x) {
+  float y;
+  asm("{\n\t.reg .f32 t;\n\tneg.f32 t, %1;\n\tex2.approx.ftz.f32 %0, t;\n\t}" : "=f"(y) : "f"(x));
+  return y;
+}
 // Packed pairs of floats in one 64-bit register (fma / add .f32x2: one issue slot for two elements).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   uint64_t r;
@@ -350,6 +362,16 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
 // 2^x for two arguments on the FMA pipe instead of the transcendental unit (one warp instruction per 8 clocks and
