@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libflamia_b200.so")
 
 # status codes (csrc/sm100.cuh)
-ABI_VERSION = 3
+ABI_VERSION = 4
 FL_OK, FL_ERR_BAD_ARG, FL_ERR_CUDA, FL_ERR_UNSUPPORTED, FL_ERR_TOO_LARGE = 0, 1, 2, 3, 4
 FL_DEV_WAIT_TIMEOUT = 0x100
 FL_DEV_BAD_TABLE = 0x200
@@ -39,7 +39,7 @@ class AttnArgs(C.Structure):
                                   "dv", "doc_start", "doc_len")] + \
                [(n, i32) for n in ("n_docs", "b", "s_q", "s_k", "h", "h_kv", "d")] + [("softmax_scale", f32)] + \
                [(n, i32) for n in ("mode", "flags")] + [("status", vp), ("wait_cycles", i64)] + \
-               [(n, i32) for n in ("window_left_p1", "window_right_p1")] + [("seqused_k", vp), ("softcap", f32)]
+               [(n, i32) for n in ("window_left_p1", "window_right_p1")] + [("seqused_k", vp), ("softcap", f32), ("dq_order", vp)]
 
 
 EXPORTS = {

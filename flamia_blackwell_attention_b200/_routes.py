@@ -275,6 +275,8 @@ def backward(plan, state, dout, docs_meta):
                            mode=L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8, had_dk=had8, status=status,
                            token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all", window=f.window, seqused_k=seqused_k,
                            softcap=f.softcap,
+                           dq_order=torch.zeros(b, h, s_q // 128, 2, dtype=torch.int32, device=out.device)
+                           if bw.deterministic else None,
                            doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype)
     _note_status(status)

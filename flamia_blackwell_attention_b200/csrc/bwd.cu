@@ -60,6 +60,7 @@ struct BwdParams {
   const int32_t* doc_start;
   const int32_t* doc_len;
   const int32_t* seqused_k;   // batched form: valid keys per batch row, or null
+  int32_t* dq_order;     // deterministic dQ: (b, h, s_q / 128, 2) counters, zero on entry, or null
   int n_docs;
   int b, s_q, s_k, h, h_kv;
   float scale_log2;
@@ -159,7 +160,27 @@ __device__ __forceinline__ void bwd_decode(const BwdParams& p, int L, BTile& t) 
   t.n_m = (t.nv > 0 && m_hi > m_lo) ? (m_hi - m_lo) : 0;
 }
 
-template <int D, bool FP4, int VAR, bool SC>
+// Deterministic dQ: how many key tiles before this one also see query tile m of the document (they add their partial sums
+// first). The key tiles that see a query tile are a contiguous range; without a left window it starts at key tile 0.
+__device__ __forceinline__ int bwd_order_rank(const BwdParams& p, const BTile& t, int m) {
+  const int kt = t.krel / 128;
+  if (p.win_l < 0) return kt;
+  // first key tile whose last query tile is not below m (key tiles are full except the document's last one)
+  int klo = 0;
+  while (klo < kt && max(0, klo * 128 + 127 - t.off + p.win_l) / 128 < m) ++klo;
+  return kt - klo;
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* ptr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.b32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int32_t* ptr, int v) {
+  asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+
+// DET: deterministic dQ order (a template flag, so that the arrival-order kernels carry none of it)
+template <int D, bool FP4, int VAR, bool SC, bool DET = false>
 __global__ void __launch_bounds__(512, 1)
 bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -442,11 +463,47 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         fence_proxy_async();
         mbar_arrive_warp(&bars[BB_R2]);
         if (!(ok = mbar_wait(&bars[BB_R2], gt & 1, p.ctl, abortp, 42))) break;
-        if (tid == 256) {
-          if (D == 128) tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, T.q0 + m * 128 + 64 * y, 0, head, T.bat);
-          else tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, 0, T.q0 + m * 128 + 64 * y, head, T.bat);
-          tma_store_commit();
+        if (!DET) {
+          if (tid == 256) {
+            if (D == 128) tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, T.q0 + m * 128 + 64 * y, 0, head, T.bat);
+            else tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, 0, T.q0 + m * 128 + 64 * y, head, T.bat);
+            tma_store_commit();
+          }
+        } else if (warp == 8) {                 // (the whole warp stays converged: lane 0 works, the others follow its verdict)
+          int go = 1;
+          int32_t* order = nullptr;
+          int rank = 0;
+          if (DET) {
+            // deterministic order: the key tiles before this one have added their partial sums of this half
+            order = p.dq_order + ((((size_t)T.bat * p.h + head) * (p.s_q / 128) + T.q0 / 128 + m) * 2 + y);
+            rank = bwd_order_rank(p, T, m);
+            if (lane == 0) {
+              const long long t_start = clock64();
+              while (ld_acquire_gpu(order) != rank) {
+                if (*abortp || clock64() - t_start > p.ctl.wait_cycles) {
+                  if (p.ctl.status) atomicCAS(p.ctl.status, 0, FL_DEV_WAIT_TIMEOUT | 44);
+                  *abortp = 1;
+                  go = 0;
+                  break;
+                }
+              }
+            }
+            go = __shfl_sync(0xFFFFFFFFu, go, 0);
+          }
+          if (go && lane == 0) {
+            if (D == 128) tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, T.q0 + m * 128 + 64 * y, 0, head, T.bat);
+            else tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, 0, T.q0 + m * 128 + 64 * y, head, T.bat);
+            tma_store_commit();
+            if (order) {
+              tma_store_wait<0>();                // the addition has completed, not only read its source
+              __threadfence();
+              st_release_gpu(order, rank + 1);
+            }
+          }
+          __syncwarp();
+          if (!go) ok = false;           // the other warps of the group see the flag at their next wait
         }
+        if (!ok) break;
       }
       gi += n_it;
     }
@@ -923,6 +980,7 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;
   p.seqused_k = a->seqused_k;
+  p.dq_order = a->dq_order;
   p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
@@ -953,7 +1011,12 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
     kern<<<grid, 512, smem, (cudaStream_t)stream>>>(mq, mk, mv, mdo, macc, mq4, mk4, mdk, mdv, p);
     return FL_OK;
   };
-  if (sc) {
+  const bool det = a->dq_order != nullptr;
+  if (det && (sc || rl || tl)) return FL_ERR_UNSUPPORTED;     // ordered dQ: the default dS-hat route only
+  if (det) {
+    if (a->d == 64) rc = launch(bwd_kernel_pipelined<64, false, 0, false, true>);
+    else rc = fp4 ? launch(bwd_kernel_pipelined<128, true, 0, false, true>) : launch(bwd_kernel_pipelined<128, false, 0, false, true>);
+  } else if (sc) {
     if (a->d == 64) rc = launch(bwd_kernel_pipelined<64, false, 0, true>);
     else rc = fp4 ? launch(bwd_kernel_pipelined<128, true, 0, true>) : launch(bwd_kernel_pipelined<128, false, 0, true>);
   } else if (a->d == 64) {

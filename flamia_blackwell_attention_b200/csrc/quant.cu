@@ -78,7 +78,8 @@ __device__ __forceinline__ float e4m3_byte_to_f32(uint32_t c) {
 }
 
 // MODE bits: 1 = the E4M3 codes are of the rotated rows, 2 = also write the NVFP4 copy, 4 = rotate only the NVFP4 copy
-template <int D, int MODE, bool PRO>
+// PK: packed source (slot tables); a template flag, so that the batched form pays nothing for it
+template <int D, int MODE, bool PRO, bool PK>
 __global__ void __launch_bounds__(QTHREADS, PRO ? 1 : 2)
 quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_o,
                     const QuantParams p) {
@@ -110,7 +111,7 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     uint8_t* dst = smem + st * STAGE_B;
     // packed source (documents stored back to back): the slot's rows start at an arbitrary row of the (1, total, h, d)
     // tensor; only the innermost TMA coordinate has an alignment rule. An empty slot loads nothing of x.
-    const int xrow = p.slot_src ? p.slot_src[tile] : tile * QT;
+    const int xrow = PK ? p.slot_src[tile] : tile * QT;
     mbar_arrive_expect_tx(&full[st], (xrow >= 0 ? TILE_B : 0) + (PRO ? TILE_B : 0));
     if (xrow >= 0) {
       tma_load_4d(dst, &tm_x, &full[st], 0, head, xrow, bat);
@@ -150,7 +151,7 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   // whatever was there) read as zero
   auto lds_chunk_x = [&](uint32_t tile_addr, int j) -> uint4 {
     uint4 v = lds_chunk(tile_addr, j);
-    if (!row_live) v = make_uint4(0, 0, 0, 0);
+    if (PK && !row_live) v = make_uint4(0, 0, 0, 0);
     return v;
   };
   auto to_f32 = [&](const uint4& v, float* dst) {      // 8 elements of one chunk
@@ -239,7 +240,7 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const size_t ri = bh * p.s + t0 + r;
     const uint32_t tile_addr = smem_u32(smem + st * STAGE_B);
     bool ok = mbar_wait(&full[st], (it / QSTAGES) & 1, p.ctl, abortp, 50);
-    if (p.slot_rows) row_live = r < p.slot_rows[tile];
+    if (PK) row_live = r < p.slot_rows[tile];
 
     if (p.zero_acc) {   // this tile's share of the accumulator: 128 * D f16 = 32 D 16-byte chunks, contiguous
       uint4* z = reinterpret_cast<uint4*>(p.zero_acc + (bh * p.s + t0) * D);
@@ -464,17 +465,23 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   }
 }
 
-template <int D, int MODE, bool PRO>
-static int launch_quant(const CUtensorMap& mx, const CUtensorMap& mo, const QuantParams& p, bool want_t, cudaStream_t st) {
+template <int D, int MODE, bool PRO, bool PK>
+static int launch_quant_pk(const CUtensorMap& mx, const CUtensorMap& mo, const QuantParams& p, bool want_t, cudaStream_t st) {
   constexpr int TILE_B = QT * D * 2;
   const int smem = QSTAGES * (PRO ? 2 : 1) * TILE_B + 1024 + (want_t ? QT * (D + 16) : 0);
-  auto kern = quant_blocks_kernel<D, MODE, PRO>;
+  auto kern = quant_blocks_kernel<D, MODE, PRO, PK>;
   if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); e != cudaSuccess)
       return cuda_fail((int)e, "fl_quant_blocks: cudaFuncSetAttribute");
   const int per_sm = (PRO || want_t) ? 1 : 2;
   const int grid = min(p.n_tiles, sm_count() * per_sm);
   kern<<<grid, QTHREADS, smem, st>>>(mx, mo, p);
   return FL_OK;
+}
+
+template <int D, int MODE, bool PRO>
+static int launch_quant(const CUtensorMap& mx, const CUtensorMap& mo, const QuantParams& p, bool want_t, cudaStream_t st) {
+  return p.slot_src ? launch_quant_pk<D, MODE, PRO, true>(mx, mo, p, want_t, st)
+                    : launch_quant_pk<D, MODE, PRO, false>(mx, mo, p, want_t, st);
 }
 
 }  // namespace fl

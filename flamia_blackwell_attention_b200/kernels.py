@@ -211,10 +211,11 @@ def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torc
 
 def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax_scale, out_dtype=torch.bfloat16,
              mode=L.FL_MODE_FP8, had_dk=False, status=None, doc_start=None, doc_len=None, wait_cycles=0,
-             token_local=False, dq_rowlocal=False, window=None, seqused_k=None, softcap=0.0):
+             token_local=False, dq_rowlocal=False, window=None, seqused_k=None, softcap=0.0, dq_order=None):
     """Backward main kernel on quantised operands. q / k / v / do: quantiser outputs (codes, fac). Adds the pre-scaled
     dQ partials into the f16 accumulator dq_acc of b * h * s_q * d elements ((b, h, d, s_q) at d = 128, (b, h, s_q, d)
-    at d = 64) and returns (dk, dv, status), each (b, s_k, h_kv, d)."""
+    at d = 64) and returns (dk, dv, status), each (b, s_k, h_kv, d). dq_order: a zeroed (b, h, s_q / 128, 2) int32 table
+    makes the key tiles add their partial sums in ascending key order (bitwise reproducible dQ)."""
     kc = k["codes"]
     b, s_k, h_kv, d = kc.shape
     dev = kc.device
@@ -230,6 +231,9 @@ def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax
     a.do_codes, a.fac_do = L.ptr(do["codes"]), L.ptr(do["token_factors" if token_local else "fac"])
     a.lse_log2, a.d_rows, a.dq_acc, a.dq_scale = L.ptr(lse_log2), L.ptr(d_rows), L.ptr(dq_acc), L.ptr(dq_scale)
     a.dk, a.dv = L.ptr(dk), L.ptr(dv)
+    if dq_order is not None:
+        assert dq_order.dtype == torch.int32 and dq_order.numel() == b * q["codes"].shape[2] * (q["codes"].shape[1] // 128) * 2
+        a.dq_order = L.ptr(dq_order)
     L.check(L.load().fl_bwd(C.byref(a), _stream()), "fl_bwd")
     return dk, dv, status
 

@@ -182,8 +182,11 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
             _fail("B9", ValueError, f"flash_attn_{entry}: seqused_k is an int32 tensor of shape (batch,); got "
                                     f"{tuple(seqused_k.shape)} {seqused_k.dtype}")
     if deterministic:
-        _fail("B5", NotImplementedError, "deterministic=True (ordered dQ reduction) is not built: the f16 dQ partials "
-                                         "are reduce-added in arrival order")
+        if (softcap or 0.0) > 0.0 or scaling_request(o) == "token_local" or o.ds_dq_rowlocal == "all":
+            _fail("B5", NotImplementedError, "deterministic=True (ordered dQ reduction) is built on the default backward "
+                                             "only: without softcap, operand_scaling='token_local' or "
+                                             "ds_dq_rowlocal='all'")
+        log("deterministic", "ordered", "the key tiles add their f16 dQ partial sums in ascending key order (bounded waits)")
     # ---- dS
     if o.ds_scaling == "per_tensor":
         _fail(33, ValueError, f"ds_scaling='per_tensor' was removed from flash_attn_{entry}: sizing a per-tensor dS needs "
@@ -257,15 +260,16 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
 
 
 def _finish(entry, route, qk_format, shape, log_rows, opts, *, softmax_scale, causal, return_lse, had, scaling, rowlocal,
-            ragged, dq_causal, window_size=(None, None), p_frame="row", seqused_k=False, softcap=0.0):
+            ragged, dq_causal, window_size=(None, None), p_frame="row", seqused_k=False, softcap=0.0,
+            deterministic=False):
     sc = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(shape.d)
     # sliding window (left, right): None / -1 = unlimited on that side; causal caps the right side at 0 in the kernels
     win = tuple(None if (w is None or w < 0) else int(w) for w in tuple(window_size))
     fwd = FwdSpec("fwd_sm100", qk_format, "e4m3", scaling, p_frame, "exp2", had, bool(causal), shape.varlen,
                   shape.aligned_varlen, ragged, bool(return_lse), None if win == (None, None) else win,
                   softcap=float(softcap or 0.0), seqused_k=bool(seqused_k))
-    bwd = BwdSpec("1cta" if shape.requires_grad else "none", scaling, "block_32x32", rowlocal, "row", "e4m3", False,
-                  "causal_tile" if dq_causal else "row")
+    bwd = BwdSpec("1cta" if shape.requires_grad else "none", scaling, "block_32x32", rowlocal, "row", "e4m3",
+                  bool(deterministic), "causal_tile" if dq_causal else "row")
     return AttnPlan(entry, route, sc, shape, fwd, bwd, opts.tuning, False, False, tuple(log_rows), opts)
 
 
@@ -312,7 +316,8 @@ def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     return _finish("fp8", "fp8", "e4m3", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
                    return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=dq_causal,
                    window_size=window_size, p_frame=p_frame,
-                   seqused_k=seqused_k is not None and not shape.aligned_varlen, softcap=softcap)
+                   seqused_k=seqused_k is not None and not shape.aligned_varlen, softcap=softcap,
+                   deterministic=deterministic)
 
 
 def _p_frame(entry, o, shape, scaling, default):
@@ -389,4 +394,5 @@ def resolve_fp4(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     return _finish("fp4", "fp4.e4m3_pv", "nvfp4", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
                    return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=False,
                    window_size=window_size, p_frame=p_frame,
-                   seqused_k=seqused_k is not None and not shape.aligned_varlen, softcap=softcap)
+                   seqused_k=seqused_k is not None and not shape.aligned_varlen, softcap=softcap,
+                   deterministic=deterministic)

@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define FL_ABI_VERSION 3
+#define FL_ABI_VERSION 4
 
 /* fl_quant_args.flags */
 #define FL_Q_HADAMARD 1            /* rotate rows by diag(signs) H_128 / sqrt(128) before quantising (d = 128) */
@@ -122,6 +122,13 @@ typedef struct fl_attn_args {
    * the factor 1 - tanh^2 (the reference's softcap, flash_attn/cute/utils.py:167-187); 0 = off. Default P-hat route only
    * (no token-local / row-local variants). */
   float softcap;
+  /* Backward, deterministic dQ (the reference's deterministic=True: semaphore-ordered dQ reduction,
+   * flash_attn/cute/flash_bwd_sm100_fp4.py:4119-4215): (b, h, s_q/128, 2) int32, ZERO on entry, or NULL = the partial
+   * sums are added in arrival order. With the table, the key tiles that see a query tile add their f16 partial sums in
+   * ascending key order: each waits (bounded by wait_cycles; status 0x100 | 44 when it gives up) until the table entry of
+   * its (head, query tile, 64-query half) has counted the key tiles before it, adds, waits for the addition to complete
+   * and counts itself. dQ is then bitwise reproducible from call to call; the other outputs always are. */
+  int32_t* dq_order;
 } fl_attn_args;
 
 /* Forward: O = softmax(scale Q K^T + mask) V, LSE.

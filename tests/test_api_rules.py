@@ -72,10 +72,10 @@ RULES = [
     ("rB1", R4, dict(pv_precision="fp4", causal=True), {}, NotImplementedError, "B1", "pv_precision='fp4'"),
     ("rB2", R8, dict(options=O8(tuning=KernelTuning(bwd_fp4_ld_rep=64))), {}, ValueError, "B2", "KernelTuning"),
     ("r28w", R8, dict(window_size=(-5, 0)), {}, ValueError, 28, "window_size entries"),
+    ("rB5", R8, dict(deterministic=True, softcap=30.0), {}, NotImplementedError, "B5", "deterministic=True"),
     ("rB4b", R8, dict(softcap=30.0, options=O8(ds_dq_rowlocal="all")), {}, NotImplementedError, "B4", "softcap"),
     ("rB4c", R8, dict(seqused_k=_I32(2), options=O8(operand_scaling="token_local", ds_dq_rowlocal="all")), {},
      NotImplementedError, "B4", "batched seqused_k"),
-    ("rB5", R8, dict(deterministic=True), {}, NotImplementedError, "B5", "deterministic=True"),
     ("rB6", R8, dict(options=O8(ds_scaling="row_local")), {}, NotImplementedError, "B6", "ds_scaling='row_local'"),
     ("rB6b", R8, dict(options=O8(p_hat_frame="group", operand_scaling="token_local", ds_dq_rowlocal="all")), {},
      NotImplementedError, "B6", "p_hat_frame='group'"),

@@ -12,6 +12,7 @@
 The last three follow the reference's tests/cute/test_lowprec_api.py:831-883, :977-1000 and
 tests/cute/test_lowprec_causal_safe_v.py.
 """
+import math
 import threading
 import warnings
 
@@ -230,6 +231,58 @@ def _raw_quant_args(x):
     a.x, a.codes, a.e_tab, a.fac = L.ptr(x), L.ptr(codes), L.ptr(e), L.ptr(fac)
     a.b, a.s, a.h, a.d = b, s, h, d
     return C.byref(a), (codes, e, fac, a)
+
+
+@pytest.mark.parametrize("route,kw", [("fp8", dict(causal=True)), ("fp4", dict(causal=True)),
+                                      ("fp8", dict(causal=False)), ("fp8", dict(causal=True, window_size=(300, 0)))])
+def test_deterministic_dq_is_bitwise_reproducible(route, kw):
+    """deterministic=True: the key tiles add their partial sums in ascending key order, so dQ is the same bits from call to
+    call (the reference's deterministic mode, flash_attn/cute/flash_bwd_sm100_fp4.py:4119-4215), and it agrees with the
+    arrival-order result to f16 rounding."""
+    import flamia_blackwell_attention_b200 as F
+    fn = F.flash_attn_fp8 if route == "fp8" else F.flash_attn_fp4
+    q, k, v, g = (t.cuda() for t in attention_inputs(2, 1536, 4, 2, 128, seed=91))
+    runs = [_eager(fn, q, k, v, g, deterministic=True, **kw) for _ in range(3)]
+    for r in runs[1:]:
+        for a, b in zip(runs[0], r):
+            assert torch.equal(a, b)
+    loose = _eager(fn, q, k, v, g, **kw)
+    assert torch.equal(loose[3], runs[0][3]) and torch.equal(loose[4], runs[0][4])      # dK, dV do not depend on it
+    assert _cos(loose[2], runs[0][2]) > 0.99999
+    assert F.check_status() == 0
+
+
+def test_deterministic_order_wait_is_bounded():
+    """An order table that never reaches a key tile's turn (here: pre-filled with a value no tile counts to): the wait
+    gives up after its budget, the status word names the site, and the context stays usable."""
+    from flamia_blackwell_attention_b200 import kernels as K
+    b, s, h, d = 1, 256, 2, 128
+    sc = 1.0 / math.sqrt(d)
+    q, k, v, g = (t.cuda() for t in attention_inputs(b, s, h, h, d, seed=92))
+    qq = K.quantize_fp8_blocks(q)
+    kq = K.quantize_fp8_blocks(k, output_tile_stats=True)
+    vq = K.quantize_fp8_blocks(v, output_tile_stats=True)
+    out, lse, st = K.attn_fwd(qq, kq, vq, causal=True, softmax_scale=sc)
+    acc = torch.empty(b, h, s, d, dtype=torch.float16, device="cuda")
+    gq = K.quantize_fp8_blocks(g, compute_d_with_output=out, shifted_log2_lse_from=lse, log2_lse_shift=8.0,
+                               d_multiplier=-2.0 ** -8, zero_accumulator=acc, output_tile_stats=True)
+    ks, _ps = K.dq_prescale(gq["tile_stats"], vq["tile_stats"], kq["tile_stats"])
+    order = torch.full((b, h, s // 128, 2), 1000, dtype=torch.int32, device="cuda")
+    st2 = K.new_status(q.device)
+    K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks, causal=True,
+               softmax_scale=sc, status=st2, wait_cycles=2_000_000, dq_order=order)
+    torch.cuda.synchronize()
+    code = K.read_status(st2)
+    assert code & 0x100 and (code & 0xFF) in (44, 40, 41, 42, 22, 23, 24, 31, 32, 33, 36, 21, 10, 11), hex(code)
+    # the same call with a zeroed table runs to the end
+    order.zero_()
+    st3 = K.new_status(q.device)
+    acc.zero_()
+    K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks, causal=True,
+               softmax_scale=sc, status=st3, dq_order=order)
+    torch.cuda.synchronize()
+    assert K.read_status(st3) == 0
+    assert order.view(-1, 2)[:, 0].tolist() == [1, 2, 1, 2]          # (head, query tile): key tiles that see it
 
 
 @pytest.mark.parametrize("route", ["fp8", "fp4"])
