@@ -239,7 +239,8 @@ def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax
 
 
 def attn_bwd_static_acc(q, k, v, do, *, lse_log2, d_rows, dq_scale, post_scale, mult, causal, softmax_scale,
-                        out_dtype=torch.bfloat16, had_dk=False, had_dq=False, status=None, wait_cycles=0):
+                        out_dtype=torch.bfloat16, had_dk=False, had_dq=False, status=None, wait_cycles=0,
+                        mode=L.FL_MODE_FP8):
     """fl_bwd_static_acc: backward main kernel + dQ postprocess with the f16 accumulator held in the library's fixed
     device array (nothing is allocated inside the call; b * h * s_q * d is limited to FL_STATIC_ACC_MAX_ELEMS and a
     larger problem raises). Returns (dq, dk, dv, status). Calls on one device must not overlap in time."""
@@ -254,7 +255,7 @@ def attn_bwd_static_acc(q, k, v, do, *, lse_log2, d_rows, dq_scale, post_scale, 
     dv = torch.empty(b, s_k, h_kv, d, dtype=out_dtype, device=dev)
     flags = (L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0) | (L.FL_A_HAD_DK if had_dk else 0) | \
         (L.FL_A_HAD_DQ if had_dq else 0)
-    a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=L.FL_MODE_FP8, flags=flags, status=status,
+    a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode, flags=flags, status=status,
                   wait_cycles=wait_cycles)
     a.do_codes, a.fac_do = L.ptr(do["codes"]), L.ptr(do["fac"])
     a.lse_log2, a.d_rows, a.dq_scale = L.ptr(lse_log2), L.ptr(d_rows), L.ptr(dq_scale)
