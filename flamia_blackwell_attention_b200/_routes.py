@@ -171,8 +171,8 @@ def state_spec(plan, n_docs=0, dtype=torch.bfloat16, capacity=None):
     spec = [((b, s_q, h, d), dtype), ((b, h, s_q), f32),                                       # O, LSE of the kernels
             ((b, s_q, h, d), f8), ((b, h, s_q // 32), f32), ((b, s_k, hk, d), f8), ((b, hk, s_k // 32), f32),
             ((b, s_k, hk, d), f8), ((b, hk, s_k // 32), f32), ((1,), i32)]                     # codes, factors, status
-    if need_bwd:
-        spec += [((b, hk, s_k // 128, 2), f32)] * 2
+    if need_bwd:      # K / V statistics of the f16 dQ pre-scale: per 128-row tile and head, or per token
+        spec += [((b, s_k), f32)] * 2 if plan.bwd.dq_prescale == "causal_row" else [((b, hk, s_k // 128, 2), f32)] * 2
     if fp4:
         spec += [((b, s_q, h, d // 2), u8), ((b, h, s_q // 128, d // 64, 32, 4, 4), u8),
                  ((b, s_k, hk, d // 2), u8), ((b, hk, s_k // 128, d // 64, 32, 4, 4), u8)]
@@ -208,16 +208,23 @@ def forward(plan, q, k, v, docs, seqused_k=None):
     qk_kw = dict(apply_hadamard_rotation=f.qk_hadamard, hadamard_rotation_scope="nvfp4_copy" if fp4 else "all",
                  also_make_nvfp4_copy=fp4, token_local_exponents=tl, packed_slots=slots)
     status = K.new_status(q.device)
+    rows = need_bwd and plan.bwd.dq_prescale == "causal_row"      # per-token K / V statistics instead of per-tile ones
+    k_rows = v_rows = None
+    if rows:
+        k_rows, v_rows = torch.zeros(2, sh.b, sh.s_k, dtype=torch.float32, device=q.device).unbind(0)
     qq = K.quantize_fp8_blocks(qp, status=status, **qk_kw)
-    kq = K.quantize_fp8_blocks(kp, output_tile_stats=need_bwd, status=status, **qk_kw)
-    vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd, token_local_exponents=tl, status=status, packed_slots=slots)
+    # max |K_j| of the codes' values; where those are rotated, the rotation-invariant 2-norm bounds it
+    kq = K.quantize_fp8_blocks(kp, output_tile_stats=need_bwd and not rows, status=status,
+                               row_stat=("norm2" if (f.qk_hadamard and not fp4) else "amax", k_rows) if rows else None, **qk_kw)
+    vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd and not rows, token_local_exponents=tl, status=status,
+                               packed_slots=slots, row_stat=("sumsq", v_rows) if rows else None)
     out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=q.dtype, mode=mode,
                              status=status, token_local=tl, window=f.window, p_group=f.p_hat_frame == "group",
                              seqused_k=seqused_k, softcap=f.softcap,
                              doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     state = [out, lse, qq["codes"], qq["fac"], kq["codes"], kq["fac"], vq["codes"], vq["fac"], status]
     if need_bwd:
-        state += [kq["tile_stats"], vq["tile_stats"]]
+        state += [k_rows, v_rows] if rows else [kq["tile_stats"], vq["tile_stats"]]
     if fp4:
         state += [qq["x4"], qq["sf4_raw"], kq["x4"], kq["sf4_raw"]]
     if tl:
@@ -264,13 +271,20 @@ def backward(plan, state, dout, docs_meta):
         gp = dout.contiguous()
     b, s_q, h, d = out.shape
     acc = torch.empty(b, h, s_q, d, dtype=torch.float16, device=out.device)
+    rows = bw.dq_prescale == "causal_row"
+    do_rows = torch.zeros(b, s_q, dtype=torch.float32, device=out.device) if rows else None
     gq = K.quantize_fp8_blocks(gp, compute_d_with_output=out, shifted_log2_lse_from=lse, log2_lse_shift=P_SHIFT_LOG2,
-                               d_multiplier=float(backward_scalars(plan.softmax_scale)[6]), zero_accumulator=acc, output_tile_stats=True,
-                               token_local_exponents=tl, status=status,
-                               packed_slots=None if docs is None else docs.slots())
-    ks, ps = K.dq_prescale(gq["tile_stats"], vstats, kstats, causal_local=bw.dq_prescale == "causal_tile")
+                               d_multiplier=float(backward_scalars(plan.softmax_scale)[6]), zero_accumulator=acc,
+                               output_tile_stats=not rows, token_local_exponents=tl, status=status,
+                               packed_slots=None if docs is None else docs.slots(),
+                               row_stat=("sumsq", do_rows) if rows else None)
+    if rows:      # kstats / vstats are the per-token tables here; the prefix maxima go into copies (the state is read-only)
+        ks, ps = K.dq_prescale_rows(do_rows, vstats.clone(), kstats.clone())
+    else:
+        ks, ps = K.dq_prescale(gq["tile_stats"], vstats, kstats, causal_local=bw.dq_prescale == "causal_tile")
     had8 = f.qk_hadamard and not fp4           # only the 8-bit route's E4M3 codes are rotated
-    dk, dv, _ = K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc, dq_scale=ks,
+    dk, dv, _ = K.attn_bwd(qq, kq, vq, gq, lse_log2=gq["lse_log2"], d_rows=gq["D"], dq_acc=acc,
+                           dq_scale=None if rows else ks, dq_scale_rows=ks if rows else None,
                            causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=out.dtype,
                            mode=L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8, had_dk=had8, status=status,
                            token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all", window=f.window, seqused_k=seqused_k,
@@ -278,7 +292,7 @@ def backward(plan, state, dout, docs_meta):
                            dq_order=torch.zeros(b, h, s_q // 128, 2, dtype=torch.int32, device=out.device)
                            if bw.deterministic else None,
                            doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
-    dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype)
+    dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype, per_row=rows)
     _note_status(status)
     if docs is not None:
         tq = sh.tot_q if sh.varlen else sh.b * sh.s_q

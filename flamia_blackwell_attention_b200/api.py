@@ -48,7 +48,7 @@ class _CallFacts:
     """Hashable description of one call: everything a plan depends on and nothing else."""
     entry: str
     grad_mode: bool
-    dq_causal_prescale: bool
+    dq_causal_prescale: Tuple[bool, str]      # the module switches the resolver reads: (on, granularity)
     q: _TensorFacts
     k: _TensorFacts
     v: _TensorFacts
@@ -70,7 +70,8 @@ def _cached_plan(resolve, q, k, v, kw) -> AttnPlan:
     entry = "fp8" if resolve is resolve_fp8 else "fp4"
     if not all(isinstance(t, torch.Tensor) for t in (q, k, v)):
         return resolve(q, k, v, **kw)           # the resolver words the refusal
-    facts = _CallFacts(entry, torch.is_grad_enabled(), bool(interface_bwd_fp4.DQ_CAUSAL_PRESCALE), _TensorFacts.of(q),
+    facts = _CallFacts(entry, torch.is_grad_enabled(),
+                       (bool(interface_bwd_fp4.DQ_CAUSAL_PRESCALE), str(interface_bwd_fp4.DQ_CAUSAL_GRANULARITY)), _TensorFacts.of(q),
                        _TensorFacts.of(k), _TensorFacts.of(v), tuple(sorted((n, _TensorFacts.of(x)) for n, x in kw.items())))
     try:
         return _plan_of(facts)

@@ -53,6 +53,7 @@ struct BwdParams {
   const float* lse_log2;
   const float* d_rows;
   const float* dq_scale;
+  const float* dq_scale_rows;   // (b, s_q) per query row instead of dq_scale per query tile, or null
   const uint8_t* sfq4;   // FL_MODE_FP4: E4M3 scale atoms of the NVFP4 Q / K copies (1 KB per 128-row tile)
   const uint8_t* sfk4;
   void* dk;
@@ -562,7 +563,15 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // token-local: the 64 per-query factors of the half (same addresses for every thread: broadcast loads)
         const float4* fq_vec = reinterpret_cast<const float4*>(p.fac_q + (TL ? bh_q * p.s_q + T.q0 + m * 128 + 64 * x : 0));
         const float4* fdo_vec = reinterpret_cast<const float4*>(p.fac_do + (TL ? bh_q * p.s_q + T.q0 + m * 128 + 64 * x : 0));
-        const float bsc = p.dq_scale[(size_t)T.bat * (p.s_q / 128) + T.q0 / 128 + m];
+        // the f16 pre-scale: one power of two per query tile (folded into K's exponent bytes below), or one per query row
+        // (folded into the dQ side's B scale bytes, whose lanes are the queries)
+        const float bsc = p.dq_scale_rows ? 1.0f : p.dq_scale[(size_t)T.bat * (p.s_q / 128) + T.q0 / 128 + m];
+        uint32_t lq0 = 0, lq1 = 0;
+        if (p.dq_scale_rows) {
+          const float* rp = p.dq_scale_rows + (size_t)T.bat * p.s_q + T.q0 + m * 128 + 64 * x;
+          lq0 = ((uint32_t)((int)((__float_as_uint(rp[lane]) >> 23) & 0xFF) - 127) & 0xFF) * 0x01010101u;
+          lq1 = ((uint32_t)((int)((__float_as_uint(rp[32 + lane]) >> 23) & 0xFF) - 127) & 0xFF) * 0x01010101u;
+        }
         // FP4: the block scales of S were applied by the tensor core; only the softmax scale remains
         const float c[2] = {FP4 ? p.scale_log2 : fk * fq0, FP4 ? p.scale_log2 : fk * fq1}, b8[2] = {fv8 * fd0, fv8 * fd1};
         // token-local: fq0 = fq1 = fd0 = fd1 = 1, i.e. unit scale bytes for the Q and dO operands
@@ -808,6 +817,8 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             sf[12] = (e0 & 0xFF) | ((e1 & 0xFF) << 8) | ((e2 & 0xFF) << 16) | ((e3 & 0xFF) << 24);
             sf[13] = ((e0 >> 8) & 0xFF) | (((e1 >> 8) & 0xFF) << 8) | (((e2 >> 8) & 0xFF) << 16) | (((e3 >> 8) & 0xFF) << 24);
           }
+          sf[12] = __vadd4(sf[12], lq0);
+          sf[13] = __vadd4(sf[13], lq1);
           sf[14] = sf[15] = 0x7F7F7F7Fu;
           FL_TMEM_ST_16(t_sx + TO_SFA_DK, sf);
         }
@@ -943,7 +954,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   using namespace fl;
   if (!a || !a->q_codes || !a->k_codes || !a->v_codes || !a->do_codes || !a->status) return FL_ERR_BAD_ARG;
-  if (!a->fac_q || !a->fac_k || !a->fac_v || !a->fac_do || !a->lse_log2 || !a->d_rows || !a->dq_acc || !a->dq_scale ||
+  if (!a->fac_q || !a->fac_k || !a->fac_v || !a->fac_do || !a->lse_log2 || !a->d_rows || !a->dq_acc || (!a->dq_scale && !a->dq_scale_rows) ||
       !a->dk || !a->dv)
     return FL_ERR_BAD_ARG;
   if (a->d != 128 && a->d != 64) return FL_ERR_UNSUPPORTED;
@@ -976,7 +987,8 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   if ((rc = make_rows_map_16(&mdv, a->dv, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
   BwdParams p;
   p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.fac_do = a->fac_do; p.lse_log2 = a->lse_log2;
-  p.d_rows = a->d_rows; p.dq_scale = a->dq_scale; p.dk = a->dk; p.dv = a->dv;
+  p.d_rows = a->d_rows; p.dq_scale = a->dq_scale; p.dq_scale_rows = a->dq_scale_rows; p.dk = a->dk; p.dv = a->dv;
+  if (a->dq_scale_rows && a->doc_start) return FL_ERR_UNSUPPORTED;      // per-row pre-scale: the batched form
   p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;
   p.seqused_k = a->seqused_k;

@@ -37,6 +37,8 @@ struct QuantParams {
   float* lse_log2;        // (b, h, s) or null
   uint16_t* zero_acc;     // f16 accumulator of b * h * s * d elements or null
   float* tile_stats;      // (b, h, s/128, 2): [amax of the values quantised, max row sum of squares] or null
+  uint32_t* row_stat;     // (b, s) per-token maximum over the heads (float bits, zero on entry) or null
+  int row_stat_kind;      // 1 = sum of squares, 2 = largest magnitude, 3 = 2-norm
   int b, s, h;
   const int32_t* slot_src;   // packed source: first source row of each 128-row slot of the output (-1: an empty slot), or null
   const int32_t* slot_rows;  // packed source: valid rows of each slot (the rest of the slot reads as zero)
@@ -321,7 +323,7 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     }
 #pragma unroll
     for (int i = 0; i < NE; i += 2) amax = fmaxf(fmaxf(amax, fabsf(x[i])), fabsf(x[i + 1]));
-    if (p.tile_stats) {     // the row norm is only wanted with the tile statistics (K, V, dO)
+    if (p.tile_stats || p.row_stat) {     // the row norm is only wanted with the statistics (K, V, dO)
       float sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < NE; ++i) sq[i & 3] = fmaf(x[i], x[i], sq[i & 3]);
@@ -331,6 +333,10 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));      // the token's maximum
     sumsq += __shfl_xor_sync(0xFFFFFFFFu, sumsq, 1);
     sumsq += __shfl_xor_sync(0xFFFFFFFFu, sumsq, 2);
+    if (p.row_stat && q == 0 && (!PK || row_live)) {     // non-negative floats order as their bit patterns
+      const float v = p.row_stat_kind == 2 ? amax : (p.row_stat_kind == 3 ? __fsqrt_rn(sumsq) : sumsq);
+      atomicMax(p.row_stat + (size_t)bat * p.s + t0 + r, __float_as_uint(v));
+    }
     float wmax = amax, wsq = sumsq;
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
@@ -505,6 +511,8 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   p.lse = a->lse; p.codes = a->codes; p.codes_t = a->codes_t; p.e_tab = a->e_tab; p.fac = a->fac; p.sf_tok = a->sf_tok;
   p.sf_dim = a->sf_dim; p.token_factors = a->token_factors; p.x4 = a->x4; p.sf4 = a->sf4; p.d_out = a->d_out;
   p.lse_log2 = a->lse_log2; p.zero_acc = (uint16_t*)a->zero_acc; p.tile_stats = a->tile_stats;
+  p.row_stat = (uint32_t*)a->row_stat; p.row_stat_kind = a->row_stat_kind;
+  if (a->row_stat && (a->row_stat_kind < 1 || a->row_stat_kind > 3)) return FL_ERR_BAD_ARG;
   p.b = a->b; p.s = a->s; p.h = a->h; p.n_tiles = (int)n_tiles;
   p.slot_src = a->slot_src; p.slot_rows = a->slot_rows;
   const bool packed = a->slot_src != nullptr;

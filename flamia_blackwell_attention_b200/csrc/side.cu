@@ -48,6 +48,43 @@ __global__ void dq_prescale_kernel(const float* __restrict__ st_do, const float*
   }
 }
 
+// Per query row i of a causal square batched call: B_i from the row's own dO statistic and the running maxima of the V / K
+// statistics over the keys j <= i (flash_attn/cute/device_scales.py:256-268, CAUSAL == 2). One CTA per batch row walks
+// the sequence in chunks of its size, carrying the running maxima; the prefix maxima overwrite row_v / row_k.
+__global__ void __launch_bounds__(1024) dq_prescale_rows_kernel(const float* __restrict__ row_do, float* row_v, float* row_k,
+                                                                int s, float unit, float* kernel_rows, float* post_rows) {
+  __shared__ float sv[32], sk[32];
+  const int bat = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t base = (size_t)bat * s;
+  float run_v = 0.f, run_k = 0.f;
+  for (int i0 = 0; i0 < s; i0 += blockDim.x) {
+    const int i = i0 + tid;
+    float v = i < s ? row_v[base + i] : 0.f, k = i < s ? row_k[base + i] : 0.f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {             // inclusive prefix maximum inside the warp
+      const float ov = __shfl_up_sync(0xFFFFFFFFu, v, o), okk = __shfl_up_sync(0xFFFFFFFFu, k, o);
+      if (lane >= o) { v = fmaxf(v, ov); k = fmaxf(k, okk); }
+    }
+    if (lane == 31) { sv[warp] = v; sk[warp] = k; }
+    __syncthreads();
+    float pv = run_v, pk = run_k;                  // everything before this warp: earlier chunks and earlier warps
+    for (int w = 0; w < warp; ++w) { pv = fmaxf(pv, sv[w]); pk = fmaxf(pk, sk[w]); }
+    v = fmaxf(v, pv);
+    k = fmaxf(k, pk);
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { run_v = fmaxf(run_v, sv[w]); run_k = fmaxf(run_k, sk[w]); }
+    if (i < s) {
+      row_v[base + i] = v;
+      row_k[base + i] = k;
+      const float dn = row_do[base + i];
+      const float bnd = __fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(4.0f, unit), 2.0f), __fsqrt_rn(dn)), __fsqrt_rn(v)), k);
+      const float bb = pow2_floor_clamped(__fdiv_rn(65504.0f, bnd), -40, 40);
+      kernel_rows[base + i] = bb;
+      post_rows[base + i] = __fdiv_rn(1.0f, __fmul_rn(unit, bb));
+    }
+    __syncthreads();
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ dQ postprocess
 // dq[b, q, h, :] = cast(f32(acc) * post[b, q / 128] * mult), optionally rotated back: (y H_128 / sqrt(128)) * signs in the
 // quantiser's butterfly order. Replaces the reference's DQPostprocess (flash_attn/cute/dq_postprocess_cute.py:46-124).
@@ -60,16 +97,17 @@ __device__ __forceinline__ uint32_t cvt_out2(float a, float b, int out_f16) {
 // head dim 64: the accumulator is (b, h, s, 64); a straight scaled copy into the (b, s, h, 64) gradient
 __global__ void __launch_bounds__(128) dq_post_rows64_kernel(const __half* __restrict__ acc, const float* __restrict__ post,
                                                              uint16_t* __restrict__ dq, int s, int h, float mult,
-                                                             int out_f16) {
+                                                             int out_f16, int per_row) {
   constexpr int D = 64, CPR = D / 8;
   const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z, tid = threadIdx.x;
   const int t0 = tile * 128;
   const __half* src = acc + (((size_t)bat * h + head) * s + t0) * D;
-  const float sc = post[(size_t)bat * (s / 128) + tile] * mult;
+  const float sc_tile = per_row ? 0.f : post[(size_t)bat * (s / 128) + tile] * mult;
   uint16_t* dst = dq + (((size_t)bat * s + t0) * h + head) * D;
   const size_t row_stride = (size_t)h * D;
   for (int i = tid; i < 128 * CPR; i += 128) {
     const int r = i / CPR, c = i % CPR;
+    const float sc = per_row ? post[(size_t)bat * s + t0 + r] * mult : sc_tile;
     uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
     const __half2* hv = reinterpret_cast<const __half2*>(&v);
     uint32_t w[4];
@@ -88,7 +126,8 @@ __global__ void __launch_bounds__(128) dq_post_rows64_kernel(const __half* __res
 // as coalesced 16-byte stores.
 __global__ void __launch_bounds__(128) dq_post_t128_kernel(const __grid_constant__ CUtensorMap tm_acc,
                                                            const float* __restrict__ post, uint16_t* __restrict__ dq,
-                                                           int s, int h, float mult, int unrotate, int out_f16) {
+                                                           int s, int h, float mult, int unrotate, int out_f16,
+                                                           int per_row) {
   constexpr int D = 128, ROWB = D * 2 + 16, CPR = D / 8;
   extern __shared__ __align__(1024) uint8_t sm_raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sm_raw) + 1023) & ~uintptr_t(1023));
@@ -106,7 +145,7 @@ __global__ void __launch_bounds__(128) dq_post_t128_kernel(const __grid_constant
     tma_load_4d(s_in, &tm_acc, &bar, t0, 0, head, bat);
     tma_load_4d(s_in + 16384, &tm_acc, &bar, t0 + 64, 0, head, bat);
   }
-  const float sc = post[(size_t)bat * (s / 128) + tile] * mult;
+  const float sc = (per_row ? post[(size_t)bat * s + t0 + tid] : post[(size_t)bat * (s / 128) + tile]) * mult;   // thread = token
   __syncthreads();
   const DevCtl ctl = {nullptr, kDefaultWaitCycles};
   bool ok = mbar_wait(&bar, 0, ctl, &abort_s, 60);
@@ -200,8 +239,8 @@ extern "C" int fl_dq_prescale(const float* stats_do, const float* stats_v, const
 
 // The accumulator layout follows the backward kernel that filled it: (b, h, d, s) for head_dim 128 (pipelined kernel,
 // transposed dQ tiles), (b, h, s, d) for head_dim 64.
-extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s,
-                          int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
+static int dq_post_launch(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s,
+                          int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, int per_row, void* stream) {
   using namespace fl;
   if (!dq_acc || !post_scale || !dq || b <= 0 || s <= 0 || (s % 128) || h <= 0) return FL_ERR_BAD_ARG;
   if ((d != 64 && d != 128) || (unrotate && d != 128)) return FL_ERR_UNSUPPORTED;
@@ -215,11 +254,30 @@ extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, float mul
     const int sm = 32768 + 128 * 272 + 1024;
     if (cudaError_t e = cudaFuncSetAttribute(dq_post_t128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); e != cudaSuccess)
       return cuda_fail((int)e, "fl_dq_post: cudaFuncSetAttribute");
-    dq_post_t128_kernel<<<grid, 128, sm, st>>>(macc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16);
+    dq_post_t128_kernel<<<grid, 128, sm, st>>>(macc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16, per_row);
   } else {
-    dq_post_rows64_kernel<<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, out_f16);
+    dq_post_rows64_kernel<<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, out_f16,
+                                                per_row);
   }
   return launch_result("fl_dq_post: kernel launch");
+}
+
+extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s,
+                          int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
+  return dq_post_launch(dq_acc, post_scale, mult, dq, b, s, h, d, unrotate, out_f16, 0, stream);
+}
+
+extern "C" int fl_dq_post_rows(const void* dq_acc, const float* post_scale_rows, float mult, void* dq, int32_t b, int32_t s,
+                               int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
+  return dq_post_launch(dq_acc, post_scale_rows, mult, dq, b, s, h, d, unrotate, out_f16, 1, stream);
+}
+
+extern "C" int fl_dq_prescale_rows(const float* row_do, float* row_v, float* row_k, int32_t b, int32_t s, float unit,
+                                   float* kernel_rows, float* post_rows, void* stream) {
+  using namespace fl;
+  if (!row_do || !row_v || !row_k || !kernel_rows || !post_rows || b <= 0 || s <= 0) return FL_ERR_BAD_ARG;
+  dq_prescale_rows_kernel<<<b, 1024, 0, (cudaStream_t)stream>>>(row_do, row_v, row_k, s, unit, kernel_rows, post_rows);
+  return launch_result("fl_dq_prescale_rows: kernel launch");
 }
 
 extern "C" int fl_pack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n_dst_rows, int32_t row_bytes,

@@ -6,3 +6,8 @@ from that tile's own dO rows and the PREFIX of key tiles it may see, so a later 
 rounding. Read by the plan when a call is resolved; the resolved value travels in the plan.
 """
 DQ_CAUSAL_PRESCALE = False
+
+# With DQ_CAUSAL_PRESCALE on: "tile" = one pre-scale per 128-query tile (the reference's form on its CTA-pair backward),
+# "row" = one per query row from per-token statistics and running maxima over the keys j <= i (the reference's form on its
+# 1-CTA backward, flash_attn/cute/interface_bwd_fp4.py:1007-1012 "rowwise": exactly causal, no key-tile granularity).
+DQ_CAUSAL_GRANULARITY = "tile"

@@ -37,14 +37,16 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
                         make_channel_major_copy=False, output_exponent_table=True, output_token_block_factors=True,
                         output_sf_atoms=False, also_make_nvfp4_copy=False, compute_d_with_output=None,
                         shifted_log2_lse_from=None, log2_lse_shift=0.0, d_multiplier=1.0, zero_accumulator=None,
-                        output_tile_stats=False, status=None, wait_cycles=0, packed_slots=None):
+                        output_tile_stats=False, status=None, wait_cycles=0, packed_slots=None, row_stat=None):
     """Token-block MXFP8 quantiser of x (b, s, h, d) bf16 / f16 (s % 128 == 0, d in {64, 128}).
     packed_slots = (slot_src, slot_rows, padded_rows): x is a packed (total, h, d) tensor of documents stored back to back
     and the outputs are those of the 128-aligned buffer (1, padded_rows, h, d): slot_src[i] = first row of x of output
     rows [128 i, 128 i + 128) (-1 = empty), slot_rows[i] = how many of them are real. Nothing is copied.
     Returns a dict: codes (b,s,h,d) float8_e4m3fn; e (b,h,s/32,d/32) uint8; fac (b,h,s/32) f32; optionally codes_t,
     sf_tok_raw, sf_dim_raw, token_factors, x4 / sf4_raw (NVFP4 copy), D, lse_log2, tile_stats.
-    hadamard_rotation_scope: "all" (codes and NVFP4 copy of the rotated rows) | "nvfp4_copy" (only the NVFP4 copy)."""
+    hadamard_rotation_scope: "all" (codes and NVFP4 copy of the rotated rows) | "nvfp4_copy" (only the NVFP4 copy).
+    row_stat = (kind, table): table (b, s) f32, zero on entry, takes per token the maximum over the heads of the row's
+    "sumsq" | "amax" | "norm2" (the statistics of the per-query-row causal dQ pre-scale)."""
     _require_cuda(x, "x")
     if x.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError("x must be bf16 or f16")
@@ -112,6 +114,10 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
     if output_tile_stats:
         out["tile_stats"] = torch.empty(b, h, s // 128, 2, dtype=torch.float32, device=dev)
         a.tile_stats = L.ptr(out["tile_stats"])
+    if row_stat is not None:
+        kind, table = row_stat
+        assert table.dtype == torch.float32 and tuple(table.shape) == (b, s) and table.is_contiguous()
+        a.row_stat, a.row_stat_kind = L.ptr(table), {"sumsq": 1, "amax": 2, "norm2": 3}[kind]
     a.lse_shift, a.d_multiplier = float(log2_lse_shift), float(d_multiplier)
     a.status, a.wait_cycles = L.ptr(status), int(wait_cycles)      # status: the call's device status word or None
     L.check(L.load().fl_quant_blocks(C.byref(a), _stream()), "fl_quant_blocks")
@@ -200,18 +206,34 @@ def dq_prescale(stats_do, stats_v, stats_k, *, causal_local=False, unit=1.0):
     return ks, ps
 
 
-def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torch.bfloat16):
-    """dq (b, s, h, d) = cast(acc * post_scale[b, s / 128] * mult), optionally rotated back. acc is the f16 accumulator
-    in the backward kernel's layout: (b, h, d, s) at d = 128, (b, h, s, d) at d = 64."""
+def dq_prescale_rows(row_do, row_v, row_k, *, unit=1.0):
+    """Power-of-two pre-scale of the f16 dQ accumulator per QUERY ROW of a causal square batched call, from the
+    quantisers' per-token statistics (b, s): row i's own dO statistic and the running maxima of the V / K statistics over
+    the keys j <= i (row_v / row_k are replaced by those prefix maxima). Returns (kernel_rows, post_rows), each (b, s)."""
+    b, s = row_do.shape
+    assert row_v.shape == row_do.shape == row_k.shape
+    ks = torch.empty(b, s, dtype=torch.float32, device=row_do.device)
+    ps = torch.empty(b, s, dtype=torch.float32, device=row_do.device)
+    L.check(L.load().fl_dq_prescale_rows(L.ptr(row_do), L.ptr(row_v), L.ptr(row_k), b, s, float(unit), L.ptr(ks),
+                                         L.ptr(ps), _stream()), "fl_dq_prescale_rows")
+    return ks, ps
+
+
+def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torch.bfloat16, per_row=False):
+    """dq (b, s, h, d) = cast(acc * post_scale[b, s / 128] * mult) (per_row: post_scale[b, s]), optionally rotated back.
+    acc is the f16 accumulator in the backward kernel's layout: (b, h, d, s) at d = 128, (b, h, s, d) at d = 64."""
     dq = torch.empty(b, s, h, d, dtype=out_dtype, device=acc.device)
-    L.check(L.load().fl_dq_post(L.ptr(acc), L.ptr(post_scale), float(mult), L.ptr(dq), b, s, h, d, int(bool(unrotate)),
-                                int(out_dtype == torch.float16), _stream()), "fl_dq_post")
+    assert post_scale.numel() == (b * s if per_row else b * (s // 128))
+    fn = L.load().fl_dq_post_rows if per_row else L.load().fl_dq_post
+    L.check(fn(L.ptr(acc), L.ptr(post_scale), float(mult), L.ptr(dq), b, s, h, d, int(bool(unrotate)),
+               int(out_dtype == torch.float16), _stream()), "fl_dq_post")
     return dq
 
 
 def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax_scale, out_dtype=torch.bfloat16,
              mode=L.FL_MODE_FP8, had_dk=False, status=None, doc_start=None, doc_len=None, wait_cycles=0,
-             token_local=False, dq_rowlocal=False, window=None, seqused_k=None, softcap=0.0, dq_order=None):
+             token_local=False, dq_rowlocal=False, window=None, seqused_k=None, softcap=0.0, dq_order=None,
+             dq_scale_rows=None):
     """Backward main kernel on quantised operands. q / k / v / do: quantiser outputs (codes, fac). Adds the pre-scaled
     dQ partials into the f16 accumulator dq_acc of b * h * s_q * d elements ((b, h, d, s_q) at d = 128, (b, h, s_q, d)
     at d = 64) and returns (dk, dv, status), each (b, s_k, h_kv, d). dq_order: a zeroed (b, h, s_q / 128, 2) int32 table
@@ -231,6 +253,9 @@ def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax
     a.do_codes, a.fac_do = L.ptr(do["codes"]), L.ptr(do["token_factors" if token_local else "fac"])
     a.lse_log2, a.d_rows, a.dq_acc, a.dq_scale = L.ptr(lse_log2), L.ptr(d_rows), L.ptr(dq_acc), L.ptr(dq_scale)
     a.dk, a.dv = L.ptr(dk), L.ptr(dv)
+    if dq_scale_rows is not None:      # one pre-scale per query row instead of dq_scale per query tile
+        assert dq_scale_rows.dtype == torch.float32 and dq_scale_rows.numel() == b * q["codes"].shape[1]
+        a.dq_scale_rows = L.ptr(dq_scale_rows)
     if dq_order is not None:
         assert dq_order.dtype == torch.int32 and dq_order.numel() == b * q["codes"].shape[2] * (q["codes"].shape[1] // 128) * 2
         a.dq_order = L.ptr(dq_order)

@@ -77,7 +77,7 @@ class BwdSpec:
     p_scaling: str         # row
     grad_format: str       # e4m3
     deterministic: bool
-    dq_prescale: str       # row | causal_tile
+    dq_prescale: str       # row | causal_tile | causal_row
 
 
 @dataclass(frozen=True)
@@ -269,7 +269,7 @@ def _finish(entry, route, qk_format, shape, log_rows, opts, *, softmax_scale, ca
                   shape.aligned_varlen, ragged, bool(return_lse), None if win == (None, None) else win,
                   softcap=float(softcap or 0.0), seqused_k=bool(seqused_k))
     bwd = BwdSpec("1cta" if shape.requires_grad else "none", scaling, "block_32x32", rowlocal, "row", "e4m3",
-                  bool(deterministic), "causal_tile" if dq_causal else "row")
+                  bool(deterministic), dq_causal if isinstance(dq_causal, str) else ("causal_tile" if dq_causal else "row"))
     return AttnPlan(entry, route, sc, shape, fwd, bwd, opts.tuning, False, False, tuple(log_rows), opts)
 
 
@@ -311,8 +311,16 @@ def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     log("backward_kernel", "1cta", "the 1-CTA backward (key-stationary, GQA in the same accumulators)")
     from . import interface_bwd_fp4
     dq_causal = bool(interface_bwd_fp4.DQ_CAUSAL_PRESCALE) and bool(causal) and not shape.varlen and shape.s_q == shape.s_k
-    log("dq_prescale", "causal_tile" if dq_causal else "row", "per query tile from the prefix of key tiles"
-        if dq_causal else "one power of two per batch row / document")
+    gran = str(interface_bwd_fp4.DQ_CAUSAL_GRANULARITY)
+    if gran not in ("tile", "row"):
+        _fail("B9", ValueError, f"interface_bwd_fp4.DQ_CAUSAL_GRANULARITY is 'tile' or 'row'; got {gran!r}")
+    if dq_causal and gran == "row" and (scaling == "token_local" or window_size not in ((None, None), (-1, -1))
+                                        or seqused_k is not None or (softcap or 0.0) > 0.0 or ragged):
+        gran = "tile"          # the per-row form serves the plain causal square call, like the reference's
+    dq_causal = "causal_row" if (dq_causal and gran == "row") else ("causal_tile" if dq_causal else False)
+    log("dq_prescale", dq_causal or "row", "per query row from per-token statistics and running maxima over the keys j <= i"
+        if dq_causal == "causal_row" else ("per query tile from the prefix of key tiles"
+        if dq_causal else "one power of two per batch row / document"))
     return _finish("fp8", "fp8", "e4m3", shape, rows, o, softmax_scale=softmax_scale, causal=causal,
                    return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=dq_causal,
                    window_size=window_size, p_frame=p_frame,

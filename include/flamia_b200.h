@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define FL_ABI_VERSION 4
+#define FL_ABI_VERSION 5
 
 /* fl_quant_args.flags */
 #define FL_Q_HADAMARD 1            /* rotate rows by diag(signs) H_128 / sqrt(128) before quantising (d = 128) */
@@ -61,6 +61,12 @@ typedef struct fl_quant_args {
   const int32_t* slot_src;
   const int32_t* slot_rows;
   int32_t src_rows;
+  /* Per-token statistic for the per-query-row causal dQ pre-scale (flash_attn/cute/interface_bwd_fp4.py:950-987
+   * dq_causal_kv_rows / dq_causal_rows): (b, s) float, ZERO on entry, or NULL. Each (token, head) takes the maximum into
+   * its token's entry (over the heads of one launch): row_stat_kind 1 = the row's sum of squares, 2 = its largest
+   * magnitude, 3 = its 2-norm (of the values quantised, i.e. after the rotation where there is one). */
+  float* row_stat;
+  int32_t row_stat_kind;
 } fl_quant_args;
 
 int fl_quant_blocks(const fl_quant_args* args, void* stream);
@@ -129,6 +135,10 @@ typedef struct fl_attn_args {
    * its (head, query tile, 64-query half) has counted the key tiles before it, adds, waits for the addition to complete
    * and counts itself. dQ is then bitwise reproducible from call to call; the other outputs always are. */
   int32_t* dq_order;
+  /* Backward: (b, s_q) power-of-two pre-scale of the f16 accumulator per QUERY ROW (the reference's row-wise causal
+   * pre-scale of its 1-CTA kernels, flash_attn/cute/device_scales.py:256-268), or NULL = dq_scale per query tile. With
+   * it dq_scale is not read. Batched form only. */
+  const float* dq_scale_rows;
 } fl_attn_args;
 
 /* Forward: O = softmax(scale Q K^T + mask) V, LSE.
@@ -147,10 +157,20 @@ int fl_dq_prescale(const float* stats_do, const float* stats_v, const float* sta
                    int32_t nt_q, int32_t nt_k, int32_t causal_local, float unit, float* kernel_scale, float* post_scale,
                    void* stream);
 
+/* The same per QUERY ROW of a causal square batched call (the reference's dq_tile_causal = 2,
+ * flash_attn/cute/device_scales.py:256-268): row i's pre-scale from its own statistic and the running maxima over the
+ * keys j <= i. row_do / row_v / row_k: (b, s) per-token statistics of the quantisers (fl_quant_args.row_stat: kind 1, 1
+ * and 2 or 3); row_v and row_k are replaced by their prefix maxima. kernel_rows / post_rows: (b, s). */
+int fl_dq_prescale_rows(const float* row_do, float* row_v, float* row_k, int32_t b, int32_t s, float unit,
+                        float* kernel_rows, float* post_rows, void* stream);
+
 /* dQ postprocess: dq[b, s, h, c] = cast(acc(b, h, s, c) * post_scale[b, s/128] * mult) with optional Hadamard
  * back-rotation, where acc(b, h, s, c) is element [b, h, c, s] of the (b, h, d, s) accumulator at d = 128 (the backward
  * kernel produces transposed dQ tiles) and element [b, h, s, c] of the (b, h, s, d) accumulator at d = 64.
  * Replaces flash_attn/cute/dq_postprocess_cute.py:46 DQPostprocess / bwd_2cta8_side.dq_postprocess_2cta8. */
+/* fl_dq_post_rows: post_scale_rows is (b, s), one value per query row. */
+int fl_dq_post_rows(const void* dq_acc, const float* post_scale_rows, float mult, void* dq, int32_t b, int32_t s,
+                    int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream);
 int fl_dq_post(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s, int32_t h,
                int32_t d, int32_t unrotate, int32_t out_f16, void* stream);
 

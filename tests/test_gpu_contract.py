@@ -51,6 +51,36 @@ def test_dq_prescale_tables_bitwise(kind, shape, unit):
         assert np.array_equal(ps.cpu().numpy().reshape(-1).view(np.uint32), want_p.view(np.uint32)), (mode, kind)
 
 
+@pytest.mark.parametrize("rotate", [False, True])
+def test_dq_prescale_rows_bitwise(rotate):
+    """The per-query-row causal pre-scale (the reference's CAUSAL == 2 table, flash_attn/cute/device_scales.py:256-268):
+    per-token statistics from the quantisers (maximum over the heads), running maxima over the keys, and the table
+    against the oracle's restatement, bit for bit."""
+    from flamia_blackwell_attention_b200 import kernels as K
+    b, s, h, hk, d = 2, 1280, 4, 2, 128
+    q, k, v, g = (t.cuda() for t in attention_inputs(b, s, h, hk, d, seed=93))
+    k = k * torch.linspace(0.2, 3.0, s, device="cuda").view(1, s, 1, 1).to(k.dtype)       # statistics that grow and shrink
+    v = v * (1.0 + torch.sin(torch.arange(s, device="cuda") / 50.0)).view(1, s, 1, 1).to(v.dtype)
+    rk, rv, rdo = (torch.zeros(b, s, dtype=torch.float32, device="cuda") for _ in range(3))
+    K.quantize_fp8_blocks(k, apply_hadamard_rotation=rotate, row_stat=("norm2" if rotate else "amax", rk))
+    K.quantize_fp8_blocks(v, row_stat=("sumsq", rv))
+    K.quantize_fp8_blocks(g, row_stat=("sumsq", rdo))
+    # the statistics themselves: maximum over the heads of the row's own figure (fp32 sums in the kernel's order: close)
+    want_k = (k.float().norm(dim=-1) if rotate else k.float().abs().amax(dim=-1)).amax(dim=-1)
+    torch.testing.assert_close(rk, want_k, rtol=2e-3, atol=1e-6)
+    torch.testing.assert_close(rv, v.float().pow(2).sum(-1).amax(-1), rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(rdo, g.float().pow(2).sum(-1).amax(-1), rtol=1e-4, atol=1e-6)
+    vn_prefix = torch.cummax(rv, dim=1).values.cpu().numpy()
+    km_prefix = torch.cummax(rk, dim=1).values.cpu().numpy()
+    dn = rdo.cpu().numpy()
+    pv, pk = rv.clone(), rk.clone()
+    ks, ps = K.dq_prescale_rows(rdo, pv, pk)
+    assert np.array_equal(pv.cpu().numpy(), vn_prefix) and np.array_equal(pk.cpu().numpy(), km_prefix)
+    want_ks, want_ps = S.dq_prescale_causal_rows(dn.reshape(-1), vn_prefix.reshape(-1), km_prefix.reshape(-1))
+    assert np.array_equal(ks.cpu().numpy().reshape(-1).view(np.uint32), want_ks.view(np.uint32))
+    assert np.array_equal(ps.cpu().numpy().reshape(-1).view(np.uint32), want_ps.view(np.uint32))
+
+
 # ------------------------------------------------------------------------------------------------ NaN-filled allocator
 def _poison_allocator(nbytes=192 << 20):
     """Allocate, fill with NaN bit patterns (as f32 and as bf16) and free: the caching allocator hands these blocks out
@@ -347,3 +377,32 @@ def test_future_rows_do_not_move_earlier_rows(route, opts):
         moved = float((base[2][:, :k0].float() - pert[2][:, :k0].float()).abs().max())
         ulp = float(base[2][:, :k0].float().abs().max()) * 2.0 ** -7
         assert moved <= max(noise, ulp), (moved, noise, ulp)
+
+
+def test_row_wise_causal_prescale_is_exactly_causal():
+    """DQ_CAUSAL_GRANULARITY = 'row' with the ordered reduction: dQ of the rows before K0 keeps every bit when later K, V
+    and dO rows change (K0 need not be a multiple of the query tile here: the pre-scale is per query row), and the
+    gradients agree with the per-tile form to f16 rounding."""
+    import flamia_blackwell_attention_b200 as F
+    import flamia_blackwell_attention_b200.interface_bwd_fp4 as I
+    s, k0 = 1024, 672                                   # a multiple of 32 (the operands' scale blocks), not of 128
+    q, k, v, g = (t.cuda() for t in attention_inputs(2, s, 4, 2, 128, seed=94))
+    k2, v2, g2 = k.clone(), v.clone(), g.clone()
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    for t in (k2, v2, g2):
+        t[:, k0:k0 + 40] = torch.randn(t[:, k0:k0 + 40].shape, generator=gen, device="cuda").sign().to(t.dtype) * 60.0
+    old = I.DQ_CAUSAL_PRESCALE, I.DQ_CAUSAL_GRANULARITY
+    try:
+        I.DQ_CAUSAL_PRESCALE, I.DQ_CAUSAL_GRANULARITY = True, "tile"
+        tile = _eager(F.flash_attn_fp8, q, k, v, g, causal=True, deterministic=True)
+        I.DQ_CAUSAL_GRANULARITY = "row"
+        assert F.resolve_fp8(q, k, v, causal=True).bwd.dq_prescale == "causal_row"
+        base = _eager(F.flash_attn_fp8, q, k, v, g, causal=True, deterministic=True)
+        pert = _eager(F.flash_attn_fp8, q, k2, v2, g2, causal=True, deterministic=True)
+    finally:
+        I.DQ_CAUSAL_PRESCALE, I.DQ_CAUSAL_GRANULARITY = old
+    assert torch.equal(base[0], tile[0]) and torch.equal(base[3], tile[3]) and torch.equal(base[4], tile[4])
+    assert _cos(base[2], tile[2]) > 0.99999
+    assert not torch.equal(base[2][:, k0:], pert[2][:, k0:])                 # the probe is not blind
+    assert torch.equal(base[2][:, :k0], pert[2][:, :k0])
+    assert F.check_status() == 0
