@@ -186,9 +186,40 @@ def state_spec(plan, n_docs=0, dtype=torch.bfloat16, capacity=None):
 
 
 # --------------------------------------------------------------------------------------------------------------- forward
-def forward(plan, q, k, v, docs, seqused_k=None):
+def _forward_prequant(plan, q8, k8, v8, descales, seqused_k):
+    """forward() for operands that are already E4M3 codes with one float descale per (batch row, kv head): no quantiser
+    runs; the descales fill the factor tables, and V's mantissa goes on the output rows."""
+    from .prequant_fa3 import mantissa
+    sh, f = plan.shape, plan.fwd
+    qd, kd, vd = descales
+    grp = sh.h // sh.h_kv
+    need_bwd = plan.bwd.kernel != "none"
+    status = K.new_status(q8.device)
+
+    def table(dsc, heads_rep, s):
+        return dsc.repeat_interleave(heads_rep, dim=1)[:, :, None].expand(sh.b, dsc.shape[1] * heads_rep, s // 32).contiguous()
+    qq = dict(codes=q8, fac=table(qd, grp, sh.s_q))
+    kq = dict(codes=k8, fac=table(kd, 1, sh.s_k))
+    vq = dict(codes=v8, fac=table(vd, 1, sh.s_k))
+    out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale,
+                             out_dtype=torch.float16 if sh.dtype == "float16" else torch.bfloat16, status=status,
+                             window=f.window, seqused_k=seqused_k, softcap=f.softcap, o_mult=mantissa(vd))
+    state = [out, lse, q8, qq["fac"], k8, kq["fac"], v8, vq["fac"], status]
+    if need_bwd:
+        state += [K.code_stats(k8, kd), K.code_stats(v8, vd)]
+    if seqused_k is not None:
+        state += [seqused_k]
+    state += [qd, kd]
+    _note_status(status)
+    return out, lse, state
+
+
+def forward(plan, q, k, v, docs, seqused_k=None, prequant=None):
     """Returns (out, lse, state): out / lse in the caller's layout, state = the tensors the backward needs.
-    seqused_k: the batched form's (b,) int32 valid-key counts, or None."""
+    seqused_k: the batched form's (b,) int32 valid-key counts, or None. prequant: (q_descale, k_descale, v_descale) when
+    q, k, v are E4M3 codes already."""
+    if prequant is not None:
+        return _forward_prequant(plan, q, k, v, prequant, seqused_k)
     sh, f = plan.shape, plan.fwd
     fp4 = plan.entry == "fp4"
     mode = L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8
@@ -257,6 +288,11 @@ def backward(plan, state, dout, docs_meta):
     if tl:
         qq["token_factors"], kq["token_factors"], vq["token_factors"] = (next(it) for _ in range(3))
     seqused_k = next(it) if f.seqused_k else None
+    dk_mult = dq_mult = None
+    if plan.prequant:       # float descales: the mantissas the block-scaled dK / dQ products left out
+        from .prequant_fa3 import mantissa
+        qd, kd = next(it), next(it)
+        dk_mult, dq_mult = mantissa(qd), mantissa(kd).repeat_interleave(sh.h // sh.h_kv, dim=1).contiguous()
     docs = None
     if docs_meta is not None:
         docs = object.__new__(Docs)
@@ -288,11 +324,12 @@ def backward(plan, state, dout, docs_meta):
                            causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=out.dtype,
                            mode=L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8, had_dk=had8, status=status,
                            token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all", window=f.window, seqused_k=seqused_k,
-                           softcap=f.softcap,
+                           softcap=f.softcap, dk_mult=dk_mult,
                            dq_order=torch.zeros(b, h, s_q // 128, 2, dtype=torch.int32, device=out.device)
                            if bw.deterministic else None,
                            doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
-    dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype, per_row=rows)
+    dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype, per_row=rows,
+                   head_mult=dq_mult)
     _note_status(status)
     if docs is not None:
         tq = sh.tot_q if sh.varlen else sh.b * sh.s_q

@@ -152,12 +152,19 @@ def flash_attn_fp8(q, k, v, *, softmax_scale: Optional[float] = None, causal: bo
     if doc_maps is not None:
         cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k = _doc_maps_args(doc_maps, q, cu_seqlens_q, cu_seqlens_k,
                                                                                 seqused_q, seqused_k)
-    if q_descale is not None or k_descale is not None or v_descale is not None or grad_proxies is not None or \
-            (isinstance(q, torch.Tensor) and q.dtype == torch.float8_e4m3fn):
-        _fail("B7", NotImplementedError, "FA3-style pre-quantised E4M3 inputs (q_descale / k_descale / v_descale / "
-                                         "grad_proxies) are not built")
     if aux_tensors is not None:
         _fail("B3", NotImplementedError, "aux_tensors belong to score_mod / mask_mod, which this library does not take")
+    if q_descale is not None or k_descale is not None or v_descale is not None or grad_proxies is not None or \
+            (isinstance(q, torch.Tensor) and q.dtype == torch.float8_e4m3fn):
+        if doc_maps is not None:
+            _fail("B7", NotImplementedError, "pre-quantised E4M3 inputs are served on the batched form, not with doc_maps")
+        from .prequant_fa3 import flash_attn_fp8_prequant
+        return flash_attn_fp8_prequant(resolve_fp8, q, k, v, q_descale, k_descale, v_descale, grad_proxies, dict(
+            softmax_scale=softmax_scale, causal=causal, window_size=tuple(window_size), softcap=softcap,
+            score_mod=score_mod, score_mod_bwd=score_mod_bwd, mask_mod=mask_mod, cu_seqlens_q=cu_seqlens_q,
+            cu_seqlens_k=cu_seqlens_k, max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, seqused_k=seqused_k,
+            seqused_q=seqused_q, deterministic=deterministic, return_lse=return_lse, qk_hadamard=qk_hadamard,
+            q_quantized=q_quantized, k_quantized=k_quantized, q_scale_fused=q_scale_fused, options=options), return_lse)
     plan = _cached_plan(resolve_fp8, q, k, v, dict(
         softmax_scale=softmax_scale, causal=causal, window_size=tuple(window_size), softcap=softcap, score_mod=score_mod,
         score_mod_bwd=score_mod_bwd, mask_mod=mask_mod, cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k,

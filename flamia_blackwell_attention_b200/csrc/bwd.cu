@@ -54,6 +54,7 @@ struct BwdParams {
   const float* d_rows;
   const float* dq_scale;
   const float* dq_scale_rows;   // (b, s_q) per query row instead of dq_scale per query tile, or null
+  const float* dk_mult;         // (b, h_kv) factor on dK (Q's mantissa with float descales), or null
   const uint8_t* sfq4;   // FL_MODE_FP4: E4M3 scale atoms of the NVFP4 Q / K copies (1 KB per 128-row tile)
   const uint8_t* sfk4;
   void* dk;
@@ -835,7 +836,8 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_after();
       {
         const uint32_t t_acc = lane_base + (x == 0 ? TC_DV : TC_DK);
-        const float mult = (x == 0) ? 0.00390625f : p.softmax_scale;       // dV carries 2^8 (P'), dK the softmax scale
+        // dV carries 2^8 (P'), dK the softmax scale (and the mantissa of a Q factor that is no power of two)
+        const float mult = (x == 0) ? 0.00390625f : p.softmax_scale * (p.dk_mult ? p.dk_mult[bh_k] : 1.0f);
         const float mk = key_valid ? mult : 0.f;       // rows past the end of the document store zeros
         uint32_t v[D];
         if (n_it > 0) {                  // (CTA-uniform: the tensor-memory loads are warp-collective)
@@ -988,6 +990,8 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   BwdParams p;
   p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.fac_do = a->fac_do; p.lse_log2 = a->lse_log2;
   p.d_rows = a->d_rows; p.dq_scale = a->dq_scale; p.dq_scale_rows = a->dq_scale_rows; p.dk = a->dk; p.dv = a->dv;
+  p.dk_mult = a->dk_mult;
+  if (a->dk_mult && a->doc_start) return FL_ERR_UNSUPPORTED;            // per-(batch row, head) factors: the batched form
   if (a->dq_scale_rows && a->doc_start) return FL_ERR_UNSUPPORTED;      // per-row pre-scale: the batched form
   p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;

@@ -61,6 +61,7 @@ struct FwdParams {
   const int32_t* doc_start;
   const int32_t* doc_len;
   const int32_t* seqused_k;   // batched form: valid keys per batch row, or null
+  const float* o_mult;        // (b, h_kv) factor on the output rows (V's mantissa with float descales), or null
   int n_docs;
   int b, s_q, s_k, h, h_kv;
   float scale_log2;
@@ -579,7 +580,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       tc_fence_after();
       const bool stage_present = T.nq > 128 * i;        // (warpgroup-uniform) an absent stage's rows belong to someone else
-      const float inv_l = (l_sum > 0.f) ? 1.0f / l_sum : 0.f;
+      const float inv_l = ((l_sum > 0.f) ? 1.0f / l_sum : 0.f) * (p.o_mult ? p.o_mult[bh_k] : 1.0f);
       uint8_t* stage = sQ + (2 * kb + i) * Q_STRIDE;
       const uint32_t srow = smem_u32(stage) + r * 128;
 #pragma unroll 1
@@ -673,6 +674,8 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;
   p.seqused_k = a->seqused_k;
+  p.o_mult = a->o_mult;
+  if (a->o_mult && a->doc_start) return FL_ERR_UNSUPPORTED;      // per-(batch row, head) factors: the batched form
   p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.causal = (a->flags & FL_A_CAUSAL) ? 1 : 0;

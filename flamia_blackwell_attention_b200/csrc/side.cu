@@ -97,10 +97,11 @@ __device__ __forceinline__ uint32_t cvt_out2(float a, float b, int out_f16) {
 // head dim 64: the accumulator is (b, h, s, 64); a straight scaled copy into the (b, s, h, 64) gradient
 __global__ void __launch_bounds__(128) dq_post_rows64_kernel(const __half* __restrict__ acc, const float* __restrict__ post,
                                                              uint16_t* __restrict__ dq, int s, int h, float mult,
-                                                             int out_f16, int per_row) {
+                                                             int out_f16, int per_row, const float* __restrict__ head_mult) {
   constexpr int D = 64, CPR = D / 8;
   const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z, tid = threadIdx.x;
   const int t0 = tile * 128;
+  if (head_mult) mult *= head_mult[(size_t)bat * h + head];
   const __half* src = acc + (((size_t)bat * h + head) * s + t0) * D;
   const float sc_tile = per_row ? 0.f : post[(size_t)bat * (s / 128) + tile] * mult;
   uint16_t* dst = dq + (((size_t)bat * s + t0) * h + head) * D;
@@ -127,7 +128,7 @@ __global__ void __launch_bounds__(128) dq_post_rows64_kernel(const __half* __res
 __global__ void __launch_bounds__(128) dq_post_t128_kernel(const __grid_constant__ CUtensorMap tm_acc,
                                                            const float* __restrict__ post, uint16_t* __restrict__ dq,
                                                            int s, int h, float mult, int unrotate, int out_f16,
-                                                           int per_row) {
+                                                           int per_row, const float* __restrict__ head_mult) {
   constexpr int D = 128, ROWB = D * 2 + 16, CPR = D / 8;
   extern __shared__ __align__(1024) uint8_t sm_raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sm_raw) + 1023) & ~uintptr_t(1023));
@@ -145,6 +146,7 @@ __global__ void __launch_bounds__(128) dq_post_t128_kernel(const __grid_constant
     tma_load_4d(s_in, &tm_acc, &bar, t0, 0, head, bat);
     tma_load_4d(s_in + 16384, &tm_acc, &bar, t0 + 64, 0, head, bat);
   }
+  if (head_mult) mult *= head_mult[(size_t)bat * h + head];
   const float sc = (per_row ? post[(size_t)bat * s + t0 + tid] : post[(size_t)bat * (s / 128) + tile]) * mult;   // thread = token
   __syncthreads();
   const DevCtl ctl = {nullptr, kDefaultWaitCycles};
@@ -206,6 +208,45 @@ __global__ void __launch_bounds__(128) dq_post_t128_kernel(const __grid_constant
   }
 }
 
+// ------------------------------------------------------------------------------------------------ statistics of codes
+// One CTA per (128-row tile, head, batch row), thread = row: the largest magnitude and the largest row sum of squares of
+// codes * descale[b, h] (fp32 sums in column order).
+__device__ __forceinline__ float e4m3_to_f32(uint32_t c) {
+  const uint32_t e = (c >> 3) & 0xF, m = c & 7;
+  const float v = e ? __uint_as_float(((e + 120) << 23) | (m << 20)) : (float)m * 0.001953125f;
+  return (c & 0x80) ? -v : v;
+}
+__global__ void __launch_bounds__(128) code_stats_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ descale,
+                                                         int s, int h, int d, float* __restrict__ tile_stats) {
+  const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z, tid = threadIdx.x;
+  const uint8_t* row = codes + (((size_t)bat * s + tile * 128 + tid) * h + head) * d;
+  const float f = descale[(size_t)bat * h + head];
+  float am = 0.f, sq = 0.f;
+  for (int c = 0; c < d; c += 16) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + c);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const float x = e4m3_to_f32((w[k >> 2] >> (8 * (k & 3))) & 0xFF) * f;
+      am = fmaxf(am, fabsf(x));
+      sq = fmaf(x, x, sq);
+    }
+  }
+  __shared__ float red[2][4];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
+    sq = fmaxf(sq, __shfl_xor_sync(0xFFFFFFFFu, sq, o));
+  }
+  if ((tid & 31) == 0) { red[0][tid >> 5] = am; red[1][tid >> 5] = sq; }
+  __syncthreads();
+  if (tid == 0) {
+    float* o = tile_stats + ((((size_t)bat * h + head) * (s / 128)) + tile) * 2;
+    o[0] = fmaxf(fmaxf(red[0][0], red[0][1]), fmaxf(red[0][2], red[0][3]));
+    o[1] = fmaxf(fmaxf(red[1][0], red[1][1]), fmaxf(red[1][2], red[1][3]));
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ packed rows
 __global__ void pack_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int32_t* __restrict__ map,
                                  int n_rows, int chunks) {
@@ -240,7 +281,8 @@ extern "C" int fl_dq_prescale(const float* stats_do, const float* stats_v, const
 // The accumulator layout follows the backward kernel that filled it: (b, h, d, s) for head_dim 128 (pipelined kernel,
 // transposed dQ tiles), (b, h, s, d) for head_dim 64.
 static int dq_post_launch(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s,
-                          int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, int per_row, void* stream) {
+                          int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, int per_row, const float* head_mult,
+                          void* stream) {
   using namespace fl;
   if (!dq_acc || !post_scale || !dq || b <= 0 || s <= 0 || (s % 128) || h <= 0) return FL_ERR_BAD_ARG;
   if ((d != 64 && d != 128) || (unrotate && d != 128)) return FL_ERR_UNSUPPORTED;
@@ -254,22 +296,29 @@ static int dq_post_launch(const void* dq_acc, const float* post_scale, float mul
     const int sm = 32768 + 128 * 272 + 1024;
     if (cudaError_t e = cudaFuncSetAttribute(dq_post_t128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); e != cudaSuccess)
       return cuda_fail((int)e, "fl_dq_post: cudaFuncSetAttribute");
-    dq_post_t128_kernel<<<grid, 128, sm, st>>>(macc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16, per_row);
+    dq_post_t128_kernel<<<grid, 128, sm, st>>>(macc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16, per_row,
+                                               head_mult);
   } else {
     dq_post_rows64_kernel<<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, out_f16,
-                                                per_row);
+                                                per_row, head_mult);
   }
   return launch_result("fl_dq_post: kernel launch");
 }
 
 extern "C" int fl_dq_post(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s,
                           int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
-  return dq_post_launch(dq_acc, post_scale, mult, dq, b, s, h, d, unrotate, out_f16, 0, stream);
+  return dq_post_launch(dq_acc, post_scale, mult, dq, b, s, h, d, unrotate, out_f16, 0, nullptr, stream);
+}
+
+extern "C" int fl_dq_post_ex(const void* dq_acc, const float* post_scale, int32_t per_row, const float* head_mult, float mult,
+                             void* dq, int32_t b, int32_t s, int32_t h, int32_t d, int32_t unrotate, int32_t out_f16,
+                             void* stream) {
+  return dq_post_launch(dq_acc, post_scale, mult, dq, b, s, h, d, unrotate, out_f16, per_row ? 1 : 0, head_mult, stream);
 }
 
 extern "C" int fl_dq_post_rows(const void* dq_acc, const float* post_scale_rows, float mult, void* dq, int32_t b, int32_t s,
                                int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
-  return dq_post_launch(dq_acc, post_scale_rows, mult, dq, b, s, h, d, unrotate, out_f16, 1, stream);
+  return dq_post_launch(dq_acc, post_scale_rows, mult, dq, b, s, h, d, unrotate, out_f16, 1, nullptr, stream);
 }
 
 extern "C" int fl_dq_prescale_rows(const float* row_do, float* row_v, float* row_k, int32_t b, int32_t s, float unit,
@@ -278,6 +327,16 @@ extern "C" int fl_dq_prescale_rows(const float* row_do, float* row_v, float* row
   if (!row_do || !row_v || !row_k || !kernel_rows || !post_rows || b <= 0 || s <= 0) return FL_ERR_BAD_ARG;
   dq_prescale_rows_kernel<<<b, 1024, 0, (cudaStream_t)stream>>>(row_do, row_v, row_k, s, unit, kernel_rows, post_rows);
   return launch_result("fl_dq_prescale_rows: kernel launch");
+}
+
+extern "C" int fl_code_stats(const void* codes, const float* descale, int32_t b, int32_t s, int32_t h, int32_t d,
+                             float* tile_stats, void* stream) {
+  using namespace fl;
+  if (!codes || !descale || !tile_stats || b <= 0 || s <= 0 || (s % 128) || h <= 0) return FL_ERR_BAD_ARG;
+  if (d != 64 && d != 128) return FL_ERR_UNSUPPORTED;
+  if (h > 65535 || b > 65535) return FL_ERR_TOO_LARGE;
+  code_stats_kernel<<<dim3(s / 128, h, b), 128, 0, (cudaStream_t)stream>>>((const uint8_t*)codes, descale, s, h, d, tile_stats);
+  return launch_result("fl_code_stats: kernel launch");
 }
 
 extern "C" int fl_pack_rows(const void* src, void* dst, const int32_t* row_map, int32_t n_dst_rows, int32_t row_bytes,

@@ -159,9 +159,10 @@ def attn_args(q, k, v, *, causal, softmax_scale, mode=L.FL_MODE_FP8, flags=0, st
 
 def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L.FL_MODE_FP8, status=None,
              doc_start=None, doc_len=None, wait_cycles=0, token_local=False, window=None, p_group=False, seqused_k=None,
-             softcap=0.0):
+             softcap=0.0, o_mult=None):
     """Forward kernel on quantised operands. Returns (out (b, s_q, h, d), lse (b, h, s_q) float32, status).
-    p_group: group-frame P-hat (one UE8M0 exponent per query row and 32 keys) instead of the row frame."""
+    p_group: group-frame P-hat (one UE8M0 exponent per query row and 32 keys) instead of the row frame.
+    o_mult: (b, h_kv) f32 factor on the output rows (the mantissa of a V factor that is no power of two)."""
     qc = q["codes"]
     b, s_q, h, d = qc.shape
     dev = qc.device
@@ -178,6 +179,9 @@ def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L
                   doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local, window=window, seqused_k=seqused_k,
                   softcap=softcap)
     a.out, a.lse = L.ptr(out), L.ptr(lse)
+    if o_mult is not None:
+        assert o_mult.dtype == torch.float32 and o_mult.numel() == b * k["codes"].shape[2] and o_mult.is_contiguous()
+        a.o_mult = L.ptr(o_mult)
     L.check(L.load().fl_fwd(C.byref(a), _stream()), "fl_fwd")
     return out, lse, status
 
@@ -219,21 +223,35 @@ def dq_prescale_rows(row_do, row_v, row_k, *, unit=1.0):
     return ks, ps
 
 
-def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torch.bfloat16, per_row=False):
-    """dq (b, s, h, d) = cast(acc * post_scale[b, s / 128] * mult) (per_row: post_scale[b, s]), optionally rotated back.
-    acc is the f16 accumulator in the backward kernel's layout: (b, h, d, s) at d = 128, (b, h, s, d) at d = 64."""
+def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torch.bfloat16, per_row=False,
+            head_mult=None):
+    """dq (b, s, h, d) = cast(acc * post_scale[b, s / 128] * mult) (per_row: post_scale[b, s]; head_mult: times a (b, h)
+    factor), optionally rotated back. acc is the f16 accumulator in the backward kernel's layout: (b, h, d, s) at
+    d = 128, (b, h, s, d) at d = 64."""
     dq = torch.empty(b, s, h, d, dtype=out_dtype, device=acc.device)
     assert post_scale.numel() == (b * s if per_row else b * (s // 128))
-    fn = L.load().fl_dq_post_rows if per_row else L.load().fl_dq_post
-    L.check(fn(L.ptr(acc), L.ptr(post_scale), float(mult), L.ptr(dq), b, s, h, d, int(bool(unrotate)),
-               int(out_dtype == torch.float16), _stream()), "fl_dq_post")
+    if head_mult is not None:
+        assert head_mult.dtype == torch.float32 and head_mult.numel() == b * h and head_mult.is_contiguous()
+    L.check(L.load().fl_dq_post_ex(L.ptr(acc), L.ptr(post_scale), int(bool(per_row)), L.ptr(head_mult), float(mult),
+                                   L.ptr(dq), b, s, h, d, int(bool(unrotate)), int(out_dtype == torch.float16), _stream()),
+            "fl_dq_post_ex")
     return dq
+
+
+def code_stats(codes, descale):
+    """Tile statistics (b, h, s / 128, 2) of E4M3 codes (b, s, h, d) times descale (b, h): largest magnitude and largest
+    row sum of squares per 128-row tile, what the quantiser writes for operands it quantises itself."""
+    b, s, h, d = codes.shape
+    assert codes.element_size() == 1 and codes.is_contiguous() and descale.dtype == torch.float32 and descale.numel() == b * h
+    out = torch.empty(b, h, s // 128, 2, dtype=torch.float32, device=codes.device)
+    L.check(L.load().fl_code_stats(L.ptr(codes), L.ptr(descale), b, s, h, d, L.ptr(out), _stream()), "fl_code_stats")
+    return out
 
 
 def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax_scale, out_dtype=torch.bfloat16,
              mode=L.FL_MODE_FP8, had_dk=False, status=None, doc_start=None, doc_len=None, wait_cycles=0,
              token_local=False, dq_rowlocal=False, window=None, seqused_k=None, softcap=0.0, dq_order=None,
-             dq_scale_rows=None):
+             dq_scale_rows=None, dk_mult=None):
     """Backward main kernel on quantised operands. q / k / v / do: quantiser outputs (codes, fac). Adds the pre-scaled
     dQ partials into the f16 accumulator dq_acc of b * h * s_q * d elements ((b, h, d, s_q) at d = 128, (b, h, s_q, d)
     at d = 64) and returns (dk, dv, status), each (b, s_k, h_kv, d). dq_order: a zeroed (b, h, s_q / 128, 2) int32 table
@@ -256,6 +274,9 @@ def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax
     if dq_scale_rows is not None:      # one pre-scale per query row instead of dq_scale per query tile
         assert dq_scale_rows.dtype == torch.float32 and dq_scale_rows.numel() == b * q["codes"].shape[1]
         a.dq_scale_rows = L.ptr(dq_scale_rows)
+    if dk_mult is not None:             # the mantissa of a Q factor that is no power of two, per (batch row, kv head)
+        assert dk_mult.dtype == torch.float32 and dk_mult.numel() == b * h_kv and dk_mult.is_contiguous()
+        a.dk_mult = L.ptr(dk_mult)
     if dq_order is not None:
         assert dq_order.dtype == torch.int32 and dq_order.numel() == b * q["codes"].shape[2] * (q["codes"].shape[1] // 128) * 2
         a.dq_order = L.ptr(dq_order)

@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define FL_ABI_VERSION 5
+#define FL_ABI_VERSION 6
 
 /* fl_quant_args.flags */
 #define FL_Q_HADAMARD 1            /* rotate rows by diag(signs) H_128 / sqrt(128) before quantising (d = 128) */
@@ -139,6 +139,12 @@ typedef struct fl_attn_args {
    * pre-scale of its 1-CTA kernels, flash_attn/cute/device_scales.py:256-268), or NULL = dq_scale per query tile. With
    * it dq_scale is not read. Batched form only. */
   const float* dq_scale_rows;
+  /* Operands whose factor tables are not powers of two (pre-quantised E4M3 inputs with float descales, the reference's
+   * flash_attn/cute/lowprec/prequant_fa3.py): a block-scaled product takes only the exponent of a factor, so the mantissa
+   * (factor / 2^floor(log2 factor), in [1, 2)) is multiplied in afterwards. Forward: o_mult (b, h_kv) = V's mantissa, on
+   * the output rows. Backward: dk_mult (b, h_kv) = Q's mantissa, on dK (dQ takes K's in fl_dq_post_ex). NULL = 1. */
+  const float* o_mult;
+  const float* dk_mult;
 } fl_attn_args;
 
 /* Forward: O = softmax(scale Q K^T + mask) V, LSE.
@@ -168,6 +174,16 @@ int fl_dq_prescale_rows(const float* row_do, float* row_v, float* row_k, int32_t
  * back-rotation, where acc(b, h, s, c) is element [b, h, c, s] of the (b, h, d, s) accumulator at d = 128 (the backward
  * kernel produces transposed dQ tiles) and element [b, h, s, c] of the (b, h, s, d) accumulator at d = 64.
  * Replaces flash_attn/cute/dq_postprocess_cute.py:46 DQPostprocess / bwd_2cta8_side.dq_postprocess_2cta8. */
+/* fl_dq_post_ex: the general form. per_row: post_scale is (b, s) instead of (b, s/128); head_mult: (b, h) extra factor per
+ * head or NULL (the mantissa of K's factor with pre-quantised inputs). */
+int fl_dq_post_ex(const void* dq_acc, const float* post_scale, int32_t per_row, const float* head_mult, float mult, void* dq,
+                  int32_t b, int32_t s, int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream);
+/* Tile statistics of E4M3 codes times a factor per (batch row, head): tile_stats (b, h, s/128, 2) = the largest
+ * magnitude and the largest row sum of squares of codes * descale[b, h] per 128-row tile, the figures the quantiser
+ * writes for operands it quantises itself (the reference sizes the f16 dQ pre-scale of pre-quantised inputs from one
+ * read of the V codes, flash_attn/cute/lowprec/prequant_fa3.py:386-470). */
+int fl_code_stats(const void* codes, const float* descale, int32_t b, int32_t s, int32_t h, int32_t d, float* tile_stats,
+                  void* stream);
 /* fl_dq_post_rows: post_scale_rows is (b, s), one value per query row. */
 int fl_dq_post_rows(const void* dq_acc, const float* post_scale_rows, float mult, void* dq, int32_t b, int32_t s,
                     int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream);
