@@ -12,13 +12,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libflamia_b200.so")
 
 # status codes (csrc/sm100.cuh)
-ABI_VERSION = 6
+ABI_VERSION = 7
 FL_OK, FL_ERR_BAD_ARG, FL_ERR_CUDA, FL_ERR_UNSUPPORTED, FL_ERR_TOO_LARGE = 0, 1, 2, 3, 4
 FL_DEV_WAIT_TIMEOUT = 0x100
 FL_DEV_BAD_TABLE = 0x200
 ERR_NAMES = {1: "bad argument", 2: "CUDA error", 3: "unsupported configuration", 4: "size beyond the supported maximum"}
 
-FL_Q_HADAMARD, FL_Q_TOKEN_LOCAL, FL_Q_HADAMARD_NVFP4_ONLY = 1, 2, 4
+FL_Q_HADAMARD, FL_Q_TOKEN_LOCAL, FL_Q_HADAMARD_NVFP4_ONLY, FL_Q_O_PACKED = 1, 2, 4, 8
 FL_MODE_FP8, FL_MODE_FP4 = 0, 1
 FL_A_CAUSAL, FL_A_OUT_F16, FL_A_TOKEN_LOCAL, FL_A_DQ_ROWLOCAL, FL_A_HAD_DQ, FL_A_HAD_DK, FL_A_P_GROUP = 1, 2, 4, 8, 16, 32, 64
 
@@ -40,7 +40,7 @@ class AttnArgs(C.Structure):
                                   "dv", "doc_start", "doc_len")] + \
                [(n, i32) for n in ("n_docs", "b", "s_q", "s_k", "h", "h_kv", "d")] + [("softmax_scale", f32)] + \
                [(n, i32) for n in ("mode", "flags")] + [("status", vp), ("wait_cycles", i64)] + \
-               [(n, i32) for n in ("window_left_p1", "window_right_p1")] + [("seqused_k", vp), ("softcap", f32), ("dq_order", vp), ("dq_scale_rows", vp), ("o_mult", vp), ("dk_mult", vp)]
+               [(n, i32) for n in ("window_left_p1", "window_right_p1")] + [("seqused_k", vp), ("softcap", f32), ("dq_order", vp), ("dq_scale_rows", vp), ("o_mult", vp), ("dk_mult", vp), ("slot_src", vp), ("slot_rows", vp), ("out_rows", i32)]
 
 
 EXPORTS = {
@@ -54,6 +54,7 @@ EXPORTS = {
     "fl_dq_post_rows": (i32, [vp, vp, f32, vp, i32, i32, i32, i32, i32, i32, vp]),
     "fl_dq_post_ex": (i32, [vp, vp, i32, vp, f32, vp, i32, i32, i32, i32, i32, i32, vp]),
     "fl_code_stats": (i32, [vp, vp, i32, i32, i32, i32, vp, vp]),
+    "fl_dq_post_packed": (i32, [vp, vp, f32, vp, i32, i32, i32, i32, i32, vp, vp, vp]),
     "fl_dq_prescale_rows": (i32, [vp, vp, vp, i32, i32, f32, vp, vp, vp]),
     "fl_pack_rows": (i32, [vp, vp, vp, i32, i32, vp]),
     "fl_unpack_rows": (i32, [vp, vp, vp, i32, i32, vp]),

@@ -61,10 +61,12 @@ def _fwd_impl(q, k, v, docs: List[torch.Tensor], plan: int, docs_id: int):
     out, lse, state = _routes.forward(p, q, k, v, d, seqused_k)
     meta = None if d is None else (d.capacity, d.aligned)
     entry = _register_entry(plan, meta)
-    # batched form: the kernels' O / LSE ARE the op's outputs (the autograd node saves those itself, an op output may not
-    # alias another); documents: the padded O / LSE of the kernels stay in the state, the outputs are the unpacked copies.
+    # The kernels' O (and LSE, except under repacked documents, whose LSE keeps the aligned buffer's rows and is not
+    # returned) ARE the op's outputs, up to a view: the autograd node saves those itself and the backward rebuilds the
+    # kernels' shapes from them, because an op output may not alias another.
     # The entry handle rides along as a 0-d tensor so that the backward op needs no Python object.
-    state = list(state if d is not None else state[2:]) + [torch.tensor(entry, dtype=torch.int64)]
+    keep_lse = d is not None and not d.aligned
+    state = list(state[1:] if keep_lse else state[2:]) + [torch.tensor(entry, dtype=torch.int64)]
     return out, lse, state
 
 
@@ -80,8 +82,8 @@ def _fake_fwd(q, k, v, docs, plan, docs_id):
     lse_shape = (sh.h, sh.tot_q) if sh.aligned_varlen else ((0,) if is_docs else (sh.b, sh.h, sh.s_q))
     n_docs = int(docs[0].shape[0]) - 1 if (len(docs) > 0 and not p.fwd.seqused_k) else 0
     spec = _routes.state_spec(p, n_docs, q.dtype, capacity=int(docs[3].numel()) if len(docs) == 6 else None)
-    # as _fwd_impl: the batched form hands O / LSE out as the op's outputs, documents keep the padded ones in the state
-    state = [q.new_empty(shape, dtype=dt) for shape, dt in (spec if is_docs else spec[2:])]
+    # as _fwd_impl: O / LSE leave as the op's outputs; repacked documents keep the aligned buffer's LSE in the state
+    state = [q.new_empty(shape, dtype=dt) for shape, dt in (spec[1:] if (is_docs and not sh.aligned_varlen) else spec[2:])]
     state.append(torch.empty((), dtype=torch.int64))
     return torch.empty_like(q), q.new_empty(lse_shape, dtype=torch.float32), state
 
@@ -119,7 +121,12 @@ def _define(entry: str):
         if dout is None:
             return None, None, None, nodocs, None, None
         entry_id = int(saved[-1])
-        state = saved[2:] if _ENTRIES[entry_id][1] is not None else saved
+        meta = _ENTRIES[entry_id][1]
+        if meta is None:                     # batched: the outputs are the kernels' O / LSE
+            state = saved
+        else:                                # documents: the kernels saw one batch entry of (rows, h, d)
+            o = saved[0].reshape(1, -1, saved[0].shape[-2], saved[0].shape[-1])
+            state = [o, saved[1].unsqueeze(0)] + saved[2:] if meta[1] else [o] + saved[2:]
         dq, dk, dv = getattr(torch.ops.lowbit_attn, entry + "_bwd")(dout.contiguous(), state, entry_id)
         return dq, dk, dv, nodocs, None, None
 

@@ -168,7 +168,10 @@ def state_spec(plan, n_docs=0, dtype=torch.bfloat16, capacity=None):
     else:
         b, s_q, s_k = sh.b, sh.s_q, sh.s_k
     h, hk, d = sh.h, sh.h_kv, sh.d
-    spec = [((b, s_q, h, d), dtype), ((b, h, s_q), f32),                                       # O, LSE of the kernels
+    o_rows = s_q
+    if docs and not sh.aligned_varlen:      # repacked documents: O has the caller's packed rows
+        o_rows = sh.tot_q if sh.varlen else sh.b * sh.s_q
+    spec = [((b, o_rows, h, d), dtype), ((b, h, s_q), f32),                                    # O, LSE of the kernels
             ((b, s_q, h, d), f8), ((b, h, s_q // 32), f32), ((b, s_k, hk, d), f8), ((b, hk, s_k // 32), f32),
             ((b, s_k, hk, d), f8), ((b, hk, s_k // 32), f32), ((1,), i32)]                     # codes, factors, status
     if need_bwd:      # K / V statistics of the f16 dQ pre-scale: per 128-row tile and head, or per token
@@ -249,9 +252,12 @@ def forward(plan, q, k, v, docs, seqused_k=None, prequant=None):
                                row_stat=("norm2" if (f.qk_hadamard and not fp4) else "amax", k_rows) if rows else None, **qk_kw)
     vq = K.quantize_fp8_blocks(vp, output_tile_stats=need_bwd and not rows, token_local_exponents=tl, status=status,
                                packed_slots=slots, row_stat=("sumsq", v_rows) if rows else None)
+    # repacked documents: the kernel writes the caller's packed rows itself (out is (1, total, h, d))
+    total = (sh.tot_q if sh.varlen else sh.b * sh.s_q) if slots is not None else None
     out, lse, _ = K.attn_fwd(qq, kq, vq, causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=q.dtype, mode=mode,
                              status=status, token_local=tl, window=f.window, p_group=f.p_hat_frame == "group",
                              seqused_k=seqused_k, softcap=f.softcap,
+                             packed_out=None if slots is None else (slots[0], slots[1], total),
                              doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     state = [out, lse, qq["codes"], qq["fac"], kq["codes"], kq["fac"], vq["codes"], vq["fac"], status]
     if need_bwd:
@@ -264,7 +270,7 @@ def forward(plan, q, k, v, docs, seqused_k=None, prequant=None):
         state += [seqused_k]
     if docs is not None:
         state += [docs.start, docs.len] + ([] if docs.row_map is None else [docs.row_map, docs.slot_src, docs.slot_rows])
-        out_user = docs.unpack(out, sh.tot_q if sh.varlen else sh.b * sh.s_q)
+        out_user = out[0]                        # aligned: in place; repacked: the kernel wrote the packed rows
         if not sh.varlen:
             out_user = out_user.reshape(sh.b, sh.s_q, sh.h, sh.d)
         lse_user = lse[0] if sh.aligned_varlen else lse.new_zeros(0)     # (h, total_q) on the aligned form only
@@ -305,8 +311,11 @@ def backward(plan, state, dout, docs_meta):
             gp = gp.unsqueeze(0)
     else:
         gp = dout.contiguous()
-    b, s_q, h, d = out.shape
+    b, s_q, h, d = qc.shape                      # (the aligned buffer's rows; out has the packed rows under repacked documents)
     acc = torch.empty(b, h, s_q, d, dtype=torch.float16, device=out.device)
+    packed_out = None
+    if docs is not None and not docs.aligned:
+        packed_out = (docs.slot_src, docs.slot_rows, int(out.shape[1]))
     rows = bw.dq_prescale == "causal_row"
     do_rows = torch.zeros(b, s_q, dtype=torch.float32, device=out.device) if rows else None
     gq = K.quantize_fp8_blocks(gp, compute_d_with_output=out, shifted_log2_lse_from=lse, log2_lse_shift=P_SHIFT_LOG2,
@@ -324,17 +333,15 @@ def backward(plan, state, dout, docs_meta):
                            causal=f.causal, softmax_scale=plan.softmax_scale, out_dtype=out.dtype,
                            mode=L.FL_MODE_FP4 if fp4 else L.FL_MODE_FP8, had_dk=had8, status=status,
                            token_local=tl, dq_rowlocal=bw.ds_dq_rowlocal == "all", window=f.window, seqused_k=seqused_k,
-                           softcap=f.softcap, dk_mult=dk_mult,
+                           softcap=f.softcap, dk_mult=dk_mult, packed_out=packed_out,
                            dq_order=torch.zeros(b, h, s_q // 128, 2, dtype=torch.int32, device=out.device)
                            if bw.deterministic else None,
                            doc_start=None if docs is None else docs.start, doc_len=None if docs is None else docs.len)
     dq = K.dq_post(acc, ps, plan.softmax_scale, b=b, s=s_q, h=h, d=d, unrotate=had8, out_dtype=out.dtype, per_row=rows,
-                   head_mult=dq_mult)
+                   head_mult=dq_mult, packed_out=packed_out)
     _note_status(status)
     if docs is not None:
-        tq = sh.tot_q if sh.varlen else sh.b * sh.s_q
-        tk = sh.tot_k if sh.varlen else sh.b * sh.s_k
-        dq, dk, dv = docs.unpack(dq, tq), docs.unpack(dk, tk), docs.unpack(dv, tk)
+        dq, dk, dv = dq[0], dk[0], dv[0]         # aligned: in place; repacked: the kernels wrote the packed rows
         if not sh.varlen:
             dq = dq.reshape(sh.b, sh.s_q, sh.h, sh.d)
             dk, dv = dk.reshape(sh.b, sh.s_k, sh.h_kv, sh.d), dv.reshape(sh.b, sh.s_k, sh.h_kv, sh.d)

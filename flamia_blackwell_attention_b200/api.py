@@ -20,11 +20,11 @@ __all__ = ["flash_attn_fp4", "flash_attn_fp8"]
 
 _REPACK_WARNED = False
 REPACK_WARNING = (
-    "flash_attn_{entry} got cu_seqlens_q / cu_seqlens_k without seqused_q / seqused_k. This library then gathers every "
-    "document into a padded buffer whose document starts are multiples of 128 and scatters the results back: one more "
-    "read and write of q, k, v, o and of dO, dQ, dK, dV. To avoid the copies, lay the documents out at starts that are "
-    "multiples of 128 yourself (cu_seqlens = those starts, total % 128 == 0) and pass the true lengths as seqused_q / "
-    "seqused_k. (Warned once.)")
+    "flash_attn_{entry} got cu_seqlens_q / cu_seqlens_k without seqused_q / seqused_k. No tensor is copied (the kernels "
+    "read and write the packed rows in place), but the document tables are rebuilt on the device on every call (a dozen "
+    "small launches) and the intermediates take a padded buffer of up to 127 extra rows per document. Build the tables "
+    "once with DocMaps.from_cu_seqlens(...) and pass doc_maps=, or lay the documents out at starts that are multiples of "
+    "128 and pass the true lengths as seqused_q / seqused_k. (Warned once.)")
 
 
 @dataclass(frozen=True)

@@ -55,6 +55,8 @@ struct BwdParams {
   const float* dq_scale;
   const float* dq_scale_rows;   // (b, s_q) per query row instead of dq_scale per query tile, or null
   const float* dk_mult;         // (b, h_kv) factor on dK (Q's mantissa with float descales), or null
+  const int32_t* slot_src;      // packed output: packed row of each 128-row slot of the aligned buffer (-1: empty), or null
+  const int32_t* slot_rows;     // packed output: real rows of each slot
   const uint8_t* sfq4;   // FL_MODE_FP4: E4M3 scale atoms of the NVFP4 Q / K copies (1 KB per 128-row tile)
   const uint8_t* sfk4;
   void* dk;
@@ -898,6 +900,15 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         uint8_t* stage0 = (D == 128) ? ((x == 0 ? sK : sV) + kb * TILE_BYTES) : (sOut64 + x * 16384);
         uint8_t* stage1 = EPI2 ? (sOut2 + x * 16384) : stage0;
         const CUtensorMap* tm_out = (x == 0) ? &tm_dv : &tm_dk;
+        // packed output: the key tile is slot T.k0 / 128 of the aligned buffer; its rows go to the packed rows out_row ..
+        // + out_n of the caller's tensor: a full slot as TMA stores, a document's last rows row by row
+        int out_row = T.k0, out_n = T.nk > 0 ? 128 : 0;
+        if (p.slot_src) {
+          out_row = T.nk > 0 ? p.slot_src[T.k0 / 128] : -1;
+          out_n = (T.nk > 0 && out_row >= 0) ? min(p.slot_rows[T.k0 / 128], 128) : 0;
+        }
+        const bool by_rows = p.slot_src && out_n < 128;   // (CTA-uniform)
+        uint16_t* out_base = reinterpret_cast<uint16_t*>(x == 0 ? p.dv : p.dk);
 #pragma unroll
         for (int pass = 0; pass < D / 64; ++pass) {
           uint8_t* stage = pass == 0 ? stage0 : stage1;
@@ -916,17 +927,24 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 w[e] = pack_bf16x2(a, b2);
               }
             }
-            sts128(srow + ((c8 ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+            if (by_rows) {
+              if (r < out_n)
+                *reinterpret_cast<uint4*>(out_base + ((size_t)(out_row + r) * p.h_kv + hkv) * D + 64 * pass + 8 * c8) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+              sts128(srow + ((c8 ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+            }
           }
+          if (by_rows) continue;
           const bool last = pass + 1 == D / 64;
           if (EPI2 && !last) continue;                    // both boxes are announced together
           fence_proxy_async();
           mbar_arrive_warp(&bars[BB_EPI + x]);            // the warpgroup's four warps have written their rows
           if (!(ok = mbar_wait(&bars[BB_EPI + x], epi & 1, p.ctl, abortp, 38))) break;
           ++epi;
-          if (r == 0 && T.nk > 0) {
-            if (EPI2) tma_store_4d(tm_out, stage0, 0, hkv, T.k0, T.bat);
-            tma_store_4d(tm_out, stage, 64 * pass, hkv, T.k0, T.bat);
+          if (r == 0 && out_n == 128) {
+            if (EPI2) tma_store_4d(tm_out, stage0, 0, hkv, out_row, T.bat);
+            tma_store_4d(tm_out, stage, 64 * pass, hkv, out_row, T.bat);
             tma_store_commit();
             if (!last) tma_store_wait_read<0>();          // the one buffer is written again by the next pass
           }
@@ -985,13 +1003,15 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   if ((rc = make_rows_map(&mk4, fp4 ? (const void*)a->k4 : (const void*)a->k_codes, a->b, a->s_k, a->h_kv, fp4 ? 64 : a->d,
                           128)))
     return rc;
-  if ((rc = make_rows_map_16(&mdk, a->dk, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
-  if ((rc = make_rows_map_16(&mdv, a->dv, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
+  if ((rc = make_rows_map_16(&mdk, a->dk, a->b, a->slot_src ? a->out_rows : a->s_k, a->h_kv, a->d, 128))) return rc;
+  if ((rc = make_rows_map_16(&mdv, a->dv, a->b, a->slot_src ? a->out_rows : a->s_k, a->h_kv, a->d, 128))) return rc;
   BwdParams p;
   p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.fac_do = a->fac_do; p.lse_log2 = a->lse_log2;
   p.d_rows = a->d_rows; p.dq_scale = a->dq_scale; p.dq_scale_rows = a->dq_scale_rows; p.dk = a->dk; p.dv = a->dv;
   p.dk_mult = a->dk_mult;
   if (a->dk_mult && a->doc_start) return FL_ERR_UNSUPPORTED;            // per-(batch row, head) factors: the batched form
+  p.slot_src = a->slot_src; p.slot_rows = a->slot_rows;
+  if (a->slot_src && (!a->doc_start || !a->slot_rows || a->out_rows <= 0)) return FL_ERR_BAD_ARG;
   if (a->dq_scale_rows && a->doc_start) return FL_ERR_UNSUPPORTED;      // per-row pre-scale: the batched form
   p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;

@@ -48,7 +48,10 @@ static constexpr int KV_STAGES = 3;
 static constexpr int Q_STRIDE = 16384;            // bytes between Q tile buffers (also the output staging: 128 rows x 128 B)
 static constexpr float P_LOG2_OFFSET = 4.0f;      // row frame: P-hat = 2^(x - m + 4) keeps small probabilities out of E4M3 subnormals
 static constexpr float P_LOG2_448 = 8.807354922057604f;   // group frame: the row maximum sits at 448 before the group bias
-static constexpr long long STAGE_SKEW_CLOCKS = 1000;   // see the UMMA issuer's prologue
+#ifndef FL_STAGE_SKEW
+#define FL_STAGE_SKEW 1000
+#endif
+static constexpr long long STAGE_SKEW_CLOCKS = FL_STAGE_SKEW;   // see the UMMA issuer's prologue
 static constexpr float RESCALE_THRESHOLD = 4.0f;  // the running maximum is refreshed only when it grew by more than this
 
 struct FwdParams {
@@ -62,6 +65,9 @@ struct FwdParams {
   const int32_t* doc_len;
   const int32_t* seqused_k;   // batched form: valid keys per batch row, or null
   const float* o_mult;        // (b, h_kv) factor on the output rows (V's mantissa with float descales), or null
+  const int32_t* slot_src;    // packed output: packed row of each 128-row slot of the aligned buffer (-1: empty), or null
+  const int32_t* slot_rows;   // packed output: real rows of each slot
+  void* out;                  // packed output: the (out_rows, h, d) tensor (row stores of a document's last rows)
   int n_docs;
   int b, s_q, s_k, h, h_kv;
   float scale_log2;
@@ -583,6 +589,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const float inv_l = ((l_sum > 0.f) ? 1.0f / l_sum : 0.f) * (p.o_mult ? p.o_mult[bh_k] : 1.0f);
       uint8_t* stage = sQ + (2 * kb + i) * Q_STRIDE;
       const uint32_t srow = smem_u32(stage) + r * 128;
+      // packed output: this stage's 128 rows are slot (T.q0 + 128 i) / 128 of the aligned buffer; they go to the packed
+      // rows out_row .. + out_n of the caller's tensor: a full slot as TMA stores, a document's last rows row by row
+      int out_row = T.q0 + 128 * i, out_n = stage_present ? 128 : 0;
+      if (p.slot_src) {
+        const int slot = (T.q0 + 128 * i) / 128;
+        out_row = stage_present ? p.slot_src[slot] : -1;
+        out_n = (stage_present && out_row >= 0) ? min(p.slot_rows[slot], 128) : 0;
+      }
+      const bool by_rows = p.slot_src && out_n < 128;    // (warpgroup-uniform)
 #pragma unroll 1
       for (int pass = 0; pass < D / 64; ++pass) {
 #pragma unroll
@@ -610,15 +625,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 w[e] = pack_bf16x2(a, b2);
               }
             }
-            fwd_sts128(srow + (((cc * 4 + q4) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+            if (by_rows) {
+              if (r < out_n)
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) +
+                                          ((size_t)(out_row + r) * p.h + head) * D + 64 * pass + 8 * (cc * 4 + q4)) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+              fwd_sts128(srow + (((cc * 4 + q4) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+            }
           }
         }
+        if (by_rows) continue;
         fence_proxy_async();
         mbar_arrive_warp(&bars[B_EPI + i]);             // the warpgroup's four warps have written their rows
         if (!(ok = mbar_wait(&bars[B_EPI + i], epi & 1, p.ctl, abortp, 38))) break;
         ++epi;
-        if (r == 0 && stage_present) {
-          tma_store_4d(&tm_o, stage, 64 * pass, head, T.q0 + 128 * i, T.bat);
+        if (r == 0 && out_n == 128) {
+          tma_store_4d(&tm_o, stage, 64 * pass, head, out_row, T.bat);
           tma_store_commit();
           tma_store_wait_read<0>();      // the shared-memory source must outlive the copy; the writes complete with the grid
         }
@@ -668,7 +691,7 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   if ((rc = make_rows_map(&mq, fp4 ? a->q4 : a->q_codes, a->b, a->s_q, a->h, fp4 ? a->d / 2 : a->d, 128))) return rc;
   if ((rc = make_rows_map(&mk, fp4 ? a->k4 : a->k_codes, a->b, a->s_k, a->h_kv, fp4 ? a->d / 2 : a->d, 128))) return rc;
   if ((rc = make_rows_map(&mv, a->v_codes, a->b, a->s_k, a->h_kv, a->d, 128))) return rc;
-  if ((rc = make_rows_map_16(&mo, a->out, a->b, a->s_q, a->h, a->d, 128))) return rc;
+  if ((rc = make_rows_map_16(&mo, a->out, a->b, a->slot_src ? a->out_rows : a->s_q, a->h, a->d, 128))) return rc;
   FwdParams p;
   p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.lse = a->lse;
   p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
@@ -676,6 +699,8 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   p.seqused_k = a->seqused_k;
   p.o_mult = a->o_mult;
   if (a->o_mult && a->doc_start) return FL_ERR_UNSUPPORTED;      // per-(batch row, head) factors: the batched form
+  p.slot_src = a->slot_src; p.slot_rows = a->slot_rows; p.out = a->out;
+  if (a->slot_src && (!a->doc_start || !a->slot_rows || a->out_rows <= 0)) return FL_ERR_BAD_ARG;
   p.b = a->b; p.s_q = a->s_q; p.s_k = a->s_k; p.h = a->h; p.h_kv = a->h_kv;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.causal = (a->flags & FL_A_CAUSAL) ? 1 : 0;

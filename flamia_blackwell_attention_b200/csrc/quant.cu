@@ -39,6 +39,7 @@ struct QuantParams {
   float* tile_stats;      // (b, h, s/128, 2): [amax of the values quantised, max row sum of squares] or null
   uint32_t* row_stat;     // (b, s) per-token maximum over the heads (float bits, zero on entry) or null
   int row_stat_kind;      // 1 = sum of squares, 2 = largest magnitude, 3 = 2-norm
+  int o_packed;           // packed source: the forward output o has the packed rows of x (else the outputs' rows)
   int b, s, h;
   const int32_t* slot_src;   // packed source: first source row of each 128-row slot of the output (-1: an empty slot), or null
   const int32_t* slot_rows;  // packed source: valid rows of each slot (the rest of the slot reads as zero)
@@ -114,14 +115,19 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     // packed source (documents stored back to back): the slot's rows start at an arbitrary row of the (1, total, h, d)
     // tensor; only the innermost TMA coordinate has an alignment rule. An empty slot loads nothing of x.
     const int xrow = PK ? p.slot_src[tile] : tile * QT;
-    mbar_arrive_expect_tx(&full[st], (xrow >= 0 ? TILE_B : 0) + (PRO ? TILE_B : 0));
+    mbar_arrive_expect_tx(&full[st], (xrow >= 0 ? TILE_B : 0) + ((PRO && (xrow >= 0 || !(PK && p.o_packed))) ? TILE_B : 0));
     if (xrow >= 0) {
       tma_load_4d(dst, &tm_x, &full[st], 0, head, xrow, bat);
       if (D == 128) tma_load_4d(dst + TILE_B / 2, &tm_x, &full[st], 64, head, xrow, bat);
     }
     if (PRO) {
-      tma_load_4d(dst + TILE_B, &tm_o, &full[st], 0, head, tile * QT, bat);
-      if (D == 128) tma_load_4d(dst + TILE_B + TILE_B / 2, &tm_o, &full[st], 64, head, tile * QT, bat);
+      // (packed source: the forward output has the packed rows too; an empty slot's stage keeps what it held, and its
+      // rows read as zero below)
+      const int orow = (PK && p.o_packed) ? xrow : tile * QT;
+      if (orow >= 0) {
+        tma_load_4d(dst + TILE_B, &tm_o, &full[st], 0, head, orow, bat);
+        if (D == 128) tma_load_4d(dst + TILE_B + TILE_B / 2, &tm_o, &full[st], 64, head, orow, bat);
+      }
     }
   };
   if (tid == 0) {
@@ -309,7 +315,10 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     uint4 o_raw[NJ];     // prologue: the forward output's row, kept as read until the codes exist
     if (PRO) {
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) o_raw[j] = lds_chunk(tile_addr + TILE_B, j);
+      for (int j = 0; j < NJ; ++j) {
+        o_raw[j] = lds_chunk(tile_addr + TILE_B, j);
+        if (PK && p.o_packed && !row_live) o_raw[j] = make_uint4(0, 0, 0, 0);
+      }
     }
 
     // ---- exponents: per token (4 lanes) and per 32-token block (4 warps)
@@ -525,7 +534,8 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   CUtensorMap mx, mo;
   int rc;
   if ((rc = make_rows_map_16(&mx, a->x, a->b, packed ? a->src_rows : a->s, a->h, a->d, 128))) return rc;
-  if ((rc = make_rows_map_16(&mo, pro ? a->o : a->x, a->b, a->s, a->h, a->d, 128))) return rc;
+  p.o_packed = (packed && (a->flags & FL_Q_O_PACKED)) ? 1 : 0;
+  if ((rc = make_rows_map_16(&mo, pro ? a->o : a->x, a->b, p.o_packed ? a->src_rows : a->s, a->h, a->d, 128))) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const bool wt = a->codes_t != nullptr;
   if (a->d == 64) {

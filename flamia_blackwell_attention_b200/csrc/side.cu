@@ -97,17 +97,22 @@ __device__ __forceinline__ uint32_t cvt_out2(float a, float b, int out_f16) {
 // head dim 64: the accumulator is (b, h, s, 64); a straight scaled copy into the (b, s, h, 64) gradient
 __global__ void __launch_bounds__(128) dq_post_rows64_kernel(const __half* __restrict__ acc, const float* __restrict__ post,
                                                              uint16_t* __restrict__ dq, int s, int h, float mult,
-                                                             int out_f16, int per_row, const float* __restrict__ head_mult) {
+                                                             int out_f16, int per_row, const float* __restrict__ head_mult,
+                                                             const int32_t* __restrict__ slot_src,
+                                                             const int32_t* __restrict__ slot_rows) {
   constexpr int D = 64, CPR = D / 8;
   const int tile = blockIdx.x, head = blockIdx.y, bat = blockIdx.z, tid = threadIdx.x;
   const int t0 = tile * 128;
   if (head_mult) mult *= head_mult[(size_t)bat * h + head];
   const __half* src = acc + (((size_t)bat * h + head) * s + t0) * D;
   const float sc_tile = per_row ? 0.f : post[(size_t)bat * (s / 128) + tile] * mult;
-  uint16_t* dst = dq + (((size_t)bat * s + t0) * h + head) * D;
+  // packed output: the tile's rows go to the packed rows slot_src[tile] .. + slot_rows[tile] of dq
+  const int n_rows = slot_src ? (slot_src[tile] >= 0 ? min(slot_rows[tile], 128) : 0) : 128;
+  uint16_t* dst = dq + (((size_t)bat * s + (slot_src ? (n_rows ? slot_src[tile] : 0) : t0)) * h + head) * D;
   const size_t row_stride = (size_t)h * D;
   for (int i = tid; i < 128 * CPR; i += 128) {
     const int r = i / CPR, c = i % CPR;
+    if (r >= n_rows) continue;
     const float sc = per_row ? post[(size_t)bat * s + t0 + r] * mult : sc_tile;
     uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)r * D + c * 8);
     const __half2* hv = reinterpret_cast<const __half2*>(&v);
@@ -128,7 +133,9 @@ __global__ void __launch_bounds__(128) dq_post_rows64_kernel(const __half* __res
 __global__ void __launch_bounds__(128) dq_post_t128_kernel(const __grid_constant__ CUtensorMap tm_acc,
                                                            const float* __restrict__ post, uint16_t* __restrict__ dq,
                                                            int s, int h, float mult, int unrotate, int out_f16,
-                                                           int per_row, const float* __restrict__ head_mult) {
+                                                           int per_row, const float* __restrict__ head_mult,
+                                                           const int32_t* __restrict__ slot_src,
+                                                           const int32_t* __restrict__ slot_rows) {
   constexpr int D = 128, ROWB = D * 2 + 16, CPR = D / 8;
   extern __shared__ __align__(1024) uint8_t sm_raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sm_raw) + 1023) & ~uintptr_t(1023));
@@ -197,11 +204,14 @@ __global__ void __launch_bounds__(128) dq_post_t128_kernel(const __grid_constant
       *reinterpret_cast<uint4*>(rowo + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     __syncthreads();
-    uint16_t* dst = dq + (((size_t)bat * s + t0) * h + head) * D;
+    // packed output: the tile's rows go to the packed rows slot_src[tile] .. + slot_rows[tile] of dq
+    const int n_rows = slot_src ? (slot_src[tile] >= 0 ? min(slot_rows[tile], 128) : 0) : 128;
+    uint16_t* dst = dq + (((size_t)bat * s + (slot_src ? (n_rows ? slot_src[tile] : 0) : t0)) * h + head) * D;
     const size_t row_stride = (size_t)h * D;
     for (int i = tid; i < 128 * CPR; i += 128) {
       const int r = i / CPR, c = i % CPR;
-      *reinterpret_cast<uint4*>(dst + (size_t)r * row_stride + c * 8) = *reinterpret_cast<const uint4*>(s_out + r * ROWB + c * 16);
+      if (r < n_rows)
+        *reinterpret_cast<uint4*>(dst + (size_t)r * row_stride + c * 8) = *reinterpret_cast<const uint4*>(s_out + r * ROWB + c * 16);
     }
   } else {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);     // loads into this CTA's shared memory may still land
@@ -282,7 +292,7 @@ extern "C" int fl_dq_prescale(const float* stats_do, const float* stats_v, const
 // transposed dQ tiles), (b, h, s, d) for head_dim 64.
 static int dq_post_launch(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t b, int32_t s,
                           int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, int per_row, const float* head_mult,
-                          void* stream) {
+                          void* stream, const int32_t* slot_src = nullptr, const int32_t* slot_rows = nullptr) {
   using namespace fl;
   if (!dq_acc || !post_scale || !dq || b <= 0 || s <= 0 || (s % 128) || h <= 0) return FL_ERR_BAD_ARG;
   if ((d != 64 && d != 128) || (unrotate && d != 128)) return FL_ERR_UNSUPPORTED;
@@ -297,10 +307,10 @@ static int dq_post_launch(const void* dq_acc, const float* post_scale, float mul
     if (cudaError_t e = cudaFuncSetAttribute(dq_post_t128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); e != cudaSuccess)
       return cuda_fail((int)e, "fl_dq_post: cudaFuncSetAttribute");
     dq_post_t128_kernel<<<grid, 128, sm, st>>>(macc, post_scale, (uint16_t*)dq, s, h, mult, unrotate, out_f16, per_row,
-                                               head_mult);
+                                               head_mult, slot_src, slot_rows);
   } else {
     dq_post_rows64_kernel<<<grid, 128, 0, st>>>((const __half*)dq_acc, post_scale, (uint16_t*)dq, s, h, mult, out_f16,
-                                                per_row, head_mult);
+                                                per_row, head_mult, slot_src, slot_rows);
   }
   return launch_result("fl_dq_post: kernel launch");
 }
@@ -319,6 +329,13 @@ extern "C" int fl_dq_post_ex(const void* dq_acc, const float* post_scale, int32_
 extern "C" int fl_dq_post_rows(const void* dq_acc, const float* post_scale_rows, float mult, void* dq, int32_t b, int32_t s,
                                int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream) {
   return dq_post_launch(dq_acc, post_scale_rows, mult, dq, b, s, h, d, unrotate, out_f16, 1, nullptr, stream);
+}
+
+extern "C" int fl_dq_post_packed(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t s, int32_t h,
+                                 int32_t d, int32_t unrotate, int32_t out_f16, const int32_t* slot_src,
+                                 const int32_t* slot_rows, void* stream) {
+  if (!slot_src || !slot_rows) return fl::FL_ERR_BAD_ARG;
+  return dq_post_launch(dq_acc, post_scale, mult, dq, 1, s, h, d, unrotate, out_f16, 0, nullptr, stream, slot_src, slot_rows);
 }
 
 extern "C" int fl_dq_prescale_rows(const float* row_do, float* row_v, float* row_k, int32_t b, int32_t s, float unit,

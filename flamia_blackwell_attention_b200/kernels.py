@@ -96,7 +96,11 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
     keep = []
     if compute_d_with_output is not None:
         o = compute_d_with_output.contiguous()
-        assert tuple(o.shape) == (b, s, h, d) and o.dtype == x.dtype
+        if packed_slots is not None and o.numel() == x.numel():      # the forward output has x's packed rows
+            a.flags = flags | L.FL_Q_O_PACKED
+        else:
+            assert tuple(o.shape) == (b, s, h, d)
+        assert o.dtype == x.dtype
         keep.append(o)
         a.o = L.ptr(o)
         out["D"] = torch.empty(b, h, s, dtype=torch.float32, device=dev)
@@ -159,10 +163,12 @@ def attn_args(q, k, v, *, causal, softmax_scale, mode=L.FL_MODE_FP8, flags=0, st
 
 def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L.FL_MODE_FP8, status=None,
              doc_start=None, doc_len=None, wait_cycles=0, token_local=False, window=None, p_group=False, seqused_k=None,
-             softcap=0.0, o_mult=None):
+             softcap=0.0, o_mult=None, packed_out=None):
     """Forward kernel on quantised operands. Returns (out (b, s_q, h, d), lse (b, h, s_q) float32, status).
     p_group: group-frame P-hat (one UE8M0 exponent per query row and 32 keys) instead of the row frame.
-    o_mult: (b, h_kv) f32 factor on the output rows (the mantissa of a V factor that is no power of two)."""
+    o_mult: (b, h_kv) f32 factor on the output rows (the mantissa of a V factor that is no power of two).
+    packed_out = (slot_src, slot_rows, total): documents; out is (1, total, h, d) with the documents stored back to back
+    (the kernel writes the caller's packed rows itself); lse keeps the aligned buffer's rows."""
     qc = q["codes"]
     b, s_q, h, d = qc.shape
     dev = qc.device
@@ -171,7 +177,8 @@ def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L
     # documents: the kernel writes only the rows of its documents; padding rows and unused tail tiles must read as
     # zeros afterwards (the backward prologue forms rowsum(O * dO) for every row of the buffer)
     alloc = torch.empty if doc_start is None else torch.zeros
-    out = alloc(b, s_q, h, d, dtype=out_dtype, device=dev)
+    out = torch.empty(1, int(packed_out[2]), h, d, dtype=out_dtype, device=dev) if packed_out is not None else \
+        alloc(b, s_q, h, d, dtype=out_dtype, device=dev)
     lse = alloc(b, h, s_q, dtype=torch.float32, device=dev)
     a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode,
                   flags=(L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0) | (L.FL_A_P_GROUP if p_group else 0),
@@ -179,6 +186,8 @@ def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L
                   doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local, window=window, seqused_k=seqused_k,
                   softcap=softcap)
     a.out, a.lse = L.ptr(out), L.ptr(lse)
+    if packed_out is not None:
+        a.slot_src, a.slot_rows, a.out_rows = L.ptr(packed_out[0]), L.ptr(packed_out[1]), int(packed_out[2])
     if o_mult is not None:
         assert o_mult.dtype == torch.float32 and o_mult.numel() == b * k["codes"].shape[2] and o_mult.is_contiguous()
         a.o_mult = L.ptr(o_mult)
@@ -224,10 +233,17 @@ def dq_prescale_rows(row_do, row_v, row_k, *, unit=1.0):
 
 
 def dq_post(acc, post_scale, mult, *, b, s, h, d, unrotate=False, out_dtype=torch.bfloat16, per_row=False,
-            head_mult=None):
+            head_mult=None, packed_out=None):
     """dq (b, s, h, d) = cast(acc * post_scale[b, s / 128] * mult) (per_row: post_scale[b, s]; head_mult: times a (b, h)
     factor), optionally rotated back. acc is the f16 accumulator in the backward kernel's layout: (b, h, d, s) at
     d = 128, (b, h, s, d) at d = 64."""
+    if packed_out is not None:      # documents: dq (1, total, h, d) takes the packed rows (see attn_fwd)
+        assert b == 1 and not per_row and head_mult is None
+        dq = torch.empty(1, int(packed_out[2]), h, d, dtype=out_dtype, device=acc.device)
+        L.check(L.load().fl_dq_post_packed(L.ptr(acc), L.ptr(post_scale), float(mult), L.ptr(dq), s, h, d, int(bool(unrotate)),
+                                           int(out_dtype == torch.float16), L.ptr(packed_out[0]), L.ptr(packed_out[1]),
+                                           _stream()), "fl_dq_post_packed")
+        return dq
     dq = torch.empty(b, s, h, d, dtype=out_dtype, device=acc.device)
     assert post_scale.numel() == (b * s if per_row else b * (s // 128))
     if head_mult is not None:
@@ -251,7 +267,7 @@ def code_stats(codes, descale):
 def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax_scale, out_dtype=torch.bfloat16,
              mode=L.FL_MODE_FP8, had_dk=False, status=None, doc_start=None, doc_len=None, wait_cycles=0,
              token_local=False, dq_rowlocal=False, window=None, seqused_k=None, softcap=0.0, dq_order=None,
-             dq_scale_rows=None, dk_mult=None):
+             dq_scale_rows=None, dk_mult=None, packed_out=None):
     """Backward main kernel on quantised operands. q / k / v / do: quantiser outputs (codes, fac). Adds the pre-scaled
     dQ partials into the f16 accumulator dq_acc of b * h * s_q * d elements ((b, h, d, s_q) at d = 128, (b, h, s_q, d)
     at d = 64) and returns (dk, dv, status), each (b, s_k, h_kv, d). dq_order: a zeroed (b, h, s_q / 128, 2) int32 table
@@ -261,13 +277,16 @@ def attn_bwd(q, k, v, do, *, lse_log2, d_rows, dq_acc, dq_scale, causal, softmax
     dev = kc.device
     if status is None:
         status = new_status(dev)
-    dk = torch.empty(b, s_k, h_kv, d, dtype=out_dtype, device=dev)
-    dv = torch.empty(b, s_k, h_kv, d, dtype=out_dtype, device=dev)
+    rows_out = s_k if packed_out is None else int(packed_out[2])      # packed_out: dk, dv (1, total, h_kv, d), see attn_fwd
+    dk = torch.empty(b, rows_out, h_kv, d, dtype=out_dtype, device=dev)
+    dv = torch.empty(b, rows_out, h_kv, d, dtype=out_dtype, device=dev)
     flags = (L.FL_A_OUT_F16 if out_dtype == torch.float16 else 0) | (L.FL_A_HAD_DK if had_dk else 0) | \
         (L.FL_A_DQ_ROWLOCAL if dq_rowlocal else 0)
     a = attn_args(q, k, v, causal=causal, softmax_scale=softmax_scale, mode=mode, flags=flags, status=status,
                   doc_start=doc_start, doc_len=doc_len, wait_cycles=wait_cycles, token_local=token_local, window=window,
                   seqused_k=seqused_k, softcap=softcap)
+    if packed_out is not None:
+        a.slot_src, a.slot_rows, a.out_rows = L.ptr(packed_out[0]), L.ptr(packed_out[1]), int(packed_out[2])
     a.do_codes, a.fac_do = L.ptr(do["codes"]), L.ptr(do["token_factors" if token_local else "fac"])
     a.lse_log2, a.d_rows, a.dq_acc, a.dq_scale = L.ptr(lse_log2), L.ptr(d_rows), L.ptr(dq_acc), L.ptr(dq_scale)
     a.dk, a.dv = L.ptr(dk), L.ptr(dv)

@@ -18,12 +18,13 @@
 extern "C" {
 #endif
 
-#define FL_ABI_VERSION 6
+#define FL_ABI_VERSION 7
 
 /* fl_quant_args.flags */
 #define FL_Q_HADAMARD 1            /* rotate rows by diag(signs) H_128 / sqrt(128) before quantising (d = 128) */
 #define FL_Q_TOKEN_LOCAL 2         /* codes / sf_tok from each token's own exponent */
 #define FL_Q_HADAMARD_NVFP4_ONLY 4 /* rotate only the values of the NVFP4 copy; the E4M3 codes stay unrotated */
+#define FL_Q_O_PACKED 8            /* packed source with the prologue: o has x's packed rows (else the outputs' rows) */
 
 /* Fused block-scaled quantiser + backward prologue.
  * Replaces flash_attn/cute/quant/fp8.py:2512 quantize_fp8_blocks (kernel :1639), the fused NVFP4 S-operand copy
@@ -145,6 +146,14 @@ typedef struct fl_attn_args {
    * the output rows. Backward: dk_mult (b, h_kv) = Q's mantissa, on dK (dQ takes K's in fl_dq_post_ex). NULL = 1. */
   const float* o_mult;
   const float* dk_mult;
+  /* Packed documents whose outputs go straight to the caller's packed tensors (with doc_start / doc_len; the counterpart
+   * of fl_quant_args.slot_src on the way out): out (forward) and dk, dv (backward) are (out_rows, heads, d) with the
+   * documents stored back to back; slot_src[i] = the packed row of row 128 i of the aligned buffer the kernels work in
+   * (-1: an empty slot), slot_rows[i] = how many rows of that slot are real. A full slot leaves as one TMA store, a
+   * document's last rows as row stores. NULL = the outputs have the aligned buffer's rows. lse keeps those rows. */
+  const int32_t* slot_src;
+  const int32_t* slot_rows;
+  int32_t out_rows;
 } fl_attn_args;
 
 /* Forward: O = softmax(scale Q K^T + mask) V, LSE.
@@ -178,6 +187,10 @@ int fl_dq_prescale_rows(const float* row_do, float* row_v, float* row_k, int32_t
  * head or NULL (the mantissa of K's factor with pre-quantised inputs). */
 int fl_dq_post_ex(const void* dq_acc, const float* post_scale, int32_t per_row, const float* head_mult, float mult, void* dq,
                   int32_t b, int32_t s, int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream);
+/* fl_dq_post_packed: b = 1, the accumulator has the aligned buffer's s rows, dq is the caller's packed (out_rows, h, d)
+ * tensor: rows of slot i go to slot_src[i] .. + slot_rows[i] (see fl_attn_args.slot_src). */
+int fl_dq_post_packed(const void* dq_acc, const float* post_scale, float mult, void* dq, int32_t s, int32_t h, int32_t d,
+                      int32_t unrotate, int32_t out_f16, const int32_t* slot_src, const int32_t* slot_rows, void* stream);
 /* Tile statistics of E4M3 codes times a factor per (batch row, head): tile_stats (b, h, s/128, 2) = the largest
  * magnitude and the largest row sum of squares of codes * descale[b, h] per 128-row tile, the figures the quantiser
  * writes for operands it quantises itself (the reference sizes the f16 dQ pre-scale of pre-quantised inputs from one

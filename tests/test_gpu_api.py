@@ -258,7 +258,8 @@ def test_state_matches_its_spec(form):
         out, lse, state = getattr(torch.ops.lowbit_attn, entry)(q.detach(), k.detach(), v.detach(), docs, pid, 0)
     spec = _routes.state_spec(plan, n_docs, q.dtype)
     is_docs = plan.shape.varlen or plan.fwd.ragged_documents
-    want = (spec if is_docs else spec[2:]) + [((), torch.int64)]
+    # O / LSE leave as the op's outputs; repacked documents keep the aligned buffer's LSE in the state
+    want = (spec[1:] if (is_docs and not plan.shape.aligned_varlen) else spec[2:]) + [((), torch.int64)]
     assert [(tuple(t.shape), t.dtype) for t in state] == [(tuple(sh), dt) for sh, dt in want]
     assert out.shape == q.shape
 

@@ -12,7 +12,8 @@ from flamia_blackwell_attention_b200 import _op, _routes
 def _expected(plan, n_docs, dtype):
     spec = _routes.state_spec(plan, n_docs, dtype)
     is_docs = plan.shape.varlen or plan.fwd.ragged_documents
-    return (spec if is_docs else spec[2:]) + [((), torch.int64)]
+    # O / LSE leave as the op's outputs; repacked documents keep the aligned buffer's LSE in the state
+    return (spec[1:] if (is_docs and not plan.shape.aligned_varlen) else spec[2:]) + [((), torch.int64)]
 
 
 CASES = [
