@@ -18,7 +18,7 @@ FL_DEV_WAIT_TIMEOUT = 0x100
 FL_DEV_BAD_TABLE = 0x200
 ERR_NAMES = {1: "bad argument", 2: "CUDA error", 3: "unsupported configuration", 4: "size beyond the supported maximum"}
 
-FL_Q_HADAMARD, FL_Q_TOKEN_LOCAL, FL_Q_HADAMARD_NVFP4_ONLY, FL_Q_O_PACKED = 1, 2, 4, 8
+FL_Q_HADAMARD, FL_Q_TOKEN_LOCAL, FL_Q_HADAMARD_NVFP4_ONLY, FL_Q_O_PACKED, FL_Q_LEGACY = 1, 2, 4, 8, 16
 FL_MODE_FP8, FL_MODE_FP4 = 0, 1
 FL_A_CAUSAL, FL_A_OUT_F16, FL_A_TOKEN_LOCAL, FL_A_DQ_ROWLOCAL, FL_A_HAD_DQ, FL_A_HAD_DK, FL_A_P_GROUP = 1, 2, 4, 8, 16, 32, 64
 

@@ -480,6 +480,222 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   }
 }
 
+// ------------------------------------------------------------------------------------------------ one thread per row
+// The plain launches of the 8-bit route at head_dim 128 (codes, exponent / factor tables, statistics; no NVFP4 copy, no
+// prologue, no token-local exponents, no packed source) run with ONE THREAD PER TOKEN ROW: CTA = 128 threads = one
+// 128-token tile, warp = one 32-token block, so the block maximum is a warp reduction, the Hadamard butterflies need no
+// shuffles, and one barrier per tile remains (it hands the input stage back to the loader and the codes to a TMA store).
+// Every floating-point operation is the one the four-lanes-per-row kernel above performs on the same operands in the same
+// order, so the two kernels' outputs are bit-identical (tests/test_gpu_quant.py compares them).
+static constexpr int QR_STAGES = 2;
+static constexpr int QR_TILE_B = QT * 128 * 2;     // one 16-bit input tile
+static constexpr int QR_CODE_B = QT * 128;         // its codes
+
+template <bool ROT>
+__global__ void __launch_bounds__(128, 2)
+quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, const QuantParams p) {
+  constexpr int D = 128;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* s_out = smem + QR_STAGES * QR_TILE_B;   // two code tiles (128 rows x 128 B, 128 B swizzle)
+  __shared__ __align__(8) uint64_t full[QR_STAGES];
+  __shared__ float s_wmax[2][4], s_wsq[2][4];
+  __shared__ int abort_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = tid;                               // token row of the tile
+  const int G = gridDim.x;
+  const int ntile = p.s / QT;
+  volatile int* abortp = &abort_s;
+
+  auto issue = [&](int L, int st) {
+    const int head = L % p.h, tile = (L / p.h) % ntile, bat = L / (p.h * ntile);
+    uint8_t* dst = smem + st * QR_TILE_B;
+    mbar_arrive_expect_tx(&full[st], QR_TILE_B);
+    tma_load_4d(dst, &tm_x, &full[st], 0, head, tile * QT, bat);
+    tma_load_4d(dst + QR_TILE_B / 2, &tm_x, &full[st], 64, head, tile * QT, bat);
+  };
+  if (tid == 0) {
+    abort_s = 0;
+    for (int i = 0; i < QR_STAGES; ++i) mbar_init(&full[i], 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_c);
+    for (int i = 0; i < QR_STAGES; ++i)
+      if (blockIdx.x + i * G < p.n_tiles) issue(blockIdx.x + i * G, i);
+  }
+  __syncthreads();
+
+  int it = 0;
+  for (int L = blockIdx.x; L < p.n_tiles; L += G, ++it) {
+    const int st = it % QR_STAGES, par = it & 1;
+    const int head = L % p.h, tile = (L / p.h) % ntile, bat = L / (p.h * ntile);
+    const int t0 = tile * QT;
+    const size_t bh = (size_t)bat * p.h + head;
+    const uint32_t tile_addr = smem_u32(smem + st * QR_TILE_B);
+    bool ok = mbar_wait(&full[st], (it / QR_STAGES) & 1, p.ctl, abortp, 51);
+
+    // ---- the row: 16 chunks of 8 elements (element 8 g + e in chunk g), rotation signs applied to the raw bits
+    float x[D];
+    {
+      constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        const uint32_t box = (uint32_t)(g >> 3) * (QR_TILE_B / 2);
+        uint4 v = lds_u4(tile_addr + box + r * 128 + (((g & 7) ^ (r & 7)) << 4));
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (ROT) {
+            const int i0 = 8 * g + 2 * k, i1 = i0 + 1;
+            const uint32_t m = (((NEG[i0 >> 5] >> (i0 & 31)) & 1u) << 15) | (((NEG[i1 >> 5] >> (i1 & 31)) & 1u) << 31);
+            w[k] ^= m;
+          }
+          if (p.in_f16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+            x[8 * g + 2 * k] = f.x;
+            x[8 * g + 2 * k + 1] = f.y;
+          } else {
+            x[8 * g + 2 * k] = __uint_as_float(w[k] << 16);
+            x[8 * g + 2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+          }
+        }
+      }
+    }
+    if (ROT) {
+      // (y * signs) H_128 / sqrt(128): butterfly levels 1, 2, ..., 64 with (a, b) -> (a + b, a - b), the last one with the
+      // scaling, subnormal results flushed
+      uint64_t Y[D / 2];
+#pragma unroll
+      for (int k = 0; k < D / 2; ++k) Y[k] = pack2(__fadd_rn(x[2 * k], x[2 * k + 1]), __fsub_rn(x[2 * k], x[2 * k + 1]));
+#pragma unroll
+      for (int hs = 1; hs < D / 4; hs <<= 1) {
+#pragma unroll
+        for (int k = 0; k < D / 2; ++k)
+          if ((k & hs) == 0) {
+            const uint64_t a = Y[k], b2 = Y[k + hs];
+            Y[k] = add2(a, b2);
+            Y[k + hs] = sub2(a, b2);
+          }
+      }
+      const uint64_t c2 = pack2(0.08838834764831845f, 0.08838834764831845f);
+#pragma unroll
+      for (int k = 0; k < D / 4; ++k) {
+        const uint64_t a = Y[k], b2 = Y[k + D / 4];
+        unpack2(mul2_ftz(add2(a, b2), c2), x[2 * k], x[2 * k + 1]);
+        unpack2(mul2_ftz(sub2(a, b2), c2), x[2 * k + D / 2], x[2 * k + D / 2 + 1]);
+      }
+    } else {           // subnormal -> zero of the same sign
+#pragma unroll
+      for (int i = 0; i < D; i += 2) unpack2(mul2_ftz(pack2(x[i], x[i + 1]), pack2(1.0f, 1.0f)), x[i], x[i + 1]);
+    }
+
+    // ---- the row's maximum and (with the statistics) its sum of squares, in the four-lane kernel's summation order
+    float amax = 0.f, sumsq = 0.f;
+    {
+      float aq[4] = {0.f, 0.f, 0.f, 0.f};          // per quarter q: elements 32 j + 8 q + e
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int e = 0; e < 8; e += 2)
+            aq[q] = fmaxf(fmaxf(aq[q], fabsf(x[32 * j + 8 * q + e])), fabsf(x[32 * j + 8 * q + e + 1]));
+      amax = fmaxf(fmaxf(aq[0], aq[1]), fmaxf(aq[2], aq[3]));
+      if (p.tile_stats || p.row_stat) {
+        float lq[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float sq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sq[e & 3] = fmaf(x[32 * j + 8 * q + e], x[32 * j + 8 * q + e], sq[e & 3]);
+          lq[q] = (sq[0] + sq[1]) + (sq[2] + sq[3]);
+        }
+        sumsq = (lq[0] + lq[1]) + (lq[2] + lq[3]);
+      }
+    }
+    if (p.row_stat) {
+      const float v = p.row_stat_kind == 2 ? amax : (p.row_stat_kind == 3 ? __fsqrt_rn(sumsq) : sumsq);
+      atomicMax(p.row_stat + (size_t)bat * p.s + t0 + r, __float_as_uint(v));
+    }
+    // the 32-token block = this warp (non-negative floats order as their bit patterns)
+    uint32_t bm_bits, bs_bits;
+    asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(bm_bits) : "r"(__float_as_uint(amax)));
+    // (a row whose sum of squares is NaN does not take part, as with the NaN-ignoring maximum of the four-lane kernel)
+    asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(bs_bits) : "r"(sumsq == sumsq ? __float_as_uint(sumsq) : 0u));
+    const float bmax = __uint_as_float(bm_bits);
+    if (lane == 0) { s_wmax[par][warp] = bmax; s_wsq[par][warp] = __uint_as_float(bs_bits); }
+    const uint32_t bbyte = ue8m0_byte(bmax);
+    const float inv = bbyte ? pow2_from_field(254 - (int)bbyte) : 0.f;
+
+    // ---- codes -> this tile's staging buffer (128 B rows, 128 B swizzle)
+    {
+      const uint64_t inv2 = pack2(inv, inv);
+      const uint32_t orow = smem_u32(s_out + par * QR_CODE_B) + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {                 // 16 codes per 16-byte chunk
+        uint32_t cw[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float a0, a1, a2, a3;
+          unpack2(mul2(pack2(x[16 * c + 4 * k], x[16 * c + 4 * k + 1]), inv2), a0, a1);
+          unpack2(mul2(pack2(x[16 * c + 4 * k + 2], x[16 * c + 4 * k + 3]), inv2), a2, a3);
+          cw[k] = cvt_e4m3x4(a0, a1, a2, a3);
+        }
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(orow + ((c ^ (r & 7)) << 4)), "r"(cw[0]), "r"(cw[1]),
+                     "r"(cw[2]), "r"(cw[3]) : "memory");
+      }
+    }
+    fence_proxy_async();
+    // the store of the previous tile has read its staging buffer (the other one): the next tile may write it
+    if (tid == 0) tma_store_wait_read<0>();
+    // every thread has read the stage and written its codes; a wait that ran out leaves the loop here, all threads together
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (!ok) break;
+    if (tid == 0) {
+      if (L + QR_STAGES * G < p.n_tiles) issue(L + QR_STAGES * G, st);
+      tma_store_4d(&tm_c, s_out + par * QR_CODE_B, 0, head, t0, bat);
+      tma_store_commit();
+    }
+    // ---- side tables
+    const float* wm = s_wmax[par];
+    if (lane == 0) {
+      const uint32_t b0 = ue8m0_byte(wm[0]), b1 = ue8m0_byte(wm[1]), b2 = ue8m0_byte(wm[2]), b3 = ue8m0_byte(wm[3]);
+      if (p.e_tab) {
+        uint8_t* e = p.e_tab + (bh * (p.s / 32) + tile * 4 + warp) * (D / 32);
+#pragma unroll
+        for (int g = 0; g < D / 32; ++g) e[g] = (uint8_t)bbyte;
+      }
+      if (p.fac) {
+        const uint32_t tm = max(max(b0, b1), max(b2, b3));
+        const uint32_t e0 = bbyte ? bbyte : tm;
+        p.fac[bh * (p.s / 32) + tile * 4 + warp] = e0 ? pow2_from_field((int)e0) : 1.0f;
+      }
+    }
+    if (p.tile_stats && tid == 0) {
+      p.tile_stats[(bh * ntile + tile) * 2] = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
+      p.tile_stats[(bh * ntile + tile) * 2 + 1] = fmaxf(fmaxf(s_wsq[par][0], s_wsq[par][1]), fmaxf(s_wsq[par][2], s_wsq[par][3]));
+    }
+  }
+  // the staging buffers must outlive the stores that read them; a CTA that gave up must not exit while loads may still land
+  if (tid == 0) tma_store_wait_read<0>();
+  if (abort_s) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+}
+
+template <bool ROT>
+static int launch_quant_rows(const CUtensorMap& mx, const CUtensorMap& mc, const QuantParams& p, cudaStream_t st) {
+  const int smem = QR_STAGES * QR_TILE_B + 2 * QR_CODE_B + 1024;
+  auto kern = quant_rows_kernel<ROT>;
+  if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); e != cudaSuccess)
+    return cuda_fail((int)e, "fl_quant_blocks: cudaFuncSetAttribute");
+  const int grid = min(p.n_tiles, sm_count() * 2);
+  kern<<<grid, 128, smem, st>>>(mx, mc, p);
+  return FL_OK;
+}
+
 template <int D, int MODE, bool PRO, bool PK>
 static int launch_quant_pk(const CUtensorMap& mx, const CUtensorMap& mo, const QuantParams& p, bool want_t, cudaStream_t st) {
   constexpr int TILE_B = QT * D * 2;
@@ -538,6 +754,15 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   if ((rc = make_rows_map_16(&mo, pro ? a->o : a->x, a->b, p.o_packed ? a->src_rows : a->s, a->h, a->d, 128))) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const bool wt = a->codes_t != nullptr;
+  // the plain launches of the 8-bit route: one thread per row (same bits, fewer instructions, no shuffles)
+  if (a->d == 128 && !nv4 && !rot4 && !pro && !wt && !packed && !p.token_local && !a->sf_tok && !a->sf_dim &&
+      !a->token_factors && !a->zero_acc && !a->lse_log2 && !(a->flags & FL_Q_LEGACY)) {
+    CUtensorMap mc;
+    if ((rc = make_rows_map(&mc, a->codes, a->b, a->s, a->h, 128, 128))) return rc;
+    rc = rot ? launch_quant_rows<true>(mx, mc, p, st) : launch_quant_rows<false>(mx, mc, p, st);
+    if (rc) return rc;
+    return launch_result("fl_quant_blocks: kernel launch");
+  }
   if (a->d == 64) {
     if (pro) rc = launch_quant<64, 0, true>(mx, mo, p, wt, st);
     else rc = nv4 ? launch_quant<64, 2, false>(mx, mo, p, wt, st) : launch_quant<64, 0, false>(mx, mo, p, wt, st);

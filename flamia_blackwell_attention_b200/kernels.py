@@ -37,7 +37,8 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
                         make_channel_major_copy=False, output_exponent_table=True, output_token_block_factors=True,
                         output_sf_atoms=False, also_make_nvfp4_copy=False, compute_d_with_output=None,
                         shifted_log2_lse_from=None, log2_lse_shift=0.0, d_multiplier=1.0, zero_accumulator=None,
-                        output_tile_stats=False, status=None, wait_cycles=0, packed_slots=None, row_stat=None):
+                        output_tile_stats=False, status=None, wait_cycles=0, packed_slots=None, row_stat=None,
+                        legacy_kernel=False):
     """Token-block MXFP8 quantiser of x (b, s, h, d) bf16 / f16 (s % 128 == 0, d in {64, 128}).
     packed_slots = (slot_src, slot_rows, padded_rows): x is a packed (total, h, d) tensor of documents stored back to back
     and the outputs are those of the 128-aligned buffer (1, padded_rows, h, d): slot_src[i] = first row of x of output
@@ -70,6 +71,8 @@ def quantize_fp8_blocks(x, *, apply_hadamard_rotation=False, hadamard_rotation_s
         flags |= L.FL_Q_HADAMARD if hadamard_rotation_scope == "all" else L.FL_Q_HADAMARD_NVFP4_ONLY
     if token_local_exponents:
         flags |= L.FL_Q_TOKEN_LOCAL
+    if legacy_kernel:       # the four-lanes-per-row kernel even where the one-thread-per-row kernel serves (same bits)
+        flags |= L.FL_Q_LEGACY
     a.flags = flags
     out["codes"] = torch.empty(b, s, h, d, **u8)
     a.codes = L.ptr(out["codes"])

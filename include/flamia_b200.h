@@ -25,6 +25,8 @@ extern "C" {
 #define FL_Q_TOKEN_LOCAL 2         /* codes / sf_tok from each token's own exponent */
 #define FL_Q_HADAMARD_NVFP4_ONLY 4 /* rotate only the values of the NVFP4 copy; the E4M3 codes stay unrotated */
 #define FL_Q_O_PACKED 8            /* packed source with the prologue: o has x's packed rows (else the outputs' rows) */
+#define FL_Q_LEGACY 16             /* keep the four-lanes-per-row kernel where the one-thread-per-row kernel would serve
+                                      (the two are bit-identical; for tests that compare them) */
 
 /* Fused block-scaled quantiser + backward prologue.
  * Replaces flash_attn/cute/quant/fp8.py:2512 quantize_fp8_blocks (kernel :1639), the fused NVFP4 S-operand copy

@@ -94,6 +94,29 @@ def test_prologue_d_lse_and_zeroed_accumulator(dist, d):
     assert float(acc.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("dist", DISTS)
+@pytest.mark.parametrize("rotate", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_one_thread_per_row_kernel(dist, rotate, dtype):
+    """The plain head_dim 128 launches (what the 8-bit route issues for Q, K, V) run on the one-thread-per-row kernel:
+    codes, exponents and factors against the oracle, and every output, statistics included, bit for bit against the
+    four-lanes-per-row kernel."""
+    if rotate and dist == "huge":
+        pytest.skip("rotated huge rows overflow to inf / NaN")
+    x = make((2, 384, 3, 128), dist, dtype)
+    b, s = x.shape[:2]
+    kind = "norm2" if rotate else "sumsq"
+    rs_new, rs_old = (torch.zeros(b, s, dtype=torch.float32, device="cuda") for _ in range(2))
+    new = run(x, apply_hadamard_rotation=rotate, output_tile_stats=True, row_stat=(kind, rs_new))
+    old = run(x, apply_hadamard_rotation=rotate, output_tile_stats=True, row_stat=(kind, rs_old), legacy_kernel=True)
+    ref = Q.fp8_token_blocks(x.float().numpy(), rotate=rotate)
+    for k in ("codes", "e", "fac"):
+        same(new[k], ref[k], f"{dist} {dtype} rot={rotate} {k}")
+        same(new[k], old[k].cpu().view(torch.uint8).numpy(), f"{dist} old/new {k}")
+    same(new["tile_stats"], old["tile_stats"].cpu().view(torch.uint8).numpy(), f"{dist} tile_stats")
+    same(rs_new, rs_old.cpu().view(torch.uint8).numpy(), f"{dist} row_stat")
+
+
 def test_golden_small_fixture_on_gpu():
     small = np.load(os.path.join(HERE, "golden", "quant_small.npz"))
     for dist in ("n01", "zeros", "mixed"):
