@@ -491,10 +491,13 @@ static constexpr int QR_STAGES = 2;
 static constexpr int QR_TILE_B = QT * 128 * 2;     // one 16-bit input tile
 static constexpr int QR_CODE_B = QT * 128;         // its codes
 
-template <bool ROT>
+// MODE as in the four-lane kernel: bit 0 = the E4M3 codes are of the rotated row, bit 1 = also the NVFP4 copy, bit 2 =
+// rotate only the NVFP4 copy.
+template <int MODE>
 __global__ void __launch_bounds__(128, 2)
 quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, const QuantParams p) {
   constexpr int D = 128;
+  constexpr bool ROT = (MODE & 1) != 0, NV4 = (MODE & 2) != 0, ROT4 = (MODE & 4) != 0;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_out = smem + QR_STAGES * QR_TILE_B;   // two code tiles (128 rows x 128 B, 128 B swizzle)
@@ -536,7 +539,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 
     // ---- the row: 16 chunks of 8 elements (element 8 g + e in chunk g), rotation signs applied to the raw bits
     float x[D];
-    {
+    auto load_row = [&](bool signs) {
       constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
 #pragma unroll
       for (int g = 0; g < 16; ++g) {
@@ -545,7 +548,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          if (ROT) {
+          if (signs) {
             const int i0 = 8 * g + 2 * k, i1 = i0 + 1;
             const uint32_t m = (((NEG[i0 >> 5] >> (i0 & 31)) & 1u) << 15) | (((NEG[i1 >> 5] >> (i1 & 31)) & 1u) << 31);
             w[k] ^= m;
@@ -560,10 +563,10 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           }
         }
       }
-    }
-    if (ROT) {
-      // (y * signs) H_128 / sqrt(128): butterfly levels 1, 2, ..., 64 with (a, b) -> (a + b, a - b), the last one with the
-      // scaling, subnormal results flushed
+    };
+    // (y * signs) H_128 / sqrt(128): butterfly levels 1, 2, ..., 64 with (a, b) -> (a + b, a - b), the last one with the
+    // scaling, subnormal results flushed
+    auto rotate_row = [&]() {
       uint64_t Y[D / 2];
 #pragma unroll
       for (int k = 0; k < D / 2; ++k) Y[k] = pack2(__fadd_rn(x[2 * k], x[2 * k + 1]), __fsub_rn(x[2 * k], x[2 * k + 1]));
@@ -584,7 +587,57 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         unpack2(mul2_ftz(add2(a, b2), c2), x[2 * k], x[2 * k + 1]);
         unpack2(mul2_ftz(sub2(a, b2), c2), x[2 * k + D / 2], x[2 * k + D / 2 + 1]);
       }
-    } else {           // subnormal -> zero of the same sign
+    };
+    // NVFP4 copy of x: per 16 along d: SF = E4M3_rn(amax * f32(1/6)); codes = E2M1_rn(ftz(x * m)), m = 1 / SF | +inf (SF
+    // rounds to 0, amax > 0) | 0. Scale bytes: group g of the row = byte g % 4 of the row's word in atom g / 4.
+    auto nvfp4_row = [&]() {
+      const size_t row_off = (((size_t)bat * p.s + t0 + r) * p.h + head) * D;
+      uint8_t* x4row = p.x4 + row_off / 2;
+      uint32_t sfw[2] = {0u, 0u};
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {                   // 16 elements
+        float am = 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float a = fabsf(flush_sub(x[16 * g + e]));
+          am = (a > am) ? a : am;                      // a NaN never wins
+        }
+        const float u = __fmul_rn(am, 1.0f / 6.0f);
+        const uint32_t sfb = cvt_e4m3x2(u, 0.f) & 0xFF;
+        const float sfv = e4m3_byte_to_f32(sfb);
+        const float m = sfv > 0.f ? __frcp_rn(sfv) : (u > 0.f ? __int_as_float(0x7F800000) : 0.f);
+        uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          const float a0 = flush_sub(__fmul_rn(flush_sub(x[16 * g + e]), m));
+          const float a1 = flush_sub(__fmul_rn(flush_sub(x[16 * g + e + 1]), m));
+          uint16_t c2;
+          asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}" : "=h"(c2) : "f"(a1), "f"(a0));
+          packed[e >> 3] |= (uint32_t)(c2 & 0xFF) << ((e & 7) * 4);
+        }
+        *reinterpret_cast<uint2*>(x4row + g * 8) = make_uint2(packed[0], packed[1]);
+        sfw[g >> 2] |= sfb << (8 * (g & 3));
+      }
+      if (p.sf4) {
+        uint8_t* atom = p.sf4 + ((bh * ntile + tile) * (D / 64)) * 512;
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a) *reinterpret_cast<uint32_t*>(atom + a * 512 + (r & 31) * 16 + (r >> 5) * 4) = sfw[a];
+      }
+    };
+    if (ROT4) {          // NVFP4 codes of the rotated row, E4M3 codes of the row as read
+      load_row(true);
+      rotate_row();
+      nvfp4_row();
+      load_row(false);
+    } else if (ROT) {
+      load_row(true);
+      rotate_row();
+      if (NV4) nvfp4_row();
+    } else {
+      load_row(false);
+      if (NV4) nvfp4_row();
+    }
+    if (!ROT || ROT4) {  // subnormal -> zero of the same sign (rotated rows were flushed by their scaling)
 #pragma unroll
       for (int i = 0; i < D; i += 2) unpack2(mul2_ftz(pack2(x[i], x[i + 1]), pack2(1.0f, 1.0f)), x[i], x[i + 1]);
     }
@@ -685,10 +738,10 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   }
 }
 
-template <bool ROT>
+template <int MODE>
 static int launch_quant_rows(const CUtensorMap& mx, const CUtensorMap& mc, const QuantParams& p, cudaStream_t st) {
   const int smem = QR_STAGES * QR_TILE_B + 2 * QR_CODE_B + 1024;
-  auto kern = quant_rows_kernel<ROT>;
+  auto kern = quant_rows_kernel<MODE>;
   if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); e != cudaSuccess)
     return cuda_fail((int)e, "fl_quant_blocks: cudaFuncSetAttribute");
   const int grid = min(p.n_tiles, sm_count() * 2);
@@ -755,11 +808,13 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const bool wt = a->codes_t != nullptr;
   // the plain launches of the 8-bit route: one thread per row (same bits, fewer instructions, no shuffles)
-  if (a->d == 128 && !nv4 && !rot4 && !pro && !wt && !packed && !p.token_local && !a->sf_tok && !a->sf_dim &&
+  if (a->d == 128 && !pro && !wt && !packed && !p.token_local && !a->sf_tok && !a->sf_dim &&
       !a->token_factors && !a->zero_acc && !a->lse_log2 && !(a->flags & FL_Q_LEGACY)) {
     CUtensorMap mc;
     if ((rc = make_rows_map(&mc, a->codes, a->b, a->s, a->h, 128, 128))) return rc;
-    rc = rot ? launch_quant_rows<true>(mx, mc, p, st) : launch_quant_rows<false>(mx, mc, p, st);
+    if (rot4) rc = launch_quant_rows<6>(mx, mc, p, st);
+    else if (rot) rc = nv4 ? launch_quant_rows<3>(mx, mc, p, st) : launch_quant_rows<1>(mx, mc, p, st);
+    else rc = nv4 ? launch_quant_rows<2>(mx, mc, p, st) : launch_quant_rows<0>(mx, mc, p, st);
     if (rc) return rc;
     return launch_result("fl_quant_blocks: kernel launch");
   }

@@ -115,6 +115,15 @@ def test_one_thread_per_row_kernel(dist, rotate, dtype):
         same(new[k], old[k].cpu().view(torch.uint8).numpy(), f"{dist} old/new {k}")
     same(new["tile_stats"], old["tile_stats"].cpu().view(torch.uint8).numpy(), f"{dist} tile_stats")
     same(rs_new, rs_old.cpu().view(torch.uint8).numpy(), f"{dist} row_stat")
+    # the NVFP4 copy modes (the mixed route's Q / K launches): rotated codes + copy, and the copy alone rotated
+    for scope in ("all", "nvfp4_copy"):
+        if not rotate:
+            continue
+        kw = dict(apply_hadamard_rotation=True, hadamard_rotation_scope=scope, also_make_nvfp4_copy=True,
+                  output_tile_stats=True)
+        new, old = run(x, **kw), run(x, legacy_kernel=True, **kw)
+        for k in ("codes", "e", "fac", "x4", "sf4_raw", "tile_stats"):
+            same(new[k], old[k].cpu().view(torch.uint8).numpy(), f"{dist} {scope} old/new {k}")
 
 
 def test_golden_small_fixture_on_gpu():
