@@ -171,34 +171,41 @@ __global__ void __launch_bounds__(128) dq_post_t128_kernel(const __grid_constant
         y[c] = __half2float(__ushort_as_half(hv)) * sc;
       }
     }
-    if (unrotate) {
+    // pairs of neighbouring head-dim columns in one 64-bit register: one instruction per pair
+    uint64_t Y[64];
+    if (unrotate) {      // (y H_128 / sqrt(128)) * signs: butterfly levels 1, 2, ..., 64, then the scaling with the signs
 #pragma unroll
-      for (int hs = 1; hs < 128; hs <<= 1) {
+      for (int i = 0; i < 64; ++i) Y[i] = pack2(__fadd_rn(y[2 * i], y[2 * i + 1]), __fsub_rn(y[2 * i], y[2 * i + 1]));
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
+      for (int hs = 1; hs < 64; hs <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
           if ((i & hs) == 0) {
-            float a = y[i], b2 = y[i + hs];
-            y[i] = __fadd_rn(a, b2);
-            y[i + hs] = __fsub_rn(a, b2);
+            const uint64_t a = Y[i], b2 = Y[i + hs];
+            Y[i] = add2(a, b2);
+            Y[i + hs] = sub2(a, b2);
           }
         }
       }
+      constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
+      constexpr float CP = 0.08838834764831845f;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const bool n0 = (NEG[(2 * i) >> 5] >> ((2 * i) & 31)) & 1, n1 = (NEG[(2 * i + 1) >> 5] >> ((2 * i + 1) & 31)) & 1;
+        Y[i] = mul2(Y[i], pack2(n0 ? -CP : CP, n1 ? -CP : CP));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) Y[i] = pack2(y[2 * i], y[2 * i + 1]);
     }
-    constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
     uint8_t* rowo = s_out + tid * ROWB;
 #pragma unroll
     for (int c = 0; c < 16; ++c) {
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int i0 = c * 8 + 2 * j, i1 = i0 + 1;
-        float a = y[i0], b2 = y[i1];
-        if (unrotate) {
-          a = __fmul_rn(a, 0.08838834764831845f);
-          b2 = __fmul_rn(b2, 0.08838834764831845f);
-          if ((NEG[i0 >> 5] >> (i0 & 31)) & 1) a = -a;
-          if ((NEG[i1 >> 5] >> (i1 & 31)) & 1) b2 = -b2;
-        }
+        float a, b2;
+        unpack2(Y[c * 4 + j], a, b2);
         w[j] = cvt_out2(a, b2, out_f16);
       }
       *reinterpret_cast<uint4*>(rowo + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
