@@ -523,18 +523,26 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
         float ps[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};     // independent partial sums (group frame: two per group)
+        [[maybe_unused]] uint64_t ps2[4] = {0ull, 0ull, 0ull, 0ull};  // the same as packed pairs (default route)
         uint32_t pw[32];
 #pragma unroll
         for (int w = 0; w < 32; ++w) {
           const float cw = c[w >> 3];
           const float mbw = GF ? mb + gb[w >> 3] : mb;
-          float p0 = ex2(fmaf(s[4 * w], cw, -mbw)), p1 = ex2(fmaf(s[4 * w + 1], cw, -mbw));
+          // exponent arguments: two columns per instruction
+          float a0, a1, a2, a3;
+          {
+            const uint64_t cw2 = pack2(cw, cw), nm2 = pack2(-mbw, -mbw);
+            unpack2(fma2(pack2(s[4 * w], s[4 * w + 1]), cw2, nm2), a0, a1);
+            unpack2(fma2(pack2(s[4 * w + 2], s[4 * w + 3]), cw2, nm2), a2, a3);
+          }
+          float p0 = ex2(a0), p1 = ex2(a1);
           float p2, p3;
           if (w & 1) {    // one pair in four on the FMA pipe (measured: -3 % kernel time on the dense cell)
-            ex2_poly2(fmaf(s[4 * w + 2], cw, -mbw), fmaf(s[4 * w + 3], cw, -mbw), p2, p3);
+            ex2_poly2(a2, a3, p2, p3);
           } else {
-            p2 = ex2(fmaf(s[4 * w + 2], cw, -mbw));
-            p3 = ex2(fmaf(s[4 * w + 3], cw, -mbw));
+            p2 = ex2(a2);
+            p3 = ex2(a3);
           }
           if (TL) {     // the row sum is that of the probabilities: take f_V(key) back out
             const float4 v4 = __ldg(fv4 + w);
@@ -542,10 +550,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                      p1 * __uint_as_float((254u << 23) - (__float_as_uint(v4.y) & 0x7F800000u))) +
                     (p2 * __uint_as_float((254u << 23) - (__float_as_uint(v4.z) & 0x7F800000u)) +
                      p3 * __uint_as_float((254u << 23) - (__float_as_uint(v4.w) & 0x7F800000u)));
-          } else if (GF) {
-            ps[2 * (w >> 3) + (w & 1)] += (p0 + p1) + (p2 + p3);
-          } else {
-            ps[w & 7] += (p0 + p1) + (p2 + p3);
+          } else if (GF) {  // packed: (p0 + p2, p1 + p3) into the group's pair accumulator
+            ps2[w >> 3] = add2(ps2[w >> 3], add2(pack2(p0, p1), pack2(p2, p3)));
+          } else {          // the same into one of four pair accumulators
+            ps2[w & 3] = add2(ps2[w & 3], add2(pack2(p0, p1), pack2(p2, p3)));
           }
           pw[w] = cvt_e4m3x4(p0, p1, p2, p3);
         }
@@ -553,10 +561,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (GF) {   // each group's sum weighs 2^bias_g
           float pg[4];
 #pragma unroll
+          for (int kbk = 0; kbk < 4; ++kbk) unpack2(ps2[kbk], ps[2 * kbk], ps[2 * kbk + 1]);
+#pragma unroll
           for (int kbk = 0; kbk < 4; ++kbk)
             pg[kbk] = (ps[2 * kbk] + ps[2 * kbk + 1]) * __uint_as_float((uint32_t)(127 + (int)gb[kbk]) << 23);
           psum = (pg[0] + pg[1]) + (pg[2] + pg[3]);
         } else {
+          if (!TL) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) unpack2(ps2[t], ps[2 * t], ps[2 * t + 1]);
+          }
           psum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         }
         l_sum = fmaf(l_sum, alpha, psum);
@@ -616,8 +630,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               // rows past the end of the document store zeros (a select: what tensor memory holds there is arbitrary)
-              const float a = row_valid ? __uint_as_float(ov[8 * q4 + 2 * e]) * inv_l : 0.f;
-              const float b2 = row_valid ? __uint_as_float(ov[8 * q4 + 2 * e + 1]) * inv_l : 0.f;
+              float a, b2;
+              unpack2(mul2(pack2(__uint_as_float(ov[8 * q4 + 2 * e]), __uint_as_float(ov[8 * q4 + 2 * e + 1])),
+                           pack2(inv_l, inv_l)), a, b2);
+              a = row_valid ? a : 0.f;
+              b2 = row_valid ? b2 : 0.f;
               if (p.out_f16) {
                 __half2 hh = __floats2half2_rn(a, b2);
                 w[e] = *reinterpret_cast<uint32_t*>(&hh);
