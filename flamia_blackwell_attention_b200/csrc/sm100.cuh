@@ -400,7 +400,12 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
   return (uint32_t)r;
 }
 __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
-  return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+  uint32_t r;      // two conversions and one register pack
+  asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\tcvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}"
+      : "=r"(r)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
