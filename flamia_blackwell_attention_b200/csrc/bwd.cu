@@ -183,8 +183,10 @@ __device__ __forceinline__ void st_release_gpu(int32_t* ptr, int v) {
   asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
 }
 
-// DET: deterministic dQ order (a template flag, so that the arrival-order kernels carry none of it)
-template <int D, bool FP4, int VAR, bool SC, bool DET = false>
+// FULL: the variants that also serve the rarer call forms (deterministic dQ order, per-query-row pre-scale, packed
+// outputs, the dK mantissa factor), each behind a run-time check of its pointer. A template flag, so that the kernels
+// of the plain calls carry none of that code: the loop is sensitive to every register and instruction added to it.
+template <int D, bool FP4, int VAR, bool SC, bool FULL = false>
 __global__ void __launch_bounds__(512, 1)
 bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -467,7 +469,8 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         fence_proxy_async();
         mbar_arrive_warp(&bars[BB_R2]);
         if (!(ok = mbar_wait(&bars[BB_R2], gt & 1, p.ctl, abortp, 42))) break;
-        if (!DET) {
+        const bool det = FULL && p.dq_order != nullptr;
+        if (!det) {
           if (tid == 256) {
             if (D == 128) tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, T.q0 + m * 128 + 64 * y, 0, head, T.bat);
             else tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, 0, T.q0 + m * 128 + 64 * y, head, T.bat);
@@ -477,7 +480,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           int go = 1;
           int32_t* order = nullptr;
           int rank = 0;
-          if (DET) {
+          {
             // deterministic order: the key tiles before this one have added their partial sums of this half
             order = p.dq_order + ((((size_t)T.bat * p.h + head) * (p.s_q / 128) + T.q0 / 128 + m) * 2 + y);
             rank = bwd_order_rank(p, T, m);
@@ -568,9 +571,10 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const float4* fdo_vec = reinterpret_cast<const float4*>(p.fac_do + (TL ? bh_q * p.s_q + T.q0 + m * 128 + 64 * x : 0));
         // the f16 pre-scale: one power of two per query tile (folded into K's exponent bytes below), or one per query row
         // (folded into the dQ side's B scale bytes, whose lanes are the queries)
-        const float bsc = p.dq_scale_rows ? 1.0f : p.dq_scale[(size_t)T.bat * (p.s_q / 128) + T.q0 / 128 + m];
-        uint32_t lq0 = 0, lq1 = 0;
-        if (p.dq_scale_rows) {
+        const bool pre_rows = FULL && p.dq_scale_rows != nullptr;
+        const float bsc = pre_rows ? 1.0f : p.dq_scale[(size_t)T.bat * (p.s_q / 128) + T.q0 / 128 + m];
+        [[maybe_unused]] uint32_t lq0 = 0, lq1 = 0;
+        if (pre_rows) {
           const float* rp = p.dq_scale_rows + (size_t)T.bat * p.s_q + T.q0 + m * 128 + 64 * x;
           lq0 = ((uint32_t)((int)((__float_as_uint(rp[lane]) >> 23) & 0xFF) - 127) & 0xFF) * 0x01010101u;
           lq1 = ((uint32_t)((int)((__float_as_uint(rp[32 + lane]) >> 23) & 0xFF) - 127) & 0xFF) * 0x01010101u;
@@ -820,8 +824,10 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             sf[12] = (e0 & 0xFF) | ((e1 & 0xFF) << 8) | ((e2 & 0xFF) << 16) | ((e3 & 0xFF) << 24);
             sf[13] = ((e0 >> 8) & 0xFF) | (((e1 >> 8) & 0xFF) << 8) | (((e2 >> 8) & 0xFF) << 16) | (((e3 >> 8) & 0xFF) << 24);
           }
-          sf[12] = __vadd4(sf[12], lq0);
-          sf[13] = __vadd4(sf[13], lq1);
+          if constexpr (FULL) {
+            sf[12] = __vadd4(sf[12], lq0);
+            sf[13] = __vadd4(sf[13], lq1);
+          }
           sf[14] = sf[15] = 0x7F7F7F7Fu;
           FL_TMEM_ST_16(t_sx + TO_SFA_DK, sf);
         }
@@ -839,7 +845,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       {
         const uint32_t t_acc = lane_base + (x == 0 ? TC_DV : TC_DK);
         // dV carries 2^8 (P'), dK the softmax scale (and the mantissa of a Q factor that is no power of two)
-        const float mult = (x == 0) ? 0.00390625f : p.softmax_scale * (p.dk_mult ? p.dk_mult[bh_k] : 1.0f);
+        const float mult = (x == 0) ? 0.00390625f : p.softmax_scale * ((FULL && p.dk_mult) ? p.dk_mult[bh_k] : 1.0f);
         const float mk = key_valid ? mult : 0.f;       // rows past the end of the document store zeros
         uint32_t v[D];
         if (n_it > 0) {                  // (CTA-uniform: the tensor-memory loads are warp-collective)
@@ -903,11 +909,11 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // packed output: the key tile is slot T.k0 / 128 of the aligned buffer; its rows go to the packed rows out_row ..
         // + out_n of the caller's tensor: a full slot as TMA stores, a document's last rows row by row
         int out_row = T.k0, out_n = T.nk > 0 ? 128 : 0;
-        if (p.slot_src) {
+        if (FULL && p.slot_src) {
           out_row = T.nk > 0 ? p.slot_src[T.k0 / 128] : -1;
           out_n = (T.nk > 0 && out_row >= 0) ? min(p.slot_rows[T.k0 / 128], 128) : 0;
         }
-        const bool by_rows = p.slot_src && out_n < 128;   // (CTA-uniform)
+        const bool by_rows = FULL && p.slot_src && out_n < 128;   // (CTA-uniform)
         uint16_t* out_base = reinterpret_cast<uint16_t*>(x == 0 ? p.dv : p.dk);
 #pragma unroll
         for (int pass = 0; pass < D / 64; ++pass) {
@@ -1049,21 +1055,23 @@ extern "C" int fl_bwd(const fl_attn_args* a, void* stream) {
   };
   const bool det = a->dq_order != nullptr;
   if (det && (sc || rl || tl)) return FL_ERR_UNSUPPORTED;     // ordered dQ: the default dS-hat route only
-  if (det) {
-    if (a->d == 64) rc = launch(bwd_kernel_pipelined<64, false, 0, false, true>);
-    else rc = fp4 ? launch(bwd_kernel_pipelined<128, true, 0, false, true>) : launch(bwd_kernel_pipelined<128, false, 0, false, true>);
-  } else if (sc) {
-    if (a->d == 64) rc = launch(bwd_kernel_pipelined<64, false, 0, true>);
-    else rc = fp4 ? launch(bwd_kernel_pipelined<128, true, 0, true>) : launch(bwd_kernel_pipelined<128, false, 0, true>);
+  // the lean kernels serve the plain calls; any of the rarer forms takes the full variant of the same kernel
+  const bool full = det || a->dq_scale_rows || a->slot_src || a->dk_mult;
+#define FL_BWD_LAUNCH(D_, FP4_, VAR_, SC_) \
+  (full ? launch(bwd_kernel_pipelined<D_, FP4_, VAR_, SC_, true>) : launch(bwd_kernel_pipelined<D_, FP4_, VAR_, SC_, false>))
+  if (sc) {
+    if (a->d == 64) rc = FL_BWD_LAUNCH(64, false, 0, true);
+    else rc = fp4 ? FL_BWD_LAUNCH(128, true, 0, true) : FL_BWD_LAUNCH(128, false, 0, true);
   } else if (a->d == 64) {
-    rc = launch(bwd_kernel_pipelined<64, false, 0, false>);
+    rc = FL_BWD_LAUNCH(64, false, 0, false);
   } else if (fp4) {
-    rc = rl ? launch(bwd_kernel_pipelined<128, true, 1, false>) : launch(bwd_kernel_pipelined<128, true, 0, false>);
+    rc = rl ? FL_BWD_LAUNCH(128, true, 1, false) : FL_BWD_LAUNCH(128, true, 0, false);
   } else if (tl) {
-    rc = launch(bwd_kernel_pipelined<128, false, 2, false>);
+    rc = FL_BWD_LAUNCH(128, false, 2, false);
   } else {
-    rc = rl ? launch(bwd_kernel_pipelined<128, false, 1, false>) : launch(bwd_kernel_pipelined<128, false, 0, false>);
+    rc = rl ? FL_BWD_LAUNCH(128, false, 1, false) : FL_BWD_LAUNCH(128, false, 0, false);
   }
+#undef FL_BWD_LAUNCH
   if (rc) return rc;
   return launch_result("fl_bwd: kernel launch");
 }
