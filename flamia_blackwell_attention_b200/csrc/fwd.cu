@@ -151,7 +151,9 @@ __device__ __forceinline__ void fwd_decode(const FwdParams& p, int L, Tile& t) {
   }
 }
 
-template <int D, bool FP4, bool TL, bool GF, bool SC>
+// FULL: the variants that also serve packed outputs and the output-row factor, each behind a run-time check of its
+// pointer. A template flag, so that the kernels of the plain calls carry none of that code (-2 % kernel time).
+template <int D, bool FP4, bool TL, bool GF, bool SC, bool FULL = false>
 __global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const FwdParams p) {
@@ -597,18 +599,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       tc_fence_after();
       const bool stage_present = T.nq > 128 * i;        // (warpgroup-uniform) an absent stage's rows belong to someone else
-      const float inv_l = ((l_sum > 0.f) ? 1.0f / l_sum : 0.f) * (p.o_mult ? p.o_mult[bh_k] : 1.0f);
+      const float inv_l = ((l_sum > 0.f) ? 1.0f / l_sum : 0.f) * ((FULL && p.o_mult) ? p.o_mult[bh_k] : 1.0f);
       uint8_t* stage = sQ + (2 * kb + i) * Q_STRIDE;
       const uint32_t srow = smem_u32(stage) + r * 128;
       // packed output: this stage's 128 rows are slot (T.q0 + 128 i) / 128 of the aligned buffer; they go to the packed
       // rows out_row .. + out_n of the caller's tensor: a full slot as TMA stores, a document's last rows row by row
       int out_row = T.q0 + 128 * i, out_n = stage_present ? 128 : 0;
-      if (p.slot_src) {
+      if (FULL && p.slot_src) {
         const int slot = (T.q0 + 128 * i) / 128;
         out_row = stage_present ? p.slot_src[slot] : -1;
         out_n = (stage_present && out_row >= 0) ? min(p.slot_rows[slot], 128) : 0;
       }
-      const bool by_rows = p.slot_src && out_n < 128;    // (warpgroup-uniform)
+      const bool by_rows = FULL && p.slot_src && out_n < 128;    // (warpgroup-uniform)
 #pragma unroll 1
       for (int pass = 0; pass < D / 64; ++pass) {
 #pragma unroll
@@ -744,18 +746,23 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   if (sc && tl) return FL_ERR_UNSUPPORTED;
   p.cap_a = sc ? a->softcap * 1.4426950408889634f : 0.f;
   p.cap_b = sc ? 1.0f / p.cap_a : 0.f;
+  // the lean kernels serve the plain calls; packed outputs and the output-row factor take the full variant
+  const bool full = a->slot_src != nullptr || a->o_mult != nullptr;
+#define FL_FWD_LAUNCH(D_, FP4_, TL_, GF_, SC_) \
+  (full ? launch(fwd_kernel<D_, FP4_, TL_, GF_, SC_, true>) : launch(fwd_kernel<D_, FP4_, TL_, GF_, SC_, false>))
   if (sc) {
-    if (fp4) rc = gf ? launch(fwd_kernel<128, true, false, true, true>) : launch(fwd_kernel<128, true, false, false, true>);
-    else if (a->d == 128) rc = gf ? launch(fwd_kernel<128, false, false, true, true>) : launch(fwd_kernel<128, false, false, false, true>);
-    else rc = launch(fwd_kernel<64, false, false, false, true>);
+    if (fp4) rc = gf ? FL_FWD_LAUNCH(128, true, false, true, true) : FL_FWD_LAUNCH(128, true, false, false, true);
+    else if (a->d == 128) rc = gf ? FL_FWD_LAUNCH(128, false, false, true, true) : FL_FWD_LAUNCH(128, false, false, false, true);
+    else rc = FL_FWD_LAUNCH(64, false, false, false, true);
   } else if (fp4) {
-    rc = gf ? launch(fwd_kernel<128, true, false, true, false>) : launch(fwd_kernel<128, true, false, false, false>);
+    rc = gf ? FL_FWD_LAUNCH(128, true, false, true, false) : FL_FWD_LAUNCH(128, true, false, false, false);
   } else if (a->d == 128) {
-    rc = tl ? launch(fwd_kernel<128, false, true, false, false>)
-            : (gf ? launch(fwd_kernel<128, false, false, true, false>) : launch(fwd_kernel<128, false, false, false, false>));
+    rc = tl ? FL_FWD_LAUNCH(128, false, true, false, false)
+            : (gf ? FL_FWD_LAUNCH(128, false, false, true, false) : FL_FWD_LAUNCH(128, false, false, false, false));
   } else {
-    rc = tl ? launch(fwd_kernel<64, false, true, false, false>) : launch(fwd_kernel<64, false, false, false, false>);
+    rc = tl ? FL_FWD_LAUNCH(64, false, true, false, false) : FL_FWD_LAUNCH(64, false, false, false, false);
   }
+#undef FL_FWD_LAUNCH
   if (rc) return rc;
   return launch_result("fl_fwd: kernel launch");
 }
