@@ -123,7 +123,14 @@ def _run(plan, q, k, v, cu_q, cu_k, su_q, su_k, return_lse, doc_maps=None):
     else:
         docs = [t for t in (cu_q, cu_k, su_q, su_k) if t is not None] if sh.varlen else \
             ([su_k.contiguous()] if plan.fwd.seqused_k else [])
+    if plan.pad_from:
+        # head dim below the kernels' 64 / 128: zero columns on the way in (differentiable: the gradients of the pad
+        # are the first head_dim columns of dQ / dK / dV), the first head_dim columns of O on the way out
+        extra = sh.d - plan.pad_from
+        q, k, v = (torch.nn.functional.pad(t, (0, extra)) for t in (q, k, v))
     out, lse = _op.op_apply(plan, q, k, v, docs)
+    if plan.pad_from:
+        out = out[..., :plan.pad_from].contiguous()
     if return_lse:
         if lse.numel() == 0:
             _fail("B8", ValueError, "return_lse is served on the batched and the aligned varlen forms, not under "
@@ -143,7 +150,8 @@ def flash_attn_fp8(q, k, v, *, softmax_scale: Optional[float] = None, causal: bo
                    v_descale=None, grad_proxies=None, doc_maps=None):
     """8-bit (MXFP8) attention, forward and backward, on B200.
 
-    q: (b, s, h, d); k, v: (b, s, h_kv, d); bf16 or f16; h % h_kv == 0; d in {64, 128}. Packed (total, h, d) with
+    q: (b, s, h, d); k, v: (b, s, h_kv, d); bf16 or f16; h % h_kv == 0; d in {64, 128}, or another multiple of 16 below
+    128 (run padded with zero columns to the next of 64 / 128). Packed (total, h, d) with
     cu_seqlens_q / cu_seqlens_k (repacked), or with seqused_q / seqused_k as well (aligned, zero-copy: starts multiples of
     128). Returns out (dtype and shape of q); with return_lse=True (out, lse) with lse (b, h, s) float32 in nats,
     non-differentiable ((h, total_q) on the aligned varlen form). causal is bottom-right aligned.

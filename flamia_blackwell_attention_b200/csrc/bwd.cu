@@ -630,12 +630,18 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const float4 l4 = lds128(v_lse + 16 * j4);
             const float cc = c[j4 >> 3];
             if (TL) {
+              // t = lse2 - s f_K f_Q(query), two columns per instruction
               const float4 f4 = __ldg(fq_vec + j4);
-              const float4 c4 = make_float4(fk * f4.x, fk * f4.y, fk * f4.z, fk * f4.w);
-              pf[4 * j4 + 0] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 0]), c4.x, -l4.x));
-              pf[4 * j4 + 1] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 1]), c4.y, -l4.y));
-              pf[4 * j4 + 2] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 2]), c4.z, -l4.z));
-              pf[4 * j4 + 3] = ex2(fmaf(__uint_as_float(pv[4 * j4 + 3]), c4.w, -l4.w));
+              const uint64_t nfk2 = pack2(-fk, -fk);
+              float t0, t1, t2, t3;
+              unpack2(fma2(pack2(__uint_as_float(pv[4 * j4 + 0]), __uint_as_float(pv[4 * j4 + 1])),
+                           mul2(pack2(f4.x, f4.y), nfk2), pack2(l4.x, l4.y)), t0, t1);
+              unpack2(fma2(pack2(__uint_as_float(pv[4 * j4 + 2]), __uint_as_float(pv[4 * j4 + 3])),
+                           mul2(pack2(f4.z, f4.w), nfk2), pack2(l4.z, l4.w)), t2, t3);
+              pf[4 * j4 + 0] = ex2_neg(t0);
+              pf[4 * j4 + 1] = ex2_neg(t1);
+              pf[4 * j4 + 2] = ex2_neg(t2);
+              pf[4 * j4 + 3] = ex2_neg(t3);
             } else {
               // two columns per instruction: t = lse2 - s c, P' = 2^-t
               const uint64_t nc2 = pack2(-cc, -cc);
@@ -667,15 +673,20 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             for (int j4 = 0; j4 < 8; ++j4) {
               const float4 f4 = __ldg(fdo_vec + qh * 8 + j4);
               const int j = qh * 32 + 4 * j4;
-              t[4 * j4 + 0] = pf[j + 0] * f4.x; t[4 * j4 + 1] = pf[j + 1] * f4.y;
-              t[4 * j4 + 2] = pf[j + 2] * f4.z; t[4 * j4 + 3] = pf[j + 3] * f4.w;
-              am = fmaxf(am, fmaxf(fmaxf(t[4 * j4], t[4 * j4 + 1]), fmaxf(t[4 * j4 + 2], t[4 * j4 + 3])));
+              unpack2(mul2(pack2(pf[j + 0], pf[j + 1]), pack2(f4.x, f4.y)), t[4 * j4 + 0], t[4 * j4 + 1]);
+              unpack2(mul2(pack2(pf[j + 2], pf[j + 3]), pack2(f4.z, f4.w)), t[4 * j4 + 2], t[4 * j4 + 3]);
+              am = fmax3_abs(fmax3_abs(am, t[4 * j4], t[4 * j4 + 1]), t[4 * j4 + 2], t[4 * j4 + 3]);   // all >= 0
             }
             ep[qh] = exp448(__float_as_uint(am));
             const float inv = pow2_inv(ep[qh]);
+            const uint64_t inv2 = pack2(inv, inv);
 #pragma unroll
-            for (int w = 0; w < 8; ++w)
-              pw[qh * 8 + w] = cvt_e4m3x4(t[4 * w] * inv, t[4 * w + 1] * inv, t[4 * w + 2] * inv, t[4 * w + 3] * inv);
+            for (int w = 0; w < 8; ++w) {
+              float a0, a1, a2, a3;
+              unpack2(mul2(pack2(t[4 * w], t[4 * w + 1]), inv2), a0, a1);
+              unpack2(mul2(pack2(t[4 * w + 2], t[4 * w + 3]), inv2), a2, a3);
+              pw[qh * 8 + w] = cvt_e4m3x4(a0, a1, a2, a3);
+            }
           }
           FL_TMEM_ST_16(t_sx + TO_P, pw);
           // every lane quadrant holds the whole A scale tile: column = key block, lane = row of the block
@@ -715,21 +726,22 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int j4 = 0; j4 < 8; ++j4) {
             const float4 d4 = lds128(v_dpp + 16 * (qh * 8 + j4));
             const int j = qh * 32 + 4 * j4;
-            float4 b4 = make_float4(b8[qh], b8[qh], b8[qh], b8[qh]);
-            float4 q4 = make_float4(1.f, 1.f, 1.f, 1.f);
             if (TL) {
+              // b = f_V(key) f_dO(query) per column; the dK side's maximum carries f_Q(query)
               const float4 f4 = __ldg(fdo_vec + qh * 8 + j4);
-              b4 = make_float4(fv8 * f4.x, fv8 * f4.y, fv8 * f4.z, fv8 * f4.w);
-              q4 = __ldg(fq_vec + qh * 8 + j4);
-            }
-            if (TL) {
-              pf[j + 0] *= fmaf(__uint_as_float(pv[j + 0]), b4.x, d4.x);
-              pf[j + 1] *= fmaf(__uint_as_float(pv[j + 1]), b4.y, d4.y);
-              pf[j + 2] *= fmaf(__uint_as_float(pv[j + 2]), b4.z, d4.z);
-              pf[j + 3] *= fmaf(__uint_as_float(pv[j + 3]), b4.w, d4.w);
-              // the dK side carries f_Q(query) when the operands are token-local
-              am = fmaxf(am, fmaxf(fmaxf(fabsf(pf[j] * q4.x), fabsf(pf[j + 1] * q4.y)),
-                                   fmaxf(fabsf(pf[j + 2] * q4.z), fabsf(pf[j + 3] * q4.w))));
+              const float4 q4 = __ldg(fq_vec + qh * 8 + j4);
+              const uint64_t fv2 = pack2(fv8, fv8);
+              const uint64_t u01 = fma2(pack2(__uint_as_float(pv[j + 0]), __uint_as_float(pv[j + 1])),
+                                        mul2(pack2(f4.x, f4.y), fv2), pack2(d4.x, d4.y));
+              const uint64_t u23 = fma2(pack2(__uint_as_float(pv[j + 2]), __uint_as_float(pv[j + 3])),
+                                        mul2(pack2(f4.z, f4.w), fv2), pack2(d4.z, d4.w));
+              const uint64_t p01 = mul2(pack2(pf[j + 0], pf[j + 1]), u01), p23 = mul2(pack2(pf[j + 2], pf[j + 3]), u23);
+              unpack2(p01, pf[j + 0], pf[j + 1]);
+              unpack2(p23, pf[j + 2], pf[j + 3]);
+              float w0, w1, w2, w3;
+              unpack2(mul2(p01, pack2(q4.x, q4.y)), w0, w1);
+              unpack2(mul2(p23, pack2(q4.z, q4.w)), w2, w3);
+              am = fmax3_abs(fmax3_abs(am, w0, w1), w2, w3);
             } else {
               // two columns per instruction
               const uint64_t b2 = pack2(b8[qh], b8[qh]);
@@ -762,16 +774,14 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
           for (int w = 0; w < 8; ++w) {
             const int j0 = qh * 32 + 4 * w;
-            float4 q4 = make_float4(inv, inv, inv, inv);
+            const uint64_t inv2 = pack2(inv, inv);
+            float a0, a1, a2, a3;
             if (TL) {
-              const float4 f4 = __ldg(fq_vec + qh * 8 + w);
-              q4 = make_float4(f4.x * inv, f4.y * inv, f4.z * inv, f4.w * inv);   // powers of two: exact, in range
-            }
-            if (TL) {
-              dsw[qh * 8 + w] = cvt_e4m3x4(pf[j0] * q4.x, pf[j0 + 1] * q4.y, pf[j0 + 2] * q4.z, pf[j0 + 3] * q4.w);
+              const float4 f4 = __ldg(fq_vec + qh * 8 + w);      // f_Q(query) 2^(127 - e): powers of two, exact, in range
+              unpack2(mul2(pack2(pf[j0], pf[j0 + 1]), mul2(pack2(f4.x, f4.y), inv2)), a0, a1);
+              unpack2(mul2(pack2(pf[j0 + 2], pf[j0 + 3]), mul2(pack2(f4.z, f4.w), inv2)), a2, a3);
+              dsw[qh * 8 + w] = cvt_e4m3x4(a0, a1, a2, a3);
             } else {
-              const uint64_t inv2 = pack2(inv, inv);
-              float a0, a1, a2, a3;
               unpack2(mul2(pack2(pf[j0], pf[j0 + 1]), inv2), a0, a1);
               unpack2(mul2(pack2(pf[j0 + 2], pf[j0 + 3]), inv2), a2, a3);
               dsw[qh * 8 + w] = cvt_e4m3x4(a0, a1, a2, a3);

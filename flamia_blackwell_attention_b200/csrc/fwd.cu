@@ -453,12 +453,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           for (int e4 = 0; e4 < 32; ++e4) {
             // log2 of a power of two without an int-to-float conversion (those run on the transcendental unit, which
             // binds this kernel): the exponent field dropped into the mantissa of 2^23 reads as 2^23 + field
+            // (two columns per instruction)
             const float4 k4 = __ldg(fk4 + e4), v4 = __ldg(fv4 + e4);
-            auto lg = [](float f) { return __uint_as_float(0x4B000000u | (__float_as_uint(f) >> 23)) - 8388735.0f; };
-            s[4 * e4 + 0] = fmaf(s[4 * e4 + 0], fq * k4.x, lg(v4.x));
-            s[4 * e4 + 1] = fmaf(s[4 * e4 + 1], fq * k4.y, lg(v4.y));
-            s[4 * e4 + 2] = fmaf(s[4 * e4 + 2], fq * k4.z, lg(v4.z));
-            s[4 * e4 + 3] = fmaf(s[4 * e4 + 3], fq * k4.w, lg(v4.w));
+            auto lgb = [](float f) { return __uint_as_float(0x4B000000u | (__float_as_uint(f) >> 23)); };
+            const uint64_t fq2 = pack2(fq, fq), off2 = pack2(8388735.0f, 8388735.0f);
+            unpack2(fma2(pack2(s[4 * e4 + 0], s[4 * e4 + 1]), mul2(pack2(k4.x, k4.y), fq2),
+                         sub2(pack2(lgb(v4.x), lgb(v4.y)), off2)), s[4 * e4 + 0], s[4 * e4 + 1]);
+            unpack2(fma2(pack2(s[4 * e4 + 2], s[4 * e4 + 3]), mul2(pack2(k4.z, k4.w), fq2),
+                         sub2(pack2(lgb(v4.z), lgb(v4.w)), off2)), s[4 * e4 + 2], s[4 * e4 + 3]);
           }
         }
         if (SC) {   // soft cap: the capped score in log2 units; the factors are used up here
@@ -544,11 +546,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             p3 = ex2(a3);
           }
           if (TL) {     // the row sum is that of the probabilities: take f_V(key) back out
+            // (the factors are pure powers of two: 1 / f is the exponent field mirrored about 127)
             const float4 v4 = __ldg(fv4 + w);
-            ps[w & 7] += (p0 * __uint_as_float((254u << 23) - (__float_as_uint(v4.x) & 0x7F800000u)) +
-                     p1 * __uint_as_float((254u << 23) - (__float_as_uint(v4.y) & 0x7F800000u))) +
-                    (p2 * __uint_as_float((254u << 23) - (__float_as_uint(v4.z) & 0x7F800000u)) +
-                     p3 * __uint_as_float((254u << 23) - (__float_as_uint(v4.w) & 0x7F800000u)));
+            auto rcp = [](float f) { return __uint_as_float((254u << 23) - __float_as_uint(f)); };
+            ps2[w & 3] = fma2(pack2(p0, p1), pack2(rcp(v4.x), rcp(v4.y)), ps2[w & 3]);
+            ps2[w & 3] = fma2(pack2(p2, p3), pack2(rcp(v4.z), rcp(v4.w)), ps2[w & 3]);
           } else if (GF) {  // packed: (p0 + p2, p1 + p3) into the group's pair accumulator
             ps2[w >> 3] = add2(ps2[w >> 3], add2(pack2(p0, p1), pack2(p2, p3)));
           } else {          // the same into one of four pair accumulators
@@ -566,10 +568,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             pg[kbk] = (ps[2 * kbk] + ps[2 * kbk + 1]) * __uint_as_float((uint32_t)(127 + (int)gb[kbk]) << 23);
           psum = (pg[0] + pg[1]) + (pg[2] + pg[3]);
         } else {
-          if (!TL) {
 #pragma unroll
-            for (int t = 0; t < 4; ++t) unpack2(ps2[t], ps[2 * t], ps[2 * t + 1]);
-          }
+          for (int t = 0; t < 4; ++t) unpack2(ps2[t], ps[2 * t], ps[2 * t + 1]);
           psum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         }
         l_sum = fmaf(l_sum, alpha, psum);

@@ -12,7 +12,7 @@ rule ids "B1".."B9" that name the missing piece.
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Optional, Tuple
 
 import torch
@@ -93,6 +93,7 @@ class AttnPlan:
     q_scale_fused: bool
     resolution_log: Tuple[Tuple[str, str, str], ...]
     options: object = field(compare=True)
+    pad_from: int = 0                                 # the call's own head dim when the kernels run it padded (else 0)
 
     def log(self) -> str:
         return "\n".join(f"{f} = {v}: {r}" for f, v, r in self.resolution_log)
@@ -209,8 +210,8 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
     if shape.d not in (64, 128):
         if shape.d > 128 and entry == "fp8":
             _fail("E13", NotImplementedError, f"flash_attn_fp8 serves head_dim <= 128; got {shape.d}")
-        _fail("E13", NotImplementedError, f"flash_attn_{entry} serves head_dim 64 and 128 here (padded head dims are not "
-                                          f"built); got {shape.d}")
+        _fail("E13", NotImplementedError, f"flash_attn_{entry} serves head_dim <= 128 (a multiple of 16; 64 and 128 "
+                                          f"natively, the others padded); got {shape.d}")
     # ---- operand scaling
     scaling = o.operand_scaling
     if scaling in ("block_32x32", "per_tensor"):
@@ -261,7 +262,7 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
 
 def _finish(entry, route, qk_format, shape, log_rows, opts, *, softmax_scale, causal, return_lse, had, scaling, rowlocal,
             ragged, dq_causal, window_size=(None, None), p_frame="row", seqused_k=False, softcap=0.0,
-            deterministic=False):
+            deterministic=False, pad_from=0):
     sc = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(shape.d)
     # sliding window (left, right): None / -1 = unlimited on that side; causal caps the right side at 0 in the kernels
     win = tuple(None if (w is None or w < 0) else int(w) for w in tuple(window_size))
@@ -270,7 +271,7 @@ def _finish(entry, route, qk_format, shape, log_rows, opts, *, softmax_scale, ca
                   softcap=float(softcap or 0.0), seqused_k=bool(seqused_k))
     bwd = BwdSpec("1cta" if shape.requires_grad else "none", scaling, "block_32x32", rowlocal, "row", "e4m3",
                   bool(deterministic), dq_causal if isinstance(dq_causal, str) else ("causal_tile" if dq_causal else "row"))
-    return AttnPlan(entry, route, sc, shape, fwd, bwd, opts.tuning, False, False, tuple(log_rows), opts)
+    return AttnPlan(entry, route, sc, shape, fwd, bwd, opts.tuning, False, False, tuple(log_rows), opts, int(pad_from))
 
 
 def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None, None), softcap=0.0, score_mod=None,
@@ -302,10 +303,30 @@ def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
     def log(f, val, why):
         rows.append((f, str(val), why))
         return val
+    # head dims 16, 32, 48, 80, 96, 112 run padded to the next of 64 / 128 (the reference's rule E13,
+    # flash_attn/cute/lowprec/plan.py:1529-1541): zero columns add nothing to S / dP and move no block exponent
+    pad_from = 0
+    if shape.d not in (64, 128) and 0 < shape.d < 128 and shape.d % 16 == 0:
+        pad_from = shape.d
+        d_pad = 64 if shape.d < 64 else 128
+        if qk_hadamard is True:
+            _fail(4, NotImplementedError, f"qk_hadamard is built for head_dim 128 (the rotation is 128-point); got {shape.d}")
+        if scaling_request(o) == "token_local":
+            _fail("E13", NotImplementedError, f"head_dim {shape.d} runs padded on token-block operands; "
+                                              "operand_scaling='token_local' serves 64 and 128")
+        log("head_dim_padding", d_pad, f"head_dim {shape.d}: the kernels run it padded to {d_pad} with zero columns; "
+                                       "O / dQ / dK / dV are the first head_dim columns")
+        had_why = "explicit" if qk_hadamard is False else f"auto: built for head_dim 128, this call has {shape.d}"
+        qk_hadamard = False
+        if softmax_scale is None:
+            softmax_scale = 1.0 / math.sqrt(shape.d)
+        shape = replace(shape, d=d_pad)
     had, scaling, rowlocal, ragged = _common("fp8", shape, log, causal=causal, window_size=window_size, softcap=softcap,
                                              score_mod=score_mod, score_mod_bwd=score_mod_bwd, mask_mod=mask_mod,
                                              seqused_k=seqused_k, deterministic=deterministic, qk_hadamard=qk_hadamard,
                                              opts=o)
+    if pad_from:
+        rows[:] = [(f, val, had_why) if f == "qk_hadamard" else (f, val, why) for f, val, why in rows]
     p_frame = _p_frame("fp8", o, shape, scaling, default="row")
     log("p_hat_frame", p_frame, "auto: the 8-bit default" if o.p_hat_frame == "auto" else "explicit")
     log("backward_kernel", "1cta", "the 1-CTA backward (key-stationary, GQA in the same accumulators)")
@@ -325,7 +346,7 @@ def resolve_fp8(q, k, v, *, softmax_scale=None, causal=False, window_size=(None,
                    return_lse=return_lse, had=had, scaling=scaling, rowlocal=rowlocal, ragged=ragged, dq_causal=dq_causal,
                    window_size=window_size, p_frame=p_frame,
                    seqused_k=seqused_k is not None and not shape.aligned_varlen, softcap=softcap,
-                   deterministic=deterministic)
+                   deterministic=deterministic, pad_from=pad_from)
 
 
 def _p_frame(entry, o, shape, scaling, default):

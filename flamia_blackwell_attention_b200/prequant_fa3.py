@@ -93,6 +93,8 @@ def flash_attn_fp8_prequant(resolve, q, k, v, q_descale, k_descale, v_descale, g
     meta = [torch.empty(t.shape, dtype=dt, device="meta", requires_grad=want_grad) for t in (q, k, v)]
     kw = dict(kw, qk_hadamard=False)
     plan = resolve(*meta, **kw)
+    if plan.pad_from:
+        _fail("B7", NotImplementedError, f"pre-quantised E4M3 inputs are served at head_dim 64 / 128; got {plan.pad_from}")
     if plan.fwd.operand_scaling != "token_block" or plan.bwd.ds_dq_rowlocal != "off":
         _fail(32, ValueError, "block-scaled operand_scaling / ds_dq_rowlocal options do not go with pre-quantised inputs: "
                               "the operands' scaling is the caller's")

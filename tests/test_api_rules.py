@@ -68,6 +68,10 @@ RULES = [
     ("r34", R4, dict(options=O4(save_bf16_inputs=False)), {}, ValueError, 34, "save_bf16_inputs=False cannot serve this call"),
     ("rE13c", R8, {}, dict(d=256, rg=False), NotImplementedError, "E13", "flash_attn_fp8 serves head_dim <= 128"),
     ("rE13b", R4, {}, dict(d=192), NotImplementedError, "E13", "flash_attn_fp4 serves head_dim 128"),
+    ("rE13d", R8, {}, dict(d=72, rg=False), NotImplementedError, "E13", "flash_attn_fp8 serves head_dim <= 128 (a multiple of 16"),
+    ("rE13e", R8, dict(options=O8(operand_scaling="token_local", ds_dq_rowlocal="all")), dict(d=96), NotImplementedError,
+     "E13", "head_dim 96 runs padded on token-block operands"),
+    ("r04c", R8, dict(qk_hadamard=True), dict(d=96), NotImplementedError, 4, "qk_hadamard is built for head_dim 128"),
     # this build's own refusals: routes and features it does not build
     ("rB1", R4, dict(pv_precision="fp4", causal=True), {}, NotImplementedError, "B1", "pv_precision='fp4'"),
     ("rB2", R8, dict(options=O8(tuning=KernelTuning(bwd_fp4_ld_rep=64))), {}, ValueError, "B2", "KernelTuning"),
@@ -146,3 +150,16 @@ def test_varlen_shapes_resolve():
     assert p.shape.aligned_varlen
     q2 = torch.empty(2, 1000, 4, 128, dtype=BF16, device="meta")
     assert R8(q2, q2, q2).fwd.ragged_documents
+
+
+@pytest.mark.parametrize("d,d_pad", [(16, 64), (48, 64), (80, 128), (96, 128)])
+def test_padded_head_dims_resolve(d, d_pad):
+    """Rule E13 of the reference (flash_attn/cute/lowprec/plan.py:1529-1541): multiples of 16 below 128 are served padded
+    to the next of 64 / 128, with the softmax scale of the call's own head dim and the rotation off."""
+    plan = resolve_fp8(*qkv(d=d), causal=True)
+    assert plan.pad_from == d and plan.shape.d == d_pad and abs(plan.softmax_scale - d ** -0.5) < 1e-12
+    assert not plan.fwd.qk_hadamard
+    rows = {f: (val, why) for f, val, why in plan.resolution_log}
+    assert rows["head_dim_padding"][0] == str(d_pad) and rows["qk_hadamard"] == ("off", f"auto: built for head_dim 128, this call has {d}")
+    assert resolve_fp8(*qkv(d=d_pad), causal=True).pad_from == 0
+    assert resolve_fp8(*qkv(d=d), softmax_scale=0.25).softmax_scale == 0.25

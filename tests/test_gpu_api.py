@@ -362,3 +362,29 @@ def test_softcap(route, d, causal, window):
     # the cap does something: the uncapped result differs
     o2, *_ = _step(fn, q, k, v, g, causal=causal, **({} if window is None else dict(window_size=window)))
     assert A.accuracy(o2, ro)["rel_l2"] > 0.05
+
+
+@pytest.mark.parametrize("d,hk", [(96, 2), (32, 4), (112, 1)])
+def test_fp8_padded_head_dims(d, hk):
+    """Head dims that are multiples of 16 below 128 run padded with zero columns to the next of 64 / 128 (the reference's
+    rule E13, flash_attn/cute/lowprec/plan.py:1529-1541): same numbers, bit for bit, as the padded call made by hand with
+    the call's own softmax scale, and within the usual tolerance of the oracle at the true head dim."""
+    from flamia_blackwell_attention_b200 import flash_attn_fp8
+    q, k, v, g = attention_inputs(2, 384, 4, hk, d, seed=21)
+    o, dq, dk, dv, lse = _step(flash_attn_fp8, q, k, v, g, causal=True, return_lse=True)
+    assert o.shape == q.shape and dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
+    dp = 64 if d < 64 else 128
+    pad = lambda t: torch.nn.functional.pad(t, (0, dp - d))      # noqa: E731
+    o2, dq2, dk2, dv2, lse2 = _step(flash_attn_fp8, pad(q), pad(k), pad(v), pad(g), causal=True, return_lse=True,
+                                    softmax_scale=1.0 / math.sqrt(d), qk_hadamard=False)
+    assert torch.equal(o, o2[..., :d]) and torch.equal(lse.cpu(), lse2.cpu())
+    assert torch.equal(dk, dk2[..., :d]) and torch.equal(dv, dv2[..., :d])
+    assert float((dq - dq2[..., :d]).abs().max()) <= 2e-3 * float(dq2.abs().max())     # f16 reduction order only
+    assert float(o2[..., d:].abs().max()) == 0.0
+    # the oracle's quantiser takes 64 / 128 columns: zero columns move no block maximum, so the padded oracle call is the
+    # definition at the true head dim; the fp32 reference is taken at the true head dim itself
+    ro, rl, rdq, rdk, rdv = A.qdq_attention(pad(q), pad(k), pad(v), pad(g), causal=True, softmax_scale=1.0 / math.sqrt(d))
+    _check((o, dq, dk, dv), (ro[..., :d], rdq[..., :d], rdk[..., :d], rdv[..., :d]))
+    assert float((lse.cpu() - rl).abs().max()) < 2e-3
+    fo, _fl, fdq, fdk, fdv = A.attention_fp32(q, k, v, g, causal=True)
+    _check((o, dq, dk, dv), (fo, fdq, fdk, fdv), tol=1e-1)
