@@ -102,6 +102,13 @@ enum { BB_KV = 0, BB_KVE = 2, BB_QFULL = 4, BB_QEMPTY = 6, BB_S = 8, BB_DP = 10,
 enum { TC_S = 0, TO_P = 0, TO_DS = 16, TO_SFA_P = 32, TO_SFB_DO = 36, TO_SFA_DK = 40, TO_SFB_Q = 44, TO_SFA_DQ = 48,
        TO_SFB_DQ = 52, TC_DV = 128, TC_DP = 256, TC_DK = 384 };
 
+// bits of the warp's largest |v| (the f32 form of the instruction is faster than masking the sign and reducing integers:
+// -8 % on the row-local backward, which runs it once per dS column)
+__device__ __forceinline__ uint32_t warp_max_abs_f32(float v) {
+  float r;
+  asm volatile("redux.sync.max.abs.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return __float_as_uint(r);
+}
 __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
   uint32_t r;
   asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
@@ -802,7 +809,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             for (int e = 0; e < 4; ++e) {
               const int j = 4 * w + e;
               const float a = TL ? pf[j] * fk_true : pf[j];
-              const uint32_t wm = warp_max_u32(__float_as_uint(a) & 0x7FFFFFFFu);
+              const uint32_t wm = warp_max_abs_f32(a);
               const uint32_t t = max((wm + 0x00200000u) & 0x7F800000u, 9u << 23);
               if (lane == (j & 31)) mine[j >> 5] = t;
               v[e] = a * __uint_as_float(0x83000000u - t);
