@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libflamia_b200.so")
 
 # status codes (csrc/sm100.cuh)
-ABI_VERSION = 7
+ABI_VERSION = 8
 FL_OK, FL_ERR_BAD_ARG, FL_ERR_CUDA, FL_ERR_UNSUPPORTED, FL_ERR_TOO_LARGE = 0, 1, 2, 3, 4
 FL_DEV_WAIT_TIMEOUT = 0x100
 FL_DEV_BAD_TABLE = 0x200
@@ -40,7 +40,7 @@ class AttnArgs(C.Structure):
                                   "dv", "doc_start", "doc_len")] + \
                [(n, i32) for n in ("n_docs", "b", "s_q", "s_k", "h", "h_kv", "d")] + [("softmax_scale", f32)] + \
                [(n, i32) for n in ("mode", "flags")] + [("status", vp), ("wait_cycles", i64)] + \
-               [(n, i32) for n in ("window_left_p1", "window_right_p1")] + [("seqused_k", vp), ("softcap", f32), ("dq_order", vp), ("dq_scale_rows", vp), ("o_mult", vp), ("dk_mult", vp), ("slot_src", vp), ("slot_rows", vp), ("out_rows", i32)]
+               [(n, i32) for n in ("window_left_p1", "window_right_p1")] + [("seqused_k", vp), ("softcap", f32), ("dq_order", vp), ("dq_scale_rows", vp), ("o_mult", vp), ("dk_mult", vp), ("slot_src", vp), ("slot_rows", vp), ("out_rows", i32), ("tok_lg_v", vp), ("tok_rcp_v", vp)]
 
 
 EXPORTS = {
@@ -54,6 +54,7 @@ EXPORTS = {
     "fl_dq_post_rows": (i32, [vp, vp, f32, vp, i32, i32, i32, i32, i32, i32, vp]),
     "fl_dq_post_ex": (i32, [vp, vp, i32, vp, f32, vp, i32, i32, i32, i32, i32, i32, vp]),
     "fl_code_stats": (i32, [vp, vp, i32, i32, i32, i32, vp, vp]),
+    "fl_token_aux": (i32, [vp, C.c_int64, vp, vp, vp]),
     "fl_dq_post_packed": (i32, [vp, vp, f32, vp, i32, i32, i32, i32, i32, vp, vp, vp]),
     "fl_dq_prescale_rows": (i32, [vp, vp, vp, i32, i32, f32, vp, vp, vp]),
     "fl_pack_rows": (i32, [vp, vp, vp, i32, i32, vp]),

@@ -55,6 +55,8 @@ struct FwdParams {
   const float* fac_q;
   const float* fac_k;
   const float* fac_v;
+  const float* tok_lg_v;   // token-local: log2 f_V(key) and 1 / f_V(key), (b, h_kv, s_k)
+  const float* tok_rcp_v;
   const uint8_t* sfq4;   // FL_MODE_FP4: E4M3 scale atoms of the NVFP4 Q / K copies, 1 KB per 128-row tile at d = 128
   const uint8_t* sfk4;
   float* lse;
@@ -429,7 +431,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         // staging them in shared memory was twice as slow: 384 broadcast reads per thread and tile saturate the
         // shared-memory port that the tensor core's operand reads also go through)
         const float4* fk4 = reinterpret_cast<const float4*>(p.fac_k + (TL ? bh_k * p.s_k + T.k0 + j * 128 : 0));
-        const float4* fv4 = reinterpret_cast<const float4*>(p.fac_v + (TL ? bh_k * p.s_k + T.k0 + j * 128 : 0));
+        const float4* lg4 = reinterpret_cast<const float4*>(TL ? p.tok_lg_v + bh_k * p.s_k + T.k0 + j * 128 : p.fac_v);
+        const float4* rc4 = reinterpret_cast<const float4*>(TL ? p.tok_rcp_v + bh_k * p.s_k + T.k0 + j * 128 : p.fac_v);
         if (TL) {
           sfv = 0x7F7F7F7Fu;
 #pragma unroll
@@ -451,16 +454,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (TL) {   // y = s f_Q f_K(key) scale + log2 f_V(key)
 #pragma unroll
           for (int e4 = 0; e4 < 32; ++e4) {
-            // log2 of a power of two without an int-to-float conversion (those run on the transcendental unit, which
-            // binds this kernel): the exponent field dropped into the mantissa of 2^23 reads as 2^23 + field
-            // (two columns per instruction)
-            const float4 k4 = __ldg(fk4 + e4), v4 = __ldg(fv4 + e4);
-            auto lgb = [](float f) { return __uint_as_float(0x4B000000u | (__float_as_uint(f) >> 23)); };
-            const uint64_t fq2 = pack2(fq, fq), off2 = pack2(8388735.0f, 8388735.0f);
-            unpack2(fma2(pack2(s[4 * e4 + 0], s[4 * e4 + 1]), mul2(pack2(k4.x, k4.y), fq2),
-                         sub2(pack2(lgb(v4.x), lgb(v4.y)), off2)), s[4 * e4 + 0], s[4 * e4 + 1]);
-            unpack2(fma2(pack2(s[4 * e4 + 2], s[4 * e4 + 3]), mul2(pack2(k4.z, k4.w), fq2),
-                         sub2(pack2(lgb(v4.z), lgb(v4.w)), off2)), s[4 * e4 + 2], s[4 * e4 + 3]);
+            // two columns per instruction; log2 f_V comes from a table (derived here it cost three integer instructions
+            // per score on loops that are issue-bound)
+            const float4 k4 = __ldg(fk4 + e4), l4 = __ldg(lg4 + e4);
+            const uint64_t fq2 = pack2(fq, fq);
+            unpack2(fma2(pack2(s[4 * e4 + 0], s[4 * e4 + 1]), mul2(pack2(k4.x, k4.y), fq2), pack2(l4.x, l4.y)),
+                    s[4 * e4 + 0], s[4 * e4 + 1]);
+            unpack2(fma2(pack2(s[4 * e4 + 2], s[4 * e4 + 3]), mul2(pack2(k4.z, k4.w), fq2), pack2(l4.z, l4.w)),
+                    s[4 * e4 + 2], s[4 * e4 + 3]);
           }
         }
         if (SC) {   // soft cap: the capped score in log2 units; the factors are used up here
@@ -546,11 +547,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             p3 = ex2(a3);
           }
           if (TL) {     // the row sum is that of the probabilities: take f_V(key) back out
-            // (the factors are pure powers of two: 1 / f is the exponent field mirrored about 127)
-            const float4 v4 = __ldg(fv4 + w);
-            auto rcp = [](float f) { return __uint_as_float((254u << 23) - __float_as_uint(f)); };
-            ps2[w & 3] = fma2(pack2(p0, p1), pack2(rcp(v4.x), rcp(v4.y)), ps2[w & 3]);
-            ps2[w & 3] = fma2(pack2(p2, p3), pack2(rcp(v4.z), rcp(v4.w)), ps2[w & 3]);
+            const float4 r4 = __ldg(rc4 + w);
+            ps2[w & 3] = fma2(pack2(p0, p1), pack2(r4.x, r4.y), ps2[w & 3]);
+            ps2[w & 3] = fma2(pack2(p2, p3), pack2(r4.z, r4.w), ps2[w & 3]);
           } else if (GF) {  // packed: (p0 + p2, p1 + p3) into the group's pair accumulator
             ps2[w >> 3] = add2(ps2[w >> 3], add2(pack2(p0, p1), pack2(p2, p3)));
           } else {          // the same into one of four pair accumulators
@@ -697,6 +696,7 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   if (fp4 && (!a->q4 || !a->k4 || !a->sfq4 || !a->sfk4)) return FL_ERR_BAD_ARG;
   const bool tl = (a->flags & FL_A_TOKEN_LOCAL) != 0, gf = (a->flags & FL_A_P_GROUP) != 0;
   if (tl && (a->doc_start || a->mode != FL_MODE_FP8)) return FL_ERR_UNSUPPORTED;   // token-local: batched 8-bit route
+  if (tl && (!a->tok_lg_v || !a->tok_rcp_v)) return FL_ERR_BAD_ARG;                 // tables of fl_token_aux over V's factors
   if (gf && (tl || a->d != 128)) return FL_ERR_UNSUPPORTED;                        // group frame: d = 128, block factors
   if (a->h <= 0 || a->h_kv <= 0 || a->h % a->h_kv) return FL_ERR_BAD_ARG;
   if ((a->s_q % 128) || (a->s_k % 128) || a->s_q <= 0 || a->s_k <= 0 || a->b <= 0) return FL_ERR_BAD_ARG;
@@ -711,6 +711,7 @@ extern "C" int fl_fwd(const fl_attn_args* a, void* stream) {
   FwdParams p;
   p.fac_q = a->fac_q; p.fac_k = a->fac_k; p.fac_v = a->fac_v; p.lse = a->lse;
   p.sfq4 = a->sfq4; p.sfk4 = a->sfk4;
+  p.tok_lg_v = a->tok_lg_v; p.tok_rcp_v = a->tok_rcp_v;
   p.doc_start = a->doc_start; p.doc_len = a->doc_len; p.n_docs = a->n_docs;
   p.seqused_k = a->seqused_k;
   p.o_mult = a->o_mult;

@@ -353,6 +353,25 @@ extern "C" int fl_dq_prescale_rows(const float* row_do, float* row_v, float* row
   return launch_result("fl_dq_prescale_rows: kernel launch");
 }
 
+namespace fl {
+// lg = log2 f, rcp = 1 / f for power-of-two factors: exponent-field arithmetic, exact
+__global__ void token_aux_kernel(const float* __restrict__ f, long long n, float* __restrict__ lg, float* __restrict__ rcp) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t bits = __float_as_uint(f[i]) & 0x7F800000u;
+  lg[i] = (float)((int)(bits >> 23) - 127);
+  rcp[i] = __uint_as_float((254u << 23) - bits);
+}
+}  // namespace fl
+
+extern "C" int fl_token_aux(const float* factors, int64_t n, float* lg, float* rcp, void* stream) {
+  using namespace fl;
+  if (!factors || !lg || !rcp || n <= 0) return FL_ERR_BAD_ARG;
+  if ((n + 255) / 256 > 0x7FFFFFFF) return FL_ERR_TOO_LARGE;
+  token_aux_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(factors, (long long)n, lg, rcp);
+  return launch_result("fl_token_aux: kernel launch");
+}
+
 extern "C" int fl_code_stats(const void* codes, const float* descale, int32_t b, int32_t s, int32_t h, int32_t d,
                              float* tile_stats, void* stream) {
   using namespace fl;

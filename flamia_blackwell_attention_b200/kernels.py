@@ -194,8 +194,20 @@ def attn_fwd(q, k, v, *, causal, softmax_scale, out_dtype=torch.bfloat16, mode=L
     if o_mult is not None:
         assert o_mult.dtype == torch.float32 and o_mult.numel() == b * k["codes"].shape[2] and o_mult.is_contiguous()
         a.o_mult = L.ptr(o_mult)
+    if token_local:     # log2 f_V and 1 / f_V per key, which the forward applies to every score
+        lg, rcp = token_aux(v["token_factors"])
+        a.tok_lg_v, a.tok_rcp_v = L.ptr(lg), L.ptr(rcp)
     L.check(L.load().fl_fwd(C.byref(a), _stream()), "fl_fwd")
     return out, lse, status
+
+
+def token_aux(factors):
+    """(log2 f, 1 / f) float32 tables of a power-of-two factor table (the quantiser's token_factors)."""
+    f = factors.contiguous()
+    assert f.dtype == torch.float32
+    lg, rcp = torch.empty_like(f), torch.empty_like(f)
+    L.check(L.load().fl_token_aux(L.ptr(f), int(f.numel()), L.ptr(lg), L.ptr(rcp), _stream()), "fl_token_aux")
+    return lg, rcp
 
 
 def selftest_mma(which, a, b, sfa=None, sfb=None, wait_cycles=0):

@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define FL_ABI_VERSION 7
+#define FL_ABI_VERSION 8
 
 /* fl_quant_args.flags */
 #define FL_Q_HADAMARD 1            /* rotate rows by diag(signs) H_128 / sqrt(128) before quantising (d = 128) */
@@ -156,6 +156,11 @@ typedef struct fl_attn_args {
   const int32_t* slot_src;
   const int32_t* slot_rows;
   int32_t out_rows;
+  /* fl_fwd with FL_A_TOKEN_LOCAL: log2 f_V(key) and 1 / f_V(key) as float tables (b, h_kv, s_k), from fl_token_aux over
+   * V's token_factors. The forward folds log2 f_V into the scores and takes f_V back out of the row sums for every score:
+   * read from tables this is one load each, derived from f_V in the kernel it was three integer instructions per score. */
+  const float* tok_lg_v;
+  const float* tok_rcp_v;
 } fl_attn_args;
 
 /* Forward: O = softmax(scale Q K^T + mask) V, LSE.
@@ -199,6 +204,10 @@ int fl_dq_post_packed(const void* dq_acc, const float* post_scale, float mult, v
  * read of the V codes, flash_attn/cute/lowprec/prequant_fa3.py:386-470). */
 int fl_code_stats(const void* codes, const float* descale, int32_t b, int32_t s, int32_t h, int32_t d, float* tile_stats,
                   void* stream);
+/* lg[i] = log2 f[i], rcp[i] = 1 / f[i] for n power-of-two factors (fl_quant_args.token_factors): the tables of
+ * fl_attn_args.tok_lg_v / tok_rcp_v. The reference keeps such per-token rows in its (6, b, h, s) token table
+ * (flash_attn/cute/lowprec/_routes.py:749-755). */
+int fl_token_aux(const float* factors, int64_t n, float* lg, float* rcp, void* stream);
 /* fl_dq_post_rows: post_scale_rows is (b, s), one value per query row. */
 int fl_dq_post_rows(const void* dq_acc, const float* post_scale_rows, float mult, void* dq, int32_t b, int32_t s,
                     int32_t h, int32_t d, int32_t unrotate, int32_t out_f16, void* stream);

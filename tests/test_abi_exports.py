@@ -21,7 +21,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), n
     assert set(_lib.EXPORTS) == set(names)
-    assert _lib.load().fl_abi_version() == _lib.ABI_VERSION == 7
+    assert _lib.load().fl_abi_version() == _lib.ABI_VERSION == 8
 
 
 def test_bad_arguments_are_refused_without_a_device():

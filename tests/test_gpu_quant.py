@@ -154,3 +154,19 @@ def test_config_shapes_digest_property():
     err = (deq - q.cuda().float()).abs()
     assert float((err / fac).max()) <= 16.0 + 1e-6      # half of the largest E4M3 step (32) in units of the block scale
     assert float(codes.abs().max()) <= 448.0
+
+
+def test_token_aux_tables_are_exact():
+    """fl_token_aux: log2 f and 1 / f of power-of-two token factors (the per-token rows the reference keeps in its
+    (6, b, h, s) table, flash_attn/cute/lowprec/_routes.py:749-755), exact for every exponent a token factor can take."""
+    from flamia_blackwell_attention_b200 import kernels as K
+    e = torch.arange(-126, 127, dtype=torch.float32)
+    f = torch.exp2(e).repeat(5).cuda()
+    lg, rcp = K.token_aux(f)
+    assert torch.equal(lg.cpu(), e.repeat(5)) and torch.equal(rcp.cpu(), torch.exp2(-e).repeat(5))
+    x = torch.randn(1, 256, 2, 128).bfloat16().cuda()
+    x[0, 7] = 0                                       # an all-zero token: factor 1
+    r = K.quantize_fp8_blocks(x, token_local_exponents=True)
+    lg, rcp = K.token_aux(r["token_factors"])
+    assert torch.equal(lg, torch.log2(r["token_factors"])) and torch.equal(rcp, 1.0 / r["token_factors"])
+    assert float(lg[0, :, 7].abs().max()) == 0.0
