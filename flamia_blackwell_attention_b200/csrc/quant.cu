@@ -595,28 +595,39 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       uint8_t* x4row = p.x4 + row_off / 2;
       uint32_t sfw[2] = {0u, 0u};
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {                   // 16 elements
-        float am = 0.f;
+      for (int g2 = 0; g2 < 4; ++g2) {                // two groups of 16 elements = one 16-byte store
+        uint32_t pk[4];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float a = fabsf(flush_sub(x[16 * g + e]));
-          am = (a > am) ? a : am;                      // a NaN never wins
-        }
-        const float u = __fmul_rn(am, 1.0f / 6.0f);
-        const uint32_t sfb = cvt_e4m3x2(u, 0.f) & 0xFF;
-        const float sfv = e4m3_byte_to_f32(sfb);
-        const float m = sfv > 0.f ? __frcp_rn(sfv) : (u > 0.f ? __int_as_float(0x7F800000) : 0.f);
-        uint32_t packed[2] = {0u, 0u};
+        for (int gg = 0; gg < 2; ++gg) {
+          const int g = 2 * g2 + gg;
+          // the largest flushed magnitude = the flushed largest magnitude (flushing is monotone; a NaN never wins a max)
+          float am = 0.f;
 #pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float a0 = flush_sub(__fmul_rn(flush_sub(x[16 * g + e]), m));
-          const float a1 = flush_sub(__fmul_rn(flush_sub(x[16 * g + e + 1]), m));
-          uint16_t c2;
-          asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}" : "=h"(c2) : "f"(a1), "f"(a0));
-          packed[e >> 3] |= (uint32_t)(c2 & 0xFF) << ((e & 7) * 4);
+          for (int e = 0; e < 16; e += 2) am = fmax3_abs(am, x[16 * g + e], x[16 * g + e + 1]);
+          am = flush_sub(am);
+          const float u = __fmul_rn(am, 1.0f / 6.0f);
+          const uint32_t sfb = cvt_e4m3x2(u, 0.f) & 0xFF;
+          const float sfv = e4m3_byte_to_f32(sfb);
+          const float m = sfv > 0.f ? __frcp_rn(sfv) : (u > 0.f ? __int_as_float(0x7F800000) : 0.f);
+          const uint64_t m2 = pack2(m, m);
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {            // eight elements -> one word, low nibble first
+            float a[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)               // the product with subnormal inputs and results flushed, two at a time
+              unpack2(mul2_ftz(pack2(x[16 * g + 8 * hh + 2 * k], x[16 * g + 8 * hh + 2 * k + 1]), m2), a[2 * k], a[2 * k + 1]);
+            uint32_t w;
+            asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\t"
+                "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\tcvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+                "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\tcvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+                "mov.b32 %0, {t0, t1, t2, t3};\n\t}"
+                : "=r"(w)
+                : "f"(a[0]), "f"(a[1]), "f"(a[2]), "f"(a[3]), "f"(a[4]), "f"(a[5]), "f"(a[6]), "f"(a[7]));
+            pk[2 * gg + hh] = w;
+          }
+          sfw[g >> 2] |= sfb << (8 * (g & 3));
         }
-        *reinterpret_cast<uint2*>(x4row + g * 8) = make_uint2(packed[0], packed[1]);
-        sfw[g >> 2] |= sfb << (8 * (g & 3));
+        *reinterpret_cast<uint4*>(x4row + g2 * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       if (p.sf4) {
         uint8_t* atom = p.sf4 + ((bh * ntile + tile) * (D / 64)) * 512;
