@@ -663,7 +663,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         for (int j = 0; j < 4; ++j)
 #pragma unroll
           for (int e = 0; e < 8; e += 2)
-            aq[q] = fmaxf(fmaxf(aq[q], fabsf(x[32 * j + 8 * q + e])), fabsf(x[32 * j + 8 * q + e + 1]));
+            aq[q] = fmax3_abs(aq[q], x[32 * j + 8 * q + e], x[32 * j + 8 * q + e + 1]);
       amax = fmaxf(fmaxf(aq[0], aq[1]), fmaxf(aq[2], aq[3]));
       if (p.tile_stats || p.row_stat) {
         float lq[4];
