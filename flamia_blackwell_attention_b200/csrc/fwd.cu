@@ -96,7 +96,7 @@ struct Tile {
 // barrier indices
 enum { B_Q = 0, B_QE = 2, B_KFULL = 4, B_KEMPTY = B_KFULL + KV_STAGES, B_VFULL = B_KEMPTY + KV_STAGES,
        B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES, B_PFULL = B_SFULL + 2, B_PVDONE = B_PFULL + 2,
-       B_SDRAIN = B_PVDONE + 2, B_EPI = B_SDRAIN + 2, B_GF = B_EPI + 2, B_COUNT = B_GF + 2 };
+       B_SDRAIN = B_PVDONE + 2, B_EPI = B_SDRAIN + 2, B_COUNT = B_EPI + 2 };
 
 template <int N>
 __device__ __forceinline__ void fwd_reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
@@ -174,7 +174,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ Tile tile_s[2];                            // the items in flight (written by the producer, item k in slot k & 1)
-  __shared__ uint32_t s_sfp[2][2][128];                 // group frame: [stage][tile parity][row] = P-hat's four exponent bytes
+  // group frame: [stage][tile parity] one scale atom (32 rows x 16 B: row r at word (r % 32) * 4 + r / 32) = P-hat's four
+  // exponent bytes per row; the issuer copies it into the A scale columns right before the stage's P.V product
+  __shared__ __align__(16) uint32_t s_sfp[2][2][128];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = gridDim.x, cta = blockIdx.x;
@@ -190,7 +192,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       mbar_init(&bars[B_PVDONE + i], 1);
       mbar_init(&bars[B_SDRAIN + i], 4);
       mbar_init(&bars[B_EPI + i], 4);
-      mbar_init(&bars[B_GF + i], 4);
     }
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(&bars[B_KFULL + i], 1);
@@ -305,9 +306,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (cy == 0) return true;
         return mbar_wait(&bars[B_SDRAIN + (1 - i)], (cy - 1) & 1, p.ctl, abortp, 26 + i);
       };
-      auto issue_pv = [&](int i, int st, uint32_t accum) {
+      auto issue_pv = [&](int i, int st, uint32_t accum, int par) {
         const uint64_t b = desc_adv(dv0, st * TILE_BYTES);
         const uint32_t ts = tm + 128 * i;
+        if (GF) tmem_cp_sf_atom(ts + 32, smem_desc(smem_u32(&s_sfp[i][par][0]), 0, 128, SWZ_NONE));
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)   // 32 keys per instruction: 32 rows of the V tile (MN-major operand)
           umma_mxf8_ts(tm + 256 + 128 * i, ts + 8 * kk, desc_adv(b, kk * 32 * D), idesc_bs(128, D, 0, 0, 0, 1, 1, kk, kk),
@@ -359,7 +361,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           tc_fence_after();
           // P.V(j) completes before S(j + 1) does (issue order), which the softmax threads wait for anyway: a
           // separate completion signal is needed only after the stage's last tile (each commit costs the issuer ~60 clocks)
-          if (elect_one()) { issue_pv(i, st, j > 0); if (j + 1 == n_i) tc_commit(&bars[B_PVDONE + i]); }
+          if (elect_one()) { issue_pv(i, st, j > 0, (ci - 1) & 1); if (j + 1 == n_i) tc_commit(&bars[B_PVDONE + i]); }
           __syncwarp();
           if (j + 1 < n_i) {
             if (!k_next_ready) {
@@ -393,7 +395,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const uint32_t t_o = tmem + 256 + 128 * i + ((uint32_t)((warp & 3) * 32) << 16);
     int cs = 0;                                       // tiles of this stage so far, over all items
     int cd = 0;                                       // items of this stage that ended with a P.V so far
-    int epi = 0, gfn = 0;                             // uses of the epilogue / group-frame barriers so far
+    int epi = 0, gfn = 0;                             // uses of the epilogue barrier / group-frame scale atoms so far
     bool ok = true;
     for (int k = 0; ok; ++k) {
       const int L = fwd_item(k, G, cta, p.zigzag);
@@ -574,13 +576,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         l_sum = fmaf(l_sum, alpha, psum);
         FL_TMEM_ST_32(t_s, pw);
         if (GF) {
-          // the A scale tile: every lane quadrant holds all 128 rows' exponent words (lane = row % 32, column = row / 32)
-          s_sfp[i][gfn & 1][r] = sfp;
-          mbar_arrive_warp(&bars[B_GF + i]);
-          if (!(ok = mbar_wait(&bars[B_GF + i], gfn & 1, p.ctl, abortp, 32 + i))) break;
-          const uint32_t* sp = s_sfp[i][gfn & 1];
+          // the A scale tile (every lane quadrant holds all 128 rows' exponent words: lane = row % 32, column = row / 32)
+          // is copied from this atom by the issuer; only the B scale columns are stored from here
+          s_sfp[i][gfn & 1][(r & 31) * 4 + (r >> 5)] = sfp;
           ++gfn;
-          uint32_t sf[8] = {sp[lane], sp[32 + lane], sp[64 + lane], sp[96 + lane], sfv, sfv, sfv, sfv};
+          fence_proxy_async();             // the atom is read by tcgen05.cp (async proxy)
+          uint32_t sf[8] = {0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, sfv, sfv, sfv, sfv};
           FL_TMEM_ST_8(t_s + 32, sf);
         } else {
           uint32_t sf[8] = {0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, sfv, sfv, sfv, sfv};
