@@ -170,7 +170,7 @@ def measure_route(fn, route, causal, tensors, args, world, dist, K, clock_gpu=No
     for _ in range(W):
         step()
     barrier()
-    # ---- the timed steps replay one captured step (8 launches + the status-word fill): no host launch gaps
+    # ---- the timed steps replay one captured step (8 launches): no host launch gaps
     run_step, mode = step, "eager"
     if not args.no_graph:
         try:

@@ -36,9 +36,23 @@ def backward_scalars(softmax_scale, dq_boost=1.0):
 # --------------------------------------------------------------------------------------------------------------- status
 # Every device-side wait of the kernels is bounded; one that runs out writes 0x100 | site into the call's status word and
 # the kernel drains, leaving its outputs partly written. Reading the word costs a host synchronisation, so the hot path
-# never does it: the word of the most recent call per device is remembered here for check_status(), and the environment
-# variable FLAMIA_B200_CHECK_STATUS=1 makes every forward and backward check its own word (a debugging mode).
+# never does it: the device's word is remembered here for check_status(), and the environment variable
+# FLAMIA_B200_CHECK_STATUS=1 makes every forward and backward check it (a debugging mode).
 _LAST_STATUS: dict = {}
+_DEVICE_STATUS: dict = {}
+
+
+def _status_word(device):
+    """The device's status word: one persistent int32 per device, zeroed when it is made and again by check_status()
+    after it reported a code (kernels only ever write it when something went wrong), so a call launches no fill kernel.
+    A first call made inside a stream capture gets a word of the capture's own."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _DEVICE_STATUS.get(idx)
+    if st is None:
+        if torch.cuda.is_current_stream_capturing():
+            return K.new_status(device)
+        st = _DEVICE_STATUS[idx] = K.new_status(device)
+    return st
 
 
 def _note_status(status):
@@ -48,8 +62,9 @@ def _note_status(status):
 
 
 def check_status(device=None) -> int:
-    """Synchronises `device` (default: the current one) and raises RuntimeError if the most recent flash_attn_fp8 /
-    flash_attn_fp4 call there (forward or backward) gave up a device-side wait; returns 0 otherwise."""
+    """Synchronises `device` (default: the current one) and raises RuntimeError if a flash_attn_fp8 / flash_attn_fp4 call
+    there (forward or backward) since the last check gave up a device-side wait or met a bad document table; returns 0
+    otherwise. The word is cleared when a code has been reported."""
     idx = torch.cuda.current_device() if device is None else torch.device(device).index
     if idx is None:
         idx = torch.cuda.current_device()
@@ -59,9 +74,11 @@ def check_status(device=None) -> int:
     with torch.cuda.device(idx):
         code = K.read_status(st)
     if code:
+        with torch.cuda.device(idx):
+            st.zero_()
         what = f"a bounded wait ran out at site {code & 0xFF}" if code & L.FL_DEV_WAIT_TIMEOUT else \
             (f"the document table is inconsistent (code {code:#x})" if code & L.FL_DEV_BAD_TABLE else f"code {code:#x}")
-        raise RuntimeError(f"flamia_blackwell_attention_b200: the last attention call on cuda:{idx} did not complete: "
+        raise RuntimeError(f"flamia_blackwell_attention_b200: an attention call on cuda:{idx} did not complete: "
                            f"{what}; its outputs are not valid")
     return 0
 
@@ -197,7 +214,7 @@ def _forward_prequant(plan, q8, k8, v8, descales, seqused_k):
     qd, kd, vd = descales
     grp = sh.h // sh.h_kv
     need_bwd = plan.bwd.kernel != "none"
-    status = K.new_status(q8.device)
+    status = _status_word(q8.device)
 
     def table(dsc, heads_rep, s):
         return dsc.repeat_interleave(heads_rep, dim=1)[:, :, None].expand(sh.b, dsc.shape[1] * heads_rep, s // 32).contiguous()
@@ -241,7 +258,7 @@ def forward(plan, q, k, v, docs, seqused_k=None, prequant=None):
     # rotation: the 8-bit route rotates the E4M3 codes; the mixed route rotates only the NVFP4 S operands
     qk_kw = dict(apply_hadamard_rotation=f.qk_hadamard, hadamard_rotation_scope="nvfp4_copy" if fp4 else "all",
                  also_make_nvfp4_copy=fp4, token_local_exponents=tl, packed_slots=slots)
-    status = K.new_status(q.device)
+    status = _status_word(q.device)
     rows = need_bwd and plan.bwd.dq_prescale == "causal_row"      # per-token K / V statistics instead of per-tile ones
     k_rows = v_rows = None
     if rows:
