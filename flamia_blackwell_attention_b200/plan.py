@@ -257,6 +257,12 @@ def _common(entry, shape, log, *, causal, window_size, softcap, score_mod, score
     if o.forward_two_cta == "on":
         _fail(15, ValueError, "forward_two_cta='on' but the forward on CTA pairs is not built here")
     ragged = (not shape.varlen) and (shape.s_q % 128 != 0 or shape.s_k % 128 != 0)
+    if scaling == "token_local" and ragged:
+        _fail(16, ValueError, "operand_scaling='token_local' runs the fold forward, which takes no documents: lengths that "
+                              f"are no multiple of 128 run as documents; got {shape.s_q} / {shape.s_k}")
+    if shape.d != 128 and shape.requires_grad and (rowlocal == "all" or scaling == "token_local"):
+        _fail("B6", NotImplementedError, "ds_dq_rowlocal='all' (and with it operand_scaling='token_local') is built in "
+                                         f"the head_dim 128 backward; this call runs at head_dim {shape.d}")
     return bool(had), scaling, rowlocal, ragged
 
 

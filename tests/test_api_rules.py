@@ -72,6 +72,12 @@ RULES = [
     ("rE13e", R8, dict(options=O8(operand_scaling="token_local", ds_dq_rowlocal="all")), dict(d=96), NotImplementedError,
      "E13", "head_dim 96 runs padded on token-block operands"),
     ("r04c", R8, dict(qk_hadamard=True), dict(d=96), NotImplementedError, 4, "qk_hadamard is built for head_dim 128"),
+    ("rB6c", R8, dict(options=O8(ds_dq_rowlocal="all")), dict(d=64), NotImplementedError, "B6",
+     "ds_dq_rowlocal='all' (and with it operand_scaling='token_local') is built in the head_dim 128 backward"),
+    ("rB6d", R8, dict(options=O8(operand_scaling="token_local", ds_dq_rowlocal="all")), dict(d=64), NotImplementedError, "B6",
+     "ds_dq_rowlocal='all' (and with it operand_scaling='token_local') is built in the head_dim 128 backward"),
+    ("r16t", R8, dict(options=O8(operand_scaling="token_local", ds_dq_rowlocal="all")), dict(s=200), ValueError, 16,
+     "operand_scaling='token_local' runs the fold forward, which takes no documents"),
     # this build's own refusals: routes and features it does not build
     ("rB1", R4, dict(pv_precision="fp4", causal=True), {}, NotImplementedError, "B1", "pv_precision='fp4'"),
     ("rB2", R8, dict(options=O8(tuning=KernelTuning(bwd_fp4_ld_rep=64))), {}, ValueError, "B2", "KernelTuning"),
