@@ -388,3 +388,37 @@ def test_fp8_padded_head_dims(d, hk):
     assert float((lse.cpu() - rl).abs().max()) < 2e-3
     fo, _fl, fdq, fdk, fdv = A.attention_fp32(q, k, v, g, causal=True)
     _check((o, dq, dk, dv), (fo, fdq, fdk, fdv), tol=1e-1)
+
+
+@pytest.mark.parametrize("b,s,h,hk,d", [(3, 256, 3, 3, 128), (2, 129, 21, 3, 96), (1, 384, 20, 5, 64), (2, 31, 7, 1, 32)])
+def test_fp8_odd_head_counts_and_lengths(b, s, h, hk, d):
+    """Head counts that are no power of two, GQA ratios 1 / 4 / 7, lengths 31 and 129 (documents of the batch rows), padded
+    head dims: against fp32 attention at the true shapes (the quantisation's own error is about 5e-2 on ragged lengths,
+    where the rotation is off)."""
+    from flamia_blackwell_attention_b200 import flash_attn_fp8, check_status
+    q, k, v, g = attention_inputs(b, s, h, hk, d, seed=31)
+    o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True)
+    check_status()
+    fo, _fl, fdq, fdk, fdv = A.attention_fp32(q, k, v, g, causal=True)
+    _check((o, dq, dk, dv), (fo, fdq, fdk, fdv), tol=1e-1)
+    assert all(torch.isfinite(t).all() for t in (o, dq, dk, dv))
+
+
+def test_single_token_and_empty_key_ranges():
+    """One query and one key per row: O is the V row, dV the dO row, dQ = dK = 0 (P = 1 has no gradient); a batch row
+    whose seqused_k is 0 sees no key at all: zero output rows, zero gradients, nothing non-finite."""
+    from flamia_blackwell_attention_b200 import flash_attn_fp8, check_status
+    q, k, v, g = attention_inputs(2, 1, 4, 2, 64, seed=32)
+    o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True)
+    assert A.accuracy(o, v.float().repeat_interleave(2, dim=2))["rel_l2"] < 3e-2
+    assert A.accuracy(dv, g.float().reshape(2, 1, 2, 2, 64).sum(3))["rel_l2"] < 3e-2
+    assert float(dq.abs().max()) < 1e-2 and float(dk.abs().max()) < 1e-2
+    q, k, v, g = attention_inputs(2, 256, 2, 2, 128, seed=33)
+    su = torch.tensor([0, 256], dtype=torch.int32)
+    o, dq, dk, dv, _ = _step(flash_attn_fp8, q, k, v, g, causal=True, seqused_k=su.cuda())
+    check_status()
+    assert all(torch.isfinite(t).all() for t in (o, dq, dk, dv))
+    assert float(o[0].abs().max()) == 0.0 and float(dq[0].abs().max()) == 0.0
+    assert float(dk[0].abs().max()) == 0.0 and float(dv[0].abs().max()) == 0.0
+    ro, _, rdq, rdk, rdv = A.qdq_attention(q[1:], k[1:], v[1:], g[1:], causal=True, rotate_qk=True)
+    _check((o[1:], dq[1:], dk[1:], dv[1:]), (ro, rdq, rdk, rdv))
