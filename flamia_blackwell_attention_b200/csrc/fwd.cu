@@ -48,7 +48,7 @@ static constexpr int KV_STAGES = 3;
 static constexpr int Q_STRIDE = 16384;            // bytes between Q tile buffers (also the output staging: 128 rows x 128 B)
 static constexpr float P_LOG2_OFFSET = 4.0f;      // row frame: P-hat = 2^(x - m + 4) keeps small probabilities out of E4M3 subnormals
 static constexpr float P_LOG2_448 = 8.807354922057604f;   // group frame: the row maximum sits at 448 before the group bias
-static constexpr long long STAGE_SKEW_CLOCKS = 1000;   // see the UMMA issuer's prologue
+static constexpr long long STAGE_SKEW_CLOCKS = 2000;   // about half a softmax period; see the UMMA issuer's prologue
 static constexpr float RESCALE_THRESHOLD = 4.0f;  // the running maximum is refreshed only when it grew by more than this
 
 struct FwdParams {
