@@ -483,7 +483,7 @@ bwd_kernel_pipelined(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             else tma_reduce_add_4d(&tm_acc, sDQ + y * 16384, 0, T.q0 + m * 128 + 64 * y, head, T.bat);
             tma_store_commit();
           }
-        } else if (warp == 8) {                 // (the whole warp stays converged: lane 0 works, the others follow its verdict)
+        } else if (warp == 8) {                 // (the whole warp stays converged: lane 0 works, the others follow its result)
           int go = 1;
           int32_t* order = nullptr;
           int rank = 0;
