@@ -74,6 +74,12 @@ __device__ __forceinline__ uint32_t ue8m0_byte(float amax) {
 }
 __device__ __forceinline__ float pow2_from_field(int field) { return __uint_as_float((uint32_t)field << 23); }
 
+// two E4M3 codes (low byte first) -> their exact values
+__device__ __forceinline__ float2 e4m3x2_to_f32(uint16_t v) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(v));
+  return __half22float2(*reinterpret_cast<const __half2*>(&h2));
+}
 __device__ __forceinline__ float e4m3_byte_to_f32(uint32_t c) {
   uint32_t e = (c >> 3) & 0xF, m = c & 7;
   float v = e ? __uint_as_float(((e + 120) << 23) | (m << 20)) : (float)m * 0.001953125f;
@@ -392,11 +398,19 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       float v[4 * NJ];                               // columns with bit 1 clear: index (j, e bit 2, e bit 0)
 #pragma unroll
       for (int j = 0; j < NJ; ++j) {
+        // the chunk's eight codes back as floats: the hardware conversion E4M3 -> f16 is exact (two codes per instruction)
+        float c8[8];
+#pragma unroll
+        for (int hw = 0; hw < 4; ++hw) {
+          const float2 f = e4m3x2_to_f32((uint16_t)(cw[2 * j + (hw >> 1)] >> (16 * (hw & 1))));
+          c8[2 * hw] = f.x;
+          c8[2 * hw + 1] = f.y;
+        }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int e = ((k >> 1) << 2) | (k & 1);   // 0, 1, 4, 5
-          const float a0 = __fmul_rn(e4m3_byte_to_f32((cw[2 * j + (e >> 2)] >> (8 * (e & 3))) & 0xFF), scale);
-          const float a2 = __fmul_rn(e4m3_byte_to_f32((cw[2 * j + ((e + 2) >> 2)] >> (8 * ((e + 2) & 3))) & 0xFF), scale);
+          const float a0 = __fmul_rn(c8[e], scale);
+          const float a2 = __fmul_rn(c8[e + 2], scale);
           v[4 * j + k] = __fmaf_rn(a0, o[8 * j + e], __fmul_rn(a2, o[8 * j + e + 2]));
         }
       }
