@@ -80,11 +80,6 @@ __device__ __forceinline__ float2 e4m3x2_to_f32(uint16_t v) {
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(v));
   return __half22float2(*reinterpret_cast<const __half2*>(&h2));
 }
-__device__ __forceinline__ float e4m3_byte_to_f32(uint32_t c) {
-  uint32_t e = (c >> 3) & 0xF, m = c & 7;
-  float v = e ? __uint_as_float(((e + 120) << 23) | (m << 20)) : (float)m * 0.001953125f;
-  return (c & 0x80) ? -v : v;
-}
 
 // MODE bits: 1 = the E4M3 codes are of the rotated rows, 2 = also write the NVFP4 copy, 4 = rotate only the NVFP4 copy
 // PK: packed source (slot tables); a template flag, so that the batched form pays nothing for it
@@ -279,7 +274,7 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         am = (oth > am) ? oth : am;
         const float u = __fmul_rn(am, 1.0f / 6.0f);
         const uint32_t sfb = cvt_e4m3x2(u, 0.f) & 0xFF;
-        const float sfv = e4m3_byte_to_f32(sfb);
+        const float sfv = e4m3x2_to_f32((uint16_t)sfb).x;
         const float m = sfv > 0.f ? __frcp_rn(sfv) : (u > 0.f ? __int_as_float(0x7F800000) : 0.f);
         uint32_t packed = 0;
 #pragma unroll
@@ -621,7 +616,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           am = flush_sub(am);
           const float u = __fmul_rn(am, 1.0f / 6.0f);
           const uint32_t sfb = cvt_e4m3x2(u, 0.f) & 0xFF;
-          const float sfv = e4m3_byte_to_f32(sfb);
+          const float sfv = e4m3x2_to_f32((uint16_t)sfb).x;
           const float m = sfv > 0.f ? __frcp_rn(sfv) : (u > 0.f ? __int_as_float(0x7F800000) : 0.f);
           const uint64_t m2 = pack2(m, m);
 #pragma unroll
