@@ -146,7 +146,7 @@ def run_reference(args, rank, world):
 # DRAM read + write bytes of one backward-kernel launch, from the ncu capture summarised in
 # profiles/bwd_kernel_pipelined_b2_s4096_h16_d128.md and profiles/mixed_route_kernels_b2_s4096_h16_d128.md (cell b2; traffic is proportional to the batch: independent (batch,
 # head) problems), per route, causal only
-NCU_BWD_TRAFFIC_B2 = {"fp8": 170.5e6, "fp4": 222.2e6}
+NCU_BWD_TRAFFIC_B2 = {"fp8": 163.8e6, "fp4": 221.8e6}
 
 
 def measure_route(fn, route, causal, tensors, args, world, dist, K, clock_gpu=None):
