@@ -490,22 +490,22 @@ quant_blocks_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 }
 
 // ------------------------------------------------------------------------------------------------ one thread per row
-// The plain launches of the 8-bit route at head_dim 128 (codes, exponent / factor tables, statistics; no NVFP4 copy, no
+// The plain launches at head_dim 128 (and, unrotated, 64) (codes, exponent / factor tables, statistics; no
 // prologue, no token-local exponents, no packed source) run with ONE THREAD PER TOKEN ROW: CTA = 128 threads = one
 // 128-token tile, warp = one 32-token block, so the block maximum is a warp reduction, the Hadamard butterflies need no
 // shuffles, and one barrier per tile remains (it hands the input stage back to the loader and the codes to a TMA store).
 // Every floating-point operation is the one the four-lanes-per-row kernel above performs on the same operands in the same
 // order, so the two kernels' outputs are bit-identical (tests/test_gpu_quant.py compares them).
 static constexpr int QR_STAGES = 2;
-static constexpr int QR_TILE_B = QT * 128 * 2;     // one 16-bit input tile
-static constexpr int QR_CODE_B = QT * 128;         // its codes
 
 // MODE as in the four-lane kernel: bit 0 = the E4M3 codes are of the rotated row, bit 1 = also the NVFP4 copy, bit 2 =
 // rotate only the NVFP4 copy.
-template <int MODE>
+template <int MODE, int D = 128>
 __global__ void __launch_bounds__(128, 2)
 quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, const QuantParams p) {
-  constexpr int D = 128;
+  static_assert(D == 128 || (D == 64 && MODE == 0), "head_dim 64 has no rotation and no NVFP4 copy");
+  constexpr int QR_TILE_B = QT * D * 2;            // one 16-bit input tile (boxes of 64 columns: 128-byte rows)
+  constexpr int QR_CODE_B = QT * D;                // its codes (rows of D bytes, the swizzle of that width)
   constexpr bool ROT = (MODE & 1) != 0, NV4 = (MODE & 2) != 0, ROT4 = (MODE & 4) != 0;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -524,7 +524,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     uint8_t* dst = smem + st * QR_TILE_B;
     mbar_arrive_expect_tx(&full[st], QR_TILE_B);
     tma_load_4d(dst, &tm_x, &full[st], 0, head, tile * QT, bat);
-    tma_load_4d(dst + QR_TILE_B / 2, &tm_x, &full[st], 64, head, tile * QT, bat);
+    if (D == 128) tma_load_4d(dst + QR_TILE_B / 2, &tm_x, &full[st], 64, head, tile * QT, bat);
   };
   if (tid == 0) {
     abort_s = 0;
@@ -546,12 +546,12 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const uint32_t tile_addr = smem_u32(smem + st * QR_TILE_B);
     bool ok = mbar_wait(&full[st], (it / QR_STAGES) & 1, p.ctl, abortp, 51);
 
-    // ---- the row: 16 chunks of 8 elements (element 8 g + e in chunk g), rotation signs applied to the raw bits
+    // ---- the row: D / 8 chunks of 8 elements (element 8 g + e in chunk g), rotation signs applied to the raw bits
     float x[D];
     auto load_row = [&](bool signs) {
       constexpr uint32_t NEG[4] = {0x10D2E03Eu, 0xE0D9F0E2u, 0x45809F07u, 0x75954FEDu};
 #pragma unroll
-      for (int g = 0; g < 16; ++g) {
+      for (int g = 0; g < D / 8; ++g) {
         const uint32_t box = (uint32_t)(g >> 3) * (QR_TILE_B / 2);
         uint4 v = lds_u4(tile_addr + box + r * 128 + (((g & 7) ^ (r & 7)) << 4));
         uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -576,6 +576,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     // (y * signs) H_128 / sqrt(128): butterfly levels 1, 2, ..., 64 with (a, b) -> (a + b, a - b), the last one with the
     // scaling, subnormal results flushed
     auto rotate_row = [&]() {
+      if constexpr (D == 128) {
       uint64_t Y[D / 2];
 #pragma unroll
       for (int k = 0; k < D / 2; ++k) Y[k] = pack2(__fadd_rn(x[2 * k], x[2 * k + 1]), __fsub_rn(x[2 * k], x[2 * k + 1]));
@@ -596,6 +597,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         unpack2(mul2_ftz(add2(a, b2), c2), x[2 * k], x[2 * k + 1]);
         unpack2(mul2_ftz(sub2(a, b2), c2), x[2 * k + D / 2], x[2 * k + D / 2 + 1]);
       }
+      }
     };
     // NVFP4 copy of x: per 16 along d: SF = E4M3_rn(amax * f32(1/6)); codes = E2M1_rn(ftz(x * m)), m = 1 / SF | +inf (SF
     // rounds to 0, amax > 0) | 0. Scale bytes: group g of the row = byte g % 4 of the row's word in atom g / 4.
@@ -604,7 +606,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       uint8_t* x4row = p.x4 + row_off / 2;
       uint32_t sfw[2] = {0u, 0u};
 #pragma unroll
-      for (int g2 = 0; g2 < 4; ++g2) {                // two groups of 16 elements = one 16-byte store
+      for (int g2 = 0; g2 < D / 32; ++g2) {           // two groups of 16 elements = one 16-byte store
         uint32_t pk[4];
 #pragma unroll
         for (int gg = 0; gg < 2; ++gg) {
@@ -669,7 +671,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
       for (int q = 0; q < 4; ++q)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < D / 32; ++j)
 #pragma unroll
           for (int e = 0; e < 8; e += 2)
             aq[q] = fmax3_abs(aq[q], x[32 * j + 8 * q + e], x[32 * j + 8 * q + e + 1]);
@@ -680,7 +682,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         for (int q = 0; q < 4; ++q) {
           float sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
+          for (int j = 0; j < D / 32; ++j)
 #pragma unroll
             for (int e = 0; e < 8; ++e) sq[e & 3] = fmaf(x[32 * j + 8 * q + e], x[32 * j + 8 * q + e], sq[e & 3]);
           lq[q] = (sq[0] + sq[1]) + (sq[2] + sq[3]);
@@ -702,12 +704,13 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const uint32_t bbyte = ue8m0_byte(bmax);
     const float inv = bbyte ? pow2_from_field(254 - (int)bbyte) : 0.f;
 
-    // ---- codes -> this tile's staging buffer (128 B rows, 128 B swizzle)
+    // ---- codes -> this tile's staging buffer (rows of D bytes, the swizzle of that width)
     {
       const uint64_t inv2 = pack2(inv, inv);
-      const uint32_t orow = smem_u32(s_out + par * QR_CODE_B) + r * 128;
+      const uint32_t orow = smem_u32(s_out + par * QR_CODE_B) + r * D;
+      const int swz = D == 128 ? (r & 7) : ((r >> 1) & 3);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {                 // 16 codes per 16-byte chunk
+      for (int c = 0; c < D / 16; ++c) {            // 16 codes per 16-byte chunk
         uint32_t cw[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -716,7 +719,7 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           unpack2(mul2(pack2(x[16 * c + 4 * k + 2], x[16 * c + 4 * k + 3]), inv2), a2, a3);
           cw[k] = cvt_e4m3x4(a0, a1, a2, a3);
         }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(orow + ((c ^ (r & 7)) << 4)), "r"(cw[0]), "r"(cw[1]),
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(orow + ((c ^ swz) << 4)), "r"(cw[0]), "r"(cw[1]),
                      "r"(cw[2]), "r"(cw[3]) : "memory");
       }
     }
@@ -758,10 +761,10 @@ quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   }
 }
 
-template <int MODE>
+template <int MODE, int D = 128>
 static int launch_quant_rows(const CUtensorMap& mx, const CUtensorMap& mc, const QuantParams& p, cudaStream_t st) {
-  const int smem = QR_STAGES * QR_TILE_B + 2 * QR_CODE_B + 1024;
-  auto kern = quant_rows_kernel<MODE>;
+  const int smem = QR_STAGES * QT * D * 2 + 2 * QT * D + 1024;
+  auto kern = quant_rows_kernel<MODE, D>;
   if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); e != cudaSuccess)
     return cuda_fail((int)e, "fl_quant_blocks: cudaFuncSetAttribute");
   const int grid = min(p.n_tiles, sm_count() * 2);
@@ -828,11 +831,12 @@ extern "C" int fl_quant_blocks(const fl_quant_args* a, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const bool wt = a->codes_t != nullptr;
   // the plain launches of the 8-bit route: one thread per row (same bits, fewer instructions, no shuffles)
-  if (a->d == 128 && !pro && !wt && !packed && !p.token_local && !a->sf_tok && !a->sf_dim &&
-      !a->token_factors && !a->zero_acc && !a->lse_log2 && !(a->flags & FL_Q_LEGACY)) {
+  if ((a->d == 128 || (a->d == 64 && !rot && !rot4 && !nv4)) && !pro && !wt && !packed && !p.token_local && !a->sf_tok &&
+      !a->sf_dim && !a->token_factors && !a->zero_acc && !a->lse_log2 && !(a->flags & FL_Q_LEGACY)) {
     CUtensorMap mc;
-    if ((rc = make_rows_map(&mc, a->codes, a->b, a->s, a->h, 128, 128))) return rc;
-    if (rot4) rc = launch_quant_rows<6>(mx, mc, p, st);
+    if ((rc = make_rows_map(&mc, a->codes, a->b, a->s, a->h, a->d, 128))) return rc;
+    if (a->d == 64) rc = launch_quant_rows<0, 64>(mx, mc, p, st);
+    else if (rot4) rc = launch_quant_rows<6>(mx, mc, p, st);
     else if (rot) rc = nv4 ? launch_quant_rows<3>(mx, mc, p, st) : launch_quant_rows<1>(mx, mc, p, st);
     else rc = nv4 ? launch_quant_rows<2>(mx, mc, p, st) : launch_quant_rows<0>(mx, mc, p, st);
     if (rc) return rc;

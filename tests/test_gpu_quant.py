@@ -126,6 +126,28 @@ def test_one_thread_per_row_kernel(dist, rotate, dtype):
             same(new[k], old[k].cpu().view(torch.uint8).numpy(), f"{dist} {scope} old/new {k}")
 
 
+@pytest.mark.parametrize("dist", DISTS)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_one_thread_per_row_kernel_at_head_dim_64(dist, dtype):
+    """Head dim 64 (no rotation there) on the one-thread-per-row kernel: against the oracle and bit for bit, statistics
+    included, against the four-lanes-per-row kernel."""
+    x = make((2, 384, 3, 64), dist, dtype)
+    b, s = x.shape[:2]
+    rs_new, rs_old = (torch.zeros(b, s, dtype=torch.float32, device="cuda") for _ in range(2))
+    new = run(x, output_tile_stats=True, row_stat=("sumsq", rs_new))
+    old = run(x, output_tile_stats=True, row_stat=("sumsq", rs_old), legacy_kernel=True)
+    ref = Q.fp8_token_blocks(x.float().numpy())
+    for k in ("codes", "e", "fac"):
+        same(new[k], ref[k], f"{dist} {dtype} d64 {k}")
+        same(new[k], old[k].cpu().view(torch.uint8).numpy(), f"{dist} d64 old/new {k}")
+    same(new["tile_stats"], old["tile_stats"].cpu().view(torch.uint8).numpy(), f"{dist} d64 tile_stats")
+    same(rs_new, rs_old.cpu().view(torch.uint8).numpy(), f"{dist} d64 row_stat")
+    for kind in ("amax", "norm2"):
+        t_new, t_old = (torch.zeros(b, s, dtype=torch.float32, device="cuda") for _ in range(2))
+        run(x, row_stat=(kind, t_new)); run(x, row_stat=(kind, t_old), legacy_kernel=True)
+        same(t_new, t_old.cpu().view(torch.uint8).numpy(), f"{dist} d64 row_stat {kind}")
+
+
 def test_golden_small_fixture_on_gpu():
     small = np.load(os.path.join(HERE, "golden", "quant_small.npz"))
     for dist in ("n01", "zeros", "mixed"):
