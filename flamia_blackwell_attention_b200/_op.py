@@ -79,7 +79,12 @@ def _fake_fwd(q, k, v, docs, plan, docs_id):
     p = _PLANS[plan]
     sh = p.shape
     is_docs = sh.varlen or p.fwd.ragged_documents
-    lse_shape = (sh.h, sh.tot_q) if sh.aligned_varlen else ((0,) if is_docs else (sh.b, sh.h, sh.s_q))
+    if sh.aligned_varlen or (is_docs and sh.varlen and p.fwd.return_lse):
+        lse_shape = (sh.h, sh.tot_q)
+    elif is_docs and not p.fwd.return_lse:
+        lse_shape = (0,)
+    else:
+        lse_shape = (sh.b, sh.h, sh.s_q)
     n_docs = int(docs[0].shape[0]) - 1 if (len(docs) > 0 and not p.fwd.seqused_k) else 0
     spec = _routes.state_spec(p, n_docs, q.dtype, capacity=int(docs[3].numel()) if len(docs) == 6 else None)
     # as _fwd_impl: O / LSE leave as the op's outputs; repacked documents keep the aligned buffer's LSE in the state

@@ -290,7 +290,19 @@ def forward(plan, q, k, v, docs, seqused_k=None, prequant=None):
         out_user = out[0]                        # aligned: in place; repacked: the kernel wrote the packed rows
         if not sh.varlen:
             out_user = out_user.reshape(sh.b, sh.s_q, sh.h, sh.d)
-        lse_user = lse[0] if sh.aligned_varlen else lse.new_zeros(0)     # (h, total_q) on the aligned form only
+        if sh.aligned_varlen:
+            lse_user = lse[0]                    # (h, total_q): the caller's rows are the kernels' rows
+        elif f.return_lse:
+            # repacked documents: the kernels' LSE has the aligned buffer's rows; its live rows go to the caller's packed
+            # rows (padding rows to a spare column), no host synchronisation
+            tot = sh.tot_q if sh.varlen else sh.b * sh.s_q
+            idx = torch.where(docs.row_map >= 0, docs.row_map, torch.full_like(docs.row_map, tot)).long()
+            buf = lse.new_zeros(sh.h, tot + 1)
+            buf.index_copy_(1, idx, lse[0])
+            lse_user = buf[:, :tot].contiguous() if sh.varlen else \
+                buf[:, :tot].reshape(sh.h, sh.b, sh.s_q).permute(1, 0, 2).contiguous()
+        else:
+            lse_user = lse.new_zeros(0)
     else:
         out_user, lse_user = out, lse
     _note_status(status)

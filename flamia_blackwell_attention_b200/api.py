@@ -154,7 +154,7 @@ def flash_attn_fp8(q, k, v, *, softmax_scale: Optional[float] = None, causal: bo
     128 (run padded with zero columns to the next of 64 / 128). Packed (total, h, d) with
     cu_seqlens_q / cu_seqlens_k (repacked), or with seqused_q / seqused_k as well (aligned, zero-copy: starts multiples of
     128). Returns out (dtype and shape of q); with return_lse=True (out, lse) with lse (b, h, s) float32 in nats,
-    non-differentiable ((h, total_q) on the aligned varlen form). causal is bottom-right aligned.
+    non-differentiable ((h, total_q) in the caller's row order on the packed forms). causal is bottom-right aligned.
     E4M3 Q, K, V, dO with one UE8M0 exponent per 32 tokens x the whole head dim; qk_hadamard=None turns the random-sign
     Hadamard rotation of Q / K on at d = 128. Every unserved combination raises with a `.rule` before any launch."""
     if doc_maps is not None:

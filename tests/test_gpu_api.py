@@ -422,3 +422,40 @@ def test_single_token_and_empty_key_ranges():
     assert float(dk[0].abs().max()) == 0.0 and float(dv[0].abs().max()) == 0.0
     ro, _, rdq, rdk, rdv = A.qdq_attention(q[1:], k[1:], v[1:], g[1:], causal=True, rotate_qk=True)
     _check((o[1:], dq[1:], dk[1:], dv[1:]), (ro, rdq, rdk, rdv))
+
+
+@pytest.mark.parametrize("route", ["fp8", "fp4"])
+def test_lse_of_repacked_documents_and_ragged_batch_rows(route):
+    """return_lse on the forms that run as repacked documents: (h, total) in the caller's packed row order under
+    cu_seqlens / doc_maps, (b, h, s) for batch rows whose length is no multiple of 128 -- each row's value is that of
+    its own document."""
+    import flamia_blackwell_attention_b200 as F
+    fn = F.flash_attn_fp8 if route == "fp8" else F.flash_attn_fp4
+    lens, h, hk, d = [200, 128, 37, 300], 4, 2, 128
+    total = sum(lens)
+    q, k, v, g = (t[0] for t in attention_inputs(1, total, h, hk, d, seed=41))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    ref = torch.empty(h, total)
+    s0 = 0
+    for n in lens:
+        sl = slice(s0, s0 + n)
+        _, rl, *_ = A.attention_fp32(q[None, sl].float(), k[None, sl].float(), v[None, sl].float(), None, True)
+        ref[:, sl] = rl[0]
+        s0 += n
+    # against fp32 attention: a row with few keys takes the quantisation error of its few scores in full (up to 0.1 on
+    # the 8-bit route), long rows average it out: bound the worst row and the typical one
+    tol, typ = (0.2, 1e-2) if route == "fp8" else (0.5, 4e-2)
+    for kw in (dict(cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens)),
+               dict(doc_maps=F.DocMaps.from_cu_seqlens(cu.cpu()).to("cuda"))):
+        with torch.no_grad():
+            out, lse = fn(q.cuda(), k.cuda(), v.cuda(), causal=True, return_lse=True, **kw)
+        assert lse.shape == (h, total) and lse.dtype == torch.float32
+        err = (lse.cpu() - ref).abs()
+        assert float(err.max()) < tol and float(err.median()) < typ
+    if route == "fp8":                               # batch rows of 200 tokens run as documents
+        q, k, v, g = attention_inputs(3, 200, h, hk, d, seed=42)
+        with torch.no_grad():
+            out, lse = fn(q.cuda(), k.cuda(), v.cuda(), causal=True, return_lse=True)
+        _, rl, *_ = A.attention_fp32(q.float(), k.float(), v.float(), None, True)
+        err = (lse.cpu() - rl).abs()
+        assert lse.shape == (3, h, 200) and float(err.max()) < tol and float(err.median()) < typ
